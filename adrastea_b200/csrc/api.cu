@@ -1,0 +1,284 @@
+// C ABI of adrastea_b200: argument checks, kernel selection, tracing.
+// The host-side logic mirrors GpuKernels::matmul_f16 of the reference
+// (adrastea_models/src/kernels.rs:821-890), which validates shapes, lowers
+// the options and launches; here the lowering has already happened on the
+// caller's side and the 22 kernel parameters arrive as they are.
+#include <cstdio>
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+
+namespace adr {
+
+bool TraceKey::operator==(const TraceKey& o) const {
+  return m == o.m && k == o.k && n == o.n && batches == o.batches &&
+         memcmp(strides, o.strides, sizeof(strides)) == 0 && store == o.store && load == o.load &&
+         mask == o.mask && kernel == o.kernel;
+}
+
+namespace {
+
+void trace_record(adr_ctx* ctx, const MatmulArgs& a, int kernel) {
+  if (!ctx->trace_on) return;
+  TraceKey key{a.m, a.k, a.n, a.batches,
+               {a.s_ox, a.s_oy, a.s_oz, a.s_lx, a.s_ly, a.s_lz, a.s_rx, a.s_ry, a.s_rz},
+               a.store, a.load, a.mask, kernel};
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  for (const auto& t : ctx->trace)
+    if (t == key) return;
+  ctx->trace.push_back(key);
+}
+
+int check_matmul_args(const adr_ctx* ctx, const MatmulArgs& a) {
+  if (!ctx || !a.out || !a.lhs || !a.rhs) return ADR_ERR_INVALID;
+  if (a.batches <= 0 || a.m <= 0 || a.k <= 0 || a.n <= 0) return ADR_ERR_INVALID;
+  if (a.store == ADR_STORE_GELU_BIAS) return ADR_ERR_UNSUPPORTED;
+  if (a.store > ADR_STORE_QUICK_GELU_BIAS || a.load > ADR_LOAD_SCALE || a.mask > ADR_MASK_CAUSAL)
+    return ADR_ERR_INVALID;
+  if (store_uses_bias((int)a.store) && !a.bias) return ADR_ERR_INVALID;
+  if (a.s_ox < 0 || a.s_oy < 0 || a.s_oz < 0 || a.s_lx < 0 || a.s_ly < 0 || a.s_lz < 0 ||
+      a.s_rx < 0 || a.s_ry < 0 || a.s_rz < 0)
+    return ADR_ERR_INVALID;
+  return ADR_OK;
+}
+
+int run_matmul(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, bool slow,
+               bool checked = false) {
+  int rc = checked ? ADR_OK : check_matmul_args(ctx, a);
+  if (rc != ADR_OK) return rc;
+  int kernel = ctx->forced_kernel;
+  if (slow) kernel = ADR_KERNEL_F16_SIMT;
+  if (kernel == ADR_KERNEL_AUTO)
+    kernel = gemm_f16_tc_supports(ctx, a) ? ADR_KERNEL_F16_TC : ADR_KERNEL_F16_SIMT;
+  if (kernel == ADR_KERNEL_F16_TC) {
+    if (!gemm_f16_tc_supports(ctx, a)) return ADR_ERR_SHAPE;
+    rc = launch_gemm_f16_tc(ctx, stream, a);
+  } else if (kernel == ADR_KERNEL_F16_SIMT) {
+    rc = launch_gemm_f16_simt(ctx, stream, a);
+  } else {
+    return ADR_ERR_INVALID;
+  }
+  if (rc == ADR_OK) {
+    ctx->last_kernel = kernel;
+    trace_record(ctx, a, kernel);
+  }
+  return rc;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+}  // namespace adr
+
+using namespace adr;
+
+extern "C" {
+
+int adr_init(int device, adr_ctx** out_ctx) {
+  if (!out_ctx) return ADR_ERR_INVALID;
+  *out_ctx = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count)
+    return ADR_ERR_CUDA;
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return ADR_ERR_CUDA;
+  if (prop.major != 10) return ADR_ERR_UNSUPPORTED;  // sm_100a code only
+  adr_ctx* ctx = new (std::nothrow) adr_ctx();
+  if (!ctx) return ADR_ERR_INVALID;
+  ctx->device = device;
+  ctx->sm_count = prop.multiProcessorCount;
+  int prev = 0;
+  cudaGetDevice(&prev);
+  cudaSetDevice(device);
+  int rc = ADR_OK;
+  if (cudaMalloc(&ctx->d_status, 64) != cudaSuccess ||
+      cudaMemset(ctx->d_status, 0, 64) != cudaSuccess) {
+    rc = ADR_ERR_CUDA;
+  }
+  if (rc == ADR_OK) rc = init_gemm_f16_tc(ctx);
+  if (rc == ADR_OK) rc = init_u8_kernels(ctx);
+  cudaSetDevice(prev);
+  if (rc != ADR_OK) {
+    adr_destroy(ctx);
+    return rc;
+  }
+  *out_ctx = ctx;
+  return ADR_OK;
+}
+
+void adr_destroy(adr_ctx* ctx) {
+  if (!ctx) return;
+  destroy_gemm_f16_tc(ctx);
+  if (ctx->d_status) cudaFree(ctx->d_status);
+  delete ctx;
+}
+
+const char* adr_strerror(int code) {
+  switch (code) {
+    case ADR_OK: return "ok";
+    case ADR_ERR_INVALID: return "invalid argument";
+    case ADR_ERR_SHAPE: return "shape, divisibility or alignment rule violated";
+    case ADR_ERR_UNSUPPORTED: return "unsupported operation or device";
+    case ADR_ERR_CUDA: return "CUDA call failed";
+    case ADR_ERR_DEVICE: return "a kernel's bounded wait ran out";
+    case ADR_ERR_NCCL: return "NCCL call failed";
+    default: return "unknown error";
+  }
+}
+
+int adr_last_cuda_error(const adr_ctx* ctx) { return ctx ? ctx->last_cuda_error : 0; }
+
+int adr_force_kernel(adr_ctx* ctx, int kernel) {
+  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_U8_SIMT) return ADR_ERR_INVALID;
+  ctx->forced_kernel = kernel;
+  return ADR_OK;
+}
+
+int adr_last_kernel(const adr_ctx* ctx) { return ctx ? ctx->last_kernel : 0; }
+uint64_t adr_launch_count(const adr_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+int adr_matmul_f16(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs, const void* rhs,
+                   int batches, int m, int k, int n, int stride_ox, int stride_oy, int stride_oz,
+                   int stride_lx, int stride_ly, int stride_lz, int stride_rx, int stride_ry,
+                   int stride_rz, const void* bias, float beta, float scale, uint32_t store_op,
+                   uint32_t load_op, uint32_t mask_op) {
+  MatmulArgs a{(__half*)out, (const __half*)lhs, (const __half*)rhs, batches, m, k, n,
+               stride_ox, stride_oy, stride_oz, stride_lx, stride_ly, stride_lz,
+               stride_rx, stride_ry, stride_rz, (const __half*)bias, beta, scale,
+               store_op, load_op, mask_op};
+  return run_matmul(ctx, (cudaStream_t)stream, a, false);
+}
+
+int adr_matmul_f16_slow(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                        const void* rhs, int batches, int m, int k, int n, int stride_ox,
+                        int stride_oy, int stride_oz, int stride_lx, int stride_ly, int stride_lz,
+                        int stride_rx, int stride_ry, int stride_rz, const void* bias, float beta,
+                        float scale, uint32_t store_op, uint32_t load_op, uint32_t mask_op) {
+  MatmulArgs a{(__half*)out, (const __half*)lhs, (const __half*)rhs, batches, m, k, n,
+               stride_ox, stride_oy, stride_oz, stride_lx, stride_ly, stride_lz,
+               stride_rx, stride_ry, stride_rz, (const __half*)bias, beta, scale,
+               store_op, load_op, mask_op};
+  return run_matmul(ctx, (cudaStream_t)stream, a, true);
+}
+
+int adr_matmul_f16_raw(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                       const void* rhs, int batches, int m, int k, int n, int stride_ox,
+                       int stride_oy, int stride_oz, int stride_lx, int stride_ly, int stride_lz,
+                       int stride_rx, int stride_ry, int stride_rz) {
+  return adr_matmul_f16(ctx, stream, out, lhs, rhs, batches, m, k, n, stride_ox, stride_oy,
+                        stride_oz, stride_lx, stride_ly, stride_lz, stride_rx, stride_ry,
+                        stride_rz, nullptr, 0.0f, 1.0f, ADR_STORE_IDENTITY, ADR_LOAD_IDENTITY,
+                        ADR_MASK_NONE);
+}
+
+int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                         const uint8_t* rhs, const void* scales, const void* zeros, int m, int p,
+                         int n, int block_size, float beta) {
+  if (!ctx || !out || !lhs || !rhs || !scales) return ADR_ERR_INVALID;
+  if (m <= 0 || p <= 0 || n <= 0 || block_size <= 0) return ADR_ERR_INVALID;
+  if (p % block_size != 0 || block_size % 16 != 0 || p % 16 != 0) return ADR_ERR_SHAPE;
+  if (!aligned16(lhs) || !aligned16(rhs)) return ADR_ERR_SHAPE;
+  U8Args a{(__half*)out, (const __half*)lhs, rhs, (const __half*)scales, (const __half*)zeros,
+           m, p, n, block_size, beta};
+  cudaStream_t st = (cudaStream_t)stream;
+  int kernel = ctx->forced_kernel;
+  if (kernel == ADR_KERNEL_AUTO) {
+    if (p % 64 != 0) kernel = m <= 4 ? ADR_KERNEL_U8_GEMV : ADR_KERNEL_U8_SIMT;
+    else kernel = ADR_KERNEL_U8_MMA;
+  }
+  int rc;
+  switch (kernel) {
+    case ADR_KERNEL_U8_GEMV: rc = launch_u8_gemv(ctx, st, a); break;
+    case ADR_KERNEL_U8_SIMT: rc = launch_u8_simt(ctx, st, a); break;
+    case ADR_KERNEL_U8_MMA: {
+      if (p % 64 != 0) return ADR_ERR_SHAPE;
+      rc = ADR_OK;
+      // m > 16: one pass over the weights per 16 tokens.
+      for (int r0 = 0; r0 < m && rc == ADR_OK; r0 += 16) {
+        U8Args c = a;
+        c.m = (m - r0 < 16) ? m - r0 : 16;
+        c.lhs = a.lhs + (size_t)r0 * p;
+        c.out = a.out + (size_t)r0 * n;
+        rc = launch_u8_mma(ctx, st, c);
+      }
+      break;
+    }
+    default: return ADR_ERR_INVALID;
+  }
+  if (rc == ADR_OK) ctx->last_kernel = kernel;
+  return rc;
+}
+
+int adr_matmul_nt_f16(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                      const void* rhs, int m, int p, int n, float beta) {
+  // out[m,n] = lhs[m,p] . rhs[n,p]^T + beta*out  ==  matmul_f16 with NT strides and
+  // a BETA store without bias; expressed through the strided entry point.
+  if (!ctx || !out || !lhs || !rhs) return ADR_ERR_INVALID;
+  if (m <= 0 || p <= 0 || n <= 0) return ADR_ERR_INVALID;
+  // The reference always reads `out` (beta * old even when beta == 0), so stale NaN/Inf in
+  // `out` propagates there; the same holds here.
+  MatmulArgs a{(__half*)out, (const __half*)lhs, (const __half*)rhs, 1, m, p, n,
+               1, n, 0, 1, p, 0, p, 1, 0, nullptr, beta, 1.0f,
+               (uint32_t)STORE_NT_BETA, ADR_LOAD_IDENTITY, ADR_MASK_NONE};
+  return run_matmul(ctx, (cudaStream_t)stream, a, false, true);
+}
+
+int adr_dequantize_absmax_uint8(adr_ctx* ctx, adr_stream stream, void* out, const void* scales,
+                                const void* zeros, const uint8_t* q, int rows, int k,
+                                int block_size) {
+  if (!ctx || !out || !scales || !q) return ADR_ERR_INVALID;
+  if (rows <= 0 || k <= 0 || block_size <= 0) return ADR_ERR_INVALID;
+  if (k % block_size != 0 || block_size % 16 != 0) return ADR_ERR_SHAPE;
+  if (!aligned16(out) || !aligned16(q)) return ADR_ERR_SHAPE;
+  return launch_dequantize_u8(ctx, (cudaStream_t)stream, (__half*)out, (const __half*)scales,
+                              (const __half*)zeros, q, rows, k, block_size);
+}
+
+int adr_quantize_absmax_uint8(adr_ctx* ctx, adr_stream stream, uint8_t* q, void* scales,
+                              const void* in, int rows, int k, int block_size) {
+  if (!ctx || !q || !scales || !in) return ADR_ERR_INVALID;
+  if (rows <= 0 || k <= 0 || block_size <= 0) return ADR_ERR_INVALID;
+  if (k % block_size != 0) return ADR_ERR_SHAPE;
+  return launch_quantize_u8(ctx, (cudaStream_t)stream, q, (__half*)scales, (const __half*)in, rows,
+                            k, block_size);
+}
+
+int adr_trace_enable(adr_ctx* ctx, int on) {
+  if (!ctx) return ADR_ERR_INVALID;
+  ctx->trace_on = on != 0;
+  return ADR_OK;
+}
+
+void adr_trace_clear(adr_ctx* ctx) {
+  if (!ctx) return;
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  ctx->trace.clear();
+}
+
+size_t adr_trace_dump(adr_ctx* ctx, char* buf, size_t cap) {
+  if (!ctx) return 0;
+  std::string s;
+  {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    char line[512];
+    for (const auto& t : ctx->trace) {
+      snprintf(line, sizeof(line),
+               "{\"m\":%d,\"k\":%d,\"n\":%d,\"batches\":%d,\"out_strides\":[%d,%d,%d],"
+               "\"lhs_strides\":[%d,%d,%d],\"rhs_strides\":[%d,%d,%d],\"store\":%u,\"load\":%u,"
+               "\"mask\":%u,\"kernel\":%d}\n",
+               t.m, t.k, t.n, t.batches, t.strides[0], t.strides[1], t.strides[2], t.strides[3],
+               t.strides[4], t.strides[5], t.strides[6], t.strides[7], t.strides[8], t.store,
+               t.load, t.mask, t.kernel);
+      s += line;
+    }
+  }
+  if (buf && cap > 0) {
+    size_t ncopy = s.size() < cap - 1 ? s.size() : cap - 1;
+    memcpy(buf, s.data(), ncopy);
+    buf[ncopy] = '\0';
+  }
+  return s.size() + 1;
+}
+
+}  // extern "C"

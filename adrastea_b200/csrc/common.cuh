@@ -1,0 +1,184 @@
+// Shared declarations of the adrastea_b200 CUDA library: context, error
+// plumbing, the fused store/load/mask arithmetic of the fp16 matmul path.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <mutex>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/adrastea_b200.h"
+
+namespace adr {
+
+// ---------------------------------------------------------------------------
+// Arguments of one fp16 matmul call, in the reference's parameter order
+// (adrastea_kernels/cpp/matmul.cu:186-190, 493-499).
+// ---------------------------------------------------------------------------
+struct MatmulArgs {
+  __half* out;
+  const __half* lhs;
+  const __half* rhs;
+  int batches, m, k, n;
+  int s_ox, s_oy, s_oz;
+  int s_lx, s_ly, s_lz;
+  int s_rx, s_ry, s_rz;
+  const __half* bias;
+  float beta, scale;
+  uint32_t store, load, mask;
+};
+
+struct TraceKey {
+  int m, k, n, batches;
+  int strides[9];
+  uint32_t store, load, mask;
+  int kernel;
+  bool operator==(const TraceKey& o) const;
+};
+
+}  // namespace adr
+
+struct adr_ctx {
+  int device = 0;
+  int sm_count = 0;
+  int last_cuda_error = 0;
+  int forced_kernel = ADR_KERNEL_AUTO;
+  int last_kernel = 0;
+  uint64_t launches = 0;
+  bool trace_on = false;
+  std::mutex mu;
+  std::vector<adr::TraceKey> trace;
+  // Device word written by kernels whose bounded waits ran out (0 = fine).
+  unsigned int* d_status = nullptr;
+  // Cache of TMA descriptors, keyed by (pointer, dims, strides, box).
+  void* tma_cache = nullptr;
+  void* encode_tiled_fn = nullptr;  // cuTensorMapEncodeTiled, resolved at init
+};
+
+namespace adr {
+
+#define ADR_CUDA_CHECK(ctx, expr)                      \
+  do {                                                 \
+    cudaError_t _e = (expr);                           \
+    if (_e != cudaSuccess) {                           \
+      (ctx)->last_cuda_error = (int)_e;                \
+      return ADR_ERR_CUDA;                             \
+    }                                                  \
+  } while (0)
+
+// Records a launch error, if any, and counts the launch.
+inline int after_launch(adr_ctx* ctx, int nlaunches = 1) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    ctx->last_cuda_error = (int)e;
+    return ADR_ERR_CUDA;
+  }
+  ctx->launches += (uint64_t)nlaunches;
+  return ADR_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Device arithmetic of the fused ops (matmul.cu:45-184, 444-491).
+// Every store functor of the reference first converts the fp32 accumulator to
+// __half; SCALE and ADD then compute in fp16, the bias/gelu/beta forms in
+// fp32 with `inner + beta * old` contracted to one fma.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ float gelu_tanh(float t) {
+  return 0.5f * t * (1.0f + tanhf(0.7978845608028654f * (t + 0.044715f * t * t * t)));
+}
+__device__ __forceinline__ float quick_gelu(float t) {
+  return t * (1.0f / (1.0f + expf(-1.702f * t)));
+}
+
+// Internal store op of adr_matmul_nt_f16: fp16(acc + beta * old) without the
+// intermediate fp16 rounding of acc (matmul_nt_wmma_128x64x64.cu:71-76).
+constexpr int STORE_NT_BETA = 16;
+
+template <int STORE>
+__device__ __forceinline__ __half store_apply(float acc, __half old, float bias, float beta,
+                                              __half hscale) {
+  __half hs = __float2half_rn(acc);
+  if constexpr (STORE == STORE_NT_BETA) {
+    return __float2half_rn(fmaf(beta, __half2float(old), acc));
+  } else if constexpr (STORE == ADR_STORE_IDENTITY) {
+    return hs;
+  } else if constexpr (STORE == ADR_STORE_SCALE) {
+    return __hmul(hs, hscale);
+  } else if constexpr (STORE == ADR_STORE_ADD) {
+    return __hadd(hs, old);
+  } else if constexpr (STORE == ADR_STORE_BETA_BIAS) {
+    float t = __half2float(hs) + bias;
+    return __float2half_rn(fmaf(beta, __half2float(old), t));
+  } else if constexpr (STORE == ADR_STORE_BETA_GELU_BIAS) {
+    float t = gelu_tanh(__half2float(hs) + bias);
+    return __float2half_rn(fmaf(beta, __half2float(old), t));
+  } else {  // QUICK_GELU_BIAS
+    return __float2half_rn(quick_gelu(__half2float(hs) + bias));
+  }
+}
+
+constexpr __host__ __device__ bool store_reads_out(int store) {
+  return store == ADR_STORE_ADD || store == ADR_STORE_BETA_BIAS ||
+         store == ADR_STORE_BETA_GELU_BIAS || store == STORE_NT_BETA;
+}
+constexpr __host__ __device__ bool store_uses_bias(int store) {
+  return store == ADR_STORE_BETA_BIAS || store == ADR_STORE_BETA_GELU_BIAS ||
+         store == ADR_STORE_QUICK_GELU_BIAS;
+}
+
+// Runtime-dispatched form used by kernels that are not specialised per op.
+__device__ __forceinline__ __half store_apply_rt(int store, float acc, __half old, float bias,
+                                                 float beta, __half hscale) {
+  switch (store) {
+    case STORE_NT_BETA: return store_apply<STORE_NT_BETA>(acc, old, bias, beta, hscale);
+    case ADR_STORE_SCALE: return store_apply<ADR_STORE_SCALE>(acc, old, bias, beta, hscale);
+    case ADR_STORE_ADD: return store_apply<ADR_STORE_ADD>(acc, old, bias, beta, hscale);
+    case ADR_STORE_BETA_BIAS: return store_apply<ADR_STORE_BETA_BIAS>(acc, old, bias, beta, hscale);
+    case ADR_STORE_BETA_GELU_BIAS:
+      return store_apply<ADR_STORE_BETA_GELU_BIAS>(acc, old, bias, beta, hscale);
+    case ADR_STORE_QUICK_GELU_BIAS:
+      return store_apply<ADR_STORE_QUICK_GELU_BIAS>(acc, old, bias, beta, hscale);
+    default: return store_apply<ADR_STORE_IDENTITY>(acc, old, bias, beta, hscale);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// u8 absmax dequantisation, bit-exact with
+//   fp16((float(q) - zero) * float(scale))
+// (matmul_nt_wmma_16x128x256_fp16u8.cu:5-7, quantize.cu:53-54).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ __half dequant_one_f32(uint32_t q, float scale, float zero) {
+  return __float2half_rn(((float)q - zero) * scale);
+}
+
+// Kernel launchers implemented in the .cu files.
+int launch_gemm_f16_simt(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a);
+int launch_gemm_f16_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a);
+bool gemm_f16_tc_supports(const adr_ctx* ctx, const MatmulArgs& a);
+int init_gemm_f16_tc(adr_ctx* ctx);
+void destroy_gemm_f16_tc(adr_ctx* ctx);
+
+struct U8Args {
+  __half* out;
+  const __half* lhs;
+  const uint8_t* rhs;
+  const __half* scales;
+  const __half* zeros;
+  int m, p, n, block_size;
+  float beta;
+};
+int launch_u8_simt(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
+int launch_u8_gemv(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
+int launch_u8_mma(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
+int init_u8_kernels(adr_ctx* ctx);
+
+int launch_dequantize_u8(adr_ctx* ctx, cudaStream_t stream, __half* out, const __half* scales,
+                         const __half* zeros, const uint8_t* q, int rows, int k, int block_size);
+int launch_quantize_u8(adr_ctx* ctx, cudaStream_t stream, uint8_t* q, __half* scales,
+                       const __half* in, int rows, int k, int block_size);
+
+}  // namespace adr

@@ -1,0 +1,358 @@
+"""Host-side mirror of the reference's kernel-call interface for the matmul path.
+
+Same names, argument meaning and error behaviour as
+adrastea_models/src/kernels.rs: ``MatmulOptions`` / ``MatmulStore`` /
+``MatmulLoad`` / ``MatmulMask`` (kernels.rs:80-167), ``GpuKernels.matmul_f16``
+and ``matmul_f16_slow`` (kernels.rs:753-890), ``MatmulTracer``
+(kernels.rs:231-248, 306-333).  Every call goes through the C ABI of
+libadrastea_b200.so; there is no PyTorch or CPU fallback.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+import json
+from dataclasses import dataclass, field
+from typing import Optional
+
+import torch
+
+from . import _lib
+from .tensor import TensorLayout, TensorView
+
+
+class AdrError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"adrastea_b200 error {code}: {msg}")
+        self.code = code
+
+
+# -- enums (kernels.rs:80-139; matmul.cu:26-36) ---------------------------
+class MatmulLoadOp(enum.IntEnum):
+    Identity = 0
+    Scale = 1
+
+
+class MatmulStoreOp(enum.IntEnum):
+    Identity = 0
+    GeluBias = 1
+    BetaGeluBias = 2
+    BetaBias = 3
+    Scale = 4
+    Add = 5
+    QuickGeluBias = 6
+
+
+class MatmulMask(enum.IntEnum):
+    None_ = 0
+    Causal = 1
+
+
+class Kernel(enum.IntEnum):
+    Auto = 0
+    F16Simt = 1
+    F16Tc = 2
+    U8Gemv = 3
+    U8Mma = 4
+    U8Tc = 5
+    U8Simt = 6
+
+
+@dataclass(frozen=True)
+class MatmulLoad:
+    op: MatmulLoadOp = MatmulLoadOp.Identity
+    scale: float = 1.0
+
+    @staticmethod
+    def Identity() -> "MatmulLoad":
+        return MatmulLoad(MatmulLoadOp.Identity, 1.0)
+
+    @staticmethod
+    def Scale(scale: float) -> "MatmulLoad":
+        return MatmulLoad(MatmulLoadOp.Scale, float(scale))
+
+    def lower(self) -> MatmulLoadOp:
+        return self.op
+
+
+@dataclass(frozen=True)
+class MatmulStore:
+    op: MatmulStoreOp = MatmulStoreOp.Identity
+    beta: float = 0.0
+    scale: float = 1.0
+    bias: Optional[TensorView] = None
+
+    @staticmethod
+    def Identity() -> "MatmulStore":
+        return MatmulStore()
+
+    @staticmethod
+    def GeluBias(bias: TensorView) -> "MatmulStore":
+        return MatmulStore(MatmulStoreOp.GeluBias, bias=bias)
+
+    @staticmethod
+    def QuickGeluBias(bias: TensorView) -> "MatmulStore":
+        return MatmulStore(MatmulStoreOp.QuickGeluBias, bias=bias)
+
+    @staticmethod
+    def BetaGeluBias(beta: float, bias: TensorView) -> "MatmulStore":
+        return MatmulStore(MatmulStoreOp.BetaGeluBias, beta=float(beta), bias=bias)
+
+    @staticmethod
+    def BetaBias(beta: float, bias: TensorView) -> "MatmulStore":
+        return MatmulStore(MatmulStoreOp.BetaBias, beta=float(beta), bias=bias)
+
+    @staticmethod
+    def Scale(scale: float) -> "MatmulStore":
+        return MatmulStore(MatmulStoreOp.Scale, scale=float(scale))
+
+    @staticmethod
+    def Add() -> "MatmulStore":
+        return MatmulStore(MatmulStoreOp.Add)
+
+    def lower(self) -> MatmulStoreOp:
+        return self.op
+
+
+@dataclass
+class MatmulOptions:
+    """Builder with the reference's defaults (kernels.rs:148-167)."""
+    load_: MatmulLoad = field(default_factory=MatmulLoad.Identity)
+    store_: MatmulStore = field(default_factory=MatmulStore.Identity)
+    mask_: MatmulMask = MatmulMask.None_
+
+    @staticmethod
+    def new() -> "MatmulOptions":
+        return MatmulOptions()
+
+    def load(self, load: MatmulLoad) -> "MatmulOptions":
+        self.load_ = load
+        return self
+
+    def store(self, store: MatmulStore) -> "MatmulOptions":
+        self.store_ = store
+        return self
+
+    def mask(self, mask: MatmulMask) -> "MatmulOptions":
+        self.mask_ = mask
+        return self
+
+
+def lower_matmul(output: TensorView, left: TensorView, right: TensorView,
+                 options: MatmulOptions) -> tuple:
+    """The marshalling of GpuKernels::matmul_f16 (kernels.rs:825-887).
+
+    Returns the 19 scalar arguments that follow the three pointers:
+    (batches, m, k, n, 9 strides, bias_view_or_None, beta, scale, store, load, mask).
+    Shape mismatches raise AssertionError where the reference's assert_eq!
+    panics (kernels.rs:825-827).
+    """
+    assert left.size(-1) == right.size(-2), "K mismatch"
+    assert output.size(-2) == left.size(-2), "M mismatch"
+    assert output.size(-1) == right.size(-1), "N mismatch"
+    store = options.store_
+    bias = store.bias  # kernels.rs:828-836
+    scale = options.load_.scale if options.load_.op == MatmulLoadOp.Scale else 1.0
+    if store.op == MatmulStoreOp.Scale:
+        scale *= store.scale  # kernels.rs:837-843
+    beta = store.beta if store.op in (MatmulStoreOp.BetaGeluBias, MatmulStoreOp.BetaBias) else 0.0
+    out_rank = len(output.layout.dims)
+    batches = output.size(-3) if out_rank > 2 else 1
+
+    def zstride(v: TensorView) -> int:
+        return v.stride(-3) if len(v.layout.dims) > 2 else 0
+
+    return (batches, left.size(-2), left.size(-1), right.size(-1),
+            output.stride(-1), output.stride(-2), zstride(output),
+            left.stride(-1), left.stride(-2), zstride(left),
+            right.stride(-1), right.stride(-2), zstride(right),
+            bias, beta, scale, int(store.lower()), int(options.load_.lower()),
+            int(options.mask_))
+
+
+def _stream_handle(stream) -> int:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream
+    if isinstance(stream, torch.cuda.Stream):
+        return stream.cuda_stream
+    return int(stream)
+
+
+class GpuKernels:
+    """Mirror of ``GpuKernels`` (kernels.rs:361-502) for the matmul path.
+
+    The reference's constructor takes the device capability and loads the
+    embedded cubins; here it takes a CUDA device ordinal and opens the
+    library.  Calls are enqueued on torch's current stream (the reference
+    uses the NULL stream) and are asynchronous.
+    """
+
+    def __init__(self, device: int | torch.device | None = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("adrastea_b200 needs a CUDA device (sm_100a); there is no CPU path")
+        if device is None:
+            device = torch.cuda.current_device()
+        if isinstance(device, torch.device):
+            device = device.index if device.index is not None else torch.cuda.current_device()
+        self.device = int(device)
+        self._lib = _lib.load()
+        ctx = C.c_void_p()
+        with torch.cuda.device(self.device):
+            torch.cuda.current_stream()  # make sure the primary context exists
+            rc = self._lib.adr_init(self.device, C.byref(ctx))
+        self._ctx = ctx
+        self._check(rc)
+
+    def close(self):
+        if getattr(self, "_ctx", None):
+            self._lib.adr_destroy(self._ctx)
+            self._ctx = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # -- helpers ----------------------------------------------------------
+    def _check(self, rc: int):
+        if rc != 0:
+            msg = self._lib.adr_strerror(rc).decode()
+            if rc == 4 and self._ctx:
+                msg += f" (cudaError {self._lib.adr_last_cuda_error(self._ctx)})"
+            raise AdrError(rc, msg)
+
+    def force_kernel(self, kernel: Kernel | int):
+        self._check(self._lib.adr_force_kernel(self._ctx, int(kernel)))
+
+    def last_kernel(self) -> Kernel:
+        return Kernel(self._lib.adr_last_kernel(self._ctx))
+
+    def launch_count(self) -> int:
+        return int(self._lib.adr_launch_count(self._ctx))
+
+    @staticmethod
+    def _f16(v: TensorView, what: str):
+        if v.dtype != torch.float16:
+            raise TypeError(f"{what} must be float16, got {v.dtype}")
+
+    # -- the reference's matmul methods -----------------------------------
+    def _matmul(self, fn, output: TensorView, left: TensorView, right: TensorView,
+                options: MatmulOptions, stream=None):
+        for v, w in ((output, "output"), (left, "left"), (right, "right")):
+            self._f16(v, w)
+        (batches, m, k, n, sox, soy, soz, slx, sly, slz, srx, sry, srz,
+         bias, beta, scale, store, load, mask) = lower_matmul(output, left, right, options)
+        bias_ptr = None
+        if bias is not None:
+            self._f16(bias, "bias")
+            bias_ptr = bias.data_ptr()
+        rc = fn(self._ctx, _stream_handle(stream), output.data_ptr(), left.data_ptr(),
+                right.data_ptr(), batches, m, k, n, sox, soy, soz, slx, sly, slz, srx, sry, srz,
+                bias_ptr, beta, scale, store, load, mask)
+        self._check(rc)
+
+    def matmul_f16(self, output: TensorView, left: TensorView, right: TensorView,
+                   options: MatmulOptions | None = None, stream=None):
+        """CommonKernels::matmul_f16 (kernels.rs:210-213, 821-890)."""
+        self._matmul(self._lib.adr_matmul_f16, output, left, right, options or MatmulOptions(),
+                     stream)
+
+    def matmul_f16_slow(self, output: TensorView, left: TensorView, right: TensorView,
+                        options: MatmulOptions | None = None, stream=None):
+        """CommonKernels::matmul_f16_slow (kernels.rs:206-209, 753-819)."""
+        self._matmul(self._lib.adr_matmul_f16_slow, output, left, right,
+                     options or MatmulOptions(), stream)
+
+    # -- kernels the reference ships without a Rust call site ---------------
+    def matmul_nt_fp16u8(self, output: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor,
+                         scales: torch.Tensor, block_size: int, beta: float = 0.0,
+                         zeros: torch.Tensor | None = None, stream=None):
+        """matmul_nt_fp16u8 / matmul_nt_wmma_16x128x256_fp16u8
+        (matmul_nt_fp16u8.cu:4-12): out[m,n] = lhs[m,p] . deq(rhs[n,p])^T + beta*out."""
+        m, p = lhs.shape
+        n = rhs.shape[0]
+        assert rhs.shape == (n, p) and output.shape == (m, n)
+        assert scales.shape == (n, p // block_size)
+        for t in (output, lhs, rhs, scales) + ((zeros,) if zeros is not None else ()):
+            assert t.is_contiguous() and t.is_cuda
+        assert rhs.dtype == torch.uint8 and lhs.dtype == torch.float16
+        assert output.dtype == torch.float16 and scales.dtype == torch.float16
+        zp = None
+        if zeros is not None:
+            assert zeros.shape == scales.shape and zeros.dtype == torch.float16
+            zp = zeros.data_ptr()
+        rc = self._lib.adr_matmul_nt_fp16u8(self._ctx, _stream_handle(stream), output.data_ptr(),
+                                            lhs.data_ptr(), rhs.data_ptr(), scales.data_ptr(), zp,
+                                            m, p, n, block_size, beta)
+        self._check(rc)
+
+    def matmul_nt_f16(self, output: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor,
+                      beta: float = 0.0, stream=None):
+        """matmul_nt_wmma_128x64x64 / matmul_nt_wmma_16x128x256
+        (matmul_nt_wmma_128x64x64.cu:8-14): out = lhs . rhs^T + beta*out."""
+        m, p = lhs.shape
+        n = rhs.shape[0]
+        assert rhs.shape == (n, p) and output.shape == (m, n)
+        for t in (output, lhs, rhs):
+            assert t.is_contiguous() and t.is_cuda and t.dtype == torch.float16
+        rc = self._lib.adr_matmul_nt_f16(self._ctx, _stream_handle(stream), output.data_ptr(),
+                                         lhs.data_ptr(), rhs.data_ptr(), m, p, n, beta)
+        self._check(rc)
+
+    def dequantize_absmax_uint8(self, output: torch.Tensor, scales: torch.Tensor,
+                                q: torch.Tensor, zeros: torch.Tensor | None = None, stream=None):
+        """dequantize_absmax_uint8 (quantize.cu:46-56)."""
+        rows, k = q.shape
+        bs = k // scales.shape[1]
+        assert output.shape == (rows, k) and output.dtype == torch.float16
+        rc = self._lib.adr_dequantize_absmax_uint8(
+            self._ctx, _stream_handle(stream), output.data_ptr(), scales.data_ptr(),
+            zeros.data_ptr() if zeros is not None else None, q.data_ptr(), rows, k, bs)
+        self._check(rc)
+
+    def quantize_absmax_uint8(self, q: torch.Tensor, scales: torch.Tensor, inp: torch.Tensor,
+                              stream=None):
+        """quantize_absmax_uint8 (quantize.cu:3-44)."""
+        rows, k = inp.shape
+        bs = k // scales.shape[1]
+        assert q.shape == (rows, k) and q.dtype == torch.uint8 and inp.dtype == torch.float16
+        rc = self._lib.adr_quantize_absmax_uint8(self._ctx, _stream_handle(stream), q.data_ptr(),
+                                                 scales.data_ptr(), inp.data_ptr(), rows, k, bs)
+        self._check(rc)
+
+    # -- library-side trace (kernel family per distinct call) -------------
+    def trace_enable(self, on: bool = True):
+        self._check(self._lib.adr_trace_enable(self._ctx, int(on)))
+
+    def trace_dump(self) -> list[dict]:
+        need = self._lib.adr_trace_dump(self._ctx, None, 0)
+        buf = C.create_string_buffer(need)
+        self._lib.adr_trace_dump(self._ctx, buf, need)
+        return [json.loads(l) for l in buf.value.decode().splitlines() if l]
+
+
+class MatmulTracer:
+    """Decorator that records the distinct (left, right, out) layouts seen by
+    the matmul methods (kernels.rs:231-248, 306-333) and forwards everything."""
+
+    def __init__(self, kernels: GpuKernels):
+        self.kernels = kernels
+        self.shape_set: set[tuple[TensorLayout, TensorLayout, TensorLayout]] = set()
+
+    def clear(self):
+        self.shape_set.clear()
+
+    def shapes(self):
+        return list(self.shape_set)
+
+    def matmul_f16(self, output, left, right, options=None, stream=None):
+        self.shape_set.add((left.layout, right.layout, output.layout))
+        return self.kernels.matmul_f16(output, left, right, options, stream)
+
+    def matmul_f16_slow(self, output, left, right, options=None, stream=None):
+        self.shape_set.add((left.layout, right.layout, output.layout))
+        return self.kernels.matmul_f16_slow(output, left, right, options, stream)
+
+    def __getattr__(self, name):
+        return getattr(self.kernels, name)

@@ -1,0 +1,178 @@
+/*
+ * adrastea_b200 — C ABI of the B200-native matmul path.
+ *
+ * Every entry point is what an FFI binding for the reference's kernel-call
+ * interface would bind for this path.  Reference citations are relative to
+ * the reference project root (eiz/adrastea).
+ *
+ * Conventions (identical to the reference's):
+ *   - all tensor pointers are device pointers owned by the caller; the
+ *     library allocates nothing on the per-call path;
+ *   - dimensions and strides are in ELEMENTS, `int`; x = last dimension,
+ *     y = second-last, z = third-last; a z-stride of 0 broadcasts that
+ *     operand over the batch (adrastea_models/src/kernels.rs:864-887);
+ *   - calls are asynchronous: work is enqueued on `stream` (0 = the legacy
+ *     default stream, which is what the reference always uses,
+ *     kernels.rs:862);
+ *   - the return value is 0 on success or an ADR_ERR_* code; nothing aborts
+ *     or traps.  Where the reference panics (shape asserts,
+ *     kernels.rs:825-827) or traps on the device (unknown op,
+ *     adrastea_kernels/cpp/matmul.cu:428-429, 489-490) this library returns
+ *     an error code before launching anything.
+ *
+ * `void*` stands for `__half*` so that the header needs no CUDA includes.
+ */
+#ifndef ADRASTEA_B200_H_
+#define ADRASTEA_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct adr_ctx adr_ctx;
+typedef void* adr_stream; /* cudaStream_t */
+
+enum {
+  ADR_OK = 0,
+  ADR_ERR_INVALID = 1,     /* null pointer, non-positive size, bad enum value */
+  ADR_ERR_SHAPE = 2,       /* shape / divisibility / alignment rule violated  */
+  ADR_ERR_UNSUPPORTED = 3, /* op the reference has no device code for         */
+  ADR_ERR_CUDA = 4,        /* a CUDA call failed; see adr_last_cuda_error     */
+  ADR_ERR_DEVICE = 5,      /* a kernel reported a bounded wait that ran out   */
+  ADR_ERR_NCCL = 6
+};
+
+/* matmul.cu:26-36, kernels.rs:80-139 */
+enum { ADR_LOAD_IDENTITY = 0, ADR_LOAD_SCALE = 1 };
+enum {
+  ADR_STORE_IDENTITY = 0,
+  ADR_STORE_GELU_BIAS = 1, /* enum value without device code in the reference: rejected */
+  ADR_STORE_BETA_GELU_BIAS = 2,
+  ADR_STORE_BETA_BIAS = 3,
+  ADR_STORE_SCALE = 4,
+  ADR_STORE_ADD = 5,
+  ADR_STORE_QUICK_GELU_BIAS = 6
+};
+enum { ADR_MASK_NONE = 0, ADR_MASK_CAUSAL = 1 };
+
+/* Kernel families the dispatcher can pick; see adr_force_kernel / adr_last_kernel. */
+enum {
+  ADR_KERNEL_AUTO = 0,
+  ADR_KERNEL_F16_SIMT = 1,    /* any strides, any op; CUDA cores                    */
+  ADR_KERNEL_F16_TC = 2,      /* TMA + tcgen05.mma, accumulators in TMEM             */
+  ADR_KERNEL_U8_GEMV = 3,     /* m <= 4: 128-bit weight loads, fp32 FMA, shuffles    */
+  ADR_KERNEL_U8_MMA = 4,      /* m <= 16: 128-bit weight loads, register-fed MMA     */
+  ADR_KERNEL_U8_TC = 5,       /* m > 16: dequantise into shared memory, tcgen05.mma  */
+  ADR_KERNEL_U8_SIMT = 6      /* any m; thread-per-output restatement (slow)         */
+};
+
+/*
+ * Replaces GpuKernels::new(capability) (kernels.rs:458-502): binds to `device`
+ * (a CUDA ordinal), checks that it is an sm_100 part, sets the opt-in shared
+ * memory sizes of the kernels.  The context is thread-compatible.
+ */
+int adr_init(int device, adr_ctx** out_ctx);
+void adr_destroy(adr_ctx* ctx);
+const char* adr_strerror(int code);
+/* cudaError_t of the last failing CUDA call seen by this context (0 if none). */
+int adr_last_cuda_error(const adr_ctx* ctx);
+/* Pin the kernel family used by the next calls (ADR_KERNEL_AUTO restores dispatch).
+ * A call whose shape the pinned kernel cannot take returns ADR_ERR_SHAPE. */
+int adr_force_kernel(adr_ctx* ctx, int kernel);
+/* Kernel family chosen by the most recent successful matmul call. */
+int adr_last_kernel(const adr_ctx* ctx);
+/* Number of kernel launches issued through this context so far. */
+uint64_t adr_launch_count(const adr_ctx* ctx);
+
+/*
+ * Replaces CommonKernels::matmul_f16 -> GpuKernels::matmul_f16 -> kernel
+ * matmul_f16_fast (kernels.rs:210-213, 821-890; matmul.cu:504-513).
+ * The 22 arguments after `stream` are, in order, exactly the kernel
+ * parameters the reference marshals (matmul.cu:186-190, 493-499):
+ *   out[b,y,x] = store(sum_k load(lhs[b,y,k]) * load(rhs[b,k,x]))
+ * with the causal mask writing -inf where x > y.
+ * `out` is read in place by ADD, BETA_BIAS and BETA_GELU_BIAS.
+ */
+int adr_matmul_f16(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs, const void* rhs,
+                   int batches, int m, int k, int n, int stride_ox, int stride_oy, int stride_oz,
+                   int stride_lx, int stride_ly, int stride_lz, int stride_rx, int stride_ry,
+                   int stride_rz, const void* bias, float beta, float scale, uint32_t store_op,
+                   uint32_t load_op, uint32_t mask_op);
+
+/*
+ * Replaces CommonKernels::matmul_f16_slow -> kernel matmul_f16
+ * (kernels.rs:206-209, 753-819; matmul.cu:493-502).  Same contract; always
+ * takes the CUDA-core kernel that accepts any strides.
+ */
+int adr_matmul_f16_slow(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                        const void* rhs, int batches, int m, int k, int n, int stride_ox,
+                        int stride_oy, int stride_oz, int stride_lx, int stride_ly, int stride_lz,
+                        int stride_rx, int stride_ry, int stride_rz, const void* bias, float beta,
+                        float scale, uint32_t store_op, uint32_t load_op, uint32_t mask_op);
+
+/*
+ * Replaces kernel matmul_f16_raw (matmul.cu:515-517): identity ops, no mask.
+ */
+int adr_matmul_f16_raw(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                       const void* rhs, int batches, int m, int k, int n, int stride_ox,
+                       int stride_oy, int stride_oz, int stride_lx, int stride_ly, int stride_lz,
+                       int stride_rx, int stride_ry, int stride_rz);
+
+/*
+ * Replaces kernels matmul_nt_fp16u8 (matmul_nt_fp16u8.cu:4-24) and
+ * matmul_nt_wmma_16x128x256_fp16u8 (matmul_nt_wmma_16x128x256_fp16u8.cu:12-83),
+ * same parameter list:  out[m,n] = lhs[m,p] . deq(rhs[n,p])^T + beta * out.
+ * rhs is u8 [n,p] row-major, scales fp16 [n, p/block_size] row-major.
+ * deq(q) = fp16((float(q) - zero) * float(scale)), bit-exact, accumulated in fp32.
+ * `zeros` NULL: zero = 127.5 (the reference's layout).  `zeros` non-NULL
+ * (fp16 [n, p/block_size]; an extension without counterpart in the
+ * reference): zero = float(zeros[n, group]).
+ * Requires p % block_size == 0, block_size % 16 == 0 and p % 16 == 0; any m, n.
+ */
+int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                         const uint8_t* rhs, const void* scales, const void* zeros, int m, int p,
+                         int n, int block_size, float beta);
+
+/*
+ * Replaces kernels matmul_nt_wmma_128x64x64 (matmul_nt_wmma_128x64x64.cu:8-78)
+ * and matmul_nt_wmma_16x128x256 (matmul_nt_wmma_16x128x256.cu:8-68), same
+ * parameter list:  out[m,n] = lhs[m,p] . rhs[n,p]^T + beta * out, contiguous
+ * row-major operands.  The reference's divisibility rules are not required.
+ */
+int adr_matmul_nt_f16(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                      const void* rhs, int m, int p, int n, float beta);
+
+/*
+ * Replaces kernel dequantize_absmax_uint8 (quantize.cu:46-56):
+ * out[r,i] = fp16((float(q[r,i]) - zero) * float(scales[r, i / block_size])),
+ * contiguous [rows,k] operands; `zeros` as in adr_matmul_nt_fp16u8.
+ */
+int adr_dequantize_absmax_uint8(adr_ctx* ctx, adr_stream stream, void* out, const void* scales,
+                                const void* zeros, const uint8_t* q, int rows, int k,
+                                int block_size);
+
+/*
+ * Replaces kernel quantize_absmax_uint8 (quantize.cu:3-44): per (row, group)
+ * scale = fp16(max|x| / 127.5), q = u8(round(127.5 + x / scale)).
+ */
+int adr_quantize_absmax_uint8(adr_ctx* ctx, adr_stream stream, uint8_t* q, void* scales,
+                              const void* in, int rows, int k, int block_size);
+
+/*
+ * Replaces MatmulTracer (kernels.rs:231-248, 306-333).  When enabled, every
+ * matmul call records (m, k, n, batches, strides, ops, kernel family) once per
+ * distinct combination.  adr_trace_dump writes one JSON object per line into
+ * `buf` (at most `cap` bytes, NUL terminated) and returns the number of bytes
+ * the full dump needs.
+ */
+int adr_trace_enable(adr_ctx* ctx, int on);
+void adr_trace_clear(adr_ctx* ctx);
+size_t adr_trace_dump(adr_ctx* ctx, char* buf, size_t cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ADRASTEA_B200_H_ */

@@ -1,0 +1,314 @@
+"""GPU parity tests: every call goes through the C ABI (libadrastea_b200.so)
+and is compared with the CPU oracle, with the golden vectors and, when the
+reference cubins travelled along, with the reference's own kernels run live.
+
+Tolerances (BASELINE north star): max relative error <= 1e-2 against the
+fp32-accumulate ("ideal") oracle; u8 dequantisation bit-exact; the CUDA-core
+fp16 kernel bit-exact against the reference kernels (it keeps their
+arithmetic), up to 2 fp16 ulps where tanhf/expf sit in the epilogue.
+"""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from adrastea_b200 import (AdrError, Kernel, MatmulLoad, MatmulLoadOp, MatmulMask, MatmulOptions,
+                           MatmulStore, MatmulTracer, TensorLayout, TensorView)
+from oracle import oracle, refcubin
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+GOLD = Path(__file__).resolve().parent / "golden"
+CANARY = 64  # guard elements either side of every output buffer
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def options_of(c, bias_view):
+    o = MatmulOptions.new()
+    if c.load == cases.LD_SCALE:
+        o = o.load(MatmulLoad.Scale(c.scale))
+    st = {cases.ST_IDENTITY: MatmulStore.Identity(), cases.ST_ADD: MatmulStore.Add(),
+          cases.ST_SCALE: MatmulStore.Scale(c.scale)}.get(c.store)
+    if st is None:
+        st = {cases.ST_BETA_BIAS: lambda: MatmulStore.BetaBias(c.beta, bias_view),
+              cases.ST_BETA_GELU_BIAS: lambda: MatmulStore.BetaGeluBias(c.beta, bias_view),
+              cases.ST_QUICK_GELU: lambda: MatmulStore.QuickGeluBias(bias_view)}[c.store]()
+    o = o.store(st)
+    if c.mask == cases.MK_CAUSAL:
+        o = o.mask(MatmulMask.Causal)
+    return o
+
+
+def view_of(t, c, strides, dims3):
+    if c.batches > 1:
+        lay = TensorLayout.new(dims3, (strides[2] or 1, strides[1], strides[0]))
+        if strides[2] == 0:  # broadcast operand: pass the 2-D view (z-stride becomes 0)
+            lay = TensorLayout.new(dims3[1:], (strides[1], strides[0]))
+    else:
+        lay = TensorLayout.new(dims3[1:], (strides[1], strides[0]))
+    return TensorView(t, lay, 0)
+
+
+def run_case(kernels, c, slow):
+    out0, lhs, rhs, bias = c.inputs()
+    guard = np.full(CANARY, 123.0, np.float16)
+    o = dev(np.concatenate([guard, out0, guard]))
+    l, r, b = dev(lhs), dev(rhs), dev(bias)
+    ov = view_of(o, c, c.out_strides, (c.batches, c.m, c.n))
+    ov.offset = CANARY
+    lv = view_of(l, c, c.lhs_strides, (c.batches, c.m, c.k))
+    rv = view_of(r, c, c.rhs_strides, (c.batches, c.k, c.n))
+    opts = options_of(c, TensorView.of(b))
+    (kernels.matmul_f16_slow if slow else kernels.matmul_f16)(ov, lv, rv, opts)
+    torch.cuda.synchronize()
+    res = o.cpu().numpy()
+    assert np.all(res[:CANARY] == guard) and np.all(res[-CANARY:] == guard), "wrote outside the output"
+    return res[CANARY:-CANARY]
+
+
+def oracle_out(c, ideal):
+    out, lhs, rhs, bias = c.inputs()
+    assert oracle.matmul_f16(out, lhs, rhs, c.batches, c.m, c.k, c.n, c.strides9(),
+                             bias if c.uses_bias() else None, c.beta, c.scale, c.store, c.load,
+                             c.mask, ideal=ideal) == 0
+    return out
+
+
+def ulp_diff(a, b):
+    return a.view(np.uint16).astype(np.int32) - b.view(np.uint16).astype(np.int32)
+
+
+@pytest.mark.parametrize("c", cases.matmul_cases(), ids=lambda c: c.name)
+def test_matmul_f16_slow_is_bit_faithful(kernels, c):
+    """The CUDA-core kernel keeps the reference's arithmetic: equal bits with the
+    faithful oracle, with the golden vectors and with the live reference kernel."""
+    got = run_case(kernels, c, slow=True)
+    assert kernels.last_kernel() == Kernel.F16Simt
+    want = oracle_out(c, ideal=False)
+    d = ulp_diff(got, want)
+    if c.exact_vs_reference:
+        assert not d.any()
+    else:
+        assert np.abs(d).max() <= 2
+    again = run_case(kernels, c, slow=True)
+    assert np.array_equal(got.view(np.uint16), again.view(np.uint16)), "not deterministic"
+    gold = GOLD / "reference_matmul_f16.npz"
+    if gold.exists():
+        ref = np.load(gold)[f"{c.name}/matmul_f16_fast"]
+        assert np.abs(ulp_diff(got, ref)).max() <= (0 if c.exact_vs_reference else 1)
+
+
+@pytest.mark.parametrize("c", cases.matmul_cases(), ids=lambda c: c.name)
+def test_matmul_f16_against_ideal_oracle(kernels, c):
+    """The dispatched kernel (tensor cores where the view allows) within 1e-2."""
+    got = run_case(kernels, c, slow=False)
+    want = oracle_out(c, ideal=True)
+    err = oracle.max_rel_err(got, want)
+    assert err <= TOL, (err, kernels.last_kernel())
+    again = run_case(kernels, c, slow=False)
+    assert np.array_equal(got.view(np.uint16), again.view(np.uint16)), "not deterministic"
+
+
+@pytest.mark.parametrize("c", cases.matmul_cases(), ids=lambda c: c.name)
+def test_live_reference_kernels_agree_with_oracle(c):
+    """Pins the oracle on this very GPU: matmul_f16 / matmul_f16_fast from the
+    reference tree against orc_matmul_f16_ref."""
+    if not refcubin.available():
+        pytest.skip("reference cubins not present")
+    want = oracle_out(c, ideal=False)
+    for kern in ("matmul_f16", "matmul_f16_fast"):
+        out0, lhs, rhs, bias = c.inputs()
+        o, l, r, b = dev(out0), dev(lhs), dev(rhs), dev(bias)
+        refcubin.matmul_f16(kern, o.data_ptr(), l.data_ptr(), r.data_ptr(), c.batches, c.m, c.k,
+                            c.n, c.strides9(), b.data_ptr() if c.uses_bias() else None, c.beta,
+                            c.scale, c.store, c.load, c.mask)
+        torch.cuda.synchronize()
+        d = ulp_diff(o.cpu().numpy(), want)
+        assert np.abs(d).max() <= (0 if c.exact_vs_reference else 2), kern
+
+
+def u8_kernels_for(c):
+    ks = [Kernel.U8Simt]
+    if c.m <= 4:
+        ks.append(Kernel.U8Gemv)
+    if c.p % 64 == 0:
+        ks.append(Kernel.U8Mma)
+    return ks
+
+
+@pytest.mark.parametrize("c", cases.u8_cases(), ids=lambda c: c.name)
+def test_u8_matmul_all_kernels(kernels, c):
+    out0, lhs, q, scales, zeros = c.inputs()
+    want = oracle.matmul_nt_fp16u8(lhs, q, scales, c.block_size, c.beta, out0, zeros)
+    l, qq, s = dev(lhs), dev(q), dev(scales)
+    z = dev(zeros) if zeros is not None else None
+    try:
+        for k in u8_kernels_for(c) + [Kernel.Auto]:
+            kernels.force_kernel(k)
+            res = []
+            for _ in range(2):
+                o = dev(out0.copy())
+                kernels.matmul_nt_fp16u8(o, l, qq, s, c.block_size, c.beta, z)
+                torch.cuda.synchronize()
+                res.append(o.cpu().numpy())
+            assert np.array_equal(res[0].view(np.uint16), res[1].view(np.uint16)), f"{k!r} not deterministic"
+            err = oracle.max_rel_err(res[0], want)
+            assert err <= TOL, (k, err)
+    finally:
+        kernels.force_kernel(Kernel.Auto)
+
+
+@pytest.mark.parametrize("c", cases.u8_cases(), ids=lambda c: c.name)
+def test_u8_dequantisation_is_bit_exact(kernels, c):
+    """The in-register dequantisation every u8 kernel uses, dumped through
+    adr_dequantize_absmax_uint8, equals fp16((q - zero) * s) bit for bit."""
+    _, _, q, scales, zeros = c.inputs()
+    want = oracle.dequantize(q, scales, c.block_size, zeros)
+    w = torch.empty((c.n, c.p), dtype=torch.float16, device="cuda")
+    kernels.dequantize_absmax_uint8(w, dev(scales), dev(q), dev(zeros) if zeros is not None else None)
+    torch.cuda.synchronize()
+    assert np.array_equal(w.cpu().numpy().view(np.uint16), want.view(np.uint16))
+    if zeros is None and refcubin.available():
+        r = torch.empty_like(w)
+        refcubin.dequantize_absmax_uint8(r.data_ptr(), dev(scales).data_ptr(), dev(q).data_ptr(), c.n, c.p, c.block_size)
+        torch.cuda.synchronize()
+        assert torch.equal(w.view(torch.int16), r.view(torch.int16))
+
+
+def test_dequantisation_every_code_and_many_scales(kernels):
+    """All 256 codes against a sweep of scale bit patterns, including subnormal,
+    tiny, large and negative scales (fast and fp32 paths of the dequantiser)."""
+    sb = np.concatenate([np.arange(0, 0x0C00, 7), np.arange(0x0C00, 0x7C00, 97), [0x7BFF, 0x8001, 0x9234, 0xB000]]).astype(np.uint16)
+    n = sb.size
+    q = np.tile(np.arange(256, dtype=np.uint8), (n, 1))
+    scales = np.repeat(sb.view(np.float16)[:, None], 256 // 16, axis=1)
+    want = oracle.dequantize(q, scales, 16)
+    w = torch.empty((n, 256), dtype=torch.float16, device="cuda")
+    kernels.dequantize_absmax_uint8(w, dev(scales), dev(q))
+    torch.cuda.synchronize()
+    assert np.array_equal(w.cpu().numpy().view(np.uint16), want.view(np.uint16))
+
+
+def test_quantizer_matches_oracle_and_reference(kernels):
+    rng = np.random.default_rng(11)
+    for rows, k, bs in ((24, 512, 128), (8, 256, 32), (5, 512, 256)):
+        x = (rng.standard_normal((rows, k)) * rng.uniform(0.01, 2.0, (rows, 1))).astype(np.float16)
+        x[1, :bs] = 0
+        q = torch.zeros((rows, k), dtype=torch.uint8, device="cuda")
+        s = torch.zeros((rows, k // bs), dtype=torch.float16, device="cuda")
+        kernels.quantize_absmax_uint8(q, s, dev(x))
+        torch.cuda.synchronize()
+        wq, ws = oracle.quantize(x, bs)
+        assert np.array_equal(s.cpu().numpy().view(np.uint16), ws.view(np.uint16))
+        assert np.array_equal(q.cpu().numpy(), wq)
+        if refcubin.available():
+            rq, rs = torch.zeros_like(q), torch.zeros_like(s)
+            refcubin.quantize_absmax_uint8(rq.data_ptr(), rs.data_ptr(), dev(x).data_ptr(), rows, k, bs)
+            torch.cuda.synchronize()
+            assert torch.equal(rq, q) and torch.equal(rs.view(torch.int16), s.view(torch.int16))
+
+
+def test_matmul_nt_f16(kernels):
+    rng = np.random.default_rng(12)
+    for m, p, n, beta in ((128, 192, 128, 0.0), (256, 128, 64, 0.5), (16, 256, 128, 1.0), (7, 40, 13, 0.25)):
+        lhs = (rng.standard_normal((m, p)) * 0.3).astype(np.float16)
+        rhs = (rng.standard_normal((n, p)) * 0.3).astype(np.float16)
+        out0 = (rng.standard_normal((m, n)) * 0.5).astype(np.float16)
+        o = dev(out0.copy())
+        kernels.matmul_nt_f16(o, dev(lhs), dev(rhs), beta)
+        torch.cuda.synchronize()
+        want = oracle.matmul_nt_f16(lhs, rhs, beta, out0)
+        assert oracle.max_rel_err(o.cpu().numpy(), want) <= TOL
+
+
+def test_error_codes_instead_of_traps(kernels):
+    t = torch.zeros(16, 16, dtype=torch.float16, device="cuda")
+    v = TensorView.of(t)
+    with pytest.raises(AdrError) as e:  # GELU_BIAS has no device code in the reference (it traps)
+        kernels.matmul_f16(v, v, v, MatmulOptions.new().store(MatmulStore.GeluBias(TensorView.of(t[0]))))
+    assert e.value.code == 3
+    with pytest.raises(AssertionError):  # shape mismatch: the reference panics
+        kernels.matmul_f16(v, v, TensorView.of(t[:8]))
+    q = torch.zeros(16, 48, dtype=torch.uint8, device="cuda")
+    s = torch.zeros(16, 2, dtype=torch.float16, device="cuda")
+    x = torch.zeros(1, 48, dtype=torch.float16, device="cuda")
+    o = torch.zeros(1, 16, dtype=torch.float16, device="cuda")
+    with pytest.raises(AdrError) as e:  # block size 24 is not a multiple of 16
+        kernels.matmul_nt_fp16u8(o, x, q, s, 24)
+    assert e.value.code == 2
+    # the context is still usable afterwards
+    kernels.matmul_f16(v, v, v)
+    torch.cuda.synchronize()
+
+
+def test_tracer_records_distinct_layouts(kernels):
+    tr = MatmulTracer(kernels)
+    a = TensorView.of(torch.zeros(8, 32, dtype=torch.float16, device="cuda"))
+    w = TensorView.of(torch.zeros(16, 32, dtype=torch.float16, device="cuda"))
+    o = TensorView.of(torch.zeros(8, 16, dtype=torch.float16, device="cuda"))
+    kernels.trace_enable(True)
+    for _ in range(3):
+        tr.matmul_f16(o, a, w.permute([1, 0]))
+    assert len(tr.shapes()) == 1
+    dump = kernels.trace_dump()
+    assert any(d["m"] == 8 and d["k"] == 32 and d["n"] == 16 and d["rhs_strides"] == [32, 1, 0] for d in dump)
+    kernels.trace_enable(False)
+
+
+# ------------------------------------------------------------ full BASELINE sizes
+def test_config1_full_size(kernels):
+    """C[64,4096] = A[64,4096] . W[4096,4096], N(0, 0.02^2), both W layouts."""
+    rng = np.random.default_rng(100)
+    m = 64
+    k = n = 4096
+    a = (rng.standard_normal((m, k)) * 0.02).astype(np.float16)
+    w = (rng.standard_normal((k, n)) * 0.02).astype(np.float16)  # W[K,N] row-major ("rrr")
+    want = np.zeros(m * n, np.float16)
+    oracle.matmul_f16(want, a.reshape(-1), w.reshape(-1), 1, m, k, n, (1, n, 0, 1, k, 0, 1, n, 0), ideal=True)
+    ad, wd = dev(a), dev(w)
+    o = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+    kernels.matmul_f16(TensorView.of(o), TensorView.of(ad), TensorView.of(wd))
+    torch.cuda.synchronize()
+    assert oracle.max_rel_err(o.cpu().numpy().reshape(-1), want) <= TOL
+    wt = dev(np.ascontiguousarray(w.T))  # the reference's storage: [N,K], passed permuted ("rrc")
+    o2 = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+    kernels.matmul_f16(TensorView.of(o2), TensorView.of(ad), TensorView.of(wt).permute([1, 0]))
+    torch.cuda.synchronize()
+    assert oracle.max_rel_err(o2.cpu().numpy().reshape(-1), want) <= TOL
+
+
+@pytest.mark.parametrize("m", [1, 4, 16])
+@pytest.mark.parametrize("n", [4096, 11008])
+def test_config2_full_size(kernels, m, n):
+    """u8 decode shapes at full size: every kernel against the oracle on a
+    random subset of output columns (a column depends on one weight row only),
+    and the kernels against each other on all columns."""
+    p, bs = 4096, 128
+    rng = np.random.default_rng(200 + m + n)
+    x = rng.standard_normal((m, p)).astype(np.float16)
+    q = rng.integers(0, 256, (n, p), dtype=np.uint8)
+    s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
+    z = rng.uniform(120, 136, (n, p // bs)).astype(np.float16)
+    cols = np.sort(rng.choice(n, 96, replace=False))
+    xd, qd, sd, zd = dev(x), dev(q), dev(s), dev(z)
+    try:
+        for zeros_np, zeros_d in ((None, None), (z, zd)):
+            want = oracle.matmul_nt_fp16u8(x, q[cols], s[cols], bs, zeros=None if zeros_np is None else zeros_np[cols])
+            outs = {}
+            for kern in [Kernel.U8Mma] + ([Kernel.U8Gemv] if m <= 4 else []) + [Kernel.Auto]:
+                kernels.force_kernel(kern)
+                o = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+                kernels.matmul_nt_fp16u8(o, xd, qd, sd, bs, 0.0, zeros_d)
+                torch.cuda.synchronize()
+                outs[kern] = o.cpu().numpy()
+                assert oracle.max_rel_err(outs[kern][:, cols], want) <= TOL, kern
+            base = outs[Kernel.U8Mma]
+            for kern, o in outs.items():
+                assert oracle.max_rel_err(o, base) <= TOL, kern
+    finally:
+        kernels.force_kernel(Kernel.Auto)
