@@ -175,7 +175,8 @@ def test_u8_dequantisation_is_bit_exact(kernels, c):
     assert np.array_equal(w.cpu().numpy().view(np.uint16), want.view(np.uint16))
     if zeros is None and refcubin.available():
         r = torch.empty_like(w)
-        refcubin.dequantize_absmax_uint8(r.data_ptr(), dev(scales).data_ptr(), dev(q).data_ptr(), c.n, c.p, c.block_size)
+        sd, qd = dev(scales), dev(q)  # keep the device buffers alive across the launch
+        refcubin.dequantize_absmax_uint8(r.data_ptr(), sd.data_ptr(), qd.data_ptr(), c.n, c.p, c.block_size)
         torch.cuda.synchronize()
         assert torch.equal(w.view(torch.int16), r.view(torch.int16))
 
@@ -208,7 +209,8 @@ def test_quantizer_matches_oracle_and_reference(kernels):
         assert np.array_equal(q.cpu().numpy(), wq)
         if refcubin.available():
             rq, rs = torch.zeros_like(q), torch.zeros_like(s)
-            refcubin.quantize_absmax_uint8(rq.data_ptr(), rs.data_ptr(), dev(x).data_ptr(), rows, k, bs)
+            xd = dev(x)
+            refcubin.quantize_absmax_uint8(rq.data_ptr(), rs.data_ptr(), xd.data_ptr(), rows, k, bs)
             torch.cuda.synchronize()
             assert torch.equal(rq, q) and torch.equal(rs.view(torch.int16), s.view(torch.int16))
 
