@@ -23,6 +23,8 @@ SIGNATURES = {
     "adr_last_cuda_error": (_c_int, [_vp]),
     "adr_force_kernel": (_c_int, [_vp, _c_int]),
     "adr_last_kernel": (_c_int, [_vp]),
+    "adr_set_tunable": (_c_int, [_vp, C.c_char_p, _c_int]),
+    "adr_device_status": (_c_int, [_vp]),
     "adr_launch_count": (C.c_uint64, [_vp]),
     "adr_matmul_f16": (_c_int, _MATMUL_F16_ARGS),
     "adr_matmul_f16_slow": (_c_int, _MATMUL_F16_ARGS),

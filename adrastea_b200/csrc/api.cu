@@ -7,7 +7,7 @@
 #include <cstring>
 #include <new>
 
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace adr {
 
@@ -66,6 +66,12 @@ int run_matmul(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, bool slow
   return rc;
 }
 
+#ifdef ADR_U8_TRACE
+constexpr size_t kStatusBytes = 1 << 22;
+#else
+constexpr size_t kStatusBytes = 64;
+#endif
+
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 }  // namespace
@@ -92,10 +98,11 @@ int adr_init(int device, adr_ctx** out_ctx) {
   cudaGetDevice(&prev);
   cudaSetDevice(device);
   int rc = ADR_OK;
-  if (cudaMalloc(&ctx->d_status, 64) != cudaSuccess ||
-      cudaMemset(ctx->d_status, 0, 64) != cudaSuccess) {
+  if (cudaMalloc(&ctx->d_status, kStatusBytes) != cudaSuccess ||
+      cudaMemset(ctx->d_status, 0, kStatusBytes) != cudaSuccess) {
     rc = ADR_ERR_CUDA;
   }
+  if (rc == ADR_OK) rc = tma_init(ctx);
   if (rc == ADR_OK) rc = init_gemm_f16_tc(ctx);
   if (rc == ADR_OK) rc = init_u8_kernels(ctx);
   cudaSetDevice(prev);
@@ -110,6 +117,7 @@ int adr_init(int device, adr_ctx** out_ctx) {
 void adr_destroy(adr_ctx* ctx) {
   if (!ctx) return;
   destroy_gemm_f16_tc(ctx);
+  tma_destroy(ctx);
   if (ctx->d_status) cudaFree(ctx->d_status);
   delete ctx;
 }
@@ -130,8 +138,30 @@ const char* adr_strerror(int code) {
 int adr_last_cuda_error(const adr_ctx* ctx) { return ctx ? ctx->last_cuda_error : 0; }
 
 int adr_force_kernel(adr_ctx* ctx, int kernel) {
-  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_U8_SIMT) return ADR_ERR_INVALID;
+  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_U8_STREAM) return ADR_ERR_INVALID;
   ctx->forced_kernel = kernel;
+  return ADR_OK;
+}
+
+int adr_set_tunable(adr_ctx* ctx, const char* name, int value) {
+  if (!ctx || !name || value < 0) return ADR_ERR_INVALID;
+  if (!strcmp(name, "u8_split")) ctx->tune_u8_split = value;
+  else if (!strcmp(name, "u8_rows")) ctx->tune_u8_rows = value;
+  else if (!strcmp(name, "tc_bn")) ctx->tune_tc_bn = value;
+  else if (!strcmp(name, "pdl")) ctx->tune_pdl = value;
+  else return ADR_ERR_INVALID;
+  return ADR_OK;
+}
+
+int adr_device_status(adr_ctx* ctx) {
+  if (!ctx) return ADR_ERR_INVALID;
+  unsigned int flag = 0;
+  ADR_CUDA_CHECK(ctx, cudaDeviceSynchronize());
+  ADR_CUDA_CHECK(ctx, cudaMemcpy(&flag, ctx->d_status, sizeof(flag), cudaMemcpyDeviceToHost));
+  if (flag) {
+    ADR_CUDA_CHECK(ctx, cudaMemset(ctx->d_status, 0, sizeof(flag)));
+    return ADR_ERR_DEVICE;
+  }
   return ADR_OK;
 }
 
@@ -185,12 +215,14 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
   int kernel = ctx->forced_kernel;
   if (kernel == ADR_KERNEL_AUTO) {
     if (p % 64 != 0) kernel = m <= 4 ? ADR_KERNEL_U8_GEMV : ADR_KERNEL_U8_SIMT;
+    else if (u8_stream_supports(ctx, a)) kernel = ADR_KERNEL_U8_STREAM;
     else kernel = ADR_KERNEL_U8_MMA;
   }
   int rc;
   switch (kernel) {
     case ADR_KERNEL_U8_GEMV: rc = launch_u8_gemv(ctx, st, a); break;
     case ADR_KERNEL_U8_SIMT: rc = launch_u8_simt(ctx, st, a); break;
+    case ADR_KERNEL_U8_STREAM: rc = launch_u8_stream(ctx, st, a); break;
     case ADR_KERNEL_U8_MMA: {
       if (p % 64 != 0) return ADR_ERR_SHAPE;
       rc = ADR_OK;
@@ -282,3 +314,7 @@ size_t adr_trace_dump(adr_ctx* ctx, char* buf, size_t cap) {
 }
 
 }  // extern "C"
+
+#ifdef ADR_U8_TRACE
+extern "C" void* adr_debug_status_ptr(adr_ctx* ctx) { return ctx->d_status; }
+#endif

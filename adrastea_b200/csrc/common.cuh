@@ -57,6 +57,11 @@ struct adr_ctx {
   // Cache of TMA descriptors, keyed by (pointer, dims, strides, box).
   void* tma_cache = nullptr;
   void* encode_tiled_fn = nullptr;  // cuTensorMapEncodeTiled, resolved at init
+  // tuning knobs (adr_set_tunable); 0 = let the planner choose
+  int tune_u8_split = 0;
+  int tune_u8_rows = 0;
+  int tune_tc_bn = 0;
+  int tune_pdl = 0;  // programmatic dependent launch of the u8 streaming kernel
 };
 
 namespace adr {
@@ -174,6 +179,8 @@ struct U8Args {
 int launch_u8_simt(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 int launch_u8_gemv(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 int launch_u8_mma(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
+int launch_u8_stream(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
+bool u8_stream_supports(const adr_ctx* ctx, const U8Args& a);
 int init_u8_kernels(adr_ctx* ctx);
 
 int launch_dequantize_u8(adr_ctx* ctx, cudaStream_t stream, __half* out, const __half* scales,

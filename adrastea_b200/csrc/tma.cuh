@@ -1,0 +1,110 @@
+// Tensor-map (TMA descriptor) construction and the PTX wrappers shared by the
+// kernels that stage operands through shared memory: mbarrier, tiled bulk
+// tensor loads (each into the issuing CTA's own shared memory), bounded waits.
+#pragma once
+
+#include <cuda.h>  // CUtensorMap and its enums; the encode function is resolved at run time
+
+#include "common.cuh"
+
+namespace adr {
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point, so that the
+// library does not link against libcuda.
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int tma_init(adr_ctx* ctx);
+void tma_destroy(adr_ctx* ctx);
+
+// A rank-`rank` (2 or 3) tiled map over `base`.  dims[0] is the innermost extent in
+// elements, strides_bytes[i] the byte pitch of dimension i+1, box the tile in elements.
+// Cached in the context by value of all arguments.  Returns ADR_OK or an error code.
+int tma_get(adr_ctx* ctx, CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base,
+            const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+            CUtensorMapSwizzle swizzle);
+
+// ---------------------------------------------------------------------------
+// device side
+// ---------------------------------------------------------------------------
+constexpr long long kWaitLimitCycles = 2000000000LL;  // about a second at 2 GHz
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, unsigned parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait: gives up after kWaitLimitCycles and returns false; the caller records the
+// failure in the context's status word and carries on to a normal exit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > kWaitLimitCycles) return false;
+  }
+}
+// 1-D bulk copy global -> this CTA's shared memory (16-byte aligned addresses and size).
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, unsigned bytes,
+                                         uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+          "r"(smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+// Tiled tensor loads into this CTA's shared memory.  x is the innermost coordinate and
+// must make x * element size a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, int x, int y, int z,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(const void* p) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(smem_u32(p)));
+  return v;
+}
+
+}  // namespace adr

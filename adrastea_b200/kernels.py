@@ -56,6 +56,7 @@ class Kernel(enum.IntEnum):
     U8Mma = 4
     U8Tc = 5
     U8Simt = 6
+    U8Stream = 7
 
 
 @dataclass(frozen=True)
@@ -224,6 +225,13 @@ class GpuKernels:
 
     def force_kernel(self, kernel: Kernel | int):
         self._check(self._lib.adr_force_kernel(self._ctx, int(kernel)))
+
+    def set_tunable(self, name: str, value: int):
+        self._check(self._lib.adr_set_tunable(self._ctx, name.encode(), int(value)))
+
+    def device_status(self):
+        """Synchronise and raise if a kernel gave up on a bounded wait."""
+        self._check(self._lib.adr_device_status(self._ctx))
 
     def last_kernel(self) -> Kernel:
         return Kernel(self._lib.adr_last_kernel(self._ctx))

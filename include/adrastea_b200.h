@@ -66,7 +66,8 @@ enum {
   ADR_KERNEL_U8_GEMV = 3,     /* m <= 4: 128-bit weight loads, fp32 FMA, shuffles    */
   ADR_KERNEL_U8_MMA = 4,      /* m <= 16: 128-bit weight loads, register-fed MMA     */
   ADR_KERNEL_U8_TC = 5,       /* m > 16: dequantise into shared memory, tcgen05.mma  */
-  ADR_KERNEL_U8_SIMT = 6      /* any m; thread-per-output restatement (slow)         */
+  ADR_KERNEL_U8_SIMT = 6,     /* any m; thread-per-output restatement (slow)         */
+  ADR_KERNEL_U8_STREAM = 7    /* m <= 16: bulk-copy staged, cluster split-k, register-fed MMA */
 };
 
 /*
@@ -82,6 +83,20 @@ int adr_last_cuda_error(const adr_ctx* ctx);
 /* Pin the kernel family used by the next calls (ADR_KERNEL_AUTO restores dispatch).
  * A call whose shape the pinned kernel cannot take returns ADR_ERR_SHAPE. */
 int adr_force_kernel(adr_ctx* ctx, int kernel);
+/* Tuning knobs for A/B runs; value 0 restores the planner's own choice.
+ *   "u8_split": cluster size (k-split) of the streaming u8 kernel, 1/2/4/8
+ *   "u8_rows":  weight rows per CTA of the streaming u8 kernel, 32/64
+ *   "tc_bn":    N-tile of the tensor-core fp16 kernel, 32/64/128/256
+ *   "pdl":      1 = launch the u8 streaming kernel with programmatic dependent launch: it
+ *               may then start, and prefetch its weight matrix, scales and zero points,
+ *               while the previous kernel of the stream is still running.  The caller
+ *               promises that those three buffers are not written by work enqueued just
+ *               before on the same stream.  Activations and output are only touched after
+ *               the previous kernel has completed.  Default 0. */
+int adr_set_tunable(adr_ctx* ctx, const char* name, int value);
+/* Synchronises the device and returns ADR_ERR_DEVICE if any kernel launched through this
+ * context gave up on a bounded wait (the flag is then cleared), ADR_OK otherwise. */
+int adr_device_status(adr_ctx* ctx);
 /* Kernel family chosen by the most recent successful matmul call. */
 int adr_last_kernel(const adr_ctx* ctx);
 /* Number of kernel launches issued through this context so far. */

@@ -138,7 +138,42 @@ def u8_kernels_for(c):
         ks.append(Kernel.U8Gemv)
     if c.p % 64 == 0:
         ks.append(Kernel.U8Mma)
+        if c.m <= 16 and c.p % 128 == 0:
+            ks.append(Kernel.U8Stream)
     return ks
+
+
+@pytest.mark.parametrize("split", [1, 2, 4, 8])
+@pytest.mark.parametrize("rows", [16, 32, 64])
+def test_u8_stream_every_plan(kernels, split, rows):
+    """Every cluster size (k-split) and rows-per-CTA choice of the streaming
+    kernel gives the same answer within tolerance, deterministically, for
+    ragged n, p not divisible by the split, both token blocks and zero points."""
+    rng = np.random.default_rng(split * 10 + rows)
+    try:
+        kernels.force_kernel(Kernel.U8Stream)
+        kernels.set_tunable("u8_split", split)
+        kernels.set_tunable("u8_rows", rows)
+        for m, p, n, bs, zp in ((1, 1024, 200, 128, False), (7, 1408, 333, 64, False),
+                                (16, 1024, 128, 128, True), (9, 1152, 97, 32, False)):
+            x = rng.standard_normal((m, p)).astype(np.float16)
+            q = rng.integers(0, 256, (n, p), dtype=np.uint8)
+            s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
+            z = rng.uniform(120, 136, (n, p // bs)).astype(np.float16) if zp else None
+            out0 = (rng.standard_normal((m, n)) * 0.5).astype(np.float16)
+            want = oracle.matmul_nt_fp16u8(x, q, s, bs, 0.5, out0, z)
+            res = []
+            for _ in range(2):
+                o = dev(out0.copy())
+                kernels.matmul_nt_fp16u8(o, dev(x), dev(q), dev(s), bs, 0.5, dev(z) if zp else None)
+                kernels.device_status()
+                res.append(o.cpu().numpy())
+            assert np.array_equal(res[0].view(np.uint16), res[1].view(np.uint16))
+            assert oracle.max_rel_err(res[0], want) <= TOL, (m, p, n)
+    finally:
+        kernels.set_tunable("u8_split", 0)
+        kernels.set_tunable("u8_rows", 0)
+        kernels.force_kernel(Kernel.Auto)
 
 
 @pytest.mark.parametrize("c", cases.u8_cases(), ids=lambda c: c.name)
@@ -302,7 +337,7 @@ def test_config2_full_size(kernels, m, n):
         for zeros_np, zeros_d in ((None, None), (z, zd)):
             want = oracle.matmul_nt_fp16u8(x, q[cols], s[cols], bs, zeros=None if zeros_np is None else zeros_np[cols])
             outs = {}
-            for kern in [Kernel.U8Mma] + ([Kernel.U8Gemv] if m <= 4 else []) + [Kernel.Auto]:
+            for kern in [Kernel.U8Mma, Kernel.U8Stream] + ([Kernel.U8Gemv] if m <= 4 else []) + [Kernel.Auto]:
                 kernels.force_kernel(kern)
                 o = torch.zeros(m, n, dtype=torch.float16, device="cuda")
                 kernels.matmul_nt_fp16u8(o, xd, qd, sd, bs, 0.0, zeros_d)
