@@ -54,6 +54,11 @@ int run_matmul(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, bool slow
   if (kernel == ADR_KERNEL_F16_TC) {
     if (!gemm_f16_tc_supports(ctx, a)) return ADR_ERR_SHAPE;
     rc = launch_gemm_f16_tc(ctx, stream, a);
+    if (rc == ADR_ERR_SHAPE && ctx->forced_kernel == ADR_KERNEL_AUTO) {
+      // the view passed the static checks but the tensor map could not be encoded
+      kernel = ADR_KERNEL_F16_SIMT;
+      rc = launch_gemm_f16_simt(ctx, stream, a);
+    }
   } else if (kernel == ADR_KERNEL_F16_SIMT) {
     rc = launch_gemm_f16_simt(ctx, stream, a);
   } else {
