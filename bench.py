@@ -193,6 +193,9 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     kern = GpuKernels(local)
+    # The weights of this workload are never written after set-up, so the decode kernel may
+    # prefetch them while the previous launch is still running (programmatic dependent launch).
+    kern.set_tunable("pdl", 0 if args.no_pdl else 1)
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
     weights = []
     for _ in range(LAYERS):
@@ -311,7 +314,7 @@ def run_ours(args):
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                      "frac": per_gpu / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
-                     "kernel": "u8_mma_kernel", "per_m_gbs": per_m,
+                     "kernel": "u8_stream_kernel", "per_m_gbs": per_m,
                      "bytes_per_launch_avg": bytes_step / max(launches / args.steps, 1)},
         "clocks": clocks,
     }
@@ -323,6 +326,39 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_profile_case(args):
+    """Small, self-terminating cases for `ncu` captures (a few hundred MB on the device).
+
+    u8 : the decode kernel over 12 distinct [4096,4096] u8 weights (201 MB, larger than L2),
+         two passes, m = --m.
+    f16: the tensor-core GEMM, [m,4096] x [4096,4096]^T over 6 distinct weights, m = --m.
+    """
+    import torch
+
+    from adrastea_b200 import GpuKernels, TensorView
+    torch.cuda.set_device(0)
+    kern = GpuKernels(0)
+    m = args.m
+    if args.profile_case == "u8":
+        ws = [(torch.randint(0, 256, (4096, K), dtype=torch.uint8, device="cuda"),
+               (torch.rand((4096, K // BS), device="cuda") * 0.009 + 0.001).half()) for _ in range(12)]
+        x = torch.randn((m, K), dtype=torch.float16, device="cuda")
+        o = torch.zeros((m, 4096), dtype=torch.float16, device="cuda")
+        for _ in range(2):
+            for q, s in ws:
+                kern.matmul_nt_fp16u8(o, x, q, s, BS)
+    else:
+        ws = [(torch.randn(4096, K, device="cuda") * 0.02).half() for _ in range(6)]
+        a = (torch.randn(m, K, device="cuda") * 0.02).half()
+        o = torch.zeros((m, 4096), dtype=torch.float16, device="cuda")
+        for _ in range(2):
+            for w in ws:
+                kern.matmul_f16(TensorView.of(o), TensorView.of(a), TensorView.of(w).permute([1, 0]))
+    torch.cuda.synchronize()
+    kern.device_status()
+    print(json.dumps({"profile_case": args.profile_case, "m": m, "kernel": kern.last_kernel().name}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -330,8 +366,14 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches")
+    ap.add_argument("--profile-case", default=None, choices=["u8", "f16"],
+                    help="run a small fixed case of one kernel family and exit (for ncu captures)")
+    ap.add_argument("--m", type=int, default=1, help="rows of the activation in --profile-case")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.profile_case:
+        run_profile_case(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
