@@ -153,6 +153,7 @@ int adr_set_tunable(adr_ctx* ctx, const char* name, int value) {
   if (!strcmp(name, "u8_split")) ctx->tune_u8_split = value;
   else if (!strcmp(name, "u8_rows")) ctx->tune_u8_rows = value;
   else if (!strcmp(name, "tc_bn")) ctx->tune_tc_bn = value;
+  else if (!strcmp(name, "tc_split")) ctx->tune_tc_split = value;
   else if (!strcmp(name, "pdl")) ctx->tune_pdl = value;
   else return ADR_ERR_INVALID;
   return ADR_OK;

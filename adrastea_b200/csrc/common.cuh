@@ -61,6 +61,7 @@ struct adr_ctx {
   int tune_u8_split = 0;
   int tune_u8_rows = 0;
   int tune_tc_bn = 0;
+  int tune_tc_split = 0;
   int tune_pdl = 0;  // programmatic dependent launch of the u8 streaming kernel
 };
 

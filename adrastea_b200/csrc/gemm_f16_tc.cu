@@ -4,7 +4,7 @@
 // 493-513) and the WMMA kernels (matmul_nt_wmma_128x64x64.cu:8-78,
 // matmul_nt_wmma_16x128x256.cu:8-68) for views TMA can describe.
 //
-// One CTA computes one 128 x BN output tile.  Six warps, specialised:
+// Tiles of 128 x BN outputs.  Six warps per CTA, specialised:
 //   warp 0    producer: one thread issues TMA loads of the A (128 x 64) and B (BN x 64)
 //             k-blocks into a ring of 128-byte-swizzled shared-memory stages
 //   warp 1    owns tensor memory (alloc/dealloc); one thread issues tcgen05.mma
@@ -13,11 +13,21 @@
 //   warps 2-5 epilogue: tcgen05.ld the accumulator (warp w reads TMEM lanes
 //             32*(w%4)..+31 = tile rows), apply the reference's fused store op, mask
 //             and scale, write fp16 to the (arbitrarily strided) output
+// Two kernels share these roles:
+//   gemm_f16_tc_kernel         persistent: one CTA per SM walks a list of tiles; two
+//                              accumulator buffers in TMEM let the epilogue of one tile
+//                              overlap the MMAs of the next
+//   gemm_f16_tc_splitk_kernel  for grids that would leave most SMs idle (skinny m, prefill
+//                              of a few hundred rows): a cluster of S CTAs splits k for one
+//                              tile, the fp32 partial tiles are exchanged through distributed
+//                              shared memory and added in rank order (deterministic, no
+//                              scratch memory in HBM)
 // Rows and k beyond the operands' extents are zero-filled by TMA, so m, n and k need no
 // divisibility; only the 16-byte alignment rules of TMA apply (gemm_f16_tc_supports).
 // Every mbarrier wait is bounded: a wait that runs out sets the context's status word,
 // the kernel still frees its tensor memory and returns.
 #include <algorithm>
+#include <cmath>
 
 #include "tcgen05.cuh"
 
@@ -39,7 +49,13 @@ struct TcCfg {
                                     ? 8
                                     : (int)((SMEM_BUDGET - 2048) / STAGE_BYTES);
   static constexpr size_t SMEM = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE_BYTES + 1024;
-  static constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+  static constexpr uint32_t TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;  // two accumulator buffers
+  // split-k: the fp32 partial tile, row-major with rows padded by 4 floats (row pitch = 16
+  // bytes mod 128) so that the 16-byte row-wise writes of 8 lanes hit distinct bank groups
+  // and the remote reads of a warp are 512 contiguous bytes
+  static constexpr int PART_LD = BN + 4;
+  static constexpr size_t PART_BYTES = (size_t)BM * PART_LD * 4;
+  static_assert(PART_BYTES <= (size_t)STAGES * STAGE_BYTES, "partial tile must fit in the ring");
 };
 
 struct TcParams {
@@ -94,6 +110,52 @@ __device__ __forceinline__ void store_chunk(const TcParams& p, const uint32_t (&
   }
 }
 
+__device__ __forceinline__ void store_chunk_rt(const TcParams& p, const uint32_t (&acc)[32],
+                                               __half* orow, int y, int x0, float pre,
+                                               __half hscale) {
+  switch (p.store) {
+    case ADR_STORE_SCALE: store_chunk<ADR_STORE_SCALE>(p, acc, orow, y, x0, pre, hscale); break;
+    case ADR_STORE_ADD: store_chunk<ADR_STORE_ADD>(p, acc, orow, y, x0, pre, hscale); break;
+    case ADR_STORE_BETA_BIAS: store_chunk<ADR_STORE_BETA_BIAS>(p, acc, orow, y, x0, pre, hscale); break;
+    case ADR_STORE_BETA_GELU_BIAS: store_chunk<ADR_STORE_BETA_GELU_BIAS>(p, acc, orow, y, x0, pre, hscale); break;
+    case ADR_STORE_QUICK_GELU_BIAS: store_chunk<ADR_STORE_QUICK_GELU_BIAS>(p, acc, orow, y, x0, pre, hscale); break;
+    case STORE_NT_BETA: store_chunk<STORE_NT_BETA>(p, acc, orow, y, x0, pre, hscale); break;
+    default: store_chunk<ADR_STORE_IDENTITY>(p, acc, orow, y, x0, pre, hscale); break;
+  }
+}
+
+// Issues the four K=16 MMAs of one 64-wide k-block held in stage memory at `sa`.
+template <int BN>
+__device__ __forceinline__ void mma_k_block(uint32_t tmem_d, uint32_t sa, bool first) {
+  constexpr uint32_t idesc = umma_idesc_f16(BN, false);
+  const uint64_t adesc = umma_desc_k_sw128(sa);
+  const uint64_t bdesc = umma_desc_k_sw128(sa + TcCfg<BN>::A_BYTES);
+#pragma unroll
+  for (int kk = 0; kk < BK / 16; ++kk) {
+    // 16 fp16 = 32 bytes further along the swizzled row: +2 in the address field
+    umma_f16(tmem_d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+             (!first || kk > 0) ? 1u : 0u);
+  }
+}
+
+// Persistent tile scheduler: CTA c works on tiles c, c + gridDim.x, ...  Tiles are numbered
+// batch-major, then in groups of GROUP_M row tiles swept along n, so that the tiles in
+// flight at one time share A and B panels in L2.
+struct TileCoord {
+  int m0, n0, b;
+};
+constexpr int GROUP_M = 8;
+__device__ __forceinline__ TileCoord tile_coord(int t, int mt, int nt, int bn) {
+  const int per_batch = mt * nt;
+  const int b = t / per_batch;
+  const int r = t - b * per_batch;
+  const int group = r / (GROUP_M * nt);
+  const int first_m = group * GROUP_M;
+  const int gsz = min(GROUP_M, mt - first_m);
+  const int local = r - group * GROUP_M * nt;
+  return {(first_m + local % gsz) * BM, (local / gsz) * bn, b};
+}
+
 template <int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap map_a,
@@ -105,12 +167,14 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   uint8_t* stages = smem;
   uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
   uint64_t* empty_bar = full_bar + Cfg::STAGES;
-  uint64_t* acc_bar = empty_bar + Cfg::STAGES;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_bar + 1);
+  uint64_t* acc_full = empty_bar + Cfg::STAGES;  // [2]: accumulator buffer complete
+  uint64_t* acc_empty = acc_full + 2;            // [2]: accumulator buffer drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * BN, m0 = blockIdx.y * BM, b = blockIdx.z;
   const int num_kb = (p.k + BK - 1) / BK;
+  const int mt = (p.m + BM - 1) / BM, nt = (p.n + BN - 1) / BN;
+  const int total_tiles = mt * nt * p.batches;
 
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&map_a);
@@ -119,7 +183,10 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(acc_bar, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
+    }
     mbar_fence_init();
   }
   if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
@@ -130,71 +197,75 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   bool ok = true;
 
   if (warp == 0) {
-    // ---------------- producer ----------------
+    // ---------------- producer: TMA loads, one ring across all of this CTA's tiles ----------
     if (lane == 0) {
-      const int az = p.a_bcast ? 0 : b, bz = p.b_bcast ? 0 : b;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % Cfg::STAGES;
-        const unsigned phase = (unsigned)(kb / Cfg::STAGES) & 1u;
-        if (!mbar_wait(&empty_bar[s], phase ^ 1u)) { ok = false; break; }
-        uint8_t* sa = stages + (size_t)s * Cfg::STAGE_BYTES;
-        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
-        tma_load_3d(sa, &map_a, kb * BK, m0, az, &full_bar[s]);
-        tma_load_3d(sa + Cfg::A_BYTES, &map_b, kb * BK, n0, bz, &full_bar[s]);
+      int it = 0;  // k-blocks issued so far
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const TileCoord tc = tile_coord(t, mt, nt, BN);
+        const int az = p.a_bcast ? 0 : tc.b, bz = p.b_bcast ? 0 : tc.b;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          const unsigned phase = (unsigned)(it / Cfg::STAGES) & 1u;
+          if (!mbar_wait(&empty_bar[s], phase ^ 1u)) { ok = false; break; }
+          uint8_t* sa = stages + (size_t)s * Cfg::STAGE_BYTES;
+          mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+          tma_load_3d(sa, &map_a, kb * BK, tc.m0, az, &full_bar[s]);
+          tma_load_3d(sa + Cfg::A_BYTES, &map_b, kb * BK, tc.n0, bz, &full_bar[s]);
+        }
       }
     }
   } else if (warp == 1) {
-    // ---------------- MMA issue ----------------
+    // ---------------- MMA issue: alternate between two accumulator buffers in TMEM ----------
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc_f16(BN, false);
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % Cfg::STAGES;
-        const unsigned phase = (unsigned)(kb / Cfg::STAGES) & 1u;
-        if (!mbar_wait(&full_bar[s], phase)) { ok = false; break; }
+      int it = 0, local = 0;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+        const int buf = local & 1;
+        const unsigned use = (unsigned)(local >> 1) & 1u;
+        if (!mbar_wait(&acc_empty[buf], use ^ 1u)) { ok = false; break; }
         tc_fence_after_sync();
-        const uint32_t sa = smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES);
-        const uint64_t adesc = umma_desc_k_sw128(sa);
-        const uint64_t bdesc = umma_desc_k_sw128(sa + Cfg::A_BYTES);
-#pragma unroll
-        for (int kk = 0; kk < BK / 16; ++kk) {
-          // 16 fp16 = 32 bytes further along the swizzled row: +2 in the address field
-          umma_f16(tmem_base, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
-                   (kb > 0 || kk > 0) ? 1u : 0u);
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          const unsigned phase = (unsigned)(it / Cfg::STAGES) & 1u;
+          if (!mbar_wait(&full_bar[s], phase)) { ok = false; break; }
+          tc_fence_after_sync();
+          mma_k_block<BN>(tmem_d, smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES), kb == 0);
+          umma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
         }
-        umma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
+        umma_commit(&acc_full[buf]);  // the accumulator is complete once every MMA is done
       }
-      umma_commit(acc_bar);  // the accumulator is complete once every MMA is done
     }
   } else {
-    // ---------------- epilogue ----------------
+    // ---------------- epilogue: drains one buffer while the other is being filled ----------
     const int quarter = warp & 3;  // TMEM lanes a warp may read: 32 * (warp id % 4) ..
     const int row = quarter * 32 + lane;
-    const int y = m0 + row;
-    ok = mbar_wait(acc_bar, 0);
-    tc_fence_after_sync();
     const __half hscale = __float2half_rn(p.scale);
     // a load-side scale multiplies both operands (matmul.cu:62): s^2 on the product
     const float hs = __half2float(hscale);
     const float pre = p.load == ADR_LOAD_SCALE ? hs * hs : 1.0f;
-    __half* orow = p.out + (int64_t)b * p.s_oz + (int64_t)y * p.s_oy;
+    int local = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+      const TileCoord tc = tile_coord(t, mt, nt, BN);
+      const int buf = local & 1;
+      const unsigned use = (unsigned)(local >> 1) & 1u;
+      if (!mbar_wait(&acc_full[buf], use)) { ok = false; break; }
+      tc_fence_after_sync();
+      const int y = tc.m0 + row;
+      __half* orow = p.out + (int64_t)tc.b * p.s_oz + (int64_t)y * p.s_oy;
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
-      const int x0 = n0 + c * 32;
-      if (x0 >= p.n) break;  // uniform across the warp
-      uint32_t acc[32];
-      tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), acc);
-      tmem_ld_wait();
-      if (y < p.m && ok) {
-        switch (p.store) {
-          case ADR_STORE_SCALE: store_chunk<ADR_STORE_SCALE>(p, acc, orow, y, x0, pre, hscale); break;
-          case ADR_STORE_ADD: store_chunk<ADR_STORE_ADD>(p, acc, orow, y, x0, pre, hscale); break;
-          case ADR_STORE_BETA_BIAS: store_chunk<ADR_STORE_BETA_BIAS>(p, acc, orow, y, x0, pre, hscale); break;
-          case ADR_STORE_BETA_GELU_BIAS: store_chunk<ADR_STORE_BETA_GELU_BIAS>(p, acc, orow, y, x0, pre, hscale); break;
-          case ADR_STORE_QUICK_GELU_BIAS: store_chunk<ADR_STORE_QUICK_GELU_BIAS>(p, acc, orow, y, x0, pre, hscale); break;
-          case STORE_NT_BETA: store_chunk<STORE_NT_BETA>(p, acc, orow, y, x0, pre, hscale); break;
-          default: store_chunk<ADR_STORE_IDENTITY>(p, acc, orow, y, x0, pre, hscale); break;
-        }
+      for (int c = 0; c < BN / 32; ++c) {
+        const int x0 = tc.n0 + c * 32;
+        if (x0 >= p.n) break;  // uniform across the warp
+        uint32_t acc[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c * 32),
+                      acc);
+        tmem_ld_wait();
+        if (y < p.m) store_chunk_rt(p, acc, orow, y, x0, pre, hscale);
       }
+      // this warp's reads of the buffer are complete: hand it back to the MMA warp
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   if (!ok) atomicOr(p.status, 2u);
@@ -206,31 +277,177 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   }
 }
 
+// Split-k: grid (S, n tiles, m tiles * batches), cluster (S, 1, 1).  CTA `rank` of a cluster
+// accumulates k-blocks [rank*num_kb/S, (rank+1)*num_kb/S) of its tile.
 template <int BN>
-int launch_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a) {
+__global__ void __launch_bounds__(TC_THREADS, 1)
+    gemm_f16_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a,
+                              const __grid_constant__ CUtensorMap map_b, TcParams p, int S) {
   using Cfg = TcCfg<BN>;
-  auto kfn = gemm_f16_tc_kernel<BN>;
-  static bool configured[64] = {};
-  const int dev = ctx->device & 63;
-  if (!configured[dev]) {
-    cudaError_t e =
-        cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
-    if (e != cudaSuccess) {
-      ctx->last_cuda_error = (int)e;
-      return ADR_ERR_CUDA;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* stages = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + Cfg::STAGES;
+  uint64_t* acc_full = empty_bar + Cfg::STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int rank = blockIdx.x;
+  const int mt = (p.m + BM - 1) / BM;
+  const int n0 = blockIdx.y * BN, m0 = (blockIdx.z % mt) * BM, b = blockIdx.z / mt;
+  const int num_kb = (p.k + BK - 1) / BK;
+  const int kb0 = (int)((long long)rank * num_kb / S);
+  const int kb1 = (int)((long long)(rank + 1) * num_kb / S);
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
     }
-    configured[dev] = true;
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
   }
+  if (warp == 1) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      const int az = p.a_bcast ? 0 : b, bz = p.b_bcast ? 0 : b;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const int it = kb - kb0;
+        const int s = it % Cfg::STAGES;
+        const unsigned phase = (unsigned)(it / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&empty_bar[s], phase ^ 1u)) { ok = false; break; }
+        uint8_t* sa = stages + (size_t)s * Cfg::STAGE_BYTES;
+        mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+        tma_load_3d(sa, &map_a, kb * BK, m0, az, &full_bar[s]);
+        tma_load_3d(sa + Cfg::A_BYTES, &map_b, kb * BK, n0, bz, &full_bar[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const int it = kb - kb0;
+        const int s = it % Cfg::STAGES;
+        const unsigned phase = (unsigned)(it / Cfg::STAGES) & 1u;
+        if (!mbar_wait(&full_bar[s], phase)) { ok = false; break; }
+        tc_fence_after_sync();
+        mma_k_block<BN>(tmem_base, smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES), kb == kb0);
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(acc_full);
+    }
+  }
+  // ---- every warp: wait until the accumulator is complete (so the ring is idle too) ----
+  ok = mbar_wait(acc_full, 0) && ok;
+  tc_fence_after_sync();
+  __syncthreads();  // producer and MMA threads are past their loops: the ring can be reused
+  float* part = reinterpret_cast<float*>(stages);  // [BM][PART_LD], row-major, padded
+  if (warp >= 2) {
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t acc[32];
+      tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), acc);
+      tmem_ld_wait();
+      float4* dst = reinterpret_cast<float4*>(part + (size_t)row * Cfg::PART_LD + c * 32);
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        dst[q] = make_float4(__uint_as_float(acc[4 * q]), __uint_as_float(acc[4 * q + 1]),
+                             __uint_as_float(acc[4 * q + 2]), __uint_as_float(acc[4 * q + 3]));
+    }
+  }
+  if (!ok) atomicOr(p.status, 4u);
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+
+  // ---- rank r finishes rows [r*128/S, (r+1)*128/S): sum the S partial tiles in rank order.
+  // A thread takes four consecutive columns; a warp reads 512 contiguous bytes per peer.
+  {
+    const int rpr = BM / S;
+    const uint32_t pbase = smem_u32(part);
+    const __half hscale = __float2half_rn(p.scale);
+    const float hs = __half2float(hscale);
+    const float pre = p.load == ADR_LOAD_SCALE ? hs * hs : 1.0f;
+    const bool causal = p.mask == ADR_MASK_CAUSAL;
+    const int store = (int)p.store;
+    const bool rd_out = store_reads_out(store), use_bias = store_uses_bias(store);
+    __half* obase = p.out + (int64_t)b * p.s_oz;
+    for (int e = threadIdx.x; e < rpr * (BN / 4); e += TC_THREADS) {
+      const int col = (e % (BN / 4)) * 4, row = rank * rpr + e / (BN / 4);
+      const int x0 = n0 + col, y = m0 + row;
+      if (x0 >= p.n || y >= p.m) continue;
+      // all S remote reads are issued before the first is used, then added in rank order
+      float4 pv[8];
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        pv[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < S) {
+          uint32_t remote;
+          asm("mapa.shared::cluster.u32 %0, %1, %2;"
+              : "=r"(remote)
+              : "r"(pbase + (uint32_t)(row * Cfg::PART_LD + col) * 4u), "r"(r));
+          asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+                       : "=f"(pv[r].x), "=f"(pv[r].y), "=f"(pv[r].z), "=f"(pv[r].w)
+                       : "r"(remote));
+        }
+      }
+      float v[4] = {pv[0].x, pv[0].y, pv[0].z, pv[0].w};
+#pragma unroll
+      for (int r = 1; r < 8; ++r)
+        if (r < S) {
+          v[0] += pv[r].x;
+          v[1] += pv[r].y;
+          v[2] += pv[r].z;
+          v[3] += pv[r].w;
+        }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int x = x0 + j;
+        if (x >= p.n) break;
+        __half* dst = obase + (int64_t)y * p.s_oy + (int64_t)x * p.s_ox;
+        __half res;
+        if (causal && x > y) {
+          res = __ushort_as_half((unsigned short)0xFC00);
+        } else {
+          const __half old = rd_out ? *dst : __float2half_rn(0.0f);
+          const float bias = use_bias ? __half2float(p.bias[x]) : 0.0f;
+          res = store_apply_rt(store, v[j] * pre, old, bias, p.beta, hscale);
+        }
+        *dst = res;
+      }
+    }
+  }
+  // every CTA stays resident until its peers have read its partial tile
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <int BN>
+int make_maps(adr_ctx* ctx, const MatmulArgs& a, CUtensorMap* map_a, CUtensorMap* map_b,
+              TcParams* p) {
   const bool a_bcast = a.batches > 1 && a.s_lz == 0;
   const bool b_bcast = a.batches > 1 && a.s_rz == 0;
-  CUtensorMap map_a, map_b;
   {
     const uint64_t za = a_bcast || a.batches == 1 ? 1 : (uint64_t)a.batches;
     const uint64_t dims[3] = {(uint64_t)a.k, (uint64_t)a.m, za};
     const uint64_t zs = za == 1 ? (uint64_t)a.s_ly * 2 * (uint64_t)a.m : (uint64_t)a.s_lz * 2;
     const uint64_t strides[2] = {(uint64_t)a.s_ly * 2, zs};
     const uint32_t box[3] = {BK, BM, 1};
-    int rc = tma_get(ctx, &map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, a.lhs, dims, strides, box,
+    int rc = tma_get(ctx, map_a, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, a.lhs, dims, strides, box,
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != ADR_OK) return rc;
   }
@@ -240,30 +457,113 @@ int launch_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a) {
     const uint64_t zs = zb == 1 ? (uint64_t)a.s_rx * 2 * (uint64_t)a.n : (uint64_t)a.s_rz * 2;
     const uint64_t strides[2] = {(uint64_t)a.s_rx * 2, zs};
     const uint32_t box[3] = {BK, (uint32_t)BN, 1};
-    int rc = tma_get(ctx, &map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, a.rhs, dims, strides, box,
+    int rc = tma_get(ctx, map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, a.rhs, dims, strides, box,
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != ADR_OK) return rc;
   }
-  TcParams p{a.out, a.bias, a.batches, a.m, a.k, a.n, a.s_ox, a.s_oy, a.s_oz,
-             a_bcast ? 1 : 0, b_bcast ? 1 : 0, a.beta, a.scale, a.store, a.load, a.mask,
-             ctx->d_status};
-  dim3 grid((a.n + BN - 1) / BN, (a.m + BM - 1) / BM, a.batches);
-  kfn<<<grid, TC_THREADS, Cfg::SMEM, stream>>>(map_a, map_b, p);
+  *p = TcParams{a.out, a.bias, a.batches, a.m, a.k, a.n, a.s_ox, a.s_oy, a.s_oz,
+                a_bcast ? 1 : 0, b_bcast ? 1 : 0, a.beta, a.scale, a.store, a.load, a.mask,
+                ctx->d_status};
+  return ADR_OK;
+}
+
+template <typename K>
+int opt_in_smem(adr_ctx* ctx, K kfn, size_t bytes, bool* configured) {
+  const int dev = ctx->device & 63;
+  if (!configured[dev]) {
+    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) {
+      ctx->last_cuda_error = (int)e;
+      return ADR_ERR_CUDA;
+    }
+    configured[dev] = true;
+  }
+  return ADR_OK;
+}
+
+template <int BN>
+int launch_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, int S) {
+  using Cfg = TcCfg<BN>;
+  CUtensorMap map_a, map_b;
+  TcParams p;
+  int rc = make_maps<BN>(ctx, a, &map_a, &map_b, &p);
+  if (rc != ADR_OK) return rc;
+  const int nt = (a.n + BN - 1) / BN, mt = (a.m + BM - 1) / BM;
+  if (S <= 1) {
+    static bool configured[64] = {};
+    auto kfn = gemm_f16_tc_kernel<BN>;
+    rc = opt_in_smem(ctx, kfn, Cfg::SMEM, configured);
+    if (rc != ADR_OK) return rc;
+    const long long tiles = (long long)nt * mt * a.batches;
+    const long long sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+    const unsigned grid = (unsigned)std::min<long long>(tiles, sms);
+    kfn<<<grid, TC_THREADS, Cfg::SMEM, stream>>>(map_a, map_b, p);
+    return after_launch(ctx);
+  }
+  static bool configured_sk[64] = {};
+  auto kfn = gemm_f16_tc_splitk_kernel<BN>;
+  rc = opt_in_smem(ctx, kfn, Cfg::SMEM, configured_sk);
+  if (rc != ADR_OK) return rc;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(S, nt, mt * a.batches);
+  cfg.blockDim = dim3(TC_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::SMEM;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, map_a, map_b, p, S);
+  if (e != cudaSuccess) {
+    ctx->last_cuda_error = (int)e;
+    return ADR_ERR_CUDA;
+  }
   return after_launch(ctx);
 }
 
-int pick_bn(const adr_ctx* ctx, const MatmulArgs& a) {
-  if (ctx->tune_tc_bn == 32 || ctx->tune_tc_bn == 64 || ctx->tune_tc_bn == 128 ||
-      ctx->tune_tc_bn == 256)
-    return ctx->tune_tc_bn;
-  const long long sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
-  const long long mt = (a.m + BM - 1) / BM;
+struct TcPlan {
+  int bn, S;
+};
+
+// Picks the N-tile and the k-split.  Measured tensor-pipe efficiency by tile width (one CTA
+// per tile, operands from shared memory): 256 -> 1.0, 128 -> 0.76 (shared-memory bandwidth
+// bound), 64 -> 0.43, 32 -> 0.22.  The score is that efficiency times the SM utilisation of
+// the schedule; a k-split costs a reduction through distributed shared memory.
+TcPlan pick_plan(const adr_ctx* ctx, const MatmulArgs& a) {
+  const double sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+  const double mt = (a.m + BM - 1) / BM;
+  const int num_kb = (a.k + BK - 1) / BK;
+  TcPlan best{32, 1};
+  double best_score = -1.0;
   for (int bn : {256, 128, 64, 32}) {
-    if (bn > 32 && a.n <= bn / 2) continue;  // do not pad n beyond the next tile size
-    const long long ctas = mt * ((a.n + bn - 1) / bn) * a.batches;
-    if (ctas >= sms || bn == 32) return bn;
+    if (ctx->tune_tc_bn && bn != ctx->tune_tc_bn) continue;
+    if (!ctx->tune_tc_bn && bn > 32 && a.n <= bn / 2) continue;  // do not pad n beyond the next tile size
+    const double tiles = mt * ((a.n + bn - 1) / bn) * a.batches;
+    const double eff = bn == 256 ? 1.0 : bn == 128 ? 0.76 : bn == 64 ? 0.43 : 0.22;
+    for (int S : {1, 2, 4, 8}) {
+      if (ctx->tune_tc_split && S != ctx->tune_tc_split) continue;
+      if (S > 1 && (num_kb < 2 * S || mt * a.batches > 65535)) continue;
+      const double ctas = tiles * S;
+      double util;
+      if (S == 1) {
+        const double waves = tiles / sms;
+        util = waves / std::ceil(waves);
+      } else {
+        if (ctas > sms && !ctx->tune_tc_split) continue;  // a split only pays on an under-filled grid
+        util = std::min(1.0, ctas / sms);
+      }
+      // measured: the exchange of partial tiles costs about 40 % at these sizes
+      const double score = util * eff * (S > 1 ? 0.6 : 1.0);
+      if (score > best_score) {
+        best_score = score;
+        best = {bn, S};
+      }
+    }
   }
-  return 32;
+  return best;
 }
 
 }  // namespace
@@ -280,11 +580,12 @@ bool gemm_f16_tc_supports(const adr_ctx* ctx, const MatmulArgs& a) {
 }
 
 int launch_gemm_f16_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a) {
-  switch (pick_bn(ctx, a)) {
-    case 256: return launch_tc<256>(ctx, stream, a);
-    case 128: return launch_tc<128>(ctx, stream, a);
-    case 64: return launch_tc<64>(ctx, stream, a);
-    default: return launch_tc<32>(ctx, stream, a);
+  const TcPlan pl = pick_plan(ctx, a);
+  switch (pl.bn) {
+    case 256: return launch_tc<256>(ctx, stream, a, pl.S);
+    case 128: return launch_tc<128>(ctx, stream, a, pl.S);
+    case 64: return launch_tc<64>(ctx, stream, a, pl.S);
+    default: return launch_tc<32>(ctx, stream, a, pl.S);
   }
 }
 

@@ -87,6 +87,7 @@ int adr_force_kernel(adr_ctx* ctx, int kernel);
  *   "u8_split": cluster size (k-split) of the streaming u8 kernel, 1/2/4/8
  *   "u8_rows":  weight rows per CTA of the streaming u8 kernel, 32/64
  *   "tc_bn":    N-tile of the tensor-core fp16 kernel, 32/64/128/256
+ *   "tc_split": cluster size (k-split) of the tensor-core fp16 kernel, 1/2/4/8
  *   "pdl":      1 = launch the u8 streaming kernel with programmatic dependent launch: it
  *               may then start, and prefetch its weight matrix, scales and zero points,
  *               while the previous kernel of the stream is still running.  The caller

@@ -349,3 +349,37 @@ def test_config2_full_size(kernels, m, n):
                 assert oracle.max_rel_err(o, base) <= TOL, kern
     finally:
         kernels.force_kernel(Kernel.Auto)
+
+
+@pytest.mark.parametrize("split", [2, 4, 8])
+@pytest.mark.parametrize("bn", [32, 64, 128, 256])
+def test_tc_gemm_every_tile_and_split(kernels, bn, split):
+    """Every N-tile and cluster k-split of the tensor-core kernel against the ideal
+    oracle, with ragged m/n/k, a fused op that reads the output, and a batch."""
+    rng = np.random.default_rng(bn + split)
+    try:
+        kernels.force_kernel(Kernel.F16Tc)
+        kernels.set_tunable("tc_bn", bn)
+        kernels.set_tunable("tc_split", split)
+        for (b, m, k, n, store, beta) in ((1, 70, 1096, 300, cases.ST_ADD, 0.0), (3, 130, 1024, 72, cases.ST_BETA_BIAS, 0.5)):
+            lhs = (rng.standard_normal(b * m * k) * 0.1).astype(np.float16)
+            rhs = (rng.standard_normal(b * n * k) * 0.1).astype(np.float16)
+            out0 = (rng.standard_normal(b * m * n) * 0.5).astype(np.float16)
+            bias = (rng.standard_normal(n) * 0.5).astype(np.float16)
+            strides = (1, n, m * n, 1, k, m * k, k, 1, n * k)
+            want = out0.copy()
+            assert oracle.matmul_f16(want, lhs, rhs, b, m, k, n, strides, bias, beta, 1.0, store, 0, 0, ideal=True) == 0
+            o, l, r, bd = dev(out0.copy()), dev(lhs), dev(rhs), dev(bias)
+            shp = (lambda *d: d if b > 1 else d[1:])
+            ov = TensorView(o, TensorLayout.row_major(shp(b, m, n)))
+            lv = TensorView(l, TensorLayout.row_major(shp(b, m, k)))
+            rv = TensorView(r, TensorLayout.row_major(shp(b, n, k))).permute([0, 2, 1] if b > 1 else [1, 0])
+            st = MatmulStore.Add() if store == cases.ST_ADD else MatmulStore.BetaBias(beta, TensorView.of(bd))
+            kernels.matmul_f16(ov, lv, rv, MatmulOptions.new().store(st))
+            kernels.device_status()
+            assert kernels.last_kernel() == Kernel.F16Tc
+            assert oracle.max_rel_err(o.cpu().numpy(), want) <= TOL, (b, m, k, n)
+    finally:
+        kernels.set_tunable("tc_bn", 0)
+        kernels.set_tunable("tc_split", 0)
+        kernels.force_kernel(Kernel.Auto)
