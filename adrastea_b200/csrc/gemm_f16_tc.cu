@@ -125,16 +125,32 @@ __device__ __forceinline__ void store_chunk_rt(const TcParams& p, const uint32_t
 }
 
 // Issues the four K=16 MMAs of one 64-wide k-block held in stage memory at `sa`.
-template <int BN>
+// B_MN: the B stage holds an N-contiguous operand as BN/64 chunks of [64 k][64 n] (8 KB each).
+template <int BN, bool B_MN>
 __device__ __forceinline__ void mma_k_block(uint32_t tmem_d, uint32_t sa, bool first) {
-  constexpr uint32_t idesc = umma_idesc_f16(BN, false);
+  constexpr uint32_t idesc = umma_idesc_f16(BN, B_MN);
   const uint64_t adesc = umma_desc_k_sw128(sa);
-  const uint64_t bdesc = umma_desc_k_sw128(sa + TcCfg<BN>::A_BYTES);
+  const uint64_t bdesc = B_MN ? umma_desc_mn_sw128(sa + TcCfg<BN>::A_BYTES, 8192)
+                              : umma_desc_k_sw128(sa + TcCfg<BN>::A_BYTES);
+  // per K=16 step: a k-major tile moves 32 bytes along its swizzled rows (+2 in the address
+  // field), an n-major tile moves 16 k-rows of 128 bytes (+128)
+  constexpr uint64_t b_step = B_MN ? 128 : 2;
 #pragma unroll
   for (int kk = 0; kk < BK / 16; ++kk) {
-    // 16 fp16 = 32 bytes further along the swizzled row: +2 in the address field
-    umma_f16(tmem_d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), idesc,
+    umma_f16(tmem_d, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)kk * b_step, idesc,
              (!first || kk > 0) ? 1u : 0u);
+  }
+}
+
+// One k-block of B into stage memory at `sb`.
+template <int BN, bool B_MN>
+__device__ __forceinline__ void load_b_block(uint8_t* sb, const CUtensorMap* map_b, int kb, int n0,
+                                             int bz, uint64_t* bar) {
+  if (B_MN) {
+#pragma unroll
+    for (int c = 0; c < BN / 64; ++c) tma_load_3d(sb + c * 8192, map_b, n0 + c * 64, kb * BK, bz, bar);
+  } else {
+    tma_load_3d(sb, map_b, kb * BK, n0, bz, bar);
   }
 }
 
@@ -156,7 +172,7 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int mt, int nt, int bn) {
   return {(first_m + local % gsz) * BM, (local / gsz) * bn, b};
 }
 
-template <int BN>
+template <int BN, bool B_MN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_b, TcParams p) {
@@ -210,7 +226,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           uint8_t* sa = stages + (size_t)s * Cfg::STAGE_BYTES;
           mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
           tma_load_3d(sa, &map_a, kb * BK, tc.m0, az, &full_bar[s]);
-          tma_load_3d(sa + Cfg::A_BYTES, &map_b, kb * BK, tc.n0, bz, &full_bar[s]);
+          load_b_block<BN, B_MN>(sa + Cfg::A_BYTES, &map_b, kb, tc.n0, bz, &full_bar[s]);
         }
       }
     }
@@ -229,7 +245,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
           const unsigned phase = (unsigned)(it / Cfg::STAGES) & 1u;
           if (!mbar_wait(&full_bar[s], phase)) { ok = false; break; }
           tc_fence_after_sync();
-          mma_k_block<BN>(tmem_d, smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES), kb == 0);
+          mma_k_block<BN, B_MN>(tmem_d, smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES), kb == 0);
           umma_commit(&empty_bar[s]);  // the stage is free once these MMAs have read it
         }
         umma_commit(&acc_full[buf]);  // the accumulator is complete once every MMA is done
@@ -279,7 +295,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 
 // Split-k: grid (S, n tiles, m tiles * batches), cluster (S, 1, 1).  CTA `rank` of a cluster
 // accumulates k-blocks [rank*num_kb/S, (rank+1)*num_kb/S) of its tile.
-template <int BN>
+template <int BN, bool B_MN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
     gemm_f16_tc_splitk_kernel(const __grid_constant__ CUtensorMap map_a,
                               const __grid_constant__ CUtensorMap map_b, TcParams p, int S) {
@@ -329,7 +345,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         uint8_t* sa = stages + (size_t)s * Cfg::STAGE_BYTES;
         mbar_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
         tma_load_3d(sa, &map_a, kb * BK, m0, az, &full_bar[s]);
-        tma_load_3d(sa + Cfg::A_BYTES, &map_b, kb * BK, n0, bz, &full_bar[s]);
+        load_b_block<BN, B_MN>(sa + Cfg::A_BYTES, &map_b, kb, n0, bz, &full_bar[s]);
       }
     }
   } else if (warp == 1) {
@@ -340,7 +356,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
         const unsigned phase = (unsigned)(it / Cfg::STAGES) & 1u;
         if (!mbar_wait(&full_bar[s], phase)) { ok = false; break; }
         tc_fence_after_sync();
-        mma_k_block<BN>(tmem_base, smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES), kb == kb0);
+        mma_k_block<BN, B_MN>(tmem_base, smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES), kb == kb0);
         umma_commit(&empty_bar[s]);
       }
       umma_commit(acc_full);
@@ -436,7 +452,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   }
 }
 
-template <int BN>
+template <int BN, bool B_MN>
 int make_maps(adr_ctx* ctx, const MatmulArgs& a, CUtensorMap* map_a, CUtensorMap* map_b,
               TcParams* p) {
   const bool a_bcast = a.batches > 1 && a.s_lz == 0;
@@ -453,10 +469,14 @@ int make_maps(adr_ctx* ctx, const MatmulArgs& a, CUtensorMap* map_a, CUtensorMap
   }
   {
     const uint64_t zb = b_bcast || a.batches == 1 ? 1 : (uint64_t)a.batches;
-    const uint64_t dims[3] = {(uint64_t)a.k, (uint64_t)a.n, zb};
-    const uint64_t zs = zb == 1 ? (uint64_t)a.s_rx * 2 * (uint64_t)a.n : (uint64_t)a.s_rz * 2;
-    const uint64_t strides[2] = {(uint64_t)a.s_rx * 2, zs};
-    const uint32_t box[3] = {BK, (uint32_t)BN, 1};
+    // k-major B: (k, n, batch) with rows of n; n-major B: (n, k, batch) with rows of k
+    const uint64_t inner = B_MN ? (uint64_t)a.n : (uint64_t)a.k;
+    const uint64_t outer = B_MN ? (uint64_t)a.k : (uint64_t)a.n;
+    const uint64_t pitch = (uint64_t)(B_MN ? a.s_ry : a.s_rx) * 2;
+    const uint64_t dims[3] = {inner, outer, zb};
+    const uint64_t zs = zb == 1 ? pitch * outer : (uint64_t)a.s_rz * 2;
+    const uint64_t strides[2] = {pitch, zs};
+    const uint32_t box[3] = {BK, B_MN ? 64u : (uint32_t)BN, 1};
     int rc = tma_get(ctx, map_b, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, a.rhs, dims, strides, box,
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != ADR_OK) return rc;
@@ -481,17 +501,17 @@ int opt_in_smem(adr_ctx* ctx, K kfn, size_t bytes, bool* configured) {
   return ADR_OK;
 }
 
-template <int BN>
+template <int BN, bool B_MN>
 int launch_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, int S) {
   using Cfg = TcCfg<BN>;
   CUtensorMap map_a, map_b;
   TcParams p;
-  int rc = make_maps<BN>(ctx, a, &map_a, &map_b, &p);
+  int rc = make_maps<BN, B_MN>(ctx, a, &map_a, &map_b, &p);
   if (rc != ADR_OK) return rc;
   const int nt = (a.n + BN - 1) / BN, mt = (a.m + BM - 1) / BM;
   if (S <= 1) {
     static bool configured[64] = {};
-    auto kfn = gemm_f16_tc_kernel<BN>;
+    auto kfn = gemm_f16_tc_kernel<BN, B_MN>;
     rc = opt_in_smem(ctx, kfn, Cfg::SMEM, configured);
     if (rc != ADR_OK) return rc;
     const long long tiles = (long long)nt * mt * a.batches;
@@ -501,7 +521,7 @@ int launch_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, int S) {
     return after_launch(ctx);
   }
   static bool configured_sk[64] = {};
-  auto kfn = gemm_f16_tc_splitk_kernel<BN>;
+  auto kfn = gemm_f16_tc_splitk_kernel<BN, B_MN>;
   rc = opt_in_smem(ctx, kfn, Cfg::SMEM, configured_sk);
   if (rc != ADR_OK) return rc;
   cudaLaunchConfig_t cfg = {};
@@ -536,9 +556,11 @@ TcPlan pick_plan(const adr_ctx* ctx, const MatmulArgs& a) {
   const double sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
   const double mt = (a.m + BM - 1) / BM;
   const int num_kb = (a.k + BK - 1) / BK;
-  TcPlan best{32, 1};
+  TcPlan best{64, 1};
   double best_score = -1.0;
+  const bool b_mn = a.s_ry != 1;  // n-contiguous B needs 64-column chunks
   for (int bn : {256, 128, 64, 32}) {
+    if (b_mn && bn < 64) continue;
     if (ctx->tune_tc_bn && bn != ctx->tune_tc_bn) continue;
     if (!ctx->tune_tc_bn && bn > 32 && a.n <= bn / 2) continue;  // do not pad n beyond the next tile size
     const double tiles = mt * ((a.n + bn - 1) / bn) * a.batches;
@@ -570,8 +592,11 @@ TcPlan pick_plan(const adr_ctx* ctx, const MatmulArgs& a) {
 
 bool gemm_f16_tc_supports(const adr_ctx* ctx, const MatmulArgs& a) {
   if (!ctx->encode_tiled_fn) return false;
-  if (a.s_lx != 1 || a.s_ry != 1) return false;             // both operands k-contiguous
-  if (a.s_ly % 8 != 0 || a.s_rx % 8 != 0) return false;     // 16-byte row pitches
+  if (a.s_lx != 1 || a.s_ly % 8 != 0) return false;  // lhs k-contiguous, 16-byte row pitch
+  // rhs either k-contiguous ([N,K] storage passed permuted) or n-contiguous ([K,N] storage)
+  const bool b_k = a.s_ry == 1 && a.s_rx % 8 == 0;
+  const bool b_n = a.s_rx == 1 && a.s_ry % 8 == 0 && a.s_ry != 1;
+  if (!b_k && !b_n) return false;
   if (a.batches > 1 && (a.s_lz % 8 != 0 || a.s_rz % 8 != 0)) return false;
   if ((reinterpret_cast<uintptr_t>(a.lhs) & 15u) || (reinterpret_cast<uintptr_t>(a.rhs) & 15u))
     return false;
@@ -581,11 +606,18 @@ bool gemm_f16_tc_supports(const adr_ctx* ctx, const MatmulArgs& a) {
 
 int launch_gemm_f16_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a) {
   const TcPlan pl = pick_plan(ctx, a);
+  if (a.s_ry != 1) {
+    switch (pl.bn) {
+      case 256: return launch_tc<256, true>(ctx, stream, a, pl.S);
+      case 128: return launch_tc<128, true>(ctx, stream, a, pl.S);
+      default: return launch_tc<64, true>(ctx, stream, a, pl.S);
+    }
+  }
   switch (pl.bn) {
-    case 256: return launch_tc<256>(ctx, stream, a, pl.S);
-    case 128: return launch_tc<128>(ctx, stream, a, pl.S);
-    case 64: return launch_tc<64>(ctx, stream, a, pl.S);
-    default: return launch_tc<32>(ctx, stream, a, pl.S);
+    case 256: return launch_tc<256, false>(ctx, stream, a, pl.S);
+    case 128: return launch_tc<128, false>(ctx, stream, a, pl.S);
+    case 64: return launch_tc<64, false>(ctx, stream, a, pl.S);
+    default: return launch_tc<32, false>(ctx, stream, a, pl.S);
   }
 }
 

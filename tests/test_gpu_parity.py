@@ -383,3 +383,50 @@ def test_tc_gemm_every_tile_and_split(kernels, bn, split):
         kernels.set_tunable("tc_bn", 0)
         kernels.set_tunable("tc_split", 0)
         kernels.force_kernel(Kernel.Auto)
+
+
+@pytest.mark.parametrize("split", [0, 2])
+@pytest.mark.parametrize("bn", [64, 128, 256])
+def test_tc_gemm_n_contiguous_rhs(kernels, bn, split):
+    """rhs stored [K, N] row-major ("rrr", BASELINE config 1 as worded) and the
+    probabilities . values product with a 16-byte-aligned score pitch (k = 257)."""
+    rng = np.random.default_rng(7 * bn + split)
+    try:
+        kernels.force_kernel(Kernel.F16Tc)
+        kernels.set_tunable("tc_bn", bn)
+        kernels.set_tunable("tc_split", split)
+        # plain NN with ragged m, k, n
+        m, k, n = 200, 328, 392
+        a = (rng.standard_normal((m, k)) * 0.1).astype(np.float16)
+        w = (rng.standard_normal((k, n)) * 0.1).astype(np.float16)
+        want = np.zeros(m * n, np.float16)
+        oracle.matmul_f16(want, a.reshape(-1), w.reshape(-1), 1, m, k, n, (1, n, 0, 1, k, 0, 1, n, 0), ideal=True)
+        o = torch.zeros(m, n, dtype=torch.float16, device="cuda")
+        kernels.matmul_f16(TensorView.of(o), TensorView.of(dev(a)), TensorView.of(dev(w)))
+        kernels.device_status()
+        assert kernels.last_kernel() == Kernel.F16Tc
+        assert oracle.max_rel_err(o.cpu().numpy().reshape(-1), want) <= TOL
+        # P.V: lhs [H, S, S] with row pitch 264 (S = 257), rhs a [S, H*hd] buffer viewed [H, S, hd],
+        # out a strided view of [S, H, hd] (llama.rs:552-554, clip.rs:378-388)
+        H, S, hd, pitch = 3, 257, 64, 264
+        D = H * hd
+        pbuf = np.zeros(H * S * pitch, np.float16)
+        pv = pbuf.reshape(H, S, pitch)
+        pv[:, :, :S] = rng.uniform(0, 2.0 / S, (H, S, S)).astype(np.float16)
+        pv[:, :, S:] = np.float16(7.0)  # padding columns must never be read
+        v = (rng.standard_normal(S * D) * 0.5).astype(np.float16)
+        want = np.zeros(S * D, np.float16)
+        strides = (1, D, hd, 1, pitch, S * pitch, 1, D, hd)
+        oracle.matmul_f16(want, pbuf, v, H, S, S, hd, strides, ideal=True)
+        o, pd, vd = dev(np.zeros(S * D, np.float16)), dev(pbuf), dev(v)
+        ov = TensorView(o, TensorLayout.new((H, S, hd), (hd, D, 1)))
+        lv = TensorView(pd, TensorLayout.new((H, S, S), (S * pitch, pitch, 1)))
+        rv = TensorView(vd, TensorLayout.new((H, S, hd), (hd, D, 1)))
+        kernels.matmul_f16(ov, lv, rv)
+        kernels.device_status()
+        assert kernels.last_kernel() == Kernel.F16Tc
+        assert oracle.max_rel_err(o.cpu().numpy(), want) <= TOL
+    finally:
+        kernels.set_tunable("tc_bn", 0)
+        kernels.set_tunable("tc_split", 0)
+        kernels.force_kernel(Kernel.Auto)
