@@ -218,17 +218,32 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
   U8Args a{(__half*)out, (const __half*)lhs, rhs, (const __half*)scales, (const __half*)zeros,
            m, p, n, block_size, beta};
   cudaStream_t st = (cudaStream_t)stream;
+  U8Args a16 = a;  // the streaming kernel takes 16 tokens per pass
+  if (a16.m > 16) a16.m = 16;
   int kernel = ctx->forced_kernel;
   if (kernel == ADR_KERNEL_AUTO) {
-    if (p % 64 != 0) kernel = m <= 4 ? ADR_KERNEL_U8_GEMV : ADR_KERNEL_U8_SIMT;
-    else if (u8_stream_supports(ctx, a)) kernel = ADR_KERNEL_U8_STREAM;
+    // up to 32 tokens two passes of the streaming kernel beat one tensor-core launch
+    if (m > 32 && u8_tc_supports(ctx, a)) kernel = ADR_KERNEL_U8_TC;
+    else if (p % 64 != 0) kernel = m <= 4 ? ADR_KERNEL_U8_GEMV : ADR_KERNEL_U8_SIMT;
+    else if (u8_stream_supports(ctx, a16)) kernel = ADR_KERNEL_U8_STREAM;
     else kernel = ADR_KERNEL_U8_MMA;
   }
   int rc;
   switch (kernel) {
     case ADR_KERNEL_U8_GEMV: rc = launch_u8_gemv(ctx, st, a); break;
     case ADR_KERNEL_U8_SIMT: rc = launch_u8_simt(ctx, st, a); break;
-    case ADR_KERNEL_U8_STREAM: rc = launch_u8_stream(ctx, st, a); break;
+    case ADR_KERNEL_U8_STREAM: {
+      rc = ADR_OK;
+      for (int r0 = 0; r0 < m && rc == ADR_OK; r0 += 16) {  // one pass per 16 tokens
+        U8Args c = a;
+        c.m = (m - r0 < 16) ? m - r0 : 16;
+        c.lhs = a.lhs + (size_t)r0 * p;
+        c.out = a.out + (size_t)r0 * n;
+        rc = launch_u8_stream(ctx, st, c);
+      }
+      break;
+    }
+    case ADR_KERNEL_U8_TC: rc = launch_u8_tc(ctx, st, a); break;
     case ADR_KERNEL_U8_MMA: {
       if (p % 64 != 0) return ADR_ERR_SHAPE;
       rc = ADR_OK;

@@ -182,6 +182,8 @@ int launch_u8_gemv(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 int launch_u8_mma(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 int launch_u8_stream(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 bool u8_stream_supports(const adr_ctx* ctx, const U8Args& a);
+int launch_u8_tc(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
+bool u8_tc_supports(const adr_ctx* ctx, const U8Args& a);
 int init_u8_kernels(adr_ctx* ctx);
 
 int launch_dequantize_u8(adr_ctx* ctx, cudaStream_t stream, __half* out, const __half* scales,

@@ -578,7 +578,7 @@ TcPlan pick_plan(const adr_ctx* ctx, const MatmulArgs& a) {
         util = std::min(1.0, ctas / sms);
       }
       // measured: the exchange of partial tiles costs about 40 % at these sizes
-      const double score = util * eff * (S > 1 ? 0.6 : 1.0);
+      const double score = util * eff * (S == 1 ? 1.0 : S == 8 ? 0.4 : 0.6);
       if (score > best_score) {
         best_score = score;
         best = {bn, S};

@@ -140,6 +140,8 @@ def u8_kernels_for(c):
         ks.append(Kernel.U8Mma)
         if c.m <= 16 and c.p % 128 == 0:
             ks.append(Kernel.U8Stream)
+    if c.p % 16 == 0:
+        ks.append(Kernel.U8Tc)
     return ks
 
 
@@ -430,3 +432,26 @@ def test_tc_gemm_n_contiguous_rhs(kernels, bn, split):
         kernels.set_tunable("tc_bn", 0)
         kernels.set_tunable("tc_split", 0)
         kernels.force_kernel(Kernel.Auto)
+
+
+@pytest.mark.parametrize("zp", [False, True])
+def test_u8_prefill_tensor_core_kernel(kernels, zp):
+    """m > 16 takes the dequantising tensor-core kernel: ragged m/n, several k-blocks
+    and tiles per CTA, beta, zero points; checked against the ideal oracle."""
+    rng = np.random.default_rng(31 + zp)
+    for m, p, n, bs, beta in ((130, 1088, 300, 64, 0.5), (512, 512, 1024, 128, 0.0), (40, 256, 192, 128, 1.0)):
+        x = rng.standard_normal((m, p)).astype(np.float16)
+        q = rng.integers(0, 256, (n, p), dtype=np.uint8)
+        s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
+        z = rng.uniform(120, 136, (n, p // bs)).astype(np.float16) if zp else None
+        out0 = (rng.standard_normal((m, n)) * 0.5).astype(np.float16)
+        want = oracle.matmul_nt_fp16u8(x, q, s, bs, beta, out0, z)
+        res = []
+        for _ in range(2):
+            o = dev(out0.copy())
+            kernels.matmul_nt_fp16u8(o, dev(x), dev(q), dev(s), bs, beta, dev(z) if zp else None)
+            kernels.device_status()
+            assert kernels.last_kernel() == Kernel.U8Tc
+            res.append(o.cpu().numpy())
+        assert np.array_equal(res[0].view(np.uint16), res[1].view(np.uint16))
+        assert oracle.max_rel_err(res[0], want) <= TOL, (m, p, n)
