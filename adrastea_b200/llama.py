@@ -1,0 +1,335 @@
+"""LLaMA-shape decoder harness with u8 weights: the caller of the matmul path.
+
+Restates the call sequence of the reference's `LlamaContext::process_layer` /
+`decode` (adrastea_models/src/llama.rs:456-589) around this library's kernels:
+every linear layer goes through `adr_matmul_nt_fp16u8`, the attention products
+through `adr_matmul_f16` with the reference's views (q.k^T with `Scale` and the
+causal mask, probabilities . v into a strided output view).  What sits between
+the matmuls (rms_norm, rotary, softmax, silu*mul, embedding, argmax) is NOT part
+of the kernel contract of this repository and is done with PyTorch ops that follow
+the reference kernels' formulas (normalize.cu:7-58, rotary.cu:4-29,
+elementwise.cu:28-33).
+
+Differences from the reference, which re-runs the whole prefix for every token
+(llama.rs:426-427): a KV cache, batches of sequences, tensor parallelism
+(adrastea_b200/tp.py) and CUDA-graph capture of the decode step are harness glue
+that BASELINE's configs 4 and 5 ask for.  Weights are seeded random u8 codes with
+the config-2 distributions; there are no checkpoints in this environment.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .kernels import GpuKernels, MatmulMask, MatmulOptions, MatmulStore
+from .tensor import TensorLayout, TensorView
+from .tp import ColumnParallelU8Linear, RowParallelU8Linear, TPContext, U8Weight
+
+
+@dataclass(frozen=True)
+class LlamaShape:
+    dim: int
+    n_heads: int
+    ffn: int
+    n_layers: int
+    vocab: int = 32000
+    block: int = 128
+    norm_eps: float = 1e-5
+    theta: float = 10000.0
+
+    @property
+    def head_dim(self) -> int:
+        return self.dim // self.n_heads
+
+
+LLAMA_7B = LlamaShape(4096, 32, 11008, 32)
+LLAMA_65B = LlamaShape(8192, 64, 22016, 80, block=64)  # block 64: 22016/8 = 2752 = 43 * 64
+
+
+def _rand_u8(n, k, block, gen, device) -> U8Weight:
+    q = torch.randint(0, 256, (n, k), dtype=torch.uint8, device=device, generator=gen)
+    s = (torch.rand((n, k // block), device=device, generator=gen) * 0.009 + 0.001).half()
+    return U8Weight(q, s, block)
+
+
+def rms_norm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """normalize.cu:7-58: weights * fp16(x * rsqrt(mean(x^2) + eps)), statistics in fp32."""
+    xf = x.float()
+    inv = torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
+    return w * (xf * inv).half()
+
+
+def rotary(x: torch.Tensor, pos: torch.Tensor, n_heads: int, theta: float) -> torch.Tensor:
+    """rotary.cu:4-29: interleaved pairs (2i, 2i+1) of every head rotated by
+    pos / theta^(2i / head_dim).  x: [rows, n_heads*head_dim], pos: [rows] (int)."""
+    rows, width = x.shape
+    hd = width // n_heads
+    c = torch.arange(0, hd, 2, device=x.device, dtype=torch.float32)
+    # theta^(c/hd) as exp(c/hd * ln theta): no host scalar becomes a device tensor here, so the
+    # function can run under CUDA-graph capture
+    ang = pos.float()[:, None] / torch.exp(c / hd * math.log(theta))[None, :]
+    cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    xv = x.float().view(rows, n_heads, hd // 2, 2)
+    re, im = xv[..., 0], xv[..., 1]
+    out = torch.stack((re * cos - im * sin, re * sin + im * cos), dim=-1)
+    return out.view(rows, width).half()
+
+
+class LlamaU8Layer:
+    def __init__(self, kernels: GpuKernels, shape: LlamaShape, tp: TPContext, gen, device):
+        t = tp.world
+        d, f, bs = shape.dim, shape.ffn, shape.block
+        assert d % t == 0 and f % t == 0 and shape.n_heads % t == 0
+        # shards are generated directly (seeded per rank); no full matrix is ever materialised
+        col = lambda n, k: ColumnParallelU8Linear(kernels, _rand_u8(n // t, k, bs, gen, device), tp, True)
+        row = lambda n, k: RowParallelU8Linear(kernels, _rand_u8(n, k // t, bs, gen, device), tp, True)
+        self.wq, self.wk, self.wv = col(d, d), col(d, d), col(d, d)
+        self.wo = row(d, d)
+        self.gate, self.up = col(f, d), col(f, d)
+        self.down = row(d, f)
+        self.attn_norm = torch.ones(d, dtype=torch.float16, device=device)
+        self.ffn_norm = torch.ones(d, dtype=torch.float16, device=device)
+
+    def linears(self):
+        return (self.wq, self.wk, self.wv, self.wo, self.gate, self.up, self.down)
+
+    def weight_bytes(self) -> int:
+        return sum(l.w.nbytes() for l in self.linears())
+
+
+class LlamaU8:
+    """Decoder stack with a KV cache.  `tp.world` ranks each hold 1/world of every
+    sharded matrix and of the heads; embeddings, norms and the output head are replicated."""
+
+    def __init__(self, kernels: GpuKernels, shape: LlamaShape, tp: TPContext | None = None,
+                 max_batch: int = 16, max_seq: int = 640, n_layers: int | None = None,
+                 seed: int = 0, device: str | torch.device = "cuda"):
+        self.k, self.shape = kernels, shape
+        self.tp = tp or TPContext()
+        self.device = torch.device(device)
+        self.B, self.S = max_batch, (max_seq + 7) // 8 * 8  # score rows stay 16-byte aligned
+        self.L = n_layers or shape.n_layers
+        gen = torch.Generator(device=self.device).manual_seed(1000 * seed + self.tp.rank)
+        self.layers = [LlamaU8Layer(kernels, shape, self.tp, gen, self.device) for _ in range(self.L)]
+        rep = torch.Generator(device=self.device).manual_seed(777 + seed)  # same on every rank
+        self.embed = (torch.randn((shape.vocab, shape.dim), device=self.device, generator=rep)).half()
+        self.out_norm = torch.ones(shape.dim, dtype=torch.float16, device=self.device)
+        self.lm_head = _rand_u8(shape.vocab, shape.dim, shape.block, rep, self.device)
+        self.Hl = shape.n_heads // self.tp.world
+        hd = shape.head_dim
+        dl = self.Hl * hd
+        f16 = dict(dtype=torch.float16, device=self.device)
+        self.k_cache = torch.zeros((self.L, self.B, self.Hl, self.S, hd), **f16)
+        self.v_cache = torch.zeros((self.L, self.B, self.Hl, self.S, hd), **f16)
+        # decode-step buffers (fixed addresses, so the step can be captured in a CUDA graph)
+        B, d, fl = self.B, shape.dim, shape.ffn // self.tp.world
+        self.h = torch.zeros((B, d), **f16)
+        self.q = torch.zeros((B, dl), **f16)
+        self.kx = torch.zeros((B, dl), **f16)
+        self.vx = torch.zeros((B, dl), **f16)
+        self.att = torch.zeros((B, dl), **f16)
+        self.scores = torch.zeros((B * self.Hl, 1, self.S), **f16)
+        self.g = torch.zeros((B, fl), **f16)
+        self.u = torch.zeros((B, fl), **f16)
+        self.partial = torch.zeros((B, d), **f16)
+        self.logits = torch.zeros((B, shape.vocab), **f16)
+        self.pos = torch.zeros((1,), dtype=torch.int64, device=self.device)
+        self.tokens = torch.zeros((B,), dtype=torch.int64, device=self.device)
+        self.next_tokens = torch.zeros((B,), dtype=torch.int64, device=self.device)
+        self._graph = None
+
+    # ------------------------------------------------------------------ sizes
+    def weight_bytes_per_token(self) -> int:
+        """u8 weights + scales this rank streams per decode step (all layers + output head)."""
+        return sum(l.weight_bytes() for l in self.layers) + self.lm_head.nbytes()
+
+    # ------------------------------------------------------------- attention
+    def _attention_decode(self, li: int):
+        """One new token per sequence against the cache: scores = q.k^T * 1/sqrt(hd)
+        (llama.rs:541-550; the causal mask degenerates to "positions <= pos"), softmax,
+        probabilities . v (llama.rs:552-554)."""
+        B, Hl, S, hd = self.B, self.Hl, self.S, self.shape.head_dim
+        kc, vc = self.k_cache[li], self.v_cache[li]
+        qv = TensorView(self.q, TensorLayout.new((B * Hl, 1, hd), (hd, hd, 1)))
+        kv = TensorView(kc, TensorLayout.new((B * Hl, hd, S), (S * hd, 1, hd)))
+        sv = TensorView(self.scores, TensorLayout.new((B * Hl, 1, S), (S, S, 1)))
+        self.k.matmul_f16(sv, qv, kv, MatmulOptions.new().store(MatmulStore.Scale(1.0 / math.sqrt(hd))))
+        mask = torch.arange(S, device=self.device)[None, None, :] > self.pos
+        probs = torch.softmax(self.scores.float().masked_fill(mask, float("-inf")), dim=-1).half()
+        self.scores.copy_(probs)
+        vv = TensorView(vc, TensorLayout.new((B * Hl, S, hd), (S * hd, hd, 1)))
+        ov = TensorView(self.att, TensorLayout.new((B * Hl, 1, hd), (hd, hd, 1)))
+        self.k.matmul_f16(ov, sv, vv)
+
+    # ----------------------------------------------------------- decode step
+    def _decode_step_body(self):
+        sh, tp = self.shape, self.tp
+        self.h.copy_(self.embed[self.tokens])
+        posv = self.pos.expand(self.B)
+        for li, ly in enumerate(self.layers):
+            x = rms_norm(self.h, ly.attn_norm, sh.norm_eps)
+            ly.wq(self.q, x)
+            ly.wk(self.kx, x)
+            ly.wv(self.vx, x)
+            self.q.copy_(rotary(self.q, posv, self.Hl, sh.theta))
+            kr = rotary(self.kx, posv, self.Hl, sh.theta)
+            idx = self.pos.view(1, 1, 1, 1).expand(self.B, self.Hl, 1, sh.head_dim)
+            self.k_cache[li].scatter_(2, idx, kr.view(self.B, self.Hl, 1, sh.head_dim))
+            self.v_cache[li].scatter_(2, idx, self.vx.view(self.B, self.Hl, 1, sh.head_dim))
+            self._attention_decode(li)
+            ly.wo(self.h, self.att, self.partial, residual=True)       # store = Add, llama.rs:555-560
+            x = rms_norm(self.h, ly.ffn_norm, sh.norm_eps)
+            ly.gate(self.g, x)
+            ly.up(self.u, x)
+            self.g.copy_(torch.nn.functional.silu(self.g.float()).half() * self.u)  # SiluMul
+            ly.down(self.h, self.g, self.partial, residual=True)       # llama.rs:584-589
+        x = rms_norm(self.h, self.out_norm, sh.norm_eps)
+        self.k.matmul_nt_fp16u8(self.logits, x, self.lm_head.q, self.lm_head.scales, self.lm_head.block)
+        self.next_tokens.copy_(torch.argmax(self.logits.float(), dim=-1))
+
+    def capture(self):
+        """Capture one decode step (fixed shapes, position and tokens in device memory)."""
+        s = torch.cuda.Stream(device=self.device)
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            self._decode_step_body()  # warm-up outside capture (allocator, descriptor cache)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        self._graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self._graph):
+            self._decode_step_body()
+
+    def decode_step(self):
+        """Consumes self.tokens at position self.pos, leaves the argmax in self.next_tokens."""
+        if self._graph is not None:
+            self._graph.replay()
+        else:
+            self._decode_step_body()
+        self.tokens.copy_(self.next_tokens)
+        self.pos.add_(1)
+
+    # ------------------------------------------------------------- prefill
+    def prefill(self, tokens: torch.Tensor):
+        """tokens: [B, S0] int64.  Fills the cache for positions [0, S0) and leaves the
+        last-position argmax in self.tokens, self.pos = S0."""
+        sh, tp = self.shape, self.tp
+        B, S0 = tokens.shape
+        assert B == self.B and S0 <= self.S
+        hd, Hl, d = sh.head_dim, self.Hl, sh.dim
+        dl, fl = Hl * hd, sh.ffn // tp.world
+        f16 = dict(dtype=torch.float16, device=self.device)
+        h = self.embed[tokens.reshape(-1)].clone()                       # [B*S0, d]
+        pos = torch.arange(S0, device=self.device).repeat(B)
+        # zero-filled like the reference's Tensor::new_gpu: the u8 kernels always read `out`
+        # (beta * old, even for beta = 0), so stale NaNs in a fresh buffer would propagate
+        q, kx, vx, att = (torch.zeros((B * S0, dl), **f16) for _ in range(4))
+        g, u = torch.zeros((B * S0, fl), **f16), torch.zeros((B * S0, fl), **f16)
+        part = torch.zeros((B * S0, d), **f16)
+        Sp = (S0 + 7) // 8 * 8
+        scores = torch.zeros((Hl, S0, Sp), **f16)
+        scale = 1.0 / math.sqrt(hd)
+        for li, ly in enumerate(self.layers):
+            x = rms_norm(h, ly.attn_norm, sh.norm_eps)
+            ly.wq(q, x)
+            ly.wk(kx, x)
+            ly.wv(vx, x)
+            q.copy_(rotary(q, pos, Hl, sh.theta))
+            kx.copy_(rotary(kx, pos, Hl, sh.theta))
+            self.k_cache[li][:, :, :S0].copy_(kx.view(B, S0, Hl, hd).permute(0, 2, 1, 3))
+            self.v_cache[li][:, :, :S0].copy_(vx.view(B, S0, Hl, hd).permute(0, 2, 1, 3))
+            for b in range(B):  # one sequence at a time, with the reference's views (llama.rs:530-554)
+                sl = slice(b * S0, (b + 1) * S0)
+                qv = TensorView.of(q[sl]).shape_cast([S0, Hl, -1]).permute([1, 0, 2])
+                kv = TensorView.of(kx[sl]).shape_cast([S0, Hl, -1]).permute([1, 2, 0])
+                vv = TensorView.of(vx[sl]).shape_cast([S0, Hl, -1]).permute([1, 0, 2])
+                sv = TensorView(scores, TensorLayout.new((Hl, S0, S0), (S0 * Sp, Sp, 1)))
+                self.k.matmul_f16(sv, qv, kv, MatmulOptions.new().store(MatmulStore.Scale(scale))
+                                  .mask(MatmulMask.Causal))
+                scores[:, :, :S0] = torch.softmax(scores[:, :, :S0].float(), dim=-1).half()
+                ov = TensorView.of(att[sl]).shape_cast([S0, Hl, -1]).permute([1, 0, 2])
+                self.k.matmul_f16(ov, sv, vv)
+            ly.wo(h, att, part, residual=True)
+            x = rms_norm(h, ly.ffn_norm, sh.norm_eps)
+            ly.gate(g, x)
+            ly.up(u, x)
+            g.copy_(torch.nn.functional.silu(g.float()).half() * u)
+            ly.down(h, g, part, residual=True)
+        last = rms_norm(h.view(B, S0, d)[:, -1].contiguous(), self.out_norm, sh.norm_eps)
+        self.k.matmul_nt_fp16u8(self.logits, last, self.lm_head.q, self.lm_head.scales, self.lm_head.block)
+        self.tokens.copy_(torch.argmax(self.logits.float(), dim=-1))
+        self.pos.fill_(S0)
+
+
+def main():
+    """python -m adrastea_b200.llama --shape 7b --batch 16 --prefill 512 --decode 128
+    (under torchrun for tensor parallelism).  Prints one JSON line with decode tokens/s,
+    timed with CUDA events around the captured decode steps, max over ranks."""
+    import argparse
+    import json
+    import os
+
+    import torch.distributed as dist
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", default="7b", choices=["7b", "65b"])
+    ap.add_argument("--batch", type=int, default=16)
+    ap.add_argument("--prefill", type=int, default=512)
+    ap.add_argument("--decode", type=int, default=128)
+    ap.add_argument("--layers", type=int, default=0, help="use only the first N layers (0 = all)")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    kern = GpuKernels(local)
+    kern.set_tunable("pdl", 0 if args.no_pdl else 1)
+    shape = LLAMA_7B if args.shape == "7b" else LLAMA_65B
+    model = LlamaU8(kern, shape, TPContext(), max_batch=args.batch,
+                    max_seq=args.prefill + args.decode, n_layers=args.layers or None,
+                    device=torch.device("cuda", local))
+    toks = torch.randint(0, shape.vocab, (args.batch, args.prefill), device=model.device)
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    e[0].record()
+    model.prefill(toks)
+    e[1].record()
+    if not args.no_graph:
+        pos0, tok0 = model.pos.clone(), model.tokens.clone()
+        model.capture()
+        model.pos.copy_(pos0)
+        model.tokens.copy_(tok0)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e[2].record()
+    for _ in range(args.decode):
+        model.decode_step()
+    e[3].record()
+    torch.cuda.synchronize()
+    ms_pre, ms_dec = e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3])
+    if world > 1:
+        t = torch.tensor([ms_pre, ms_dec], device=model.device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_pre, ms_dec = t.tolist()
+    kern.device_status()
+    if int(os.environ.get("RANK", "0")) == 0:
+        wb = model.weight_bytes_per_token()
+        print(json.dumps({
+            "model": f"llama-{args.shape}-shape u8", "layers": model.L, "tp": world, "batch": args.batch,
+            "prefill_tokens": args.batch * args.prefill, "prefill_ms": ms_pre,
+            "prefill_tok_s": args.batch * args.prefill / (ms_pre * 1e-3),
+            "decode_steps": args.decode, "decode_ms_per_step": ms_dec / args.decode,
+            "decode_tok_s": args.batch * args.decode / (ms_dec * 1e-3),
+            "weight_bytes_per_step_per_gpu": wb,
+            "weight_stream_gbs_per_gpu": wb * args.decode / (ms_dec * 1e-3) / 1e9,
+            "graph": not args.no_graph}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,127 @@
+"""Tensor-parallel sharding of the u8 linear layers (one process per GPU).
+
+The reference has no multi-GPU path ("bring back multi-gpu and quantization",
+adrastea_models/src/llama.rs:28-29); this is the Megatron-style split BASELINE's
+config 5 asks for, around the reference's weight layout (`[N, K]` u8 codes, fp16
+scales `[N, K/block]`, adrastea_kernels/cpp/quantize.cu:3-56):
+
+  column split (q, k, v, gate, up): rank r keeps rows [r*N/t, (r+1)*N/t) of the
+      `[N, K]` storage and of the scales: independent GEMVs, no exchange;
+  row split (o, down): rank r keeps columns [r*K/t, (r+1)*K/t) of every row (a
+      contiguous `[N, K/t]` copy made once at load time) and the matching scale
+      groups; each rank produces a partial `[M, N]` and one all-reduce (sum) over
+      NCCL completes it.  The quantisation block must divide K/t.
+
+The sharding functions are pure slicing and run anywhere; `RowParallelU8Linear` and
+`ColumnParallelU8Linear` launch the library's kernels and need a GPU.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class U8Weight:
+    """One quantised matrix in the reference's layout."""
+    q: torch.Tensor        # uint8 [N, K]
+    scales: torch.Tensor   # float16 [N, K // block]
+    block: int
+    zeros: torch.Tensor | None = None
+
+    @property
+    def n(self) -> int:
+        return self.q.shape[0]
+
+    @property
+    def k(self) -> int:
+        return self.q.shape[1]
+
+    def nbytes(self) -> int:
+        b = self.q.numel() + 2 * self.scales.numel()
+        if self.zeros is not None:
+            b += 2 * self.zeros.numel()
+        return b
+
+
+def shard_column(w: U8Weight, rank: int, world: int) -> U8Weight:
+    """Rows [rank*N/world, (rank+1)*N/world) of codes and scales (output features)."""
+    if w.n % world != 0:
+        raise ValueError(f"N={w.n} is not divisible by the tensor-parallel size {world}")
+    lo, hi = rank * w.n // world, (rank + 1) * w.n // world
+    z = None if w.zeros is None else w.zeros[lo:hi].contiguous()
+    return U8Weight(w.q[lo:hi].contiguous(), w.scales[lo:hi].contiguous(), w.block, z)
+
+
+def shard_row(w: U8Weight, rank: int, world: int) -> U8Weight:
+    """Columns [rank*K/world, (rank+1)*K/world) of every row (input features), with the
+    scale groups that cover them.  A group may not straddle two ranks."""
+    if w.k % world != 0:
+        raise ValueError(f"K={w.k} is not divisible by the tensor-parallel size {world}")
+    kk = w.k // world
+    if kk % w.block != 0:
+        raise ValueError(f"the quantisation block {w.block} does not divide K/world = {kk}: "
+                         "groups would straddle ranks (use a smaller block for this matrix)")
+    g = kk // w.block
+    z = None if w.zeros is None else w.zeros[:, rank * g:(rank + 1) * g].contiguous()
+    return U8Weight(w.q[:, rank * kk:(rank + 1) * kk].contiguous(),
+                    w.scales[:, rank * g:(rank + 1) * g].contiguous(), w.block, z)
+
+
+class TPContext:
+    """Rank, world size and the process group; world 1 needs no process group."""
+
+    def __init__(self, group=None):
+        if dist.is_available() and dist.is_initialized():
+            self.group = group
+            self.rank = dist.get_rank(group)
+            self.world = dist.get_world_size(group)
+        else:
+            self.group, self.rank, self.world = None, 0, 1
+
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+
+class ColumnParallelU8Linear:
+    """y[:, shard] = x . deq(W[shard rows])^T; the output stays sharded along N."""
+
+    def __init__(self, kernels, w_full_or_shard: U8Weight, tp: TPContext, already_sharded=False):
+        self.kernels, self.tp = kernels, tp
+        self.w = w_full_or_shard if already_sharded else shard_column(w_full_or_shard, tp.rank, tp.world)
+
+    def __call__(self, out: torch.Tensor, x: torch.Tensor, beta: float = 0.0) -> torch.Tensor:
+        self.kernels.matmul_nt_fp16u8(out, x, self.w.q, self.w.scales, self.w.block, beta, self.w.zeros)
+        return out
+
+
+class RowParallelU8Linear:
+    """y = all_reduce_sum_r( x[:, shard_r] . deq(W[:, shard_r])^T ).
+
+    `beta` (accumulate into `out`, e.g. the residual) is applied after the reduction on
+    the reduced value, so the residual is added exactly once."""
+
+    def __init__(self, kernels, w_full_or_shard: U8Weight, tp: TPContext, already_sharded=False):
+        self.kernels, self.tp = kernels, tp
+        self.w = w_full_or_shard if already_sharded else shard_row(w_full_or_shard, tp.rank, tp.world)
+
+    def __call__(self, out: torch.Tensor, x_shard: torch.Tensor, partial: torch.Tensor | None = None,
+                 residual: bool = False) -> torch.Tensor:
+        if self.tp.world == 1 and not residual:
+            self.kernels.matmul_nt_fp16u8(out, x_shard, self.w.q, self.w.scales, self.w.block, 0.0, self.w.zeros)
+            return out
+        if self.tp.world == 1:
+            self.kernels.matmul_nt_fp16u8(out, x_shard, self.w.q, self.w.scales, self.w.block, 1.0, self.w.zeros)
+            return out
+        buf = partial if partial is not None else torch.zeros_like(out)
+        self.kernels.matmul_nt_fp16u8(buf, x_shard, self.w.q, self.w.scales, self.w.block, 0.0, self.w.zeros)
+        self.tp.all_reduce(buf)
+        if residual:
+            out.add_(buf)
+        else:
+            out.copy_(buf)
+        return out

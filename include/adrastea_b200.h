@@ -147,6 +147,8 @@ int adr_matmul_f16_raw(adr_ctx* ctx, adr_stream stream, void* out, const void* l
  * (fp16 [n, p/block_size]; an extension without counterpart in the
  * reference): zero = float(zeros[n, group]).
  * Requires p % block_size == 0, block_size % 16 == 0 and p % 16 == 0; any m, n.
+ * Like the reference kernels, `out` is always read (beta * old even when beta == 0), so a
+ * NaN or Inf left in an uninitialised `out` propagates: pass a defined buffer.
  */
 int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
                          const uint8_t* rhs, const void* scales, const void* zeros, int m, int p,
