@@ -326,6 +326,182 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_ours_tp(args):
+    """N > 1: BASELINE configs[4], the LLaMA-65B-shape decode linears (hidden 8192, FFN 22016,
+    block 64), batch 16, tensor-parallel over the N ranks: column-split q/k/v/gate/up, row-split
+    o/down, one NCCL all-reduce of [16, 8192] fp16 after each row-split product.  One step =
+    TP_LAYERS distinct layers (6.5 GB of u8 weights in total, sharded N ways, so every launch
+    streams from HBM).  Strong scaling: the model is fixed, the shards shrink with N.  The
+    metric is the same as at N = 1: algorithmic bytes of all ranks per second."""
+    import torch
+    import torch.distributed as dist
+
+    from adrastea_b200 import GpuKernels
+    from adrastea_b200.llama import LLAMA_65B, LlamaU8Layer
+    from adrastea_b200.tp import TPContext
+
+    world = int(os.environ["WORLD_SIZE"])
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    def note(msg):
+        if os.environ.get("ADR_BENCH_VERBOSE"):
+            print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    note("process group up")
+    tp = TPContext()
+    kern = GpuKernels(local)
+    kern.set_tunable("pdl", 0 if args.no_pdl else 1)
+    sh, M, TP_LAYERS = LLAMA_65B, 16, 8
+    gen = torch.Generator(device=dev).manual_seed(4321 + rank)
+    layers = [LlamaU8Layer(kern, sh, tp, gen, dev) for _ in range(TP_LAYERS)]
+    d, dl, fl = sh.dim, sh.dim // world, sh.ffn // world
+    f16 = dict(dtype=torch.float16, device=dev)
+    x_host = torch.randn((M, d), dtype=torch.float16).pin_memory()
+    x = x_host.to(dev)
+    h = torch.zeros((M, d), **f16)
+    q, kx, vx = (torch.zeros((M, dl), **f16) for _ in range(3))
+    g, u = torch.zeros((M, fl), **f16), torch.zeros((M, fl), **f16)
+    part = torch.zeros((M, d), **f16)
+    h_host = torch.zeros((M, d), dtype=torch.float16).pin_memory()
+    stream = torch.cuda.current_stream()
+
+    # The step is cut at every all-reduce: the kernels between two collectives form one
+    # segment.  Segments are captured into CUDA graphs (launching from Python costs about
+    # 14 us per kernel); the NCCL calls stay eager between the replays, because capturing
+    # them hung in this environment.
+    def seg_attn(ly):
+        ly.wq(q, x)
+        ly.wk(kx, x)
+        ly.wv(vx, x)
+        # row-split product of this rank's slice (the attention itself is not part of this workload)
+        ly.wo.kernels.matmul_nt_fp16u8(part, q, ly.wo.w.q, ly.wo.w.scales, ly.wo.w.block)
+
+    def seg_ffn(ly):
+        h.copy_(part)  # the reduced o-projection
+        ly.gate(g, x)
+        ly.up(u, x)
+        ly.down.kernels.matmul_nt_fp16u8(part, g, ly.down.w.q, ly.down.w.scales, ly.down.w.block)
+
+    segments = []
+    for ly in layers:
+        segments.append(lambda ly=ly: seg_attn(ly))
+        segments.append(lambda ly=ly: seg_ffn(ly))
+    replay = list(segments)
+
+    def step():
+        for seg in replay:
+            seg()
+            tp.all_reduce(part)
+        h.copy_(part)
+
+    def act_bytes(ly):
+        b = 0
+        for lin in ly.linears():
+            b += 2 * M * lin.w.k + 2 * M * lin.w.n
+        return b
+
+    bytes_rank = sum(ly.weight_bytes() + act_bytes(ly) for ly in layers)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    note("weights ready")
+    step()
+    torch.cuda.synchronize()
+    note("first eager step done")
+    launches0 = kern.launch_count()
+    step()
+    launches_per_step = kern.launch_count() - launches0
+    torch.cuda.synchronize()
+    note("second eager step done")
+    graph = None
+    if not args.no_graph:
+        graphs = []
+        for seg in segments:
+            gph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gph):
+                seg()
+            graphs.append(gph)
+        replay = [gph.replay for gph in graphs]
+        graph = graphs
+    note("segments captured" if graph else "eager segments")
+    run = step
+    note(f"graph={'yes' if graph is not None else 'no'}")
+    stream = torch.cuda.current_stream()
+    for _ in range(max(args.warmup, 3)):
+        run()
+    torch.cuda.synchronize()
+    note("warm-up done")
+    uuid = None
+    try:
+        uuid = "GPU-" + str(torch.cuda.get_device_properties(local).uuid)
+    except Exception:
+        pass
+    sampler = ClockSampler(uuid)
+    if rank == 0:
+        sampler.start()
+    ms = timed(run, args.steps)
+    note(f"timed {ms:.2f} ms")
+
+    def run_e2e():
+        x.copy_(x_host, non_blocking=True)
+        run()
+        h_host.copy_(h, non_blocking=True)
+        stream.synchronize()
+
+    run_e2e()
+    ms_e2e = timed(run_e2e, args.steps)
+    clocks = sampler.stop() if rank == 0 else {}
+    tb = torch.tensor([float(bytes_rank)], device=dev, dtype=torch.float64)
+    dist.all_reduce(tb)
+    total_bytes = float(tb.item())
+    if rank == 0:
+        peak, peak_kind = measured_peak()
+        value = total_bytes * args.steps / (ms * 1e-3) / 1e9
+        line = {
+            "metric": "u8_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic",
+            "config": {"workload": "configs[4]: LLaMA-65B-shape decode linears, M=16, hidden 8192, FFN 22016, "
+                                   "block 64, tensor-parallel: column-split q/k/v/gate/up, row-split o/down, "
+                                   "NCCL all-reduce after o and down",
+                       "layers_per_step": TP_LAYERS, "tp": world,
+                       "weight_bytes_per_step_all_ranks": int(total_bytes),
+                       "all_reduces_per_step": 2 * TP_LAYERS, "all_reduce_bytes": M * d * 2,
+                       "cuda_graph": graph is not None,
+                       "l2_policy": "inputs larger than L2: each rank streams its own "
+                                    f"{bytes_rank / 1e9:.2f} GB of distinct weights per step"},
+            "e2e": {"value": total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
+                    "h2d_bytes_per_step": M * d * 2, "d2h_bytes_per_step": M * d * 2,
+                    "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": int(launches_per_step * args.steps),
+            "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
+                         "frac": value / world / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                         "kernel": "u8_stream_kernel (+ ncclAllReduce between row-split products)"},
+            "clocks": clocks,
+        }
+        print(json.dumps(line))
+    dist.destroy_process_group()
+
+
 def run_profile_case(args):
     """Small, self-terminating cases for `ncu` captures (a few hundred MB on the device).
 
@@ -367,6 +543,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches")
+    ap.add_argument("--no-graph", action="store_true", help="N > 1: do not capture the step in a CUDA graph")
     ap.add_argument("--profile-case", default=None, choices=["u8", "f16"],
                     help="run a small fixed case of one kernel family and exit (for ncu captures)")
     ap.add_argument("--m", type=int, default=1, help="rows of the activation in --profile-case")
@@ -375,6 +552,8 @@ def main():
         run_profile_case(args)
     elif args.impl == "reference":
         run_reference(args)
+    elif int(os.environ.get("WORLD_SIZE", "1")) > 1:
+        run_ours_tp(args)
     else:
         run_ours(args)
 
