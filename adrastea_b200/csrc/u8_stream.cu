@@ -36,7 +36,6 @@ namespace adr {
 namespace {
 
 constexpr int MAX_TILES = 96;  // 128-byte tiles per k-slice (12 KB of k)
-constexpr int BAR_BYTES = 1024;  // MAX_TILES + 1 mbarriers
 
 // Not volatile: the compiler may move it among the surrounding arithmetic.
 __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
@@ -65,12 +64,16 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
   constexpr int TOK = 8 * MT;
   constexpr int TILE_BYTES = R * 128;
 
-  extern __shared__ uint8_t smem_raw[];
-  // 1024-byte alignment for the swizzled tiles
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem);  // [0..MAX_TILES): tiles, [MAX_TILES]: x
-  uint8_t* Wsm = smem + BAR_BYTES;
+  // Shared memory, tightly packed so that three CTAs fit an SM at k = 4096, m = 1 (which
+  // leaves room for the next launch's CTAs under programmatic dependent launch):
+  //   [tiles: nt * R * 128] [activations: m * XS] [scale table] [mbarriers: nt + 1]
+  // The swizzled tiles need a 1024-byte aligned base.
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* Wsm = smem_raw;
+  if ((smem_u32(Wsm) & 1023u) != 0) {  // same for every CTA of the launch
+    if (threadIdx.x == 0) atomicOr(status, 16u);
+    return;
+  }
 
   const int tid = threadIdx.x;
   const int lane = tid & 31, warp = tid >> 5;
@@ -108,8 +111,12 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
   // served roughly in issue order, so the small operands that gate the first MMA (scales,
   // zero points, activations) go out before the weight tiles.
   // Scale table in shared memory, one 8-byte entry per (row, group - g_lo):
-  //   .x = (s, s) as packed halves;  .y = (s/2, s/2), or (z, z) when zero points are given.
-  uint2* Ssm = reinterpret_cast<uint2*>(Xsm + (size_t)a.m * XS);
+  //   (s, s) as packed halves, plus (z, z) when zero points are given.
+  using Entry = std::conditional_t<HAS_ZERO, uint2, uint32_t>;
+  Entry* Ssm = reinterpret_cast<Entry*>(Xsm + (size_t)a.m * XS);
+  // mbarriers behind the table: [0, nt) one per tile, [nt] the activations
+  uint64_t* bars = reinterpret_cast<uint64_t*>(Ssm + (size_t)R * NG);
+  uint64_t* xbar = bars + nt;
   const int g_lo = k0 >> bs_shift;
   const int ng = ((k0 + nt * 128 - 1) >> bs_shift) - g_lo + 1;
   constexpr int EARLY = 4;  // table entries per thread fetched into registers first
@@ -133,14 +140,14 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
     if (lane == 0) {
       tma_prefetch_desc(&wmap);
       for (int i = 0; i < nt; ++i) mbar_init(&bars[i], 1);
-      mbar_init(&bars[MAX_TILES], 1);
+      mbar_init(xbar, 1);
       mbar_fence_init();
-      mbar_expect_tx(&bars[MAX_TILES], (unsigned)(a.m * nt * 256));
+      mbar_expect_tx(&xbar[0], (unsigned)(a.m * nt * 256));
     }
     __syncwarp();
     if (!PDL && lane < a.m)
       bulk_g2s(Xsm + (size_t)lane * XS, a.lhs + (size_t)lane * a.p + k0, (unsigned)(nt * 256),
-               &bars[MAX_TILES]);
+               &xbar[0]);
     if (lane == 0) {
       for (int i = 0; i < nt; ++i) {
         mbar_expect_tx(&bars[i], TILE_BYTES);
@@ -154,7 +161,7 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if (warp == 0 && lane < a.m)
       bulk_g2s(Xsm + (size_t)lane * XS, a.lhs + (size_t)lane * a.p + k0, (unsigned)(nt * 256),
-               &bars[MAX_TILES]);
+               &xbar[0]);
   }
   // The packed-half dequantisation is exact for a scale whose half is exact (biased
   // exponent >= 2, finite) and only without zero points; one scale outside that range
@@ -163,8 +170,11 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
     const unsigned short bits = __half_as_ushort(s) & 0x7FFFu;
     fast = fast && !HAS_ZERO && bits >= 0x0800u && bits < 0x7C00u;
     const __half2 s2 = __half2half2(s);
-    const __half2 y2 = HAS_ZERO ? __half2half2(z) : __hmul2(s2, __float2half2_rn(0.5f));
-    return make_uint2(half2_as_u32(s2), half2_as_u32(y2));
+    if constexpr (HAS_ZERO) {
+      return make_uint2(half2_as_u32(s2), half2_as_u32(__half2half2(z)));
+    } else {
+      return half2_as_u32(s2);
+    }
   };
   bool fast = true;
 #pragma unroll
@@ -198,8 +208,16 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
   const bool x1_ok = MT > 1 && (g + 8) < a.m;
   const int row_a = rs * 16 + pg;  // tile row of MMA row g; row g+8 is 8 rows further
   const uint8_t* w_a = Wsm + row_a * 128;
-  const uint2* s_a = Ssm + (size_t)row_a * NG - g_lo;
-  const uint2* s_b = s_a + (size_t)8 * NG;
+  const Entry* s_a = Ssm + (size_t)row_a * NG - g_lo;
+  const Entry* s_b = s_a + (size_t)8 * NG;
+  // a table entry as (packed scale, packed scale/2 or packed zero point)
+  auto expand = [&](Entry e) {
+    if constexpr (HAS_ZERO) {
+      return e;
+    } else {
+      return make_uint2(e, half2_as_u32(__hmul2(u32_as_half2(e), __float2half2_rn(0.5f))));
+    }
+  };
   const int kbase = k0 + t * 16;
 
   using P = Piece<MT, HAS_ZERO>;
@@ -212,8 +230,8 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
     pc.qb = *reinterpret_cast<const uint4*>(tile + 8 * 128);
     pc.xoff = ti * 256 + j * 32;
     const int grp = (kbase + ti * 128 + h * 64) >> bs_shift;
-    pc.sa = s_a[grp];
-    pc.sb = s_b[grp];
+    pc.sa = expand(s_a[grp]);
+    pc.sb = expand(s_b[grp]);
   };
   auto compute_piece = [&](const P& pc, auto fast_tag) {
     constexpr bool FAST = decltype(fast_tag)::value;
@@ -260,7 +278,7 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
     }
   };
 
-  bool ok = mbar_wait(&bars[MAX_TILES], 0);
+  bool ok = mbar_wait(&xbar[0], 0);
   ADR_TRACE(3);
   auto run_tiles = [&](auto fast_tag) {
     P cur, nxt;
@@ -401,12 +419,11 @@ bool plan_stream(const adr_ctx* ctx, const U8Args& a, int force_split, int force
       if (maxt > MAX_TILES) continue;
       const int xs = 2 * maxt * 128 + 16;
       const int ngmax = (maxt * 128) / a.block_size + 2;  // groups a slice can touch
-      const size_t tables = (size_t)R * ngmax * 8 + 16;
+      const size_t tables = (size_t)R * ngmax * (a.zeros ? 8 : 4) + (size_t)(maxt + 1) * 8;
       // the reduction buffers reuse the staging area once the copies are consumed
       const int nw = 8;
       const size_t alias = (size_t)(nw * 16 * 17 + R * 16) * 4;
-      const size_t smem = 1024 /*alignment slack*/ + BAR_BYTES +
-                          std::max((size_t)maxt * R * 128 + (size_t)a.m * xs + tables, alias);
+      const size_t smem = std::max((size_t)maxt * R * 128 + (size_t)a.m * xs + tables, alias);
       if (smem > 200 * 1024) continue;
       const double ctas = (double)((a.n + R - 1) / R) * S;
       const int per_sm = (int)std::min<size_t>(8, (227 * 1024) / (smem + 1024));
