@@ -1,0 +1,146 @@
+"""CLIP ViT image-encoder harness: the second caller of the matmul path.
+
+Restates the call sequence of the reference's `ClipAttention::forward`,
+`ClipMLP::forward` and `ClipVisionTransformer` (adrastea_models/src/clip.rs:342-486,
+754-817) around this library's fp16 GEMM: q/k/v projections with `BetaBias(0.0)`,
+scores `q.k^T` with `Scale(1/sqrt(hd))`, probabilities . v, the output projection and
+fc2 with `BetaBias(1.0)` (the residual), fc1 with `QuickGeluBias`.  Layer norms, the
+softmax, the patch embedding and the head re-layout between the projections and the
+batched attention products are harness glue done with PyTorch ops; they are not part
+of this repository's kernel contract.
+
+The reference encodes one image at a time ([257, 1024]); BASELINE's config 3 asks for a
+batch of 64, which this harness runs as [B*257, 1024] linears and B*heads batched
+attention products.  The score tensor is allocated with a row pitch that is a multiple
+of 8 elements (264 for 257 tokens) so that both attention products take the tensor-core
+path (a 514-byte pitch cannot be described to TMA).  Weights are seeded N(0, 0.02^2).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .kernels import GpuKernels, MatmulOptions, MatmulStore
+from .tensor import TensorLayout, TensorView
+
+
+@dataclass(frozen=True)
+class ClipVisionShape:
+    hidden: int = 1024
+    heads: int = 16
+    mlp: int = 4096
+    layers: int = 24
+    patch: int = 14
+    image: int = 224
+    eps: float = 1e-5
+
+    @property
+    def tokens(self) -> int:
+        return (self.image // self.patch) ** 2 + 1
+
+
+VIT_L_14 = ClipVisionShape()
+
+
+class _Linear:
+    def __init__(self, n, k, gen, device):
+        self.w = (torch.randn((n, k), device=device, generator=gen) * 0.02).half()
+        self.b = (torch.randn((n,), device=device, generator=gen) * 0.02).half()
+
+
+class ClipVisionU:
+    def __init__(self, kernels: GpuKernels, shape: ClipVisionShape = VIT_L_14, batch: int = 64,
+                 seed: int = 0, device="cuda"):
+        self.k, self.shape, self.B = kernels, shape, batch
+        self.device = torch.device(device)
+        gen = torch.Generator(device=self.device).manual_seed(4242 + seed)
+        d, f = shape.hidden, shape.mlp
+        L = lambda n, k: _Linear(n, k, gen, self.device)
+        self.blocks = [dict(q=L(d, d), k=L(d, d), v=L(d, d), o=L(d, d), fc1=L(f, d), fc2=L(d, f))
+                       for _ in range(shape.layers)]
+        self.patch_w = (torch.randn((d, 3, shape.patch, shape.patch), device=self.device, generator=gen) * 0.02).half()
+        self.cls = (torch.randn((d,), device=self.device, generator=gen) * 0.02).half()
+        self.pos = (torch.randn((shape.tokens, d), device=self.device, generator=gen) * 0.02).half()
+        S, H, hd, B = shape.tokens, shape.heads, shape.hidden // shape.heads, batch
+        self.Sp = (S + 7) // 8 * 8
+        f16 = dict(dtype=torch.float16, device=self.device)
+        z = lambda *s: torch.zeros(s, **f16)
+        self.h, self.q, self.kx, self.v, self.att = (z(B * S, d) for _ in range(5))
+        self.qh, self.kh, self.vh, self.oh = (z(B * H, S, hd) for _ in range(4))
+        self.scores = z(B * H, S, self.Sp)
+        self.mid = z(B * S, f)
+
+    def _linear(self, out, x, lin, store):
+        self.k.matmul_f16(TensorView.of(out), TensorView.of(x), TensorView.of(lin.w).permute([1, 0]),
+                          MatmulOptions.new().store(store))
+
+    def _ln(self, x):
+        return torch.nn.functional.layer_norm(x, (x.shape[-1],), eps=self.shape.eps)  # fp32 statistics inside
+
+    def forward(self, pixels: torch.Tensor) -> torch.Tensor:
+        """pixels: [B, 3, image, image] fp16 -> final hidden state [B, tokens, hidden]."""
+        sh, B = self.shape, self.B
+        S, H, d = sh.tokens, sh.heads, sh.hidden
+        hd = d // H
+        emb = torch.nn.functional.conv2d(pixels, self.patch_w, stride=sh.patch)  # clip.rs:767-779
+        emb = emb.flatten(2).transpose(1, 2)                                      # [B, 256, d]
+        x = torch.cat([self.cls.expand(B, 1, d), emb], dim=1) + self.pos
+        self.h.copy_(self._ln(x).reshape(B * S, d))                               # pre-layernorm
+        heads = lambda t: t.view(B, S, H, hd).permute(0, 2, 1, 3).reshape(B * H, S, hd)
+        for blk in self.blocks:
+            n1 = self._ln(self.h)
+            self._linear(self.q, n1, blk["q"], MatmulStore.BetaBias(0.0, TensorView.of(blk["q"].b)))
+            self._linear(self.kx, n1, blk["k"], MatmulStore.BetaBias(0.0, TensorView.of(blk["k"].b)))
+            self._linear(self.v, n1, blk["v"], MatmulStore.BetaBias(0.0, TensorView.of(blk["v"].b)))
+            self.qh.copy_(heads(self.q))
+            self.kh.copy_(heads(self.kx))
+            self.vh.copy_(heads(self.v))
+            sv = TensorView(self.scores, TensorLayout.new((B * H, S, S), (S * self.Sp, self.Sp, 1)))
+            self.k.matmul_f16(sv, TensorView.of(self.qh), TensorView.of(self.kh).permute([0, 2, 1]),
+                              MatmulOptions.new().store(MatmulStore.Scale(1.0 / math.sqrt(hd))))
+            self.scores[:, :, :S] = torch.softmax(self.scores[:, :, :S], dim=-1)  # fp32 inside
+            self.k.matmul_f16(TensorView.of(self.oh), sv, TensorView.of(self.vh))
+            self.att.copy_(self.oh.view(B, H, S, hd).permute(0, 2, 1, 3).reshape(B * S, d))
+            self._linear(self.h, self.att, blk["o"], MatmulStore.BetaBias(1.0, TensorView.of(blk["o"].b)))
+            n2 = self._ln(self.h)
+            self._linear(self.mid, n2, blk["fc1"], MatmulStore.QuickGeluBias(TensorView.of(blk["fc1"].b)))
+            self._linear(self.h, self.mid, blk["fc2"], MatmulStore.BetaBias(1.0, TensorView.of(blk["fc2"].b)))
+        return self.h.view(B, S, d)
+
+    def flops(self) -> float:
+        sh, B = self.shape, self.B
+        S, d, f, H = sh.tokens, sh.hidden, sh.mlp, sh.heads
+        per_layer = 2 * B * S * (4 * d * d + 2 * d * f) + 4 * B * H * S * S * (d // H)
+        return float(sh.layers * per_layer)
+
+
+def main():
+    """python -m adrastea_b200.clip [--batch 64]: one JSON line with the forward time."""
+    import argparse
+    import json
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=64)
+    ap.add_argument("--iters", type=int, default=5)
+    args = ap.parse_args()
+    kern = GpuKernels(0)
+    model = ClipVisionU(kern, VIT_L_14, args.batch)
+    px = torch.randn((args.batch, 3, 224, 224), device="cuda").half()
+    model.forward(px)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.iters):
+        model.forward(px)
+    e1.record()
+    torch.cuda.synchronize()
+    kern.device_status()
+    ms = e0.elapsed_time(e1) / args.iters
+    print(json.dumps({"model": "CLIP ViT-L/14 image encoder, fp16", "batch": args.batch,
+                      "ms_per_forward": ms, "images_per_s": args.batch / (ms * 1e-3),
+                      "matmul_tflops": model.flops() / (ms * 1e-3) / 1e12}))
+
+
+if __name__ == "__main__":
+    main()

@@ -4,15 +4,17 @@
 // 493-513) and the WMMA kernels (matmul_nt_wmma_128x64x64.cu:8-78,
 // matmul_nt_wmma_16x128x256.cu:8-68) for views TMA can describe.
 //
-// Tiles of 128 x BN outputs.  Six warps per CTA, specialised:
+// Tiles of 128 x BN outputs.  Warps are specialised:
 //   warp 0    producer: one thread issues TMA loads of the A (128 x 64) and B (BN x 64)
 //             k-blocks into a ring of 128-byte-swizzled shared-memory stages
 //   warp 1    owns tensor memory (alloc/dealloc); one thread issues tcgen05.mma
 //             (M = 128, N = BN, K = 16 per instruction, fp32 accumulators in TMEM) and
 //             frees each stage with tcgen05.commit
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (warp w reads TMEM lanes
+//   warps 2.. epilogue: tcgen05.ld the accumulator (warp w reads TMEM lanes
 //             32*(w%4)..+31 = tile rows), apply the reference's fused store op, mask
-//             and scale, write fp16 to the (arbitrarily strided) output
+//             and scale, write fp16 to the (arbitrarily strided) output; eight warps in
+//             the persistent kernel (two per lane quarter, alternating 32-column chunks),
+//             four in the split-k kernel
 // Two kernels share these roles:
 //   gemm_f16_tc_kernel         persistent: one CTA per SM walks a list of tiles; two
 //                              accumulator buffers in TMEM let the epilogue of one tile
@@ -37,7 +39,8 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 64;  // fp16 elements: one 128-byte swizzle row
-constexpr int TC_THREADS = 192;
+constexpr int TC_THREADS = 192;   // split-k kernel: producer, MMA, four epilogue warps
+constexpr int TCP_THREADS = 320;  // persistent kernel: producer, MMA, eight epilogue warps
 constexpr size_t SMEM_BUDGET = 200 * 1024;
 
 template <int BN>
@@ -69,58 +72,109 @@ struct TcParams {
   unsigned int* status;
 };
 
-// One 32-column chunk of one accumulator row: apply the fused op and store.
+__device__ __forceinline__ __half half_lo(uint32_t w) { return __ushort_as_half((unsigned short)(w & 0xFFFFu)); }
+__device__ __forceinline__ __half half_hi(uint32_t w) { return __ushort_as_half((unsigned short)(w >> 16)); }
+
+// The epilogue of one accumulator tile for one warp: the warp's 32 TMEM lanes are 32 tile
+// rows (one per thread), and it walks the 32-column chunks chunk0, chunk0 + 2, ...  The
+// loads of the old output and of the bias are in flight while tcgen05.ld completes.
+// QuickGelu uses the fast exponential and reciprocal (the tensor-core path is held to a
+// tolerance, not to the bits of the sequential reference sum).
 template <int STORE>
-__device__ __forceinline__ void store_chunk(const TcParams& p, const uint32_t (&acc)[32],
-                                            __half* orow, int y, int x0, float pre, __half hscale) {
-  const bool causal = p.mask == ADR_MASK_CAUSAL;
-  const bool vec = p.s_ox == 1 && x0 + 32 <= p.n &&
-                   (reinterpret_cast<uintptr_t>(orow + x0) & 15u) == 0;
-  __align__(16) __half oldv[32];
-  if (store_reads_out(STORE)) {
-    if (vec) {
-      const uint4* src = reinterpret_cast<const uint4*>(orow + x0);
-#pragma unroll
-      for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(&oldv[q * 8]) = src[q];
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j)
-        oldv[j] = (x0 + j < p.n) ? orow[(int64_t)(x0 + j) * p.s_ox] : __float2half_rn(0.0f);
-    }
-  }
-  __align__(16) __half res[32];
-#pragma unroll
-  for (int j = 0; j < 32; ++j) {
-    const int x = x0 + j;
-    float bias = 0.0f;
-    if (store_uses_bias(STORE)) bias = (x < p.n) ? __half2float(p.bias[x]) : 0.0f;
-    const __half old = store_reads_out(STORE) ? oldv[j] : __float2half_rn(0.0f);
-    __half r = store_apply<STORE>(__uint_as_float(acc[j]) * pre, old, bias, p.beta, hscale);
-    if (causal && x > y) r = __ushort_as_half((unsigned short)0xFC00);  // -inf
-    res[j] = r;
-  }
-  if (vec) {
-    uint4* dst = reinterpret_cast<uint4*>(orow + x0);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) dst[q] = *reinterpret_cast<const uint4*>(&res[q * 8]);
+__device__ __forceinline__ __half epilogue_op(const TcParams& p, float a, __half old, float bias,
+                                              __half hscale) {
+  if constexpr (STORE == ADR_STORE_QUICK_GELU_BIAS) {
+    const float t = __half2float(__float2half_rn(a)) + bias;
+    return __float2half_rn(__fdividef(t, 1.0f + __expf(-1.702f * t)));
   } else {
-#pragma unroll
-    for (int j = 0; j < 32; ++j)
-      if (x0 + j < p.n) orow[(int64_t)(x0 + j) * p.s_ox] = res[j];
+    return store_apply<STORE>(a, old, bias, p.beta, hscale);
   }
 }
 
-__device__ __forceinline__ void store_chunk_rt(const TcParams& p, const uint32_t (&acc)[32],
-                                               __half* orow, int y, int x0, float pre,
-                                               __half hscale) {
+template <int STORE, int BN>
+__device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_acc, __half* orow,
+                                              int y, int n0, int chunk0, float pre, __half hscale) {
+  const bool causal = p.mask == ADR_MASK_CAUSAL;
+  const bool row_ok = y < p.m;
+  // tcgen05.ld and its wait are warp-collective: every branch that contains one must be
+  // uniform across the warp, so the vector path is taken only when all live rows allow it
+  const bool lane_vec = p.s_ox == 1 && (reinterpret_cast<uintptr_t>(orow) & 15u) == 0 &&
+                        (!store_uses_bias(STORE) || (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0);
+  const bool row_vec = __all_sync(0xffffffffu, lane_vec || !row_ok);
+  const __half ninf = __ushort_as_half((unsigned short)0xFC00);
+#pragma unroll 1
+  for (int c = chunk0; c < BN / 32; c += 2) {
+    const int x0 = n0 + c * 32;
+    if (x0 >= p.n) break;  // uniform across the warp
+    uint32_t acc[32];
+    __syncwarp();
+    tmem_ld_32x32(tmem_acc + (uint32_t)(c * 32), acc);
+    if (row_vec && x0 + 32 <= p.n) {
+      // 64 contiguous, aligned bytes per row: vector loads in flight under the TMEM load
+      uint4 oldw[4], biasw[4];
+      if (row_ok) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if (store_reads_out(STORE)) oldw[q] = reinterpret_cast<const uint4*>(orow + x0)[q];
+          if (store_uses_bias(STORE)) biasw[q] = reinterpret_cast<const uint4*>(p.bias + x0)[q];
+        }
+      }
+      __syncwarp();
+      tmem_ld_wait();
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        if (!row_ok) break;
+        const uint32_t ow[4] = {oldw[q].x, oldw[q].y, oldw[q].z, oldw[q].w};
+        const uint32_t bw[4] = {biasw[q].x, biasw[q].y, biasw[q].z, biasw[q].w};
+        uint32_t rw[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = q * 8 + e * 2;
+          const float a0 = __uint_as_float(acc[j]) * pre, a1 = __uint_as_float(acc[j + 1]) * pre;
+          const float b0 = store_uses_bias(STORE) ? __half2float(half_lo(bw[e])) : 0.0f;
+          const float b1 = store_uses_bias(STORE) ? __half2float(half_hi(bw[e])) : 0.0f;
+          const __half o0 = store_reads_out(STORE) ? half_lo(ow[e]) : __float2half_rn(0.0f);
+          const __half o1 = store_reads_out(STORE) ? half_hi(ow[e]) : __float2half_rn(0.0f);
+          __half r0 = epilogue_op<STORE>(p, a0, o0, b0, hscale);
+          __half r1 = epilogue_op<STORE>(p, a1, o1, b1, hscale);
+          if (causal && x0 + j > y) r0 = ninf;
+          if (causal && x0 + j + 1 > y) r1 = ninf;
+          rw[e] = (uint32_t)__half_as_ushort(r0) | ((uint32_t)__half_as_ushort(r1) << 16);
+        }
+        reinterpret_cast<uint4*>(orow + x0)[q] = make_uint4(rw[0], rw[1], rw[2], rw[3]);
+      }
+    } else {
+      // strided, unaligned or ragged rows: one element at a time
+      __syncwarp();
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const int x = x0 + j;
+        if (row_ok && x < p.n) {
+          __half* dst = orow + (int64_t)x * p.s_ox;
+          const float bias = store_uses_bias(STORE) ? __half2float(p.bias[x]) : 0.0f;
+          const __half old = store_reads_out(STORE) ? *dst : __float2half_rn(0.0f);
+          __half r = epilogue_op<STORE>(p, __uint_as_float(acc[j]) * pre, old, bias, hscale);
+          if (causal && x > y) r = ninf;
+          *dst = r;
+        }
+      }
+    }
+  }
+}
+
+template <int BN>
+__device__ __forceinline__ void epilogue_tile_rt(const TcParams& p, uint32_t tmem_acc, __half* orow,
+                                                 int y, int n0, int chunk0, float pre,
+                                                 __half hscale) {
   switch (p.store) {
-    case ADR_STORE_SCALE: store_chunk<ADR_STORE_SCALE>(p, acc, orow, y, x0, pre, hscale); break;
-    case ADR_STORE_ADD: store_chunk<ADR_STORE_ADD>(p, acc, orow, y, x0, pre, hscale); break;
-    case ADR_STORE_BETA_BIAS: store_chunk<ADR_STORE_BETA_BIAS>(p, acc, orow, y, x0, pre, hscale); break;
-    case ADR_STORE_BETA_GELU_BIAS: store_chunk<ADR_STORE_BETA_GELU_BIAS>(p, acc, orow, y, x0, pre, hscale); break;
-    case ADR_STORE_QUICK_GELU_BIAS: store_chunk<ADR_STORE_QUICK_GELU_BIAS>(p, acc, orow, y, x0, pre, hscale); break;
-    case STORE_NT_BETA: store_chunk<STORE_NT_BETA>(p, acc, orow, y, x0, pre, hscale); break;
-    default: store_chunk<ADR_STORE_IDENTITY>(p, acc, orow, y, x0, pre, hscale); break;
+    case ADR_STORE_SCALE: epilogue_tile<ADR_STORE_SCALE, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
+    case ADR_STORE_ADD: epilogue_tile<ADR_STORE_ADD, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
+    case ADR_STORE_BETA_BIAS: epilogue_tile<ADR_STORE_BETA_BIAS, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
+    case ADR_STORE_BETA_GELU_BIAS: epilogue_tile<ADR_STORE_BETA_GELU_BIAS, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
+    case ADR_STORE_QUICK_GELU_BIAS: epilogue_tile<ADR_STORE_QUICK_GELU_BIAS, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
+    case STORE_NT_BETA: epilogue_tile<STORE_NT_BETA, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
+    default: epilogue_tile<ADR_STORE_IDENTITY, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
   }
 }
 
@@ -173,7 +227,7 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int mt, int nt, int bn) {
 }
 
 template <int BN, bool B_MN>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TCP_THREADS, 1)
     gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_b, TcParams p) {
   using Cfg = TcCfg<BN>;
@@ -201,7 +255,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&acc_full[i], 1);
-      mbar_init(&acc_empty[i], 4);  // one arrival per epilogue warp
+      mbar_init(&acc_empty[i], 8);  // one arrival per epilogue warp
     }
     mbar_fence_init();
   }
@@ -253,7 +307,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
     }
   } else {
     // ---------------- epilogue: drains one buffer while the other is being filled ----------
+    // Warps 2-5 take the even 32-column chunks of the tile, warps 6-9 the odd ones.
     const int quarter = warp & 3;  // TMEM lanes a warp may read: 32 * (warp id % 4) ..
+    const int chunk0 = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const __half hscale = __float2half_rn(p.scale);
     // a load-side scale multiplies both operands (matmul.cu:62): s^2 on the product
@@ -268,16 +324,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
       tc_fence_after_sync();
       const int y = tc.m0 + row;
       __half* orow = p.out + (int64_t)tc.b * p.s_oz + (int64_t)y * p.s_oy;
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        const int x0 = tc.n0 + c * 32;
-        if (x0 >= p.n) break;  // uniform across the warp
-        uint32_t acc[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c * 32),
-                      acc);
-        tmem_ld_wait();
-        if (y < p.m) store_chunk_rt(p, acc, orow, y, x0, pre, hscale);
-      }
+      epilogue_tile_rt<BN>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN),
+                           orow, y, tc.n0, chunk0, pre, hscale);
       // this warp's reads of the buffer are complete: hand it back to the MMA warp
       tc_fence_before_sync();
       __syncwarp();
@@ -517,7 +565,7 @@ int launch_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, int S) {
     const long long tiles = (long long)nt * mt * a.batches;
     const long long sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
     const unsigned grid = (unsigned)std::min<long long>(tiles, sms);
-    kfn<<<grid, TC_THREADS, Cfg::SMEM, stream>>>(map_a, map_b, p);
+    kfn<<<grid, TCP_THREADS, Cfg::SMEM, stream>>>(map_a, map_b, p);
     return after_launch(ctx);
   }
   static bool configured_sk[64] = {};
