@@ -11,9 +11,10 @@ of this repository's kernel contract.
 
 The reference encodes one image at a time ([257, 1024]); BASELINE's config 3 asks for a
 batch of 64, which this harness runs as [B*257, 1024] linears and B*heads batched
-attention products.  The score tensor is allocated with a row pitch that is a multiple
-of 8 elements (264 for 257 tokens) so that both attention products take the tensor-core
-path (a 514-byte pitch cannot be described to TMA).  Weights are seeded N(0, 0.02^2).
+attention products.  Activations are kept token-major so that the per-head operands are
+strided views (no copies); the score tensor has a row pitch that is a multiple of 8
+elements (264 for 257 tokens) so that both attention products take the tensor-core path
+(a 514-byte pitch cannot be described to TMA).  Weights are seeded N(0, 0.02^2).
 """
 from __future__ import annotations
 
@@ -67,10 +68,19 @@ class ClipVisionU:
         self.Sp = (S + 7) // 8 * 8
         f16 = dict(dtype=torch.float16, device=self.device)
         z = lambda *s: torch.zeros(s, **f16)
-        self.h, self.q, self.kx, self.v, self.att = (z(B * S, d) for _ in range(5))
-        self.qh, self.kh, self.vh, self.oh = (z(B * H, S, hd) for _ in range(4))
-        self.scores = z(B * H, S, self.Sp)
-        self.mid = z(B * S, f)
+        # activations are token-major, [S*B, d] (row = token * B + image): the [B*H, S, hd]
+        # operand of the batched attention products is then a plain strided view
+        # (z = image*H + head -> stride hd, token -> stride B*d) and no re-layout is needed
+        self.h, self.q, self.kx, self.v, self.att = (z(S * B, d) for _ in range(5))
+        # raw scores keep -inf in the pad columns (the GEMM writes only the first S of each
+        # row), so a softmax over whole padded rows leaves exact zeros there
+        self.scores = torch.full((B * H, S, self.Sp), float("-inf"), **f16)
+        self.probs = z(B * H, S, self.Sp)
+        self.mid = z(S * B, f)
+        heads = TensorLayout.new((B * H, S, hd), (hd, B * d, 1))
+        self.qv, self.kv, self.vv, self.ov = (TensorView(t, heads) for t in (self.q, self.kx, self.v, self.att))
+        sl = TensorLayout.new((B * H, S, S), (S * self.Sp, self.Sp, 1))
+        self.sv, self.pv = TensorView(self.scores, sl), TensorView(self.probs, sl)
 
     def _linear(self, out, x, lin, store):
         self.k.matmul_f16(TensorView.of(out), TensorView.of(x), TensorView.of(lin.w).permute([1, 0]),
@@ -85,29 +95,23 @@ class ClipVisionU:
         S, H, d = sh.tokens, sh.heads, sh.hidden
         hd = d // H
         emb = torch.nn.functional.conv2d(pixels, self.patch_w, stride=sh.patch)  # clip.rs:767-779
-        emb = emb.flatten(2).transpose(1, 2)                                      # [B, 256, d]
-        x = torch.cat([self.cls.expand(B, 1, d), emb], dim=1) + self.pos
-        self.h.copy_(self._ln(x).reshape(B * S, d))                               # pre-layernorm
-        heads = lambda t: t.view(B, S, H, hd).permute(0, 2, 1, 3).reshape(B * H, S, hd)
+        emb = emb.flatten(2).permute(2, 0, 1)                                     # [256, B, d]
+        x = torch.cat([self.cls.expand(1, B, d), emb], dim=0) + self.pos[:, None, :]
+        self.h.copy_(self._ln(x).reshape(S * B, d))                               # pre-layernorm
         for blk in self.blocks:
             n1 = self._ln(self.h)
             self._linear(self.q, n1, blk["q"], MatmulStore.BetaBias(0.0, TensorView.of(blk["q"].b)))
             self._linear(self.kx, n1, blk["k"], MatmulStore.BetaBias(0.0, TensorView.of(blk["k"].b)))
             self._linear(self.v, n1, blk["v"], MatmulStore.BetaBias(0.0, TensorView.of(blk["v"].b)))
-            self.qh.copy_(heads(self.q))
-            self.kh.copy_(heads(self.kx))
-            self.vh.copy_(heads(self.v))
-            sv = TensorView(self.scores, TensorLayout.new((B * H, S, S), (S * self.Sp, self.Sp, 1)))
-            self.k.matmul_f16(sv, TensorView.of(self.qh), TensorView.of(self.kh).permute([0, 2, 1]),
+            self.k.matmul_f16(self.sv, self.qv, self.kv.permute([0, 2, 1]),
                               MatmulOptions.new().store(MatmulStore.Scale(1.0 / math.sqrt(hd))))
-            self.scores[:, :, :S] = torch.softmax(self.scores[:, :, :S], dim=-1)  # fp32 inside
-            self.k.matmul_f16(TensorView.of(self.oh), sv, TensorView.of(self.vh))
-            self.att.copy_(self.oh.view(B, H, S, hd).permute(0, 2, 1, 3).reshape(B * S, d))
+            torch.softmax(self.scores, dim=-1, out=self.probs)                    # fp32 inside
+            self.k.matmul_f16(self.ov, self.pv, self.vv)
             self._linear(self.h, self.att, blk["o"], MatmulStore.BetaBias(1.0, TensorView.of(blk["o"].b)))
             n2 = self._ln(self.h)
             self._linear(self.mid, n2, blk["fc1"], MatmulStore.QuickGeluBias(TensorView.of(blk["fc1"].b)))
             self._linear(self.h, self.mid, blk["fc2"], MatmulStore.BetaBias(1.0, TensorView.of(blk["fc2"].b)))
-        return self.h.view(B, S, d)
+        return self.h.view(S, B, d).transpose(0, 1)
 
     def flops(self) -> float:
         sh, B = self.shape, self.B
