@@ -6,6 +6,6 @@ Public surface (mirrors adrastea_models/src/kernels.rs and tensor.rs for this pa
 """
 from .tensor import TensorLayout, TensorView, TensorViewMut  # noqa: F401
 from .kernels import (  # noqa: F401
-    AdrError, GpuKernels, Kernel, MatmulLoad, MatmulLoadOp, MatmulMask, MatmulOptions,
+    AdrError, BinaryOp, GpuKernels, Kernel, MatmulLoad, MatmulLoadOp, MatmulMask, MatmulOptions,
     MatmulStore, MatmulStoreOp, MatmulTracer, lower_matmul,
 )

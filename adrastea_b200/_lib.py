@@ -34,6 +34,14 @@ SIGNATURES = {
     "adr_matmul_nt_f16": (_c_int, [_vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, C.c_float]),
     "adr_dequantize_absmax_uint8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),
     "adr_quantize_absmax_uint8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),
+    "adr_rms_norm": (_c_int, [_vp, _vp, _vp, _vp, _vp] + [_c_int] * 6 + [C.c_float]),
+    "adr_softmax_rows": (_c_int, [_vp, _vp, _vp, _vp] + [_c_int] * 4 + [C.c_float]),
+    "adr_rotary": (_c_int, [_vp, _vp, _vp, _vp] + [_c_int] * 8 + [C.c_float]),
+    "adr_elementwise_binary_2d_f16": (_c_int, [_vp, _vp, _vp, _vp, _vp] + [_c_int] * 5 + [C.c_uint32]),
+    "adr_decode_rope_append": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp] + [_c_int] * 7
+                               + [_vp, C.c_float]),
+    "adr_decode_attention": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp] + [_c_int] * 6
+                             + [_vp, C.c_float]),
     "adr_trace_enable": (_c_int, [_vp, _c_int]),
     "adr_trace_clear": (None, [_vp]),
     "adr_trace_dump": (C.c_size_t, [_vp, C.c_char_p, C.c_size_t]),

@@ -48,6 +48,12 @@ class MatmulMask(enum.IntEnum):
     Causal = 1
 
 
+class BinaryOp(enum.IntEnum):
+    """enum BinaryOp (kernels.rs:70-74, elementwise.cu:16-19)."""
+    Add = 1
+    SiluMul = 2
+
+
 class Kernel(enum.IntEnum):
     Auto = 0
     F16Simt = 1
@@ -327,6 +333,78 @@ class GpuKernels:
         assert q.shape == (rows, k) and q.dtype == torch.uint8 and inp.dtype == torch.float16
         rc = self._lib.adr_quantize_absmax_uint8(self._ctx, _stream_handle(stream), q.data_ptr(),
                                                  scales.data_ptr(), inp.data_ptr(), rows, k, bs)
+        self._check(rc)
+
+    # -- the kernels either side of the matmuls ------------------------------
+    def rms_norm(self, output: TensorView, input: TensorView, weight: TensorView, eps: float,
+                 stream=None):
+        """CommonKernels::rms_norm (kernels.rs:198-201, 680-706)."""
+        assert input.size(-1) == output.size(-1) and input.size(-2) == output.size(-2)
+        assert weight.stride(-1) == 1 and weight.size(-1) == output.size(-1)
+        rc = self._lib.adr_rms_norm(self._ctx, _stream_handle(stream), output.data_ptr(),
+                                    input.data_ptr(), weight.data_ptr(), output.size(-1),
+                                    output.size(-2), output.stride(-1), output.stride(-2),
+                                    input.stride(-1), input.stride(-2), eps)
+        self._check(rc)
+
+    def rotary_inplace(self, inout: TensorView, n_heads: int, pos_offset: int, theta: float,
+                       stream=None):
+        """CommonKernels::rotary_inplace (kernels.rs:203-205, 722-751)."""
+        rc = self._lib.adr_rotary(self._ctx, _stream_handle(stream), inout.data_ptr(),
+                                  inout.data_ptr(), inout.size(-1), inout.size(-2),
+                                  inout.stride(-1), inout.stride(-2), inout.stride(-1),
+                                  inout.stride(-2), n_heads, pos_offset, theta)
+        self._check(rc)
+
+    def softmax_rows_inplace(self, output: TensorView, temperature: float = 1.0, stream=None):
+        """CommonKernels::softmax_rows_inplace (kernels.rs:214-216, 892-915); rows may be
+        padded (stride(-2) >= size(-1)), matrices must follow one another."""
+        nd = len(output.layout.dims)
+        heads = output.size(-3) if nd > 2 else 1
+        h, w, pitch = output.size(-2), output.size(-1), output.stride(-2)
+        assert output.stride(-1) == 1 and (nd <= 2 or output.stride(-3) == h * pitch)
+        rc = self._lib.adr_softmax_rows(self._ctx, _stream_handle(stream), output.data_ptr(),
+                                        output.data_ptr(), heads, h, w, pitch, temperature)
+        self._check(rc)
+
+    def elementwise_binary_2d_f16_inplace(self, inout_left: TensorView, right: TensorView,
+                                          op: "BinaryOp", stream=None):
+        """CommonKernels::elementwise_binary_2d_f16_inplace (kernels.rs:191-193, 633-650)."""
+        assert inout_left.stride(-1) == 1 and right.stride(-1) == 1
+        assert inout_left.size(-1) == right.size(-1) and inout_left.size(-2) == right.size(-2)
+        rc = self._lib.adr_elementwise_binary_2d_f16(
+            self._ctx, _stream_handle(stream), inout_left.data_ptr(), inout_left.data_ptr(),
+            right.data_ptr(), inout_left.size(-2), inout_left.size(-1), inout_left.stride(-2),
+            inout_left.stride(-2), right.stride(-2), int(op))
+        self._check(rc)
+
+    def decode_rope_append(self, q: TensorView, k: TensorView, v: TensorView,
+                           k_cache: torch.Tensor, v_cache: torch.Tensor, n_heads: int,
+                           pos_dev: torch.Tensor, theta: float, stream=None):
+        """No reference counterpart (the reference keeps no cache): q[b] rotated in place,
+        k[b] rotated into k_cache[b, pos], v[b] copied into v_cache[b, pos]; caches
+        [B, S, n_heads*head_dim], pos_dev an int32 device scalar."""
+        B, width = q.size(-2), q.size(-1)
+        assert k_cache.shape == v_cache.shape and k_cache.shape[0] == B and k_cache.shape[2] == width
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and pos_dev.dtype == torch.int32
+        rc = self._lib.adr_decode_rope_append(
+            self._ctx, _stream_handle(stream), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+            k_cache.data_ptr(), v_cache.data_ptr(), B, n_heads, width // n_heads, k_cache.shape[1],
+            q.stride(-2), k.stride(-2), v.stride(-2), pos_dev.data_ptr(), theta)
+        self._check(rc)
+
+    def decode_attention(self, out: TensorView, q: TensorView, k_cache: torch.Tensor,
+                         v_cache: torch.Tensor, n_heads: int, pos_dev: torch.Tensor, scale: float,
+                         stream=None):
+        """No reference counterpart: one new token per sequence against the cache, with the
+        rounding points of matmul(Scale) -> softmax_rows -> matmul (llama.rs:538-554)."""
+        B, width = q.size(-2), q.size(-1)
+        assert k_cache.shape == v_cache.shape and k_cache.shape[0] == B and k_cache.shape[2] == width
+        assert k_cache.is_contiguous() and v_cache.is_contiguous() and pos_dev.dtype == torch.int32
+        rc = self._lib.adr_decode_attention(
+            self._ctx, _stream_handle(stream), out.data_ptr(), q.data_ptr(), k_cache.data_ptr(),
+            v_cache.data_ptr(), B, n_heads, width // n_heads, k_cache.shape[1], q.stride(-2),
+            out.stride(-2), pos_dev.data_ptr(), scale)
         self._check(rc)
 
     # -- library-side trace (kernel family per distinct call) -------------

@@ -57,6 +57,8 @@ enum {
   ADR_STORE_QUICK_GELU_BIAS = 6
 };
 enum { ADR_MASK_NONE = 0, ADR_MASK_CAUSAL = 1 };
+/* enum BinaryOp, elementwise.cu:16-19 */
+enum { ADR_BINARY_ADD = 1, ADR_BINARY_SILU_MUL = 2 };
 
 /* Kernel families the dispatcher can pick; see adr_force_kernel / adr_last_kernel. */
 enum {
@@ -178,6 +180,80 @@ int adr_dequantize_absmax_uint8(adr_ctx* ctx, adr_stream stream, void* out, cons
  */
 int adr_quantize_absmax_uint8(adr_ctx* ctx, adr_stream stream, uint8_t* q, void* scales,
                               const void* in, int rows, int k, int block_size);
+
+/* ------------------------------------------------------------------------
+ * The kernels either side of the matmuls in a decoder layer.  The first four
+ * restate reference kernels with the same order of floating-point operations
+ * (the bits of those kernels compiled for this GPU); parameters are in the
+ * reference kernels' order, strides in elements.
+ * ------------------------------------------------------------------------ */
+
+/*
+ * Replaces kernel rms_norm (normalize.cu:7-58; host side kernels.rs:680-706):
+ * out[r,i] = weights[i] *h fp16(in[r,i] * rsqrt(sum_i in[r,i]^2 / length_x + eps)).
+ * One difference: the reference addresses the output columns with stride_ix
+ * (normalize.cu:56); here stride_ox is used (identical whenever the two are
+ * equal, as at every call site of the reference).
+ */
+int adr_rms_norm(adr_ctx* ctx, adr_stream stream, void* out, const void* in, const void* weights,
+                 int length_x, int length_y, int stride_ox, int stride_oy, int stride_ix,
+                 int stride_iy, float eps);
+
+/*
+ * Replaces kernel softmax_rows (normalize.cu:150-220; kernels.rs:892-915):
+ * `heads` matrices of h rows, softmax over the first w elements of every row,
+ * out = fp16(expf(x/temperature - max) / sum).  `pitch` is the distance between
+ * rows in elements; the reference kernel is the case pitch == w.  In place
+ * (out == in) is allowed.
+ */
+int adr_softmax_rows(adr_ctx* ctx, adr_stream stream, void* out, const void* in, int heads, int h,
+                     int w, int pitch, float temperature);
+
+/*
+ * Replaces kernel rotary (rotary.cu:4-29; kernels.rs:722-751): the pairs
+ * (c, c+1) of every head of row r are rotated by the angle
+ * (pos_offset + r) / powf(theta, (c % head_dim) / head_dim), head_dim =
+ * length_x / n_heads.  In place (out == in) is allowed.
+ */
+int adr_rotary(adr_ctx* ctx, adr_stream stream, void* out, const void* in, int length_x,
+               int length_y, int stride_ox, int stride_oy, int stride_ix, int stride_iy, int n_heads,
+               int pos_offset, float theta);
+
+/*
+ * Replaces kernel elementwise_binary_2d_f16 (elementwise.cu:16-33, 118-160;
+ * kernels.rs:633-650) for rows of contiguous columns `stride_*` elements apart:
+ * ADR_BINARY_ADD: left +h right; ADR_BINARY_SILU_MUL:
+ * fp16(float(left) / (1 + expf(-left)) * float(right)).  out may be left.
+ */
+int adr_elementwise_binary_2d_f16(adr_ctx* ctx, adr_stream stream, void* out, const void* left,
+                                  const void* right, int rows, int cols, int stride_o, int stride_l,
+                                  int stride_r, uint32_t op);
+
+/*
+ * No counterpart in the reference, which keeps no key/value cache and re-runs
+ * the whole prefix for every token (llama.rs:426-427).  Caches are
+ * [batch, max_seq, n_heads*head_dim] fp16; *pos_dev (device memory, so that a
+ * captured step can be replayed) is the position of the new token.
+ *
+ * adr_decode_rope_append: q[b,:] rotated in place, k[b,:] rotated into
+ * k_cache[b, pos, :], v[b,:] copied into v_cache[b, pos, :] (formula of
+ * adr_rotary with the angle taken at `pos` for every row).  A position outside
+ * [0, max_seq) writes nothing.
+ *
+ * adr_decode_attention: for every (sequence, head), over positions 0..pos:
+ * score = fp16(q.k) *h fp16(scale), softmax in fp32, probabilities rounded to
+ * fp16, out = fp16(sum_t p_t * v_t) - the rounding points of the reference's
+ * matmul(Scale) -> softmax_rows -> matmul chain (llama.rs:538-554).
+ * head_dim % 8 == 0, head_dim <= 256, max_seq % 8 == 0.
+ */
+int adr_decode_rope_append(adr_ctx* ctx, adr_stream stream, void* q, const void* k, const void* v,
+                           void* k_cache, void* v_cache, int batch, int n_heads, int head_dim,
+                           int max_seq, int stride_q, int stride_k, int stride_v,
+                           const int32_t* pos_dev, float theta);
+int adr_decode_attention(adr_ctx* ctx, adr_stream stream, void* out, const void* q,
+                         const void* k_cache, const void* v_cache, int batch, int n_heads,
+                         int head_dim, int max_seq, int stride_q, int stride_o,
+                         const int32_t* pos_dev, float scale);
 
 /*
  * Replaces MatmulTracer (kernels.rs:231-248, 306-333).  When enabled, every

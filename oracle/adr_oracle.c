@@ -490,3 +490,154 @@ int orc_num_threads(void) {
   return 1;
 #endif
 }
+
+/* ------------------------------------------------------------------------ */
+/* The kernels either side of the matmuls (row ops).  The reductions follow  */
+/* the reference's order: thread `tid` of 256 sums elements tid, tid+256, .. */
+/* in that order, lanes combine by an xor butterfly (16, 8, 4, 2, 1), the    */
+/* eight warp results by a second butterfly (4, 2, 1).  Where the device     */
+/* uses approximate intrinsics (rsqrt, expf, powf, sinf, cosf) this file     */
+/* uses libm, so agreement with a GPU is to a unit in the last place of the  */
+/* fp16 result, not to the bit.                                              */
+/* ------------------------------------------------------------------------ */
+static float butterfly_256(float part[256], int is_max) {
+  float warp[8];
+  for (int w = 0; w < 8; ++w) {
+    float v[32];
+    for (int l = 0; l < 32; ++l) v[l] = part[w * 32 + l];
+    for (int off = 16; off > 0; off >>= 1) {
+      float nv[32];
+      for (int l = 0; l < 32; ++l)
+        nv[l] = is_max ? fmaxf(v[l], v[l ^ off]) : v[l] + v[l ^ off];
+      memcpy(v, nv, sizeof v);
+    }
+    warp[w] = v[0];
+  }
+  for (int off = 4; off > 0; off >>= 1) {
+    float nv[8];
+    for (int l = 0; l < 8; ++l)
+      nv[l] = is_max ? fmaxf(warp[l], warp[l ^ off]) : warp[l] + warp[l ^ off];
+    memcpy(warp, nv, sizeof warp);
+  }
+  return warp[0];
+}
+
+/* normalize.cu:7-58 (output columns addressed with stride_ox; see the header of the
+ * library for the one difference from normalize.cu:56) */
+void orc_rms_norm(h16* out, const h16* in, const h16* w, int lx, int ly, int s_ox, int s_oy,
+                  int s_ix, int s_iy, float eps) {
+  for (int r = 0; r < ly; ++r) {
+    const h16* irow = in + (ptrdiff_t)r * s_iy;
+    h16* orow = out + (ptrdiff_t)r * s_oy;
+    float part[256];
+    for (int t = 0; t < 256; ++t) {
+      float s = 0.0f;
+      for (int i = t; i < lx; i += 256) {
+        float v = h2f(irow[(ptrdiff_t)i * s_ix]);
+        s = fmaf(v, v, s); /* nvcc contracts sum += v * v */
+      }
+      part[t] = s;
+    }
+    float total = butterfly_256(part, 0);
+    float rms_inv = 1.0f / sqrtf((total / (float)lx) + eps);
+    for (int i = 0; i < lx; ++i) {
+      float v = h2f(irow[(ptrdiff_t)i * s_ix]);
+      orow[(ptrdiff_t)i * s_ox] = hmul(w[i], f2h(v * rms_inv));
+    }
+  }
+}
+
+/* normalize.cu:150-220, rows `pitch` elements apart (pitch == w in the reference) */
+void orc_softmax_rows(h16* out, const h16* in, int heads, int h, int w, int pitch, float temp) {
+  for (int hd = 0; hd < heads; ++hd)
+    for (int r = 0; r < h; ++r) {
+      const h16* irow = in + ((ptrdiff_t)hd * h + r) * pitch;
+      h16* orow = out + ((ptrdiff_t)hd * h + r) * pitch;
+      float part[256];
+      for (int t = 0; t < 256; ++t) {
+        float m = -INFINITY;
+        for (int i = t; i < w; i += 256) m = fmaxf(m, h2f(irow[i]) / temp);
+        part[t] = m;
+      }
+      float mx = butterfly_256(part, 1);
+      for (int t = 0; t < 256; ++t) {
+        float s = 0.0f;
+        for (int i = t; i < w; i += 256) s += expf(h2f(irow[i]) / temp - mx);
+        part[t] = s;
+      }
+      float sum = butterfly_256(part, 0);
+      for (int i = 0; i < w; ++i) orow[i] = f2h(expf(h2f(irow[i]) / temp - mx) / sum);
+    }
+}
+
+/* rotary.cu:4-29; `same_pos` != 0 takes the angle at pos_offset for every row (the
+ * decode form, one new token per sequence) instead of pos_offset + row */
+void orc_rotary(h16* out, const h16* in, int lx, int ly, int s_ox, int s_oy, int s_ix, int s_iy,
+                int n_heads, int pos_offset, float theta, int same_pos) {
+  int head_dim = lx / n_heads;
+  for (int r = 0; r < ly; ++r)
+    for (int c = 0; c < lx; c += 2) {
+      int head_c = c % head_dim;
+      int pos = same_pos ? pos_offset : pos_offset + r;
+      float angle = (float)pos / powf(theta, (float)head_c / (float)head_dim);
+      float re = h2f(in[(ptrdiff_t)r * s_iy + (ptrdiff_t)c * s_ix]);
+      float im = h2f(in[(ptrdiff_t)r * s_iy + (ptrdiff_t)(c + 1) * s_ix]);
+      float a_cos = cosf(angle), a_sin = sinf(angle);
+      /* nvcc contracts one product of each line into an fma; which one cannot be told from
+       * the source, one more reason why agreement with the GPU is to one unit, not the bit */
+      out[(ptrdiff_t)r * s_oy + (ptrdiff_t)c * s_ox] = f2h(fmaf(re, a_cos, -(im * a_sin)));
+      out[(ptrdiff_t)r * s_oy + (ptrdiff_t)(c + 1) * s_ox] = f2h(fmaf(re, a_sin, im * a_cos));
+    }
+}
+
+/* elementwise.cu:16-33: op 1 = Add (left +h right), 2 = SiluMul */
+int orc_elementwise_binary_2d_f16(h16* out, const h16* left, const h16* right, int rows, int cols,
+                                  int s_o, int s_l, int s_r, int op) {
+  if (op != 1 && op != 2) return ORC_ERR_UNSUPPORTED;
+  for (int r = 0; r < rows; ++r)
+    for (int c = 0; c < cols; ++c) {
+      h16 l = left[(ptrdiff_t)r * s_l + c], rr = right[(ptrdiff_t)r * s_r + c];
+      if (op == 1) {
+        out[(ptrdiff_t)r * s_o + c] = hadd(l, rr);
+      } else {
+        float lf = h2f(l);
+        out[(ptrdiff_t)r * s_o + c] = f2h(lf / (1.0f + expf(-lf)) * h2f(rr));
+      }
+    }
+  return ORC_OK;
+}
+
+/* One new token per sequence against caches [batch, max_seq, n_heads*head_dim]: the chain
+ * matmul(Scale) -> softmax_rows -> matmul of llama.rs:538-554 over positions 0..pos, with
+ * exact products and wide accumulation in the two contractions. */
+void orc_decode_attention(h16* out, const h16* q, const h16* k_cache, const h16* v_cache, int batch,
+                          int n_heads, int head_dim, int max_seq, int s_q, int s_o, int pos,
+                          float scale) {
+  int width = n_heads * head_dim;
+  int T = pos + 1 < max_seq ? pos + 1 : max_seq;
+  h16 hscale = f2h(scale);
+  float* sc = (float*)malloc(sizeof(float) * (size_t)(T > 0 ? T : 1));
+  for (int b = 0; b < batch; ++b)
+    for (int h = 0; h < n_heads; ++h) {
+      const h16* qh = q + (ptrdiff_t)b * s_q + (ptrdiff_t)h * head_dim;
+      const h16* kb = k_cache + (ptrdiff_t)b * max_seq * width + (ptrdiff_t)h * head_dim;
+      const h16* vb = v_cache + (ptrdiff_t)b * max_seq * width + (ptrdiff_t)h * head_dim;
+      float mx = -INFINITY;
+      for (int t = 0; t < T; ++t) {
+        double d = 0.0;
+        for (int j = 0; j < head_dim; ++j)
+          d += (double)h2f(qh[j]) * (double)h2f(kb[(ptrdiff_t)t * width + j]);
+        sc[t] = h2f(hmul(d2h(d), hscale));
+        mx = fmaxf(mx, sc[t]);
+      }
+      double sum = 0.0;
+      for (int t = 0; t < T; ++t) sum += (double)expf(sc[t] - mx);
+      for (int t = 0; t < T; ++t) sc[t] = h2f(f2h(expf(sc[t] - mx) / (float)sum));
+      for (int j = 0; j < head_dim; ++j) {
+        double a = 0.0;
+        for (int t = 0; t < T; ++t) a += (double)sc[t] * (double)h2f(vb[(ptrdiff_t)t * width + j]);
+        out[(ptrdiff_t)b * s_o + (ptrdiff_t)h * head_dim + j] = d2h(a);
+      }
+    }
+  free(sc);
+}

@@ -189,3 +189,75 @@ def max_rel_err(got: np.ndarray, ref: np.ndarray) -> float:
     rms = float(np.sqrt(np.mean(r * r)))
     den = np.maximum(np.abs(r), max(rms, 1e-30))
     return float(np.max(np.abs(g - r) / den))
+
+
+# ---------------------------------------------------------------------------
+# row ops (the kernels either side of the matmuls)
+# ---------------------------------------------------------------------------
+def rms_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
+    ly, lx = x.shape
+    x = np.ascontiguousarray(x)
+    _chk16(x)
+    out = np.zeros_like(x)
+    f = lib().orc_rms_norm
+    f.restype = None
+    f.argtypes = [C.c_void_p] * 3 + [C.c_int] * 6 + [C.c_float]
+    f(_p(out), _p(x), _p(np.ascontiguousarray(w)), lx, ly, 1, lx, 1, lx, float(eps))
+    return out
+
+
+def softmax_rows(x: np.ndarray, w: int | None = None, temp: float = 1.0) -> np.ndarray:
+    """x: [heads, h, pitch]; softmax over the first w elements of every row (others kept)."""
+    heads, h, pitch = x.shape
+    x = np.ascontiguousarray(x)
+    _chk16(x)
+    out = x.copy()
+    f = lib().orc_softmax_rows
+    f.restype = None
+    f.argtypes = [C.c_void_p] * 2 + [C.c_int] * 4 + [C.c_float]
+    f(_p(out), _p(x), heads, h, pitch if w is None else w, pitch, float(temp))
+    return out
+
+
+def rotary(x: np.ndarray, n_heads: int, pos_offset: int, theta: float, same_pos=False) -> np.ndarray:
+    ly, lx = x.shape
+    x = np.ascontiguousarray(x)
+    _chk16(x)
+    out = np.zeros_like(x)
+    f = lib().orc_rotary
+    f.restype = None
+    f.argtypes = [C.c_void_p] * 2 + [C.c_int] * 8 + [C.c_float, C.c_int]
+    f(_p(out), _p(x), lx, ly, 1, lx, 1, lx, n_heads, pos_offset, float(theta), int(same_pos))
+    return out
+
+
+def elementwise_binary(left: np.ndarray, right: np.ndarray, op: int) -> np.ndarray:
+    rows, cols = left.shape
+    left, right = np.ascontiguousarray(left), np.ascontiguousarray(right)
+    _chk16(left)
+    _chk16(right)
+    out = np.zeros_like(left)
+    f = lib().orc_elementwise_binary_2d_f16
+    f.restype = C.c_int
+    f.argtypes = [C.c_void_p] * 3 + [C.c_int] * 6
+    rc = f(_p(out), _p(left), _p(right), rows, cols, cols, cols, cols, op)
+    if rc != 0:
+        raise ValueError(f"unsupported binary op {op}")
+    return out
+
+
+def decode_attention(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, n_heads: int,
+                     pos: int, scale: float) -> np.ndarray:
+    """q: [B, H*hd]; caches: [B, S, H*hd] -> [B, H*hd]."""
+    B, width = q.shape
+    S = k_cache.shape[1]
+    q, k_cache, v_cache = (np.ascontiguousarray(a) for a in (q, k_cache, v_cache))
+    for a in (q, k_cache, v_cache):
+        _chk16(a)
+    out = np.zeros_like(q)
+    f = lib().orc_decode_attention
+    f.restype = None
+    f.argtypes = [C.c_void_p] * 4 + [C.c_int] * 7 + [C.c_float]
+    f(_p(out), _p(q), _p(k_cache), _p(v_cache), B, n_heads, width // n_heads, S, width, width,
+      pos, float(scale))
+    return out

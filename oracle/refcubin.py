@@ -141,3 +141,36 @@ def dequantize_absmax_uint8(out_ptr, scales_ptr, q_ptr, rows, k, block_size):
     groups = k // block_size
     holders = [_desc2d(out_ptr, rows, k), _desc2d(scales_ptr, rows, groups), _desc2d(q_ptr, rows, k)]
     _launch(fn, (groups, rows, 1), (min(block_size, 1024), 1, 1), 0, holders)
+
+
+def rms_norm(out_ptr, in_ptr, w_ptr, lx, ly, s_ox, s_oy, s_ix, s_iy, eps):
+    """normalize.cu:7-16 with the launch of kernels.rs:686-704 (one block of 256 per row)."""
+    fn = _function("normalize", "rms_norm")
+    holders = [C.c_void_p(out_ptr), C.c_void_p(in_ptr), C.c_void_p(w_ptr)]
+    holders += [C.c_int(int(v)) for v in (lx, ly, s_ox, s_oy, s_ix, s_iy)] + [C.c_float(eps)]
+    _launch(fn, (ly, 1, 1), (256, 1, 1), 0, holders)
+
+
+def softmax_rows(out_ptr, in_ptr, heads, h, w, temp):
+    """normalize.cu:150-154 with the launch of kernels.rs:895-913 (contiguous rows)."""
+    fn = _function("normalize", "softmax_rows")
+    holders = [C.c_void_p(out_ptr), C.c_void_p(in_ptr), C.c_int(h), C.c_int(w), C.c_float(temp)]
+    _launch(fn, (h, heads, 1), (256, 1, 1), 0, holders)
+
+
+def rotary(out_ptr, in_ptr, lx, ly, s_ox, s_oy, s_ix, s_iy, n_heads, pos_offset, theta):
+    """rotary.cu:4-14 with the launch of kernels.rs:725-749."""
+    fn = _function("rotary", "rotary")
+    holders = [C.c_void_p(out_ptr), C.c_void_p(in_ptr)]
+    holders += [C.c_int(int(v)) for v in (lx, ly, s_ox, s_oy, s_ix, s_iy, n_heads, pos_offset)]
+    holders += [C.c_float(theta)]
+    _launch(fn, (_cdiv(lx, 16), _cdiv(ly, 16), 1), (16, 16, 1), 0, holders)
+
+
+def elementwise_binary_2d_f16(out_ptr, left_ptr, right_ptr, rows, cols, op):
+    """elementwise.cu `elementwise_binary_2d_f16` with the launch of kernels.rs:636-648
+    (contiguous [rows, cols] operands)."""
+    fn = _function("elementwise", "elementwise_binary_2d_f16")
+    holders = [_desc2d(out_ptr, rows, cols), _desc2d(left_ptr, rows, cols),
+               _desc2d(right_ptr, rows, cols), C.c_uint(op)]
+    _launch(fn, (_cdiv(cols, 16), _cdiv(rows, 16), 1), (16, 16, 1), 0, holders)

@@ -221,3 +221,32 @@ def digest(*arrays) -> str:
         if a is not None:
             h.update(np.ascontiguousarray(a).tobytes())
     return h.hexdigest()
+
+
+# ---------------------------------------------------------------------------
+# Row ops (rms_norm, softmax_rows, rotary, elementwise binary): seeded inputs.
+# ---------------------------------------------------------------------------
+def rowop_cases():
+    """name -> dict(kind=..., inputs and parameters).  Sizes cover a ragged tail of the
+    256-thread loops, rows shorter than one pass, and large rotary positions."""
+    rng = np.random.default_rng(4242)
+    f16 = lambda a: np.ascontiguousarray(a, dtype=np.float16)
+    out = {}
+    for name, rows, lx in (("rms_4096", 5, 4096), ("rms_ragged", 3, 777), ("rms_short", 2, 96)):
+        out[name] = dict(kind="rms", x=f16(rng.standard_normal((rows, lx)) * rng.uniform(0.1, 3.0, (rows, 1))),
+                         w=f16(rng.uniform(0.5, 1.5, lx)), eps=1e-5)
+    for name, heads, h, w, temp in (("softmax_257", 3, 7, 257, 1.0), ("softmax_1000_t", 2, 4, 1000, 0.7),
+                                    ("softmax_causal", 2, 33, 33, 1.0)):
+        x = rng.standard_normal((heads, h, w)) * 3.0
+        if name == "softmax_causal":  # -inf above the diagonal, as the Causal mask stores it
+            x[:, np.triu_indices(h, 1)[0], np.triu_indices(h, 1)[1]] = -np.inf
+        out[name] = dict(kind="softmax", x=f16(x), temp=temp)
+    for name, ly, lx, heads, pos in (("rotary_0", 9, 512, 4, 0), ("rotary_500", 4, 256, 2, 500),
+                                     ("rotary_hd64", 17, 128, 2, 3)):
+        out[name] = dict(kind="rotary", x=f16(rng.standard_normal((ly, lx))), n_heads=heads,
+                         pos_offset=pos, theta=10000.0)
+    for name, rows, cols, op in (("add_1000", 6, 1000, 1), ("silu_mul_1000", 6, 1000, 2),
+                                 ("silu_mul_wide", 3, 4096, 2)):
+        out[name] = dict(kind="binary", left=f16(rng.standard_normal((rows, cols)) * 2.5),
+                         right=f16(rng.standard_normal((rows, cols))), op=op)
+    return out

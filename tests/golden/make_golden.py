@@ -6,9 +6,10 @@ Needs a GPU.  Run from the repository root:
 
     python tests/golden/make_golden.py [output_dir]
 
-It writes reference_matmul_f16.npz, reference_u8.npz and
-reference_quantize.npz.  Inputs are not stored; each entry carries a SHA-1 of
-the regenerated inputs so that a drifting generator is caught.
+It writes reference_matmul_f16.npz, reference_u8.npz, reference_quantize.npz and
+reference_rowops.npz (`--only rowops` writes just the last).  Inputs of the first
+two are not stored; each entry carries a SHA-1 of the regenerated inputs so that
+a drifting generator is caught.
 """
 from __future__ import annotations
 
@@ -30,9 +31,46 @@ def dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def main(outdir: Path):
+def rowops(outdir: Path):
+    """rms_norm, softmax_rows, rotary and elementwise_binary_2d_f16 of the reference
+    (normalize.cu, rotary.cu, elementwise.cu) on tests/cases.rowop_cases()."""
+    store = {}
+    for name, c in cases.rowop_cases().items():
+        if c["kind"] == "rms":
+            x, w = dev(c["x"]), dev(c["w"])
+            o = torch.zeros_like(x)
+            ly, lx = c["x"].shape
+            refcubin.rms_norm(o.data_ptr(), x.data_ptr(), w.data_ptr(), lx, ly, 1, lx, 1, lx, c["eps"])
+        elif c["kind"] == "softmax":
+            x = dev(c["x"])
+            o = torch.zeros_like(x)
+            heads, h, w_ = c["x"].shape
+            refcubin.softmax_rows(o.data_ptr(), x.data_ptr(), heads, h, w_, c["temp"])
+        elif c["kind"] == "rotary":
+            x = dev(c["x"])
+            o = torch.zeros_like(x)
+            ly, lx = c["x"].shape
+            refcubin.rotary(o.data_ptr(), x.data_ptr(), lx, ly, 1, lx, 1, lx, c["n_heads"],
+                            c["pos_offset"], c["theta"])
+        else:
+            l, r = dev(c["left"]), dev(c["right"])
+            o = torch.zeros_like(l)
+            rows, cols = c["left"].shape
+            refcubin.elementwise_binary_2d_f16(o.data_ptr(), l.data_ptr(), r.data_ptr(), rows, cols, c["op"])
+        torch.cuda.synchronize()
+        ins = [c[k] for k in ("x", "w", "left", "right") if k in c]
+        store[name + "/digest"] = np.frombuffer(cases.digest(*ins).encode(), np.uint8)
+        store[name + "/out"] = o.cpu().numpy()
+    np.savez_compressed(outdir / "reference_rowops.npz", **store)
+    print("row-op golden vectors written to", outdir)
+
+
+def main(outdir: Path, only: str | None = None):
     assert refcubin.available(), "needs a GPU and oracle/_ref/*.cubin"
     outdir.mkdir(parents=True, exist_ok=True)
+    rowops(outdir)
+    if only == "rowops":
+        return
 
     # ---- matmul_f16 (slow) and matmul_f16_fast ----
     store = {}
@@ -106,4 +144,6 @@ def main(outdir: Path):
 
 
 if __name__ == "__main__":
-    main(Path(sys.argv[1]) if len(sys.argv) > 1 else ROOT / "tests" / "golden")
+    argv = [a for a in sys.argv[1:] if a != "--only" and a != "rowops"]
+    main(Path(argv[0]) if argv else ROOT / "tests" / "golden",
+         "rowops" if "--only" in sys.argv else None)

@@ -1,0 +1,198 @@
+"""GPU parity of the row ops (rms_norm, softmax_rows, rotary, elementwise binary and the two
+decode forms), called through the C ABI.
+
+Three checks per reference-derived kernel: the same bits as the reference's own kernel run
+live (oracle/_ref cubins), the same bits as the committed golden vectors those kernels
+produced, and agreement with the CPU oracle to one unit in the last place of the fp16 result
+(the oracle uses libm where the device uses its own expf/powf/sinf/cosf/rsqrt)."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import cases
+from oracle import oracle, refcubin
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden" / "reference_rowops.npz"
+CASES = cases.rowop_cases()
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def ulp_diff(a: np.ndarray, b: np.ndarray) -> np.ndarray:
+    """Distance in fp16 units in the last place between finite values (0 where both are
+    the same non-finite pattern)."""
+    def key(x):
+        u = x.view(np.uint16).astype(np.int32)
+        return np.where(u & 0x8000, 0x8000 - u, u)
+    d = np.abs(key(np.ascontiguousarray(a)) - key(np.ascontiguousarray(b)))
+    same = a.view(np.uint16) == b.view(np.uint16)
+    return np.where(same, 0, d)
+
+
+def run_ours(kernels, c):
+    from adrastea_b200 import BinaryOp, TensorView
+    if c["kind"] == "rms":
+        x, w = dev(c["x"]), dev(c["w"])
+        o = torch.zeros_like(x)
+        kernels.rms_norm(TensorView.of(o), TensorView.of(x), TensorView.of(w), c["eps"])
+    elif c["kind"] == "softmax":
+        o = dev(c["x"])
+        kernels.softmax_rows_inplace(TensorView.of(o), c["temp"])
+    elif c["kind"] == "rotary":
+        o = dev(c["x"])
+        kernels.rotary_inplace(TensorView.of(o), c["n_heads"], c["pos_offset"], c["theta"])
+    else:
+        o, r = dev(c["left"]), dev(c["right"])
+        kernels.elementwise_binary_2d_f16_inplace(TensorView.of(o), TensorView.of(r), BinaryOp(c["op"]))
+    torch.cuda.synchronize()
+    kernels.device_status()
+    return o.cpu().numpy()
+
+
+def run_oracle(c):
+    if c["kind"] == "rms":
+        return oracle.rms_norm(c["x"], c["w"], c["eps"])
+    if c["kind"] == "softmax":
+        return oracle.softmax_rows(c["x"], temp=c["temp"])
+    if c["kind"] == "rotary":
+        return oracle.rotary(c["x"], c["n_heads"], c["pos_offset"], c["theta"])
+    return oracle.elementwise_binary(c["left"], c["right"], c["op"])
+
+
+def run_reference(c):
+    if c["kind"] == "rms":
+        x, w = dev(c["x"]), dev(c["w"])
+        o = torch.zeros_like(x)
+        ly, lx = c["x"].shape
+        refcubin.rms_norm(o.data_ptr(), x.data_ptr(), w.data_ptr(), lx, ly, 1, lx, 1, lx, c["eps"])
+    elif c["kind"] == "softmax":
+        x = dev(c["x"])
+        o = torch.zeros_like(x)
+        heads, h, w_ = c["x"].shape
+        refcubin.softmax_rows(o.data_ptr(), x.data_ptr(), heads, h, w_, c["temp"])
+    elif c["kind"] == "rotary":
+        x = dev(c["x"])
+        o = torch.zeros_like(x)
+        ly, lx = c["x"].shape
+        refcubin.rotary(o.data_ptr(), x.data_ptr(), lx, ly, 1, lx, 1, lx, c["n_heads"],
+                        c["pos_offset"], c["theta"])
+    else:
+        l, r = dev(c["left"]), dev(c["right"])
+        o = torch.zeros_like(l)
+        rows, cols = c["left"].shape
+        refcubin.elementwise_binary_2d_f16(o.data_ptr(), l.data_ptr(), r.data_ptr(), rows, cols, c["op"])
+    torch.cuda.synchronize()
+    return o.cpu().numpy()
+
+
+@pytest.mark.parametrize("name", list(CASES), ids=list(CASES))
+def test_rowop_against_oracle(kernels, name):
+    c = CASES[name]
+    got, want = run_ours(kernels, c), run_oracle(c)
+    d = ulp_diff(got, want)
+    if c["kind"] == "binary" and c["op"] == 1:
+        assert d.max() == 0
+    else:
+        assert d.max() <= 1 and (d != 0).mean() < 0.02, (int(d.max()), float((d != 0).mean()))
+
+
+@pytest.mark.parametrize("name", list(CASES), ids=list(CASES))
+def test_rowop_same_bits_as_live_reference_kernel(kernels, name):
+    if not refcubin.available():
+        pytest.skip("reference cubins not built")
+    c = CASES[name]
+    got, ref = run_ours(kernels, c), run_reference(c)
+    assert np.array_equal(got.view(np.uint16), ref.view(np.uint16)), int(ulp_diff(got, ref).max())
+
+
+@pytest.mark.parametrize("name", list(CASES), ids=list(CASES))
+def test_rowop_same_bits_as_golden(kernels, name):
+    if not GOLD.exists():
+        pytest.skip("reference_rowops.npz not generated yet")
+    g = np.load(GOLD)
+    c = CASES[name]
+    ins = [c[k] for k in ("x", "w", "left", "right") if k in c]
+    assert bytes(g[name + "/digest"]).decode() == cases.digest(*ins), "input generator drifted"
+    got = run_ours(kernels, c)
+    assert np.array_equal(got.view(np.uint16), g[name + "/out"].view(np.uint16))
+
+
+def test_softmax_padded_rows_and_strided_rms(kernels):
+    """Extensions over the reference launch: padded softmax rows keep their pad columns;
+    rms_norm with row strides on both sides."""
+    from adrastea_b200 import TensorLayout, TensorView
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((4, 9, 40)) * 2).astype(np.float16)
+    o = dev(x)
+    view = TensorView(o, TensorLayout.new((4, 9, 33), (9 * 40, 40, 1)))
+    kernels.softmax_rows_inplace(view, 1.0)
+    got = o.cpu().numpy()
+    want = oracle.softmax_rows(x, w=33)
+    assert ulp_diff(got[:, :, :33], want[:, :, :33]).max() <= 1
+    assert np.array_equal(got[:, :, 33:].view(np.uint16), x[:, :, 33:].view(np.uint16))
+    xs = (rng.standard_normal((6, 300))).astype(np.float16)
+    w = rng.uniform(0.5, 1.5, 256).astype(np.float16)
+    xi, oo = dev(xs), torch.zeros((6, 320), dtype=torch.float16, device="cuda")
+    kernels.rms_norm(TensorView(oo, TensorLayout.new((6, 256), (320, 1))),
+                     TensorView(xi, TensorLayout.new((6, 256), (300, 1))), TensorView.of(dev(w)), 1e-6)
+    want = oracle.rms_norm(xs[:, :256], w, 1e-6)
+    assert ulp_diff(oo.cpu().numpy()[:, :256], want).max() <= 1
+    assert float(oo[:, 256:].abs().max()) == 0.0
+    kernels.device_status()
+
+
+@pytest.mark.parametrize("B,H,hd,S,pos", [(3, 4, 128, 64, 0), (2, 2, 128, 640, 517), (5, 3, 64, 40, 39),
+                                          (1, 2, 256, 24, 10)])
+def test_decode_rope_append_and_attention(kernels, B, H, hd, S, pos):
+    from adrastea_b200 import TensorView
+    rng = np.random.default_rng(B * 1000 + pos)
+    width = H * hd
+    f16 = lambda a: np.ascontiguousarray(a, dtype=np.float16)
+    # q, k, v as three column blocks of one [B, 3*width] buffer (row stride 3*width)
+    qkv = f16(rng.standard_normal((B, 3 * width)))
+    kc = f16(rng.standard_normal((B, S, width)) * 0.7)
+    vc = f16(rng.standard_normal((B, S, width)))
+    d_qkv, d_kc, d_vc = dev(qkv), dev(kc), dev(vc)
+    pos_dev = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    tv = lambda i: TensorView.of(d_qkv[:, i * width:(i + 1) * width])
+    kernels.decode_rope_append(tv(0), tv(1), tv(2), d_kc, d_vc, H, pos_dev, 10000.0)
+    torch.cuda.synchronize()
+    q_rot = oracle.rotary(qkv[:, :width], H, pos, 10000.0, same_pos=True)
+    k_rot = oracle.rotary(qkv[:, width:2 * width], H, pos, 10000.0, same_pos=True)
+    got = d_qkv.cpu().numpy()
+    assert ulp_diff(got[:, :width], q_rot).max() <= 1
+    assert np.array_equal(got[:, width:], qkv[:, width:])  # k and v inputs untouched
+    kc2, vc2 = d_kc.cpu().numpy(), d_vc.cpu().numpy()
+    assert ulp_diff(kc2[:, pos], k_rot).max() <= 1
+    assert np.array_equal(vc2[:, pos], qkv[:, 2 * width:])
+    keep = np.arange(S) != pos
+    assert np.array_equal(kc2[:, keep], kc[:, keep]) and np.array_equal(vc2[:, keep], vc[:, keep])
+    # attention over the cache as the device left it
+    out = torch.zeros((B, width), dtype=torch.float16, device="cuda")
+    scale = 1.0 / np.sqrt(hd)
+    kernels.decode_attention(TensorView.of(out), tv(0), d_kc, d_vc, H, pos_dev, scale)
+    torch.cuda.synchronize()
+    kernels.device_status()
+    want = oracle.decode_attention(got[:, :width], kc2, vc2, H, pos, scale)
+    assert oracle.max_rel_err(out.cpu().numpy(), want) <= 2e-3
+    again = torch.zeros_like(out)
+    kernels.decode_attention(TensorView.of(again), tv(0), d_kc, d_vc, H, pos_dev, scale)
+    assert torch.equal(out, again), "not deterministic"
+
+
+def test_rowop_argument_errors(kernels):
+    from adrastea_b200 import AdrError, TensorLayout, TensorView
+    x = torch.zeros((4, 30), dtype=torch.float16, device="cuda")
+    with pytest.raises(AdrError):  # 30 columns over 4 heads: odd head_dim 7.5
+        kernels.rotary_inplace(TensorView.of(x), 4, 0, 10000.0)
+    with pytest.raises(AdrError):  # temperature must be positive
+        kernels.softmax_rows_inplace(TensorView.of(x), 0.0)
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    kc = torch.zeros((4, 12, 30), dtype=torch.float16, device="cuda")
+    with pytest.raises(AdrError):  # head_dim 15 is not a multiple of 8
+        kernels.decode_attention(TensorView.of(x), TensorView.of(x), kc, kc, 2, pos, 1.0)

@@ -240,3 +240,51 @@ def test_quantizer_and_nt_oracles_match_reference_kernels():
     for name in ("nt_128x64x64", "nt_128x64x64_beta", "nt_16x128x256", "nt_16x128x256_beta"):
         want = oracle.matmul_nt_f16(g[name + "/lhs"], g[name + "/rhs"], float(g[name + "/beta"]), g[name + "/out0"])
         assert oracle.max_rel_err(g[name + "/out"], want) <= 1e-2, name
+
+
+@pytest.mark.parametrize("name", list(cases.rowop_cases()), ids=list(cases.rowop_cases()))
+def test_rowop_oracle_matches_reference_kernels(name):
+    """orc_rms_norm / orc_softmax_rows / orc_rotary / orc_elementwise_binary_2d_f16 against
+    the reference's normalize.cu, rotary.cu and elementwise.cu kernels run on a B200: equal
+    to one unit in the last place (libm here, device intrinsics there), Add bit-exact."""
+    g = _gold("reference_rowops.npz")
+    c = cases.rowop_cases()[name]
+    ins = [c[k] for k in ("x", "w", "left", "right") if k in c]
+    assert bytes(g[name + "/digest"]).decode() == cases.digest(*ins), "input generator drifted"
+    if c["kind"] == "rms":
+        got = oracle.rms_norm(c["x"], c["w"], c["eps"])
+    elif c["kind"] == "softmax":
+        got = oracle.softmax_rows(c["x"], temp=c["temp"])
+    elif c["kind"] == "rotary":
+        got = oracle.rotary(c["x"], c["n_heads"], c["pos_offset"], c["theta"])
+    else:
+        got = oracle.elementwise_binary(c["left"], c["right"], c["op"])
+    ref = g[name + "/out"]
+    same = got.view(np.uint16) == ref.view(np.uint16)
+    d = np.abs(got.astype(np.float32) - ref.astype(np.float32))
+    ulp = np.spacing(np.abs(ref).astype(np.float16)).astype(np.float32)
+    ok = same | (d <= ulp)
+    assert ok.all()
+    if c["kind"] == "binary" and c["op"] == 1:
+        assert same.all()
+    else:
+        assert (~same).mean() < 0.02
+
+
+def test_decode_attention_oracle_against_numpy():
+    """orc_decode_attention against a float64 numpy softmax attention (tolerance: the fp16
+    rounding points of the chain)."""
+    rng = np.random.default_rng(9)
+    B, H, hd, S, pos = 2, 3, 32, 24, 17
+    q = rng.standard_normal((B, H * hd)).astype(np.float16)
+    kc = rng.standard_normal((B, S, H * hd)).astype(np.float16)
+    vc = rng.standard_normal((B, S, H * hd)).astype(np.float16)
+    got = oracle.decode_attention(q, kc, vc, H, pos, 1 / np.sqrt(hd)).astype(np.float64)
+    qh = q.astype(np.float64).reshape(B, H, hd)
+    kh = kc.astype(np.float64).reshape(B, S, H, hd)[:, :pos + 1]
+    vh = vc.astype(np.float64).reshape(B, S, H, hd)[:, :pos + 1]
+    sc = np.einsum("bhd,bthd->bht", qh, kh) / np.sqrt(hd)
+    p = np.exp(sc - sc.max(-1, keepdims=True))
+    p /= p.sum(-1, keepdims=True)
+    want = np.einsum("bht,bthd->bhd", p, vh).reshape(B, H * hd)
+    assert np.abs(got - want).max() / np.abs(want).max() < 5e-3
