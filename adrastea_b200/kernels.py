@@ -367,6 +367,18 @@ class GpuKernels:
                                         output.data_ptr(), heads, h, w, pitch, temperature)
         self._check(rc)
 
+    def elementwise_binary_2d_f16(self, output: TensorView, left: TensorView, right: TensorView,
+                                  op: "BinaryOp", stream=None):
+        """The kernel behind elementwise_binary_2d_f16_inplace with a separate output
+        (elementwise.cu `elementwise_binary_2d_f16` takes one: kernels.rs:647)."""
+        for t in (output, left, right):
+            assert t.stride(-1) == 1 and t.size(-1) == output.size(-1) and t.size(-2) == output.size(-2)
+        rc = self._lib.adr_elementwise_binary_2d_f16(
+            self._ctx, _stream_handle(stream), output.data_ptr(), left.data_ptr(), right.data_ptr(),
+            output.size(-2), output.size(-1), output.stride(-2), left.stride(-2), right.stride(-2),
+            int(op))
+        self._check(rc)
+
     def elementwise_binary_2d_f16_inplace(self, inout_left: TensorView, right: TensorView,
                                           op: "BinaryOp", stream=None):
         """CommonKernels::elementwise_binary_2d_f16_inplace (kernels.rs:191-193, 633-650)."""
