@@ -143,7 +143,7 @@ const char* adr_strerror(int code) {
 int adr_last_cuda_error(const adr_ctx* ctx) { return ctx ? ctx->last_cuda_error : 0; }
 
 int adr_force_kernel(adr_ctx* ctx, int kernel) {
-  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_U8_STREAM) return ADR_ERR_INVALID;
+  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_U8_RING) return ADR_ERR_INVALID;
   ctx->forced_kernel = kernel;
   return ADR_OK;
 }
@@ -155,6 +155,7 @@ int adr_set_tunable(adr_ctx* ctx, const char* name, int value) {
   else if (!strcmp(name, "tc_bn")) ctx->tune_tc_bn = value;
   else if (!strcmp(name, "tc_split")) ctx->tune_tc_split = value;
   else if (!strcmp(name, "pdl")) ctx->tune_pdl = value;
+  else if (!strcmp(name, "u8_exact")) ctx->tune_u8_exact = value;
   else return ADR_ERR_INVALID;
   return ADR_OK;
 }
@@ -225,6 +226,9 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
     // up to 32 tokens two passes of the streaming kernel beat one tensor-core launch
     if (m > 32 && u8_tc_supports(ctx, a)) kernel = ADR_KERNEL_U8_TC;
     else if (p % 64 != 0) kernel = m <= 4 ? ADR_KERNEL_U8_GEMV : ADR_KERNEL_U8_SIMT;
+    else if (!ctx->tune_u8_exact && !ctx->tune_u8_split && !ctx->tune_u8_rows &&
+             u8_ring_supports(ctx, a16))
+      kernel = ADR_KERNEL_U8_RING;
     else if (u8_stream_supports(ctx, a16)) kernel = ADR_KERNEL_U8_STREAM;
     else kernel = ADR_KERNEL_U8_MMA;
   }
@@ -240,6 +244,17 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
         c.lhs = a.lhs + (size_t)r0 * p;
         c.out = a.out + (size_t)r0 * n;
         rc = launch_u8_stream(ctx, st, c);
+      }
+      break;
+    }
+    case ADR_KERNEL_U8_RING: {
+      rc = ADR_OK;
+      for (int r0 = 0; r0 < m && rc == ADR_OK; r0 += 16) {  // one pass per 16 tokens
+        U8Args c = a;
+        c.m = (m - r0 < 16) ? m - r0 : 16;
+        c.lhs = a.lhs + (size_t)r0 * p;
+        c.out = a.out + (size_t)r0 * n;
+        rc = launch_u8_ring(ctx, st, c);
       }
       break;
     }

@@ -60,6 +60,7 @@ struct adr_ctx {
   // tuning knobs (adr_set_tunable); 0 = let the planner choose
   int tune_u8_split = 0;
   int tune_u8_rows = 0;
+  int tune_u8_exact = 0;  // 1: fp16-rounded dequantisation in the streaming kernel
   int tune_tc_bn = 0;
   int tune_tc_split = 0;
   int tune_pdl = 0;  // programmatic dependent launch of the u8 streaming kernel
@@ -182,6 +183,8 @@ int launch_u8_gemv(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 int launch_u8_mma(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 int launch_u8_stream(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 bool u8_stream_supports(const adr_ctx* ctx, const U8Args& a);
+int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
+bool u8_ring_supports(const adr_ctx* ctx, const U8Args& a);
 int launch_u8_tc(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 bool u8_tc_supports(const adr_ctx* ctx, const U8Args& a);
 int init_u8_kernels(adr_ctx* ctx);

@@ -1,0 +1,407 @@
+// u8-weight decode GEMV/GEMM, persistent ring form (m <= 16, block_size 64 or 128):
+//   out[m,n] = lhs[m,p] . deq(Q[n,p])^T + beta * out
+// (replaces adrastea_kernels/cpp/matmul_nt_fp16u8.cu:4-24 and
+// matmul_nt_wmma_16x128x256_fp16u8.cu:12-83 for decode shapes).
+//
+// One CTA per SM walks a list of units (16 weight rows x all of k) and streams them through
+// a ring of shared-memory stages, so that the memory pipe is kept full by a bounded amount of
+// data in flight and a CTA's lifetime does not depend on the whole matrix having landed:
+//   * a stage is eight 128-byte-wide tiles of the unit's 16 rows (16 KB, one 3-D TMA load,
+//     128-byte swizzle) plus the scales (and zero points) of those 16 rows x 1024 k, which
+//     the producer warp copies with 4-byte cp.async tied to the stage's mbarrier;
+//   * warp 0 produces (waits for a free stage, issues the loads); the consumer warps work in
+//     groups of eight, a group per stage, a warp per tile: one PRMT per weight pair puts
+//     the byte under the fp16 exponent of 1024 (1024 + q, exact), mma.sync.m16n8k16 sums
+//     (1024 + q) x and, with an all-ones operand, sum x; the scale and the zero point are
+//     applied in fp32 once per scale group:
+//        sum_k (q_k - z) s x_k = s * (sum_k (1024 + q_k) x_k - (1024 + z) sum_k x_k)
+//     which is the arithmetic of matmul_nt_fp16u8.cu:13-23 (weights not rounded to fp16);
+//   * at the end of a unit the consumer warps add their partial sums through shared memory
+//     in a fixed order and write 16 output columns for every token;
+//   * the activations stay in shared memory for the whole launch.
+// Under programmatic dependent launch the producer starts filling the ring while the
+// previous kernel of the stream is still running (weights, scales and zero points are by
+// contract not written by it); activations and output are touched only after
+// griddepcontrol.wait.  The CTA is sized to leave room for such a successor on the SM when
+// the activations are small.  Every wait is bounded; a wait that runs out sets the status
+// word and the kernel drains its copies and returns.
+#include <algorithm>
+
+#include "tma.cuh"
+#include "u8_common.cuh"
+
+namespace adr {
+
+namespace {
+
+constexpr int RING_TILES = 8;                       // tiles per stage = warps per consumer group
+constexpr int RING_TILE_BYTES = 16 * 128;           // 16 rows x 128 k
+constexpr int RING_W_BYTES = RING_TILES * RING_TILE_BYTES;  // 16 KB
+constexpr int RING_STAGE_BYTES = RING_W_BYTES + 1024;       // + scales/zeros, keeps 1 KB alignment
+constexpr int RING_MAX_STAGES = 12;
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                            uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+__device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+// The mbarrier receives one (pre-counted) arrival when all earlier cp.async of this thread
+// have landed.
+__device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+struct RingParams {
+  U8Args a;
+  int NS;        // stages in the ring
+  int XS;        // bytes between activation rows in shared memory
+  int gps;       // scale groups per stage (1024 / block_size)
+  int bs_shift;  // log2(block_size)
+  int units;     // ceil(n / 16)
+  int spu;       // stages per unit
+  unsigned int* status;
+};
+
+// MT: 8-token column blocks.  NCW: consumer warps (a multiple of 8).
+template <int MT, int NCW, bool HAS_ZERO, bool PDL>
+__global__ void __launch_bounds__((NCW + 1) * 32, 2)
+    u8_ring_kernel(const __grid_constant__ CUtensorMap wmap, RingParams p) {
+  constexpr int TOK = 8 * MT;
+  constexpr int NG = NCW / 8;  // consumer groups
+  constexpr int RED_LD = TOK + 1;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const U8Args& a = p.a;
+  if ((smem_u32(smem_raw) & 1023u) != 0) {  // same for every CTA of the launch
+    if (threadIdx.x == 0) atomicOr(p.status, 16u);
+    return;
+  }
+  uint8_t* ring = smem_raw;
+  uint8_t* Xsm = ring + (size_t)p.NS * RING_STAGE_BYTES;
+  float* red = reinterpret_cast<float*>(Xsm + (size_t)a.m * p.XS);  // [2][NCW][16][RED_LD]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * NCW * 16 * RED_LD);
+  uint64_t* empty = full + RING_MAX_STAGES;
+  uint64_t* xbar = empty + RING_MAX_STAGES;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(xbar + 1);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int ntiles = a.p / 128;
+  const int groups = a.p >> p.bs_shift;
+  // units of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
+  const int my_units = (p.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int total_stages = my_units * p.spu;
+
+  if (tid == 0) {
+    tma_prefetch_desc(&wmap);
+    for (int s = 0; s < p.NS; ++s) {
+      mbar_init(&full[s], 33);  // expect_tx arrival + one cp.async arrival per producer lane
+      mbar_init(&empty[s], 8);  // the eight warps of the group that consumed the stage
+    }
+    mbar_init(xbar, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (PDL) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (warp == 0) {
+    // ------------------------------- producer -------------------------------
+    bool ok = true;
+    const int half_g = p.gps / 2;          // 4-byte copies per row
+    const int copies = 16 * half_g;        // per stage and table
+    auto issue = [&](int q) {
+      const int s = q % p.NS;
+      const int ui = q / p.spu, st = q - ui * p.spu;
+      const int n0 = ((int)blockIdx.x + ui * (int)gridDim.x) * 16;
+      uint8_t* stage = ring + (size_t)s * RING_STAGE_BYTES;
+      if (lane == 0) {
+        mbar_expect_tx(&full[s], RING_W_BYTES);
+        tma_load_3d(stage, &wmap, 0, n0, st * RING_TILES, &full[s]);
+      }
+      __half* stab = reinterpret_cast<__half*>(stage + RING_W_BYTES);
+      for (int c = lane; c < copies; c += 32) {
+        const int row = c / half_g, j = c - row * half_g;
+        const int gi = st * p.gps + 2 * j;
+        if (gi < groups) {
+          const size_t src = (size_t)min(n0 + row, a.n - 1) * groups + gi;
+          cp_async_4(stab + row * p.gps + 2 * j, a.scales + src);
+          if (HAS_ZERO) cp_async_4(stab + 16 * p.gps + row * p.gps + 2 * j, a.zeros + src);
+        }
+      }
+      cp_async_arrive(&full[s]);
+    };
+    int q = 0;
+    // fill the ring before waiting for the previous kernel: these loads touch only weights
+    for (; q < total_stages && q < p.NS; ++q) issue(q);
+    if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (lane == 0) mbar_expect_tx(xbar, (unsigned)(a.m * a.p * 2));
+    __syncwarp();
+    if (lane < a.m)
+      bulk_g2s(Xsm + (size_t)lane * p.XS, a.lhs + (size_t)lane * a.p, (unsigned)(a.p * 2), xbar);
+    for (; q < total_stages && ok; ++q) {
+      const int s = q % p.NS;
+      const unsigned par = (unsigned)(q / p.NS) & 1u;
+      if (!mbar_wait(&empty[s], par ^ 1u) || *abort_flag) { ok = false; break; }
+      issue(q);
+    }
+    if (!ok) {
+      *abort_flag = 1;
+      if (lane == 0) atomicOr(p.status, 32u);
+    }
+    // drain: every issued stage has landed before the CTA may exit
+    const int issued = q;
+    for (int qq = max(0, issued - p.NS); qq < issued; ++qq)
+      if (!mbar_wait(&full[qq % p.NS], (unsigned)(qq / p.NS) & 1u) && lane == 0) atomicOr(p.status, 64u);
+    if (!mbar_wait(xbar, 0) && lane == 0) atomicOr(p.status, 64u);
+  } else {
+    // ------------------------------- consumers -------------------------------
+    const int cw = warp - 1;
+    const int grp = cw >> 3, tile = cw & 7;
+    const int g = lane >> 2, t = lane & 3;
+    const int pg = (g >> 1) + 4 * (g & 1);  // tile row read by MMA row g (conflict-free under the swizzle)
+    const uint8_t* xa = Xsm + (size_t)g * p.XS;
+    const uint8_t* xb = Xsm + (size_t)(g + 8) * p.XS;
+    const bool x0_ok = g < a.m;
+    const bool x1_ok = MT > 1 && (g + 8) < a.m;
+    const bool per_piece = p.bs_shift < 7;
+    bool ok = true;
+    if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
+    ok = mbar_wait(xbar, 0);
+
+    float acc0[MT][4], acc1[MT][4], xs[MT][4];
+    auto compute_piece = [&](const uint8_t* wrow, int xoff, auto first_tag) {
+      constexpr bool FIRST = decltype(first_tag)::value;
+      const uint4 qa = *reinterpret_cast<const uint4*>(wrow);
+      const uint4 qb = *reinterpret_cast<const uint4*>(wrow + 8 * 128);
+      const uint32_t wwa[4] = {qa.x, qa.y, qa.z, qa.w};
+      const uint32_t wwb[4] = {qb.x, qb.y, qb.z, qb.w};
+      const uint4 zero4 = make_uint4(0, 0, 0, 0);
+      const uint4 v0 = x0_ok ? *reinterpret_cast<const uint4*>(xa + xoff) : zero4;
+      const uint4 v1 = x0_ok ? *reinterpret_cast<const uint4*>(xa + xoff + 16) : zero4;
+      uint4 v2 = zero4, v3 = zero4;
+      if (MT > 1 && x1_ok) {
+        v2 = *reinterpret_cast<const uint4*>(xb + xoff);
+        v3 = *reinterpret_cast<const uint4*>(xb + xoff + 16);
+      }
+      const uint32_t xw[2][8] = {{v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w},
+                                 {v2.x, v2.y, v2.z, v2.w, v3.x, v3.y, v3.z, v3.w}};
+      constexpr uint32_t ONES = 0x3C003C00u;
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const uint32_t A0 = prmt(wwa[w], 0x64646464u, 0x4140u), A2 = prmt(wwa[w], 0x64646464u, 0x4342u);
+        const uint32_t A1 = prmt(wwb[w], 0x64646464u, 0x4140u), A3 = prmt(wwb[w], 0x64646464u, 0x4342u);
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+          const uint32_t b0 = xw[i][2 * w], b1 = xw[i][2 * w + 1];
+          if (FIRST && w < 2) mma_16816_z((w & 1) ? acc1[i] : acc0[i], A0, A1, A2, A3, b0, b1);
+          else mma_16816((w & 1) ? acc1[i] : acc0[i], A0, A1, A2, A3, b0, b1);
+          if (FIRST && w == 0) mma_16816_z(xs[i], ONES, ONES, ONES, ONES, b0, b1);
+          else mma_16816(xs[i], ONES, ONES, ONES, ONES, b0, b1);
+        }
+      }
+    };
+
+    int q = 0;
+    for (int ui = 0; ui < my_units; ++ui) {
+      const int n0 = ((int)blockIdx.x + ui * (int)gridDim.x) * 16;
+      float d[MT][4];
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) d[i][j] = 0.0f;
+      for (int st = 0; st < p.spu; ++st, ++q) {
+        if (q % NG != grp) continue;  // another group's stage
+        const int s = q % p.NS;
+        if (ok) ok = mbar_wait(&full[s], (unsigned)(q / p.NS) & 1u) && !*abort_flag;
+        const int kt = st * RING_TILES + tile;
+        if (ok && kt < ntiles) {
+          const uint8_t* stage = ring + (size_t)s * RING_STAGE_BYTES;
+          const uint8_t* trow = stage + tile * RING_TILE_BYTES + pg * 128;
+          const __half* stab = reinterpret_cast<const __half*>(stage + RING_W_BYTES);
+          // d += s * ((acc0 + acc1) - (1024 + z) * sum x) for scale group `gi` of the stage
+          auto correct = [&](int gi) {
+            const float sa = __half2float(stab[pg * p.gps + gi]);
+            const float sb = __half2float(stab[(pg + 8) * p.gps + gi]);
+            float ca = 1151.5f, cb = 1151.5f;
+            if (HAS_ZERO) {
+              ca = 1024.0f + __half2float(stab[16 * p.gps + pg * p.gps + gi]);
+              cb = 1024.0f + __half2float(stab[16 * p.gps + (pg + 8) * p.gps + gi]);
+            }
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+              d[i][0] = fmaf(sa, fmaf(-ca, xs[i][0], acc0[i][0] + acc1[i][0]), d[i][0]);
+              d[i][1] = fmaf(sa, fmaf(-ca, xs[i][1], acc0[i][1] + acc1[i][1]), d[i][1]);
+              d[i][2] = fmaf(sb, fmaf(-cb, xs[i][2], acc0[i][2] + acc1[i][2]), d[i][2]);
+              d[i][3] = fmaf(sb, fmaf(-cb, xs[i][3], acc0[i][3] + acc1[i][3]), d[i][3]);
+            }
+          };
+          // piece h: the 16 bytes at logical offset (t + 4h) * 16 of the 128-byte row
+          const int xoff = kt * 256 + t * 32;
+          compute_piece(trow + ((t ^ pg) * 16), xoff, std::true_type{});
+          if (per_piece) {
+            correct(2 * tile);
+            compute_piece(trow + (((t + 4) ^ pg) * 16), xoff + 128, std::true_type{});
+            correct(2 * tile + 1);
+          } else {
+            compute_piece(trow + (((t + 4) ^ pg) * 16), xoff + 128, std::false_type{});
+            correct(tile);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);  // also on failure, so that the producer can finish
+      }
+      // ---- add the partial sums of all consumer warps in warp order, write 16 columns ----
+      float* rb = red + (size_t)(ui & 1) * NCW * 16 * RED_LD;
+      {
+        float* rw = rb + (size_t)cw * 16 * RED_LD;
+#pragma unroll
+        for (int i = 0; i < MT; ++i) {
+          rw[pg * RED_LD + i * 8 + 2 * t] = d[i][0];
+          rw[pg * RED_LD + i * 8 + 2 * t + 1] = d[i][1];
+          rw[(pg + 8) * RED_LD + i * 8 + 2 * t] = d[i][2];
+          rw[(pg + 8) * RED_LD + i * 8 + 2 * t + 1] = d[i][3];
+        }
+      }
+      named_bar_sync(1, NCW * 32);
+      const int e = tid - 32;
+      if (e < 16 * a.m) {
+        const int row = e & 15, tok = e >> 4;
+        if (n0 + row < a.n) {
+          float v = 0.0f;
+#pragma unroll
+          for (int w = 0; w < NCW; ++w) v += rb[(size_t)w * 16 * RED_LD + row * RED_LD + tok];
+          __half* dst = a.out + (size_t)tok * a.n + n0 + row;
+          *dst = __float2half_rn(fmaf(a.beta, __half2float(*dst), v));
+        }
+      }
+    }
+    if (!ok && lane == 0) atomicOr(p.status, 1u);
+  }
+}
+
+struct RingPlan {
+  int NS, XS, gps, shift, ncw;
+  size_t smem;
+};
+
+bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
+  if (a.m < 1 || a.m > 16 || a.p % 128 != 0 || a.n < 16) return false;
+  if (a.block_size != 64 && a.block_size != 128) return false;
+  if (a.p % a.block_size != 0 || ((a.p / a.block_size) & 1)) return false;  // 4-byte scale copies
+  if (a.p > 65536) return false;  // one bulk copy per activation row
+  if ((reinterpret_cast<uintptr_t>(a.rhs) & 15u) || (reinterpret_cast<uintptr_t>(a.lhs) & 15u) ||
+      (reinterpret_cast<uintptr_t>(a.scales) & 3u) ||
+      (a.zeros && (reinterpret_cast<uintptr_t>(a.zeros) & 3u)))
+    return false;
+  if (!ctx->encode_tiled_fn) return false;
+  const int tok = a.m > 8 ? 16 : 8;
+  pl.ncw = 8;
+  pl.XS = a.p * 2 + 16;
+  pl.gps = 1024 / a.block_size;
+  pl.shift = a.block_size == 64 ? 6 : 7;
+  const size_t fixed = (size_t)a.m * pl.XS + (size_t)2 * pl.ncw * 16 * (tok + 1) * 4 +
+                       (2 * RING_MAX_STAGES + 2) * 8;
+  const int spu = (a.p / 128 + RING_TILES - 1) / RING_TILES;
+  // leave half of the SM's shared memory to a successor launched early, when that still
+  // leaves a useful ring; otherwise take what there is
+  const size_t half = 113 * 1024, all = 224 * 1024;
+  int ns = fixed < half ? (int)((half - fixed) / RING_STAGE_BYTES) : 0;
+  if (ns < 4) ns = fixed < all ? (int)((all - fixed) / RING_STAGE_BYTES) : 0;
+  ns = std::min(ns, RING_MAX_STAGES);
+  if (ns < 3) return false;
+  (void)spu;
+  pl.NS = ns;
+  pl.smem = (size_t)ns * RING_STAGE_BYTES + fixed;
+  return true;
+}
+
+template <int MT, bool Z, bool PDL>
+int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl) {
+  constexpr int NCW = 8;  // two CTAs (this launch and an early successor) fit an SM's registers
+  auto kfn = u8_ring_kernel<MT, NCW, Z, PDL>;
+  static bool configured[64] = {};
+  cudaError_t e;
+  const int dev = ctx->device & 63;
+  if (!configured[dev]) {
+    e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+    if (e != cudaSuccess) {
+      ctx->last_cuda_error = (int)e;
+      return ADR_ERR_CUDA;
+    }
+    configured[dev] = true;
+  }
+  // weights as (k within tile, row, k-tile): a box of 128 x 16 x 8 lands as eight tiles of
+  // [16 rows][128 bytes], each swizzled by its own row index
+  CUtensorMap wmap;
+  const uint64_t dims[3] = {128u, (uint64_t)a.n, (uint64_t)(a.p / 128)};
+  const uint64_t strides[2] = {(uint64_t)a.p, 128u};
+  const uint32_t box[3] = {128u, 16u, (uint32_t)RING_TILES};
+  int rc = tma_get(ctx, &wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.rhs, dims, strides, box,
+                   CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc != ADR_OK) return rc;
+  RingParams p;
+  p.a = a;
+  p.NS = pl.NS;
+  p.XS = pl.XS;
+  p.gps = pl.gps;
+  p.bs_shift = pl.shift;
+  p.units = (a.n + 15) / 16;
+  p.spu = (a.p / 128 + RING_TILES - 1) / RING_TILES;
+  p.status = ctx->d_status;
+  const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(std::min(p.units, sms), 1, 1);
+  cfg.blockDim = dim3((NCW + 1) * 32, 1, 1);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = PDL ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, kfn, wmap, p);
+  if (e != cudaSuccess) {
+    ctx->last_cuda_error = (int)e;
+    return ADR_ERR_CUDA;
+  }
+  return after_launch(ctx);
+}
+
+}  // namespace
+
+bool u8_ring_supports(const adr_ctx* ctx, const U8Args& a) {
+  RingPlan pl;
+  return plan_ring(ctx, a, pl);
+}
+
+int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
+  RingPlan pl;
+  if (!plan_ring(ctx, a, pl)) return ADR_ERR_SHAPE;
+  const bool z = a.zeros != nullptr, two = a.m > 8, pdl = ctx->tune_pdl != 0;
+#define ADR_RING_CASE(MT, Z)                                                       \
+  return pdl ? launch_ring_p<MT, Z, true>(ctx, stream, a, pl)                      \
+             : launch_ring_p<MT, Z, false>(ctx, stream, a, pl)
+  if (two) {
+    if (z) { ADR_RING_CASE(2, true); }
+    ADR_RING_CASE(2, false);
+  }
+  if (z) { ADR_RING_CASE(1, true); }
+  ADR_RING_CASE(1, false);
+#undef ADR_RING_CASE
+}
+
+}  // namespace adr

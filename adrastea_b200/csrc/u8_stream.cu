@@ -46,6 +46,15 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// The same with a zero accumulator on input (starts a chain without clearing registers).
+__device__ __forceinline__ void mma_16816_z(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                            uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
+      "{%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
+}
+
 template <int MT, bool HAS_ZERO>
 struct Piece {  // 16 bytes of two weight rows and their scale-table entries; fetched one ahead
   uint4 qa, qb;
@@ -54,7 +63,16 @@ struct Piece {  // 16 bytes of two weight rows and their scale-table entries; fe
 };
 
 // MT: 8-token column blocks (1: m <= 8, 2: m <= 16).  R: weight rows per CTA.  NW: warps per CTA.
-template <int MT, int R, int NW, bool HAS_ZERO, bool PDL>
+// DEFER: the scale and the zero point are applied to fp32 partial sums, once per scale group
+// (or per 128-byte tile when a group is longer), instead of to every weight:
+//   sum_k (q_k - z) s x_k = s * (sum_k (1024 + q_k) x_k  -  (1024 + z) * sum_k x_k)
+// The operand 1024 + q_k is the byte under the fp16 exponent 0x64, one PRMT per pair and
+// exact; sum_k x_k comes from a second MMA whose weight operand is all ones, which lands it
+// in the accumulator layout the correction needs.  The products are exact in fp32 and the
+// weights are not rounded to fp16 first, which is the arithmetic of matmul_nt_fp16u8.cu:13-23
+// rather than that of the WMMA kernel; the dequantise-multiply work per weight pair drops from
+// three instructions to one.  Needs block_size >= 64 (a 64-wide piece must lie in one group).
+template <int MT, int R, int NW, bool HAS_ZERO, bool PDL, bool DEFER>
 __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
     u8_stream_kernel(const __grid_constant__ CUtensorMap wmap, U8Args a, int S, int XS, int NG,
                      int bs_shift, unsigned int* status) {
@@ -112,7 +130,9 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
   // zero points, activations) go out before the weight tiles.
   // Scale table in shared memory, one 8-byte entry per (row, group - g_lo):
   //   (s, s) as packed halves, plus (z, z) when zero points are given.
-  using Entry = std::conditional_t<HAS_ZERO, uint2, uint32_t>;
+  // (DEFER: the scale as a float, plus 1024 + zero point when zero points are given)
+  using Entry = std::conditional_t<DEFER, std::conditional_t<HAS_ZERO, float2, float>,
+                                   std::conditional_t<HAS_ZERO, uint2, uint32_t>>;
   Entry* Ssm = reinterpret_cast<Entry*>(Xsm + (size_t)a.m * XS);
   // mbarriers behind the table: [0, nt) one per tile, [nt] the activations
   uint64_t* bars = reinterpret_cast<uint64_t*>(Ssm + (size_t)R * NG);
@@ -167,13 +187,21 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
   // exponent >= 2, finite) and only without zero points; one scale outside that range
   // sends the whole CTA down the general path.
   auto table_entry = [&](__half s, __half z, bool& fast) {
-    const unsigned short bits = __half_as_ushort(s) & 0x7FFFu;
-    fast = fast && !HAS_ZERO && bits >= 0x0800u && bits < 0x7C00u;
-    const __half2 s2 = __half2half2(s);
-    if constexpr (HAS_ZERO) {
-      return make_uint2(half2_as_u32(s2), half2_as_u32(__half2half2(z)));
+    if constexpr (DEFER) {
+      if constexpr (HAS_ZERO) {
+        return make_float2(__half2float(s), 1024.0f + __half2float(z));
+      } else {
+        return __half2float(s);
+      }
     } else {
-      return half2_as_u32(s2);
+      const unsigned short bits = __half_as_ushort(s) & 0x7FFFu;
+      fast = fast && !HAS_ZERO && bits >= 0x0800u && bits < 0x7C00u;
+      const __half2 s2 = __half2half2(s);
+      if constexpr (HAS_ZERO) {
+        return make_uint2(half2_as_u32(s2), half2_as_u32(__half2half2(z)));
+      } else {
+        return half2_as_u32(s2);
+      }
     }
   };
   bool fast = true;
@@ -212,7 +240,9 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
   const Entry* s_b = s_a + (size_t)8 * NG;
   // a table entry as (packed scale, packed scale/2 or packed zero point)
   auto expand = [&](Entry e) {
-    if constexpr (HAS_ZERO) {
+    if constexpr (DEFER) {
+      return make_uint2(0u, 0u);  // scales are read at the correction step instead
+    } else if constexpr (HAS_ZERO) {
       return e;
     } else {
       return make_uint2(e, half2_as_u32(__hmul2(u32_as_half2(e), __float2half2_rn(0.5f))));
@@ -229,9 +259,11 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
     pc.qa = *reinterpret_cast<const uint4*>(tile);
     pc.qb = *reinterpret_cast<const uint4*>(tile + 8 * 128);
     pc.xoff = ti * 256 + j * 32;
-    const int grp = (kbase + ti * 128 + h * 64) >> bs_shift;
-    pc.sa = expand(s_a[grp]);
-    pc.sb = expand(s_b[grp]);
+    if constexpr (!DEFER) {
+      const int grp = (kbase + ti * 128 + h * 64) >> bs_shift;
+      pc.sa = expand(s_a[grp]);
+      pc.sb = expand(s_b[grp]);
+    }
   };
   auto compute_piece = [&](const P& pc, auto fast_tag) {
     constexpr bool FAST = decltype(fast_tag)::value;
@@ -278,6 +310,58 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
     }
   };
 
+  // ---- deferred-scale form: per-group accumulators, corrected and scaled in fp32 ----
+  float acc0[MT][4], acc1[MT][4], xs[MT][4];
+  auto compute_piece_defer = [&](const P& pc, auto first_tag) {
+    constexpr bool FIRST = decltype(first_tag)::value;
+    const uint32_t wwa[4] = {pc.qa.x, pc.qa.y, pc.qa.z, pc.qa.w};
+    const uint32_t wwb[4] = {pc.qb.x, pc.qb.y, pc.qb.z, pc.qb.w};
+    const uint4 zero4 = make_uint4(0, 0, 0, 0);
+    const uint4 v0 = x0_ok ? *reinterpret_cast<const uint4*>(xa + pc.xoff) : zero4;
+    const uint4 v1 = x0_ok ? *reinterpret_cast<const uint4*>(xa + pc.xoff + 16) : zero4;
+    uint4 v2 = zero4, v3 = zero4;
+    if (MT > 1 && x1_ok) {
+      v2 = *reinterpret_cast<const uint4*>(xb + pc.xoff);
+      v3 = *reinterpret_cast<const uint4*>(xb + pc.xoff + 16);
+    }
+    const uint32_t xw[2][8] = {{v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w},
+                               {v2.x, v2.y, v2.z, v2.w, v3.x, v3.y, v3.z, v3.w}};
+    constexpr uint32_t ONES = 0x3C003C00u;  // (1.0, 1.0)
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      // byte pairs (0,1) and (2,3) of each word under the exponent of 1024: 1024 + q, exact
+      const uint32_t A0 = prmt(wwa[w], 0x64646464u, 0x4140u), A2 = prmt(wwa[w], 0x64646464u, 0x4342u);
+      const uint32_t A1 = prmt(wwb[w], 0x64646464u, 0x4140u), A3 = prmt(wwb[w], 0x64646464u, 0x4342u);
+#pragma unroll
+      for (int i = 0; i < MT; ++i) {
+        const uint32_t b0 = xw[i][2 * w], b1 = xw[i][2 * w + 1];
+        if (FIRST && w < 2) mma_16816_z((w & 1) ? acc1[i] : acc0[i], A0, A1, A2, A3, b0, b1);
+        else mma_16816((w & 1) ? acc1[i] : acc0[i], A0, A1, A2, A3, b0, b1);
+        if (FIRST && w == 0) mma_16816_z(xs[i], ONES, ONES, ONES, ONES, b0, b1);
+        else mma_16816(xs[i], ONES, ONES, ONES, ONES, b0, b1);
+      }
+    }
+  };
+  // d += s * ((acc0 + acc1) - (1024 + z) * sum x) for the group `grp` just accumulated
+  auto correct = [&](int grp) {
+    float sa, sb, ca, cb;
+    if constexpr (DEFER && HAS_ZERO) {
+      const float2 ea = s_a[grp], eb = s_b[grp];
+      sa = ea.x, ca = ea.y, sb = eb.x, cb = eb.y;
+    } else if constexpr (DEFER) {
+      sa = s_a[grp], sb = s_b[grp], ca = 1151.5f, cb = 1151.5f;
+    } else {
+      sa = sb = ca = cb = 0.0f;
+    }
+#pragma unroll
+    for (int i = 0; i < MT; ++i) {
+      d[i][0] = fmaf(sa, fmaf(-ca, xs[i][0], acc0[i][0] + acc1[i][0]), d[i][0]);
+      d[i][1] = fmaf(sa, fmaf(-ca, xs[i][1], acc0[i][1] + acc1[i][1]), d[i][1]);
+      d[i][2] = fmaf(sb, fmaf(-cb, xs[i][2], acc0[i][2] + acc1[i][2]), d[i][2]);
+      d[i][3] = fmaf(sb, fmaf(-cb, xs[i][3], acc0[i][3] + acc1[i][3]), d[i][3]);
+    }
+  };
+
   bool ok = mbar_wait(&xbar[0], 0);
   ADR_TRACE(3);
   auto run_tiles = [&](auto fast_tag) {
@@ -306,8 +390,46 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
       ti = tn;
     }
   };
-  if (all_fast) run_tiles(std::true_type{});
-  else run_tiles(std::false_type{});
+  auto run_tiles_defer = [&]() {
+    P cur, nxt;
+    int ti = kp;
+    const bool per_piece = bs_shift < 7;  // 64-wide groups: correct after every piece
+    if (ti < nt) {
+      ok = mbar_wait(&bars[ti], 0) && ok;
+      load_piece(ti, 0, cur);
+    }
+#pragma unroll 1
+    while (ti < nt) {
+      load_piece(ti, 1, nxt);
+      compute_piece_defer(cur, std::true_type{});
+      const int grp0 = (k0 + ti * 128) >> bs_shift;
+      if (per_piece) correct(grp0);
+      const int tn = ti + KP;
+      bool pre = false;
+      if (tn < nt && mbar_try_wait(&bars[tn], 0)) {
+        load_piece(tn, 0, cur);
+        pre = true;
+      }
+      if (per_piece) {
+        compute_piece_defer(nxt, std::true_type{});
+        correct(grp0 + 1);
+      } else {
+        compute_piece_defer(nxt, std::false_type{});
+        correct(grp0);
+      }
+      if (tn < nt && !pre) {
+        ok = mbar_wait(&bars[tn], 0) && ok;
+        load_piece(tn, 0, cur);
+      }
+      ti = tn;
+    }
+  };
+  if constexpr (DEFER) {
+    run_tiles_defer();
+  } else {
+    if (all_fast) run_tiles(std::true_type{});
+    else run_tiles(std::false_type{});
+  }
   ADR_TRACE(5);
 #pragma unroll
   for (int j = 0; j < 4; ++j) d[0][j] += d2[j];
@@ -442,10 +564,10 @@ bool plan_stream(const adr_ctx* ctx, const U8Args& a, int force_split, int force
   return found;
 }
 
-template <int MT, int R, bool Z, bool PDL>
+template <int MT, int R, bool Z, bool PDL, bool DEFER>
 int launch_stream_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const StreamPlan& pl) {
   constexpr int NW = 8;
-  auto kfn = u8_stream_kernel<MT, R, NW, Z, PDL>;
+  auto kfn = u8_stream_kernel<MT, R, NW, Z, PDL, DEFER>;
   // opt in to large dynamic shared memory once per device for this instantiation
   static bool configured[64] = {};
   cudaError_t e;
@@ -493,8 +615,14 @@ int launch_stream_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const St
 
 template <int MT, int R, bool Z>
 int launch_stream_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const StreamPlan& pl) {
-  return ctx->tune_pdl ? launch_stream_p<MT, R, Z, true>(ctx, stream, a, pl)
-                       : launch_stream_p<MT, R, Z, false>(ctx, stream, a, pl);
+  // deferred scaling unless the caller asked for the fp16-rounded dequantisation of the WMMA
+  // kernel (tunable "u8_exact") or the groups are shorter than a 64-wide piece
+  const bool defer = !ctx->tune_u8_exact && a.block_size >= 64;
+  if (defer)
+    return ctx->tune_pdl ? launch_stream_p<MT, R, Z, true, true>(ctx, stream, a, pl)
+                         : launch_stream_p<MT, R, Z, false, true>(ctx, stream, a, pl);
+  return ctx->tune_pdl ? launch_stream_p<MT, R, Z, true, false>(ctx, stream, a, pl)
+                       : launch_stream_p<MT, R, Z, false, false>(ctx, stream, a, pl);
 }
 
 }  // namespace

@@ -63,6 +63,7 @@ class Kernel(enum.IntEnum):
     U8Tc = 5
     U8Simt = 6
     U8Stream = 7
+    U8Ring = 8
 
 
 @dataclass(frozen=True)

@@ -69,7 +69,8 @@ enum {
   ADR_KERNEL_U8_MMA = 4,      /* m <= 16: 128-bit weight loads, register-fed MMA     */
   ADR_KERNEL_U8_TC = 5,       /* m > 16: dequantise into shared memory, tcgen05.mma  */
   ADR_KERNEL_U8_SIMT = 6,     /* any m; thread-per-output restatement (slow)         */
-  ADR_KERNEL_U8_STREAM = 7    /* m <= 16: bulk-copy staged, cluster split-k, register-fed MMA */
+  ADR_KERNEL_U8_STREAM = 7,   /* m <= 16: bulk-copy staged, cluster split-k, register-fed MMA */
+  ADR_KERNEL_U8_RING = 8      /* m <= 16, block 64/128: persistent CTAs, TMA ring, scale applied per group */
 };
 
 /*
@@ -95,7 +96,13 @@ int adr_force_kernel(adr_ctx* ctx, int kernel);
  *               while the previous kernel of the stream is still running.  The caller
  *               promises that those three buffers are not written by work enqueued just
  *               before on the same stream.  Activations and output are only touched after
- *               the previous kernel has completed.  Default 0. */
+ *               the previous kernel has completed.  The row-op kernels honour it too.
+ *               Default 0.
+ *   "u8_exact": 1 = the streaming u8 kernel rounds every dequantised weight to fp16 before
+ *               the product, the arithmetic of matmul_nt_wmma_16x128x256_fp16u8.cu:5-7.
+ *               Default 0: weights are not rounded and scale and zero point are applied to
+ *               fp32 partial sums per scale group, the arithmetic of
+ *               matmul_nt_fp16u8.cu:13-23 (used when block_size >= 64). */
 int adr_set_tunable(adr_ctx* ctx, const char* name, int value);
 /* Synchronises the device and returns ADR_ERR_DEVICE if any kernel launched through this
  * context gave up on a bounded wait (the flag is then cleared), ADR_OK otherwise. */

@@ -140,6 +140,8 @@ def u8_kernels_for(c):
         ks.append(Kernel.U8Mma)
         if c.m <= 16 and c.p % 128 == 0:
             ks.append(Kernel.U8Stream)
+            if c.block_size in (64, 128) and c.n >= 16 and (c.p // c.block_size) % 2 == 0:
+                ks.append(Kernel.U8Ring)
     if c.p % 16 == 0:
         ks.append(Kernel.U8Tc)
     return ks
@@ -175,6 +177,53 @@ def test_u8_stream_every_plan(kernels, split, rows):
     finally:
         kernels.set_tunable("u8_split", 0)
         kernels.set_tunable("u8_rows", 0)
+        kernels.force_kernel(Kernel.Auto)
+
+
+@pytest.mark.parametrize("pdl", [0, 1])
+def test_u8_ring_kernel(kernels, pdl):
+    """The persistent ring kernel: ragged n (partial last unit), k with a partial last stage,
+    more units than SMs, both block sizes, both token blocks, zero points, beta; twice for
+    determinism; then the dispatcher's choice and the fp16-rounded mode of the streaming
+    kernel ("u8_exact") on the same inputs."""
+    rng = np.random.default_rng(77 + pdl)
+    try:
+        kernels.set_tunable("pdl", pdl)
+        for m, p, n, bs, zp in ((1, 1024, 200, 128, False), (7, 1280, 333, 64, False),
+                                (16, 2048, 128, 128, True), (9, 1536, 97, 64, True),
+                                (4, 4096, 3000, 128, False), (1, 11008, 64, 128, False)):
+            x = rng.standard_normal((m, p)).astype(np.float16)
+            q = rng.integers(0, 256, (n, p), dtype=np.uint8)
+            s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
+            z = rng.uniform(120, 136, (n, p // bs)).astype(np.float16) if zp else None
+            out0 = (rng.standard_normal((m, n)) * 0.5).astype(np.float16)
+            want = oracle.matmul_nt_fp16u8(x, q, s, bs, 0.5, out0, z)
+            xd, qd, sd, zd = dev(x), dev(q), dev(s), dev(z) if zp else None
+            kernels.force_kernel(Kernel.U8Ring)
+            res = []
+            for _ in range(2):
+                o = dev(out0.copy())
+                kernels.matmul_nt_fp16u8(o, xd, qd, sd, bs, 0.5, zd)
+                kernels.device_status()
+                res.append(o.cpu().numpy())
+            assert kernels.last_kernel() == Kernel.U8Ring
+            assert np.array_equal(res[0].view(np.uint16), res[1].view(np.uint16))
+            assert oracle.max_rel_err(res[0], want) <= 2e-3, (m, p, n, oracle.max_rel_err(res[0], want))
+            kernels.force_kernel(Kernel.Auto)
+            o = dev(out0.copy())
+            kernels.matmul_nt_fp16u8(o, xd, qd, sd, bs, 0.5, zd)
+            assert kernels.last_kernel() == Kernel.U8Ring
+            assert np.array_equal(o.cpu().numpy().view(np.uint16), res[0].view(np.uint16))
+            kernels.set_tunable("u8_exact", 1)
+            o = dev(out0.copy())
+            kernels.matmul_nt_fp16u8(o, xd, qd, sd, bs, 0.5, zd)
+            assert kernels.last_kernel() == Kernel.U8Stream
+            assert oracle.max_rel_err(o.cpu().numpy(), want) <= 2e-3
+            kernels.set_tunable("u8_exact", 0)
+            kernels.device_status()
+    finally:
+        kernels.set_tunable("pdl", 0)
+        kernels.set_tunable("u8_exact", 0)
         kernels.force_kernel(Kernel.Auto)
 
 
@@ -339,7 +388,7 @@ def test_config2_full_size(kernels, m, n):
         for zeros_np, zeros_d in ((None, None), (z, zd)):
             want = oracle.matmul_nt_fp16u8(x, q[cols], s[cols], bs, zeros=None if zeros_np is None else zeros_np[cols])
             outs = {}
-            for kern in [Kernel.U8Mma, Kernel.U8Stream] + ([Kernel.U8Gemv] if m <= 4 else []) + [Kernel.Auto]:
+            for kern in [Kernel.U8Mma, Kernel.U8Stream, Kernel.U8Ring] + ([Kernel.U8Gemv] if m <= 4 else []) + [Kernel.Auto]:
                 kernels.force_kernel(kern)
                 o = torch.zeros(m, n, dtype=torch.float16, device="cuda")
                 kernels.matmul_nt_fp16u8(o, xd, qd, sd, bs, 0.0, zeros_d)
