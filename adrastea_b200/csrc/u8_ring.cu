@@ -26,6 +26,7 @@
 // the activations are small.  Every wait is bounded; a wait that runs out sets the status
 // word and the kernel drains its copies and returns.
 #include <algorithm>
+#include <cstdlib>
 
 #include "tma.cuh"
 #include "u8_common.cuh"
@@ -56,6 +57,9 @@ __device__ __forceinline__ void mma_16816_z(float (&d)[4], uint32_t a0, uint32_t
 }
 __device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
 }
 // The mbarrier receives one (pre-counted) arrival when all earlier cp.async of this thread
 // have landed.
@@ -121,42 +125,63 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
   if (warp == 0) {
     // ------------------------------- producer -------------------------------
     bool ok = true;
-    const int half_g = p.gps / 2;          // 4-byte copies per row
-    const int copies = 16 * half_g;        // per stage and table
-    auto issue = [&](int q) {
-      const int s = q % p.NS;
-      const int ui = q / p.spu, st = q - ui * p.spu;
-      const int n0 = ((int)blockIdx.x + ui * (int)gridDim.x) * 16;
+    // scales of a stage: 16 rows x gps halves, copied in 16-byte pieces when every row of the
+    // scale matrix starts on a 16-byte boundary, else in 4-byte pieces.  A lane's share of the
+    // copies (row, position in the row) is the same for every stage and is worked out once.
+    const bool wide = (groups % 8) == 0 && (reinterpret_cast<uintptr_t>(a.scales) & 15u) == 0 &&
+                      (!HAS_ZERO || (reinterpret_cast<uintptr_t>(a.zeros) & 15u) == 0);
+    const int per = wide ? 8 : 2;          // halves per copy
+    const int per_row = p.gps / per;       // copies per row
+    const int copies = 16 * per_row;       // per stage and table (16..128)
+    int c_row[4], c_col[4];                // this lane's copies: row, first group within the stage
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = lane + 32 * u;
+      c_row[u] = c < copies ? c / per_row : -1;
+      c_col[u] = c < copies ? (c % per_row) * per : 0;
+    }
+    // stage counters, advanced without divisions: ring slot s, k-position st within the unit,
+    // first row n0 of the unit
+    int s = 0, st = 0, n0 = (int)blockIdx.x * 16;
+    unsigned par = 0;  // parity of the current pass over the ring
+    auto issue = [&]() {
       uint8_t* stage = ring + (size_t)s * RING_STAGE_BYTES;
       if (lane == 0) {
         mbar_expect_tx(&full[s], RING_W_BYTES);
         tma_load_3d(stage, &wmap, 0, n0, st * RING_TILES, &full[s]);
       }
       __half* stab = reinterpret_cast<__half*>(stage + RING_W_BYTES);
-      for (int c = lane; c < copies; c += 32) {
-        const int row = c / half_g, j = c - row * half_g;
-        const int gi = st * p.gps + 2 * j;
-        if (gi < groups) {
-          const size_t src = (size_t)min(n0 + row, a.n - 1) * groups + gi;
-          cp_async_4(stab + row * p.gps + 2 * j, a.scales + src);
-          if (HAS_ZERO) cp_async_4(stab + 16 * p.gps + row * p.gps + 2 * j, a.zeros + src);
+      const int g0 = st * p.gps;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (c_row[u] >= 0 && g0 + c_col[u] < groups) {
+          const size_t src = (size_t)min(n0 + c_row[u], a.n - 1) * groups + g0 + c_col[u];
+          __half* dst = stab + c_row[u] * p.gps + c_col[u];
+          if (wide) {
+            cp_async_16(dst, a.scales + src);
+            if (HAS_ZERO) cp_async_16(dst + 16 * p.gps, a.zeros + src);
+          } else {
+            cp_async_4(dst, a.scales + src);
+            if (HAS_ZERO) cp_async_4(dst + 16 * p.gps, a.zeros + src);
+          }
         }
       }
       cp_async_arrive(&full[s]);
+      if (++s == p.NS) s = 0, par ^= 1u;
+      if (++st == p.spu) st = 0, n0 += (int)gridDim.x * 16;
     };
     int q = 0;
     // fill the ring before waiting for the previous kernel: these loads touch only weights
-    for (; q < total_stages && q < p.NS; ++q) issue(q);
+    for (; q < total_stages && q < p.NS; ++q) issue();
     if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
     if (lane == 0) mbar_expect_tx(xbar, (unsigned)(a.m * a.p * 2));
     __syncwarp();
     if (lane < a.m)
       bulk_g2s(Xsm + (size_t)lane * p.XS, a.lhs + (size_t)lane * a.p, (unsigned)(a.p * 2), xbar);
     for (; q < total_stages && ok; ++q) {
-      const int s = q % p.NS;
-      const unsigned par = (unsigned)(q / p.NS) & 1u;
+      // slot s was last filled one pass ago: wait until its consumers have released that use
       if (!mbar_wait(&empty[s], par ^ 1u) || *abort_flag) { ok = false; break; }
-      issue(q);
+      issue();
     }
     if (!ok) {
       *abort_flag = 1;
@@ -215,7 +240,9 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
       }
     };
 
-    int q = 0;
+    int cs = 0;          // ring slot of the next stage
+    unsigned cpar = 0;   // parity of the current pass over the ring
+    int cgrp = 0;        // consumer group whose turn it is
     for (int ui = 0; ui < my_units; ++ui) {
       const int n0 = ((int)blockIdx.x + ui * (int)gridDim.x) * 16;
       float d[MT][4];
@@ -223,12 +250,29 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
       for (int i = 0; i < MT; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) d[i][j] = 0.0f;
-      for (int st = 0; st < p.spu; ++st, ++q) {
-        if (q % NG != grp) continue;  // another group's stage
-        const int s = q % p.NS;
-        if (ok) ok = mbar_wait(&full[s], (unsigned)(q / p.NS) & 1u) && !*abort_flag;
+      // the old output value this thread will combine at the end of the unit: requested now,
+      // so that its latency is hidden behind the unit's stages
+      const int oe = tid - 32;
+      const int orow = oe & 15, otok = oe >> 4;
+      const bool writer = oe < 16 * a.m && n0 + orow < a.n;
+      __half* odst = a.out + (size_t)otok * a.n + n0 + orow;
+      float old = 0.0f;
+      if (writer) old = __half2float(*odst);
+      for (int st = 0; st < p.spu; ++st) {
+        const int s = cs;
+        const unsigned par = cpar;
+        const bool mine = NG == 1 || cgrp == grp;
+        if (++cs == p.NS) cs = 0, cpar ^= 1u;
+        if (NG > 1 && ++cgrp == NG) cgrp = 0;
+        if (!mine) continue;  // another group's stage
+        if (ok) ok = mbar_wait(&full[s], par) && !*abort_flag;
         const int kt = st * RING_TILES + tile;
+#ifdef ADR_RING_PROBE
+        // measurement builds only: beta == 123 streams the weights without the arithmetic
+        if (ok && kt < ntiles && a.beta != 123.0f) {
+#else
         if (ok && kt < ntiles) {
+#endif
           const uint8_t* stage = ring + (size_t)s * RING_STAGE_BYTES;
           const uint8_t* trow = stage + tile * RING_TILE_BYTES + pg * 128;
           const __half* stab = reinterpret_cast<const __half*>(stage + RING_W_BYTES);
@@ -277,16 +321,11 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
         }
       }
       named_bar_sync(1, NCW * 32);
-      const int e = tid - 32;
-      if (e < 16 * a.m) {
-        const int row = e & 15, tok = e >> 4;
-        if (n0 + row < a.n) {
-          float v = 0.0f;
+      if (writer) {
+        float v = 0.0f;
 #pragma unroll
-          for (int w = 0; w < NCW; ++w) v += rb[(size_t)w * 16 * RED_LD + row * RED_LD + tok];
-          __half* dst = a.out + (size_t)tok * a.n + n0 + row;
-          *dst = __float2half_rn(fmaf(a.beta, __half2float(*dst), v));
-        }
+        for (int w = 0; w < NCW; ++w) v += rb[(size_t)w * 16 * RED_LD + orow * RED_LD + otok];
+        *odst = __float2half_rn(fmaf(a.beta, old, v));
       }
     }
     if (!ok && lane == 0) atomicOr(p.status, 1u);
@@ -322,6 +361,12 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   int ns = fixed < half ? (int)((half - fixed) / RING_STAGE_BYTES) : 0;
   if (ns < 4) ns = fixed < all ? (int)((all - fixed) / RING_STAGE_BYTES) : 0;
   ns = std::min(ns, RING_MAX_STAGES);
+#ifdef ADR_RING_PROBE
+  if (const char* e = getenv("ADR_RING_NS")) {  // measurement builds only
+    const int want = atoi(e);
+    if (want >= 3 && fixed + (size_t)want * RING_STAGE_BYTES <= all) ns = std::min(want, RING_MAX_STAGES);
+  }
+#endif
   if (ns < 3) return false;
   (void)spu;
   pl.NS = ns;
