@@ -12,8 +12,9 @@
 //   * warp 0 produces (waits for a free stage, issues the loads); the consumer warps work in
 //     groups of eight, a group per stage, a warp per tile: one PRMT per weight pair puts
 //     the byte under the fp16 exponent of 1024 (1024 + q, exact), mma.sync.m16n8k16 sums
-//     (1024 + q) x and, with an all-ones operand, sum x; the scale and the zero point are
-//     applied in fp32 once per scale group:
+//     (1024 + q) x; sum x per scale group comes from one pass of MMAs with an all-ones
+//     operand at the start of the launch; the scale and the zero point are applied in fp32
+//     once per scale group:
 //        sum_k (q_k - z) s x_k = s * (sum_k (1024 + q_k) x_k - (1024 + z) sum_k x_k)
 //     which is the arithmetic of matmul_nt_fp16u8.cu:13-23 (weights not rounded to fp16);
 //   * at the end of a unit the consumer warps add their partial sums through shared memory
@@ -69,6 +70,10 @@ __device__ __forceinline__ void cp_async_arrive(uint64_t* bar) {
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+__device__ __forceinline__ void named_bar_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+constexpr int RING_RED_BUFS = 4;  // partial-sum buffers (and named barriers) in rotation
 
 struct RingParams {
   U8Args a;
@@ -78,6 +83,7 @@ struct RingParams {
   int bs_shift;  // log2(block_size)
   int units;     // ceil(n / 16)
   int spu;       // stages per unit
+  int xsum_entries;  // k-units of the activation-sum table
   unsigned int* status;
 };
 
@@ -96,8 +102,12 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
   }
   uint8_t* ring = smem_raw;
   uint8_t* Xsm = ring + (size_t)p.NS * RING_STAGE_BYTES;
-  float* red = reinterpret_cast<float*>(Xsm + (size_t)a.m * p.XS);  // [2][NCW][16][RED_LD]
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * NCW * 16 * RED_LD);
+  float* red = reinterpret_cast<float*>(Xsm + (size_t)a.m * p.XS);  // [RING_RED_BUFS][NCW][16][RED_LD]
+  // sum of the activations over every scale-group unit (a tile, or a 64-wide piece when
+  // block_size is 64), per token: [units of k][TOK]
+  constexpr int RBUFS = MT == 1 ? RING_RED_BUFS : 2;  // m > 8 synchronises every unit: two suffice
+  float* xsum = red + RBUFS * NCW * 16 * RED_LD;
+  uint64_t* full = reinterpret_cast<uint64_t*>(xsum + (size_t)p.xsum_entries * TOK);
   uint64_t* empty = full + RING_MAX_STAGES;
   uint64_t* xbar = empty + RING_MAX_STAGES;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(xbar + 1);
@@ -207,7 +217,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
     if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
     ok = mbar_wait(xbar, 0);
 
-    float acc0[MT][4], acc1[MT][4], xs[MT][4];
+    float acc0[MT][4], acc1[MT][4];
     auto compute_piece = [&](const uint8_t* wrow, int xoff, auto first_tag) {
       constexpr bool FIRST = decltype(first_tag)::value;
       const uint4 qa = *reinterpret_cast<const uint4*>(wrow);
@@ -224,7 +234,6 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
       }
       const uint32_t xw[2][8] = {{v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w},
                                  {v2.x, v2.y, v2.z, v2.w, v3.x, v3.y, v3.z, v3.w}};
-      constexpr uint32_t ONES = 0x3C003C00u;
 #pragma unroll
       for (int w = 0; w < 4; ++w) {
         const uint32_t A0 = prmt(wwa[w], 0x64646464u, 0x4140u), A2 = prmt(wwa[w], 0x64646464u, 0x4342u);
@@ -234,11 +243,53 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
           const uint32_t b0 = xw[i][2 * w], b1 = xw[i][2 * w + 1];
           if (FIRST && w < 2) mma_16816_z((w & 1) ? acc1[i] : acc0[i], A0, A1, A2, A3, b0, b1);
           else mma_16816((w & 1) ? acc1[i] : acc0[i], A0, A1, A2, A3, b0, b1);
-          if (FIRST && w == 0) mma_16816_z(xs[i], ONES, ONES, ONES, ONES, b0, b1);
-          else mma_16816(xs[i], ONES, ONES, ONES, ONES, b0, b1);
         }
       }
     };
+    // ---- the activation sums, once per launch: an MMA with an all-ones weight operand leaves
+    // sum_k x[k][token] in the accumulator layout; warp cw takes tiles cw, cw + NCW, ...
+    {
+      constexpr uint32_t ONES = 0x3C003C00u;  // (1.0, 1.0)
+      for (int kt = cw; kt < ntiles && ok; kt += NCW) {
+        float xs[2][MT][4];  // one chain per 64-wide piece
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int xoff = kt * 256 + (t + 4 * h) * 32;
+          const uint4 zero4 = make_uint4(0, 0, 0, 0);
+          const uint4 v0 = x0_ok ? *reinterpret_cast<const uint4*>(xa + xoff) : zero4;
+          const uint4 v1 = x0_ok ? *reinterpret_cast<const uint4*>(xa + xoff + 16) : zero4;
+          uint4 v2 = zero4, v3 = zero4;
+          if (MT > 1 && x1_ok) {
+            v2 = *reinterpret_cast<const uint4*>(xb + xoff);
+            v3 = *reinterpret_cast<const uint4*>(xb + xoff + 16);
+          }
+          const uint32_t xw[2][8] = {{v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w},
+                                     {v2.x, v2.y, v2.z, v2.w, v3.x, v3.y, v3.z, v3.w}};
+#pragma unroll
+          for (int w = 0; w < 4; ++w)
+#pragma unroll
+            for (int i = 0; i < MT; ++i) {
+              if (w == 0) mma_16816_z(xs[h][i], ONES, ONES, ONES, ONES, xw[i][0], xw[i][1]);
+              else mma_16816(xs[h][i], ONES, ONES, ONES, ONES, xw[i][2 * w], xw[i][2 * w + 1]);
+            }
+        }
+        if (g == 0) {
+#pragma unroll
+          for (int i = 0; i < MT; ++i) {
+            if (per_piece) {
+              *reinterpret_cast<float2*>(xsum + (size_t)(2 * kt) * TOK + i * 8 + 2 * t) =
+                  make_float2(xs[0][i][0], xs[0][i][1]);
+              *reinterpret_cast<float2*>(xsum + (size_t)(2 * kt + 1) * TOK + i * 8 + 2 * t) =
+                  make_float2(xs[1][i][0], xs[1][i][1]);
+            } else {
+              *reinterpret_cast<float2*>(xsum + (size_t)kt * TOK + i * 8 + 2 * t) =
+                  make_float2(xs[0][i][0] + xs[1][i][0], xs[0][i][1] + xs[1][i][1]);
+            }
+          }
+        }
+      }
+      named_bar_sync(15, NCW * 32);
+    }
 
     int cs = 0;          // ring slot of the next stage
     unsigned cpar = 0;   // parity of the current pass over the ring
@@ -250,14 +301,22 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
       for (int i = 0; i < MT; ++i)
 #pragma unroll
         for (int j = 0; j < 4; ++j) d[i][j] = 0.0f;
-      // the old output value this thread will combine at the end of the unit: requested now,
-      // so that its latency is hidden behind the unit's stages
-      const int oe = tid - 32;
-      const int orow = oe & 15, otok = oe >> 4;
-      const bool writer = oe < 16 * a.m && n0 + orow < a.n;
-      __half* odst = a.out + (size_t)otok * a.n + n0 + orow;
-      float old = 0.0f;
-      if (writer) old = __half2float(*odst);
+      // m <= 8: one warp per unit, in rotation, adds the partial sums and writes the unit's
+      // 16 x m outputs; lane l takes outputs l, l + 32, ... (output e = token * 16 + row).
+      // m > 8: every consumer thread takes one output.  Either way the old output values are
+      // requested now, so that their latency is hidden behind the unit's stages.
+      constexpr bool ROTATE = MT == 1;
+      const bool summer = ROTATE ? (ui % NCW) == cw : true;
+      constexpr int OPL = ROTATE ? 16 * TOK / 32 : 1;  // outputs per summing thread
+      float old[OPL];
+      if (summer) {
+#pragma unroll
+        for (int j = 0; j < OPL; ++j) {
+          const int e = ROTATE ? lane + 32 * j : tid - 32, row = e & 15, tok = e >> 4;
+          old[j] = (tok < a.m && n0 + row < a.n)
+                       ? __half2float(a.out[(size_t)tok * a.n + n0 + row]) : 0.0f;
+        }
+      }
       for (int st = 0; st < p.spu; ++st) {
         const int s = cs;
         const unsigned par = cpar;
@@ -276,8 +335,9 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
           const uint8_t* stage = ring + (size_t)s * RING_STAGE_BYTES;
           const uint8_t* trow = stage + tile * RING_TILE_BYTES + pg * 128;
           const __half* stab = reinterpret_cast<const __half*>(stage + RING_W_BYTES);
-          // d += s * ((acc0 + acc1) - (1024 + z) * sum x) for scale group `gi` of the stage
-          auto correct = [&](int gi) {
+          // d += s * ((acc0 + acc1) - (1024 + z) * sum x) for scale group `gi` of the stage,
+          // whose activation sums are entry `xe` of the table
+          auto correct = [&](int gi, int xe) {
             const float sa = __half2float(stab[pg * p.gps + gi]);
             const float sb = __half2float(stab[(pg + 8) * p.gps + gi]);
             float ca = 1151.5f, cb = 1151.5f;
@@ -287,29 +347,35 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
             }
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
-              d[i][0] = fmaf(sa, fmaf(-ca, xs[i][0], acc0[i][0] + acc1[i][0]), d[i][0]);
-              d[i][1] = fmaf(sa, fmaf(-ca, xs[i][1], acc0[i][1] + acc1[i][1]), d[i][1]);
-              d[i][2] = fmaf(sb, fmaf(-cb, xs[i][2], acc0[i][2] + acc1[i][2]), d[i][2]);
-              d[i][3] = fmaf(sb, fmaf(-cb, xs[i][3], acc0[i][3] + acc1[i][3]), d[i][3]);
+              const float2 xv = *reinterpret_cast<const float2*>(xsum + (size_t)xe * TOK + i * 8 + 2 * t);
+              d[i][0] = fmaf(sa, fmaf(-ca, xv.x, acc0[i][0] + acc1[i][0]), d[i][0]);
+              d[i][1] = fmaf(sa, fmaf(-ca, xv.y, acc0[i][1] + acc1[i][1]), d[i][1]);
+              d[i][2] = fmaf(sb, fmaf(-cb, xv.x, acc0[i][2] + acc1[i][2]), d[i][2]);
+              d[i][3] = fmaf(sb, fmaf(-cb, xv.y, acc0[i][3] + acc1[i][3]), d[i][3]);
             }
           };
           // piece h: the 16 bytes at logical offset (t + 4h) * 16 of the 128-byte row
           const int xoff = kt * 256 + t * 32;
           compute_piece(trow + ((t ^ pg) * 16), xoff, std::true_type{});
           if (per_piece) {
-            correct(2 * tile);
+            correct(2 * tile, 2 * kt);
             compute_piece(trow + (((t + 4) ^ pg) * 16), xoff + 128, std::true_type{});
-            correct(2 * tile + 1);
+            correct(2 * tile + 1, 2 * kt + 1);
           } else {
             compute_piece(trow + (((t + 4) ^ pg) * 16), xoff + 128, std::false_type{});
-            correct(tile);
+            correct(tile, kt);
           }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);  // also on failure, so that the producer can finish
       }
       // ---- add the partial sums of all consumer warps in warp order, write 16 columns ----
-      float* rb = red + (size_t)(ui & 1) * NCW * 16 * RED_LD;
+      // The other warps only announce their partial sums and go on to the next unit.  Buffer
+      // and barrier `ui % RING_RED_BUFS` are reused four units later; a warp cannot be that
+      // far ahead of the summing warp, because the ring (at most 4 * spu - 1 stages, see
+      // plan_ring) refills a stage only after all eight warps have released it.
+      const int rbuf = ui % RBUFS;
+      float* rb = red + (size_t)rbuf * NCW * 16 * RED_LD;
       {
         float* rw = rb + (size_t)cw * 16 * RED_LD;
 #pragma unroll
@@ -320,12 +386,22 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
           rw[(pg + 8) * RED_LD + i * 8 + 2 * t + 1] = d[i][3];
         }
       }
-      named_bar_sync(1, NCW * 32);
-      if (writer) {
-        float v = 0.0f;
+      if (!summer) {
+        __threadfence_block();  // the partial sums are visible before the arrival is counted
+        __syncwarp();
+        named_bar_arrive(1 + rbuf, NCW * 32);
+      } else {
+        named_bar_sync(1 + rbuf, NCW * 32);
 #pragma unroll
-        for (int w = 0; w < NCW; ++w) v += rb[(size_t)w * 16 * RED_LD + orow * RED_LD + otok];
-        *odst = __float2half_rn(fmaf(a.beta, old, v));
+        for (int j = 0; j < OPL; ++j) {
+          const int e = ROTATE ? lane + 32 * j : tid - 32, row = e & 15, tok = e >> 4;
+          if (tok < a.m && n0 + row < a.n) {
+            float v = 0.0f;
+#pragma unroll
+            for (int w = 0; w < NCW; ++w) v += rb[(size_t)w * 16 * RED_LD + row * RED_LD + tok];
+            a.out[(size_t)tok * a.n + n0 + row] = __float2half_rn(fmaf(a.beta, old[j], v));
+          }
+        }
       }
     }
     if (!ok && lane == 0) atomicOr(p.status, 1u);
@@ -333,7 +409,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
 }
 
 struct RingPlan {
-  int NS, XS, gps, shift, ncw;
+  int NS, XS, gps, shift, ncw, xsum_entries;
   size_t smem;
 };
 
@@ -352,8 +428,9 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   pl.XS = a.p * 2 + 16;
   pl.gps = 1024 / a.block_size;
   pl.shift = a.block_size == 64 ? 6 : 7;
-  const size_t fixed = (size_t)a.m * pl.XS + (size_t)2 * pl.ncw * 16 * (tok + 1) * 4 +
-                       (2 * RING_MAX_STAGES + 2) * 8;
+  pl.xsum_entries = (a.p / 128) * (a.block_size == 64 ? 2 : 1);
+  const size_t fixed = (size_t)a.m * pl.XS + (size_t)(a.m > 8 ? 2 : RING_RED_BUFS) * pl.ncw * 16 * (tok + 1) * 4 +
+                       (size_t)pl.xsum_entries * tok * 4 + (2 * RING_MAX_STAGES + 2) * 8;
   const int spu = (a.p / 128 + RING_TILES - 1) / RING_TILES;
   // leave half of the SM's shared memory to a successor launched early, when that still
   // leaves a useful ring; otherwise take what there is
@@ -361,6 +438,7 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   int ns = fixed < half ? (int)((half - fixed) / RING_STAGE_BYTES) : 0;
   if (ns < 4) ns = fixed < all ? (int)((all - fixed) / RING_STAGE_BYTES) : 0;
   ns = std::min(ns, RING_MAX_STAGES);
+  if (a.m <= 8) ns = std::min(ns, RING_RED_BUFS * spu - 1);  // keeps the rotation of partial-sum buffers safe
 #ifdef ADR_RING_PROBE
   if (const char* e = getenv("ADR_RING_NS")) {  // measurement builds only
     const int want = atoi(e);
@@ -368,7 +446,6 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   }
 #endif
   if (ns < 3) return false;
-  (void)spu;
   pl.NS = ns;
   pl.smem = (size_t)ns * RING_STAGE_BYTES + fixed;
   return true;
@@ -406,6 +483,7 @@ int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
   p.bs_shift = pl.shift;
   p.units = (a.n + 15) / 16;
   p.spu = (a.p / 128 + RING_TILES - 1) / RING_TILES;
+  p.xsum_entries = pl.xsum_entries;
   p.status = ctx->d_status;
   const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
   cudaLaunchConfig_t cfg = {};

@@ -505,8 +505,8 @@ def run_ours_tp(args):
 def run_profile_case(args):
     """Small, self-terminating cases for `ncu` captures (a few hundred MB on the device).
 
-    u8 : the decode kernel over 12 distinct [4096,4096] u8 weights (201 MB, larger than L2),
-         two passes, m = --m.
+    u8 : the decode kernel over 12 distinct [--n,4096] u8 weights (201 MB at n = 4096, larger
+         than L2), two passes, m = --m.
     f16: the tensor-core GEMM, [m,4096] x [4096,4096]^T over 6 distinct weights, m = --m.
     """
     import torch
@@ -516,10 +516,10 @@ def run_profile_case(args):
     kern = GpuKernels(0)
     m = args.m
     if args.profile_case == "u8":
-        ws = [(torch.randint(0, 256, (4096, K), dtype=torch.uint8, device="cuda"),
-               (torch.rand((4096, K // BS), device="cuda") * 0.009 + 0.001).half()) for _ in range(12)]
+        ws = [(torch.randint(0, 256, (args.n, K), dtype=torch.uint8, device="cuda"),
+               (torch.rand((args.n, K // BS), device="cuda") * 0.009 + 0.001).half()) for _ in range(12)]
         x = torch.randn((m, K), dtype=torch.float16, device="cuda")
-        o = torch.zeros((m, 4096), dtype=torch.float16, device="cuda")
+        o = torch.zeros((m, args.n), dtype=torch.float16, device="cuda")
         for _ in range(2):
             for q, s in ws:
                 kern.matmul_nt_fp16u8(o, x, q, s, BS)
@@ -547,6 +547,7 @@ def main():
     ap.add_argument("--profile-case", default=None, choices=["u8", "f16"],
                     help="run a small fixed case of one kernel family and exit (for ncu captures)")
     ap.add_argument("--m", type=int, default=1, help="rows of the activation in --profile-case")
+    ap.add_argument("--n", type=int, default=4096, help="weight rows in --profile-case u8")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args)
