@@ -89,7 +89,7 @@ struct RingParams {
 
 // MT: 8-token column blocks.  NCW: consumer warps (a multiple of 8).
 template <int MT, int NCW, bool HAS_ZERO, bool PDL>
-__global__ void __launch_bounds__((NCW + 1) * 32, 2)
+__global__ void __launch_bounds__((NCW + 1) * 32, NCW == 8 ? 2 : 1)
     u8_ring_kernel(const __grid_constant__ CUtensorMap wmap, RingParams p) {
   constexpr int TOK = 8 * MT;
   constexpr int NG = NCW / 8;  // consumer groups
@@ -105,7 +105,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
   float* red = reinterpret_cast<float*>(Xsm + (size_t)a.m * p.XS);  // [RING_RED_BUFS][NCW][16][RED_LD]
   // sum of the activations over every scale-group unit (a tile, or a 64-wide piece when
   // block_size is 64), per token: [units of k][TOK]
-  constexpr int RBUFS = MT == 1 ? RING_RED_BUFS : 2;  // m > 8 synchronises every unit: two suffice
+  constexpr int RBUFS = (MT == 1 && NG == 1) ? RING_RED_BUFS : 2;  // the all-sync form needs two
   float* xsum = red + RBUFS * NCW * 16 * RED_LD;
   uint64_t* full = reinterpret_cast<uint64_t*>(xsum + (size_t)p.xsum_entries * TOK);
   uint64_t* empty = full + RING_MAX_STAGES;
@@ -181,6 +181,9 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
       if (++st == p.spu) st = 0, n0 += (int)gridDim.x * 16;
     };
     int q = 0;
+#ifdef ADR_RING_PROBE
+    if (a.beta == 124.0f) q = total_stages;  // measurement builds only: arithmetic without loads
+#endif
     // fill the ring before waiting for the previous kernel: these loads touch only weights
     for (; q < total_stages && q < p.NS; ++q) issue();
     if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -198,6 +201,9 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
       if (lane == 0) atomicOr(p.status, 32u);
     }
     // drain: every issued stage has landed before the CTA may exit
+#ifdef ADR_RING_PROBE
+    if (a.beta == 124.0f) q = 0;
+#endif
     const int issued = q;
     for (int qq = max(0, issued - p.NS); qq < issued; ++qq)
       if (!mbar_wait(&full[qq % p.NS], (unsigned)(qq / p.NS) & 1u) && lane == 0) atomicOr(p.status, 64u);
@@ -217,9 +223,11 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
     if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
     ok = mbar_wait(xbar, 0);
 
-    float acc0[MT][4], acc1[MT][4];
-    auto compute_piece = [&](const uint8_t* wrow, int xoff, auto first_tag) {
-      constexpr bool FIRST = decltype(first_tag)::value;
+    // four accumulator chains per token block (piece x parity of the k16 step): two dependent
+    // MMAs each, so that the tensor pipe's latency is overlapped within one warp
+    float acc[2][2][MT][4];
+    auto compute_piece = [&](const uint8_t* wrow, int xoff, auto piece_tag) {
+      constexpr int H = decltype(piece_tag)::value;
       const uint4 qa = *reinterpret_cast<const uint4*>(wrow);
       const uint4 qb = *reinterpret_cast<const uint4*>(wrow + 8 * 128);
       const uint32_t wwa[4] = {qa.x, qa.y, qa.z, qa.w};
@@ -241,8 +249,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
 #pragma unroll
         for (int i = 0; i < MT; ++i) {
           const uint32_t b0 = xw[i][2 * w], b1 = xw[i][2 * w + 1];
-          if (FIRST && w < 2) mma_16816_z((w & 1) ? acc1[i] : acc0[i], A0, A1, A2, A3, b0, b1);
-          else mma_16816((w & 1) ? acc1[i] : acc0[i], A0, A1, A2, A3, b0, b1);
+          if (w < 2) mma_16816_z(acc[H][w & 1][i], A0, A1, A2, A3, b0, b1);
+          else mma_16816(acc[H][w & 1][i], A0, A1, A2, A3, b0, b1);
         }
       }
     };
@@ -305,7 +313,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
       // 16 x m outputs; lane l takes outputs l, l + 32, ... (output e = token * 16 + row).
       // m > 8: every consumer thread takes one output.  Either way the old output values are
       // requested now, so that their latency is hidden behind the unit's stages.
-      constexpr bool ROTATE = MT == 1;
+      // (the rotation relies on every stage being released by all consumer warps, i.e. one group)
+      constexpr bool ROTATE = MT == 1 && NG == 1;
       const bool summer = ROTATE ? (ui % NCW) == cw : true;
       constexpr int OPL = ROTATE ? 16 * TOK / 32 : 1;  // outputs per summing thread
       float old[OPL];
@@ -324,6 +333,9 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
         if (++cs == p.NS) cs = 0, cpar ^= 1u;
         if (NG > 1 && ++cgrp == NG) cgrp = 0;
         if (!mine) continue;  // another group's stage
+#ifdef ADR_RING_PROBE
+        if (a.beta != 124.0f)
+#endif
         if (ok) ok = mbar_wait(&full[s], par) && !*abort_flag;
         const int kt = st * RING_TILES + tile;
 #ifdef ADR_RING_PROBE
@@ -337,7 +349,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
           const __half* stab = reinterpret_cast<const __half*>(stage + RING_W_BYTES);
           // d += s * ((acc0 + acc1) - (1024 + z) * sum x) for scale group `gi` of the stage,
           // whose activation sums are entry `xe` of the table
-          auto correct = [&](int gi, int xe) {
+          auto correct = [&](int gi, int xe, int h0, int h1) {  // pieces h0..h1 were accumulated
             const float sa = __half2float(stab[pg * p.gps + gi]);
             const float sb = __half2float(stab[(pg + 8) * p.gps + gi]);
             float ca = 1151.5f, cb = 1151.5f;
@@ -348,22 +360,28 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
               const float2 xv = *reinterpret_cast<const float2*>(xsum + (size_t)xe * TOK + i * 8 + 2 * t);
-              d[i][0] = fmaf(sa, fmaf(-ca, xv.x, acc0[i][0] + acc1[i][0]), d[i][0]);
-              d[i][1] = fmaf(sa, fmaf(-ca, xv.y, acc0[i][1] + acc1[i][1]), d[i][1]);
-              d[i][2] = fmaf(sb, fmaf(-cb, xv.x, acc0[i][2] + acc1[i][2]), d[i][2]);
-              d[i][3] = fmaf(sb, fmaf(-cb, xv.y, acc0[i][3] + acc1[i][3]), d[i][3]);
+              float sum[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                sum[j] = acc[0][0][i][j] + acc[0][1][i][j];
+                if (h0 == 1) sum[j] = acc[1][0][i][j] + acc[1][1][i][j];
+                else if (h1 == 1) sum[j] += acc[1][0][i][j] + acc[1][1][i][j];
+              }
+              d[i][0] = fmaf(sa, fmaf(-ca, xv.x, sum[0]), d[i][0]);
+              d[i][1] = fmaf(sa, fmaf(-ca, xv.y, sum[1]), d[i][1]);
+              d[i][2] = fmaf(sb, fmaf(-cb, xv.x, sum[2]), d[i][2]);
+              d[i][3] = fmaf(sb, fmaf(-cb, xv.y, sum[3]), d[i][3]);
             }
           };
           // piece h: the 16 bytes at logical offset (t + 4h) * 16 of the 128-byte row
           const int xoff = kt * 256 + t * 32;
-          compute_piece(trow + ((t ^ pg) * 16), xoff, std::true_type{});
+          compute_piece(trow + ((t ^ pg) * 16), xoff, std::integral_constant<int, 0>{});
+          compute_piece(trow + (((t + 4) ^ pg) * 16), xoff + 128, std::integral_constant<int, 1>{});
           if (per_piece) {
-            correct(2 * tile, 2 * kt);
-            compute_piece(trow + (((t + 4) ^ pg) * 16), xoff + 128, std::true_type{});
-            correct(2 * tile + 1, 2 * kt + 1);
+            correct(2 * tile, 2 * kt, 0, 0);
+            correct(2 * tile + 1, 2 * kt + 1, 1, 1);
           } else {
-            compute_piece(trow + (((t + 4) ^ pg) * 16), xoff + 128, std::false_type{});
-            correct(tile, kt);
+            correct(tile, kt, 0, 1);
           }
         }
         __syncwarp();
@@ -409,7 +427,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, 2)
 }
 
 struct RingPlan {
-  int NS, XS, gps, shift, ncw, xsum_entries;
+  int NS, XS, gps, shift, ncw, xsum_entries, cps;
   size_t smem;
 };
 
@@ -424,7 +442,7 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
     return false;
   if (!ctx->encode_tiled_fn) return false;
   const int tok = a.m > 8 ? 16 : 8;
-  pl.ncw = 8;
+  pl.ncw = 8;  // two CTAs (this launch and an early successor) fit an SM's registers
   pl.XS = a.p * 2 + 16;
   pl.gps = 1024 / a.block_size;
   pl.shift = a.block_size == 64 ? 6 : 7;
@@ -432,11 +450,25 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   const size_t fixed = (size_t)a.m * pl.XS + (size_t)(a.m > 8 ? 2 : RING_RED_BUFS) * pl.ncw * 16 * (tok + 1) * 4 +
                        (size_t)pl.xsum_entries * tok * 4 + (2 * RING_MAX_STAGES + 2) * 8;
   const int spu = (a.p / 128 + RING_TILES - 1) / RING_TILES;
-  // leave half of the SM's shared memory to a successor launched early, when that still
-  // leaves a useful ring; otherwise take what there is
+  const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+  const int units = (a.n + 15) / 16;
   const size_t half = 113 * 1024, all = 224 * 1024;
-  int ns = fixed < half ? (int)((half - fixed) / RING_STAGE_BYTES) : 0;
-  if (ns < 4) ns = fixed < all ? (int)((all - fixed) / RING_STAGE_BYTES) : 0;
+  // Shared memory per CTA.  Half an SM's worth lets a second CTA run beside this one: a
+  // second CTA of this launch when there are one or two tokens and at least four units per
+  // CTA (sixteen consumer warps per SM hide the latency of the arithmetic better than eight),
+  // else the first CTAs of the next launch, started early under programmatic dependent
+  // launch.  When half an SM leaves fewer than five stages, one CTA takes all of it.
+  const int ns_half = fixed < half ? (int)((half - fixed) / RING_STAGE_BYTES) : 0;
+  int ns;
+  pl.cps = 1;
+  if (a.m <= 2 && units >= 4 * sms && ns_half >= 4) {
+    pl.cps = 2;
+    ns = ns_half;
+  } else if (ns_half >= 5) {
+    ns = ns_half;
+  } else {
+    ns = fixed < all ? (int)((all - fixed) / RING_STAGE_BYTES) : 0;
+  }
   ns = std::min(ns, RING_MAX_STAGES);
   if (a.m <= 8) ns = std::min(ns, RING_RED_BUFS * spu - 1);  // keeps the rotation of partial-sum buffers safe
 #ifdef ADR_RING_PROBE
@@ -444,6 +476,7 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
     const int want = atoi(e);
     if (want >= 3 && fixed + (size_t)want * RING_STAGE_BYTES <= all) ns = std::min(want, RING_MAX_STAGES);
   }
+  if (const char* e = getenv("ADR_RING_GRID")) pl.cps = atoi(e) == 2 ? 2 : 1;
 #endif
   if (ns < 3) return false;
   pl.NS = ns;
@@ -451,9 +484,8 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   return true;
 }
 
-template <int MT, bool Z, bool PDL>
+template <int MT, bool Z, bool PDL, int NCW>
 int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl) {
-  constexpr int NCW = 8;  // two CTAs (this launch and an early successor) fit an SM's registers
   auto kfn = u8_ring_kernel<MT, NCW, Z, PDL>;
   static bool configured[64] = {};
   cudaError_t e;
@@ -487,7 +519,7 @@ int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
   p.status = ctx->d_status;
   const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(std::min(p.units, sms), 1, 1);
+  cfg.gridDim = dim3(std::min(p.units, sms * pl.cps), 1, 1);
   cfg.blockDim = dim3((NCW + 1) * 32, 1, 1);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = stream;
@@ -516,8 +548,11 @@ int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
   if (!plan_ring(ctx, a, pl)) return ADR_ERR_SHAPE;
   const bool z = a.zeros != nullptr, two = a.m > 8, pdl = ctx->tune_pdl != 0;
 #define ADR_RING_CASE(MT, Z)                                                       \
-  return pdl ? launch_ring_p<MT, Z, true>(ctx, stream, a, pl)                      \
-             : launch_ring_p<MT, Z, false>(ctx, stream, a, pl)
+  if (pl.ncw == 16)                                                                \
+    return pdl ? launch_ring_p<MT, Z, true, 16>(ctx, stream, a, pl)                \
+               : launch_ring_p<MT, Z, false, 16>(ctx, stream, a, pl);              \
+  return pdl ? launch_ring_p<MT, Z, true, 8>(ctx, stream, a, pl)                   \
+             : launch_ring_p<MT, Z, false, 8>(ctx, stream, a, pl)
   if (two) {
     if (z) { ADR_RING_CASE(2, true); }
     ADR_RING_CASE(2, false);
