@@ -18,9 +18,9 @@ def ref_forward(model, kernels, tokens_hist):
     H, hd = sh.n_heads, sh.head_dim
 
     def deq(w):
-        out = torch.empty(w.q.shape, dtype=torch.float16, device=w.q.device)
-        kernels.dequantize_absmax_uint8(out, w.scales, w.q)
-        return out.float()
+        # (q - 127.5) * scale in fp32, not rounded to fp16: the arithmetic of
+        # matmul_nt_fp16u8.cu:13-23, which the decode kernels follow
+        return (w.q.float() - 127.5) * w.scales.float().repeat_interleave(w.block, dim=1)
 
     def lin(x, w):
         return (x.float() @ deq(w).t()).half()
