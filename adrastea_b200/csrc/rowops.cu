@@ -380,6 +380,237 @@ __global__ void __launch_bounds__(ATT_THREADS)
   }
 }
 
+// The same computation for head_dim 64, 128 or 256, built for bandwidth: 16-byte loads (a
+// group of head_dim/8 lanes per position, so a warp reads 32/(head_dim/8) positions at a
+// time, four such steps in flight), and a thread-block cluster of CS CTAs per (head,
+// sequence) that splits the positions when there are few (head, sequence) pairs.  The CTAs
+// of a cluster exchange their maxima, their sums of exponentials and their partial outputs
+// through distributed shared memory; rank 0 adds the partial outputs in rank order, so the
+// result does not depend on timing.  Rounding points as above.
+constexpr int ATT2_THREADS = 256;
+constexpr int ATT2_WARPS = ATT2_THREADS / 32;
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_cluster_f32(const float* local, unsigned rank) {
+  uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(local)), remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(addr), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+__device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
+  const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __low2float(h[i]);
+    f[2 * i + 1] = __high2float(h[i]);
+  }
+}
+
+template <int HD, int CS, bool PDL>
+__global__ void __launch_bounds__(ATT2_THREADS)
+    decode_attention_wide_kernel(__half* out, const __half* q, const __half* k_cache,
+                                 const __half* v_cache, int n_heads, int S, int chunk_cap, int s_q,
+                                 int s_o, const int* pos_dev, float scale) {
+  constexpr int LPT = HD / 8;    // lanes per position
+  constexpr int TPW = 32 / LPT;  // positions per warp step
+  constexpr int U = 4;           // steps in flight
+  extern __shared__ float att_smem[];
+  float* sc = att_smem;                // [chunk_cap] scores, then probabilities, of this CTA's positions
+  float* red = att_smem + chunk_cap;   // [ATT2_WARPS][HD] partial outputs of the warps
+  __shared__ float s_warp[ATT2_WARPS];
+  __shared__ float s_stat[2];          // this CTA's maximum and sum of exponentials
+  __shared__ float s_part[HD];         // this CTA's partial output
+  pdl_enter<PDL>();
+  const int h = blockIdx.x / CS, rank = blockIdx.x % CS, b = blockIdx.y;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int sg = lane / LPT, li = lane % LPT;
+  const int width = n_heads * HD;
+  int T = *pos_dev + 1;
+  T = T < 0 ? 0 : (T > S ? S : T);
+  // positions of this CTA: a contiguous chunk
+  const int per = (T + CS - 1) / CS;
+  const int t_lo = min(T, rank * per), t_hi = min(T, t_lo + per);
+  const int nloc = t_hi - t_lo;
+  const __half* kb = k_cache + (int64_t)b * S * width + (int64_t)h * HD + li * 8;
+  const __half* vb = v_cache + (int64_t)b * S * width + (int64_t)h * HD + li * 8;
+  const __half hscale = __float2half_rn(scale);
+  float qf[8];
+  unpack8(*reinterpret_cast<const uint4*>(q + (int64_t)b * s_q + (int64_t)h * HD + li * 8), qf);
+
+  // ---- scores
+  // (the loop bound is the same for all lanes of a warp: the shuffles inside need every lane)
+  for (int ib = warp * TPW; ib < nloc; ib += U * ATT2_WARPS * TPW) {
+    const int i0 = ib + sg;
+    uint4 kv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * ATT2_WARPS * TPW;
+      kv[u] = i < nloc ? *reinterpret_cast<const uint4*>(kb + (int64_t)(t_lo + i) * width)
+                       : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float kf[8];
+      unpack8(kv[u], kf);
+      float d = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) d += qf[j] * kf[j];
+#pragma unroll
+      for (int off = LPT / 2; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+      const int i = i0 + u * ATT2_WARPS * TPW;
+      if (li == 0 && i < nloc) sc[i] = __half2float(__hmul(__float2half_rn(d), hscale));
+    }
+  }
+  __syncthreads();
+  // ---- maximum over all positions
+  float mx = -INFINITY;
+  for (int i = tid; i < nloc; i += ATT2_THREADS) mx = fmaxf(mx, sc[i]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  if (lane == 0) s_warp[warp] = mx;
+  __syncthreads();
+  if (tid == 0) {
+    float m = s_warp[0];
+    for (int w = 1; w < ATT2_WARPS; ++w) m = fmaxf(m, s_warp[w]);
+    s_stat[0] = m;
+  }
+  if (CS > 1) cluster_sync_all(); else __syncthreads();
+  mx = s_stat[0];
+  if (CS > 1) {
+    mx = -INFINITY;
+    for (int r = 0; r < CS; ++r) mx = fmaxf(mx, ld_cluster_f32(&s_stat[0], r));
+  }
+  // ---- sum of exponentials
+  float sum = 0.0f;
+  for (int i = tid; i < nloc; i += ATT2_THREADS) sum += expf(sc[i] - mx);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if (lane == 0) s_warp[warp] = sum;
+  __syncthreads();
+  if (tid == 0) {
+    float t = 0.0f;
+    for (int w = 0; w < ATT2_WARPS; ++w) t += s_warp[w];
+    s_stat[1] = t;
+  }
+  if (CS > 1) cluster_sync_all(); else __syncthreads();
+  sum = s_stat[1];
+  if (CS > 1) {
+    sum = 0.0f;
+    for (int r = 0; r < CS; ++r) sum += ld_cluster_f32(&s_stat[1], r);
+  }
+  for (int i = tid; i < nloc; i += ATT2_THREADS)
+    sc[i] = __half2float(__float2half_rn(expf(sc[i] - mx) / sum));
+  __syncthreads();
+  // ---- probabilities . v
+  float acc[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+  for (int ib = warp * TPW; ib < nloc; ib += U * ATT2_WARPS * TPW) {
+    const int i0 = ib + sg;
+    uint4 vv[U];
+    float pr[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int i = i0 + u * ATT2_WARPS * TPW;
+      vv[u] = i < nloc ? *reinterpret_cast<const uint4*>(vb + (int64_t)(t_lo + i) * width)
+                       : make_uint4(0, 0, 0, 0);
+      pr[u] = i < nloc ? sc[i] : 0.0f;
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      float vf[8];
+      unpack8(vv[u], vf);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += pr[u] * vf[j];
+    }
+  }
+  // the position groups of a warp, then the warps, then the CTAs of the cluster
+#pragma unroll
+  for (int off = LPT; off < 32; off <<= 1)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] += __shfl_xor_sync(0xffffffffu, acc[j], off);
+  if (sg == 0) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) red[warp * HD + li * 8 + j] = acc[j];
+  }
+  __syncthreads();
+  for (int j = tid; j < HD; j += ATT2_THREADS) {
+    float t = 0.0f;
+#pragma unroll
+    for (int w = 0; w < ATT2_WARPS; ++w) t += red[w * HD + j];
+    s_part[j] = t;
+  }
+  if (CS > 1) cluster_sync_all(); else __syncthreads();
+  if (rank == 0) {
+    __half* orow = out + (int64_t)b * s_o + (int64_t)h * HD;
+    for (int j = tid; j < HD; j += ATT2_THREADS) {
+      float t = s_part[j];
+      if (CS > 1)
+        for (int r = 1; r < CS; ++r) t += ld_cluster_f32(&s_part[j], r);
+      orow[j] = __float2half_rn(t);
+    }
+  }
+  if (CS > 1) cluster_sync_all();  // peers stay resident until rank 0 has read their partial outputs
+}
+
+template <int HD, int CS>
+int launch_attention_wide(adr_ctx* ctx, cudaStream_t stream, __half* out, const __half* q,
+                          const __half* k_cache, const __half* v_cache, int batch, int n_heads,
+                          int S, int s_q, int s_o, const int* pos_dev, float scale) {
+  const int chunk_cap = ((S + CS - 1) / CS + 7) & ~7;
+  const size_t smem = ((size_t)chunk_cap + (size_t)ATT2_WARPS * HD) * sizeof(float);
+  if (smem > 48 * 1024) return ADR_ERR_SHAPE;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_heads * CS, batch, 1);
+  cfg.blockDim = dim3(ATT2_THREADS, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (CS > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = CS;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (ctx->tune_pdl) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = ctx->tune_pdl
+      ? cudaLaunchKernelEx(&cfg, decode_attention_wide_kernel<HD, CS, true>, out, q, k_cache, v_cache,
+                           n_heads, S, chunk_cap, s_q, s_o, pos_dev, scale)
+      : cudaLaunchKernelEx(&cfg, decode_attention_wide_kernel<HD, CS, false>, out, q, k_cache, v_cache,
+                           n_heads, S, chunk_cap, s_q, s_o, pos_dev, scale);
+  if (e != cudaSuccess) {
+    ctx->last_cuda_error = (int)e;
+    return ADR_ERR_CUDA;
+  }
+  return after_launch(ctx);
+}
+
+template <int HD>
+int launch_attention_wide_hd(adr_ctx* ctx, cudaStream_t stream, __half* out, const __half* q,
+                             const __half* k_cache, const __half* v_cache, int batch, int n_heads,
+                             int S, int s_q, int s_o, const int* pos_dev, float scale) {
+  // enough CTAs to fill the machine: split the positions when (head, sequence) pairs are few
+  const int pairs = batch * n_heads;
+  const int cs = pairs >= 256 ? 1 : pairs >= 128 ? 2 : pairs >= 64 ? 4 : 8;
+  switch (cs) {
+    case 1: return launch_attention_wide<HD, 1>(ctx, stream, out, q, k_cache, v_cache, batch, n_heads, S, s_q, s_o, pos_dev, scale);
+    case 2: return launch_attention_wide<HD, 2>(ctx, stream, out, q, k_cache, v_cache, batch, n_heads, S, s_q, s_o, pos_dev, scale);
+    case 4: return launch_attention_wide<HD, 4>(ctx, stream, out, q, k_cache, v_cache, batch, n_heads, S, s_q, s_o, pos_dev, scale);
+    default: return launch_attention_wide<HD, 8>(ctx, stream, out, q, k_cache, v_cache, batch, n_heads, S, s_q, s_o, pos_dev, scale);
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // launch helper: plain launch, or one with programmatic stream serialisation
 // ---------------------------------------------------------------------------------------
@@ -494,6 +725,18 @@ int adr_decode_attention(adr_ctx* ctx, adr_stream stream, void* out, const void*
   if (head_dim % 8 != 0 || head_dim > ATT_MAX_HD || max_seq % 8 != 0 || batch > 65535)
     return ADR_ERR_SHAPE;
   if (stride_q % 4 != 0 || !al16(q) || !al16(k_cache) || !al16(v_cache)) return ADR_ERR_SHAPE;
+  if (stride_q % 8 == 0 && n_heads * head_dim % 8 == 0 && n_heads <= 8191) {
+    // the bandwidth-oriented form for the usual head sizes; its own limit on max_seq falls
+    // through to the general kernel
+    int rc = ADR_ERR_SHAPE;
+    if (head_dim == 64)
+      rc = launch_attention_wide_hd<64>(ctx, (cudaStream_t)stream, (__half*)out, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, batch, n_heads, max_seq, stride_q, stride_o, (const int*)pos_dev, scale);
+    else if (head_dim == 128)
+      rc = launch_attention_wide_hd<128>(ctx, (cudaStream_t)stream, (__half*)out, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, batch, n_heads, max_seq, stride_q, stride_o, (const int*)pos_dev, scale);
+    else if (head_dim == 256)
+      rc = launch_attention_wide_hd<256>(ctx, (cudaStream_t)stream, (__half*)out, (const __half*)q, (const __half*)k_cache, (const __half*)v_cache, batch, n_heads, max_seq, stride_q, stride_o, (const int*)pos_dev, scale);
+    if (rc != ADR_ERR_SHAPE) return rc;
+  }
   const size_t smem = ((size_t)max_seq + (size_t)ATT_WARPS * head_dim) * sizeof(float);
   if (smem > 48 * 1024) return ADR_ERR_SHAPE;
   return launch_row(ctx, (cudaStream_t)stream, decode_attention_kernel<false>,

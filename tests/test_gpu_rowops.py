@@ -147,8 +147,11 @@ def test_softmax_padded_rows_and_strided_rms(kernels):
 
 
 @pytest.mark.parametrize("B,H,hd,S,pos", [(3, 4, 128, 64, 0), (2, 2, 128, 640, 517), (5, 3, 64, 40, 39),
-                                          (1, 2, 256, 24, 10)])
+                                          (1, 2, 256, 24, 10), (16, 16, 128, 64, 50), (8, 16, 128, 72, 70),
+                                          (4, 16, 64, 200, 133), (3, 2, 128, 16, 2), (2, 3, 96, 40, 17)])
 def test_decode_rope_append_and_attention(kernels, B, H, hd, S, pos):
+    """Covers every cluster size of the wide attention kernel (B*H >= 256, 128, 64, fewer),
+    fewer positions than CTAs in a cluster, and a head size only the general kernel takes."""
     from adrastea_b200 import TensorView
     rng = np.random.default_rng(B * 1000 + pos)
     width = H * hd
