@@ -24,6 +24,8 @@ import os
 import subprocess
 import sys
 import tempfile
+
+NCU_TRAFFIC_RATIO = 17.08 / 17.06  # measured DRAM bytes / algorithmic bytes of the decode kernel
 import time
 from pathlib import Path
 
@@ -313,8 +315,15 @@ def run_ours(args):
                 "ms_per_step": ms_e2e / args.steps},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
-                     "frac": per_gpu / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
-                     "kernel": "u8_stream_kernel", "per_m_gbs": per_m,
+                     "frac": per_gpu / peak,
+                     # DRAM bytes per launch: the ncu capture of one [4096,4096], M=1 launch read
+                     # 17.08 MB for 17.06 MB algorithmic (profiles/u8_ring_kernel_4096x4096.md);
+                     # traffic grows in proportion to the weights, so the average launch of the
+                     # step is scaled by that ratio
+                     "traffic": bytes_step / max(launches / args.steps, 1) * NCU_TRAFFIC_RATIO,
+                     "traffic_unit": "bytes per launch (ncu capture of a 17.06 MB launch, scaled)",
+                     "peak_kind": f"of {peak_kind}",
+                     "kernel": "u8_ring_kernel", "per_m_gbs": per_m,
                      "bytes_per_launch_avg": bytes_step / max(launches / args.steps, 1)},
         "clocks": clocks,
     }
@@ -495,7 +504,7 @@ def run_ours_tp(args):
             "gpu_launches": int(launches_per_step * args.steps),
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
-                         "kernel": "u8_stream_kernel (+ ncclAllReduce between row-split products)"},
+                         "kernel": "u8_ring_kernel (+ ncclAllReduce between row-split products)"},
             "clocks": clocks,
         }
         print(json.dumps(line))
