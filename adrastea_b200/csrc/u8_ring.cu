@@ -89,7 +89,7 @@ struct RingParams {
 
 // MT: 8-token column blocks.  NCW: consumer warps (a multiple of 8).
 template <int MT, int NCW, bool HAS_ZERO, bool PDL>
-__global__ void __launch_bounds__((NCW + 1) * 32, NCW == 8 ? 2 : 1)
+__global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     u8_ring_kernel(const __grid_constant__ CUtensorMap wmap, RingParams p) {
   constexpr int TOK = 8 * MT;
   constexpr int NG = NCW / 8;  // consumer groups
@@ -548,9 +548,6 @@ int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
   if (!plan_ring(ctx, a, pl)) return ADR_ERR_SHAPE;
   const bool z = a.zeros != nullptr, two = a.m > 8, pdl = ctx->tune_pdl != 0;
 #define ADR_RING_CASE(MT, Z)                                                       \
-  if (pl.ncw == 16)                                                                \
-    return pdl ? launch_ring_p<MT, Z, true, 16>(ctx, stream, a, pl)                \
-               : launch_ring_p<MT, Z, false, 16>(ctx, stream, a, pl);              \
   return pdl ? launch_ring_p<MT, Z, true, 8>(ctx, stream, a, pl)                   \
              : launch_ring_p<MT, Z, false, 8>(ctx, stream, a, pl)
   if (two) {
