@@ -19,7 +19,8 @@
 //     which is the arithmetic of matmul_nt_fp16u8.cu:13-23 (weights not rounded to fp16);
 //   * at the end of a unit the consumer warps add their partial sums through shared memory
 //     in a fixed order and write 16 output columns for every token;
-//   * the activations stay in shared memory for the whole launch.
+//   * the activations stay in shared memory for the whole launch when they fit beside a ring of
+//     at least four stages; otherwise every stage carries its own slice of them.
 // Under programmatic dependent launch the producer starts filling the ring while the
 // previous kernel of the stream is still running (weights, scales and zero points are by
 // contract not written by it); activations and output are touched only after
@@ -84,11 +85,17 @@ struct RingParams {
   int units;     // ceil(n / 16)
   int spu;       // stages per unit
   int xsum_entries;  // k-units of the activation-sum table
+  int stage_bytes;   // distance between ring stages
+  int xss;           // XR: bytes between activation rows inside a stage
   unsigned int* status;
 };
 
 // MT: 8-token column blocks.  NCW: consumer warps (a multiple of 8).
-template <int MT, int NCW, bool HAS_ZERO, bool PDL>
+// XR: the activations do not fit beside the ring (m x k x 2 bytes: 262 KB at m = 16, k = 8192),
+// so every stage carries its own 1024-wide slice of them (m bulk copies next to the weight box);
+// the activation sums are then taken per tile by an extra MMA with an all-ones weight operand, and
+// nothing is loaded before griddepcontrol.wait.
+template <int MT, int NCW, bool HAS_ZERO, bool PDL, bool XR>
 __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     u8_ring_kernel(const __grid_constant__ CUtensorMap wmap, RingParams p) {
   constexpr int TOK = 8 * MT;
@@ -101,13 +108,13 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     return;
   }
   uint8_t* ring = smem_raw;
-  uint8_t* Xsm = ring + (size_t)p.NS * RING_STAGE_BYTES;
-  float* red = reinterpret_cast<float*>(Xsm + (size_t)a.m * p.XS);  // [RING_RED_BUFS][NCW][16][RED_LD]
+  uint8_t* Xsm = ring + (size_t)p.NS * p.stage_bytes;
+  float* red = reinterpret_cast<float*>(Xsm + (XR ? 0 : (size_t)a.m * p.XS));  // [RBUFS][NCW][16][RED_LD]
   // sum of the activations over every scale-group unit (a tile, or a 64-wide piece when
   // block_size is 64), per token: [units of k][TOK]
   constexpr int RBUFS = (MT == 1 && NG == 1) ? RING_RED_BUFS : 2;  // the all-sync form needs two
   float* xsum = red + RBUFS * NCW * 16 * RED_LD;
-  uint64_t* full = reinterpret_cast<uint64_t*>(xsum + (size_t)p.xsum_entries * TOK);
+  uint64_t* full = reinterpret_cast<uint64_t*>(xsum + (XR ? 0 : (size_t)p.xsum_entries * TOK));
   uint64_t* empty = full + RING_MAX_STAGES;
   uint64_t* xbar = empty + RING_MAX_STAGES;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(xbar + 1);
@@ -155,10 +162,18 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     int s = 0, st = 0, n0 = (int)blockIdx.x * 16;
     unsigned par = 0;  // parity of the current pass over the ring
     auto issue = [&]() {
-      uint8_t* stage = ring + (size_t)s * RING_STAGE_BYTES;
+      uint8_t* stage = ring + (size_t)s * p.stage_bytes;
+      // XR: this stage's slice of every activation row (the last stage of a unit may be short)
+      const int xbytes = XR ? min(2048, (a.p - st * 1024) * 2) : 0;
       if (lane == 0) {
-        mbar_expect_tx(&full[s], RING_W_BYTES);
+        mbar_expect_tx(&full[s], (unsigned)(RING_W_BYTES + a.m * xbytes));
         tma_load_3d(stage, &wmap, 0, n0, st * RING_TILES, &full[s]);
+      }
+      if (XR) {
+        __syncwarp();  // the transaction count is posted before any of the copies can complete
+        if (lane < a.m)
+          bulk_g2s(stage + RING_STAGE_BYTES + (size_t)lane * p.xss,
+                   a.lhs + (size_t)lane * a.p + (size_t)st * 1024, (unsigned)xbytes, &full[s]);
       }
       __half* stab = reinterpret_cast<__half*>(stage + RING_W_BYTES);
       const int g0 = st * p.gps;
@@ -184,13 +199,20 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
 #ifdef ADR_RING_PROBE
     if (a.beta == 124.0f) q = total_stages;  // measurement builds only: arithmetic without loads
 #endif
-    // fill the ring before waiting for the previous kernel: these loads touch only weights
-    for (; q < total_stages && q < p.NS; ++q) issue();
-    if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
-    if (lane == 0) mbar_expect_tx(xbar, (unsigned)(a.m * a.p * 2));
-    __syncwarp();
-    if (lane < a.m)
-      bulk_g2s(Xsm + (size_t)lane * p.XS, a.lhs + (size_t)lane * a.p, (unsigned)(a.p * 2), xbar);
+    if (XR) {
+      // the stages carry activations: nothing may be requested before the previous kernel is done
+      if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
+      for (; q < total_stages && q < p.NS; ++q) issue();
+      if (lane == 0) mbar_arrive(xbar);  // unused in this mode; completed for the drain below
+    } else {
+      // fill the ring before waiting for the previous kernel: these loads touch only weights
+      for (; q < total_stages && q < p.NS; ++q) issue();
+      if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
+      if (lane == 0) mbar_expect_tx(xbar, (unsigned)(a.m * a.p * 2));
+      __syncwarp();
+      if (lane < a.m)
+        bulk_g2s(Xsm + (size_t)lane * p.XS, a.lhs + (size_t)lane * a.p, (unsigned)(a.p * 2), xbar);
+    }
     for (; q < total_stages && ok; ++q) {
       // slot s was last filled one pass ago: wait until its consumers have released that use
       if (!mbar_wait(&empty[s], par ^ 1u) || *abort_flag) { ok = false; break; }
@@ -214,6 +236,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     const int grp = cw >> 3, tile = cw & 7;
     const int g = lane >> 2, t = lane & 3;
     const int pg = (g >> 1) + 4 * (g & 1);  // tile row read by MMA row g (conflict-free under the swizzle)
+    // activation rows g and g + 8 (XR: re-pointed at every stage's own slice)
     const uint8_t* xa = Xsm + (size_t)g * p.XS;
     const uint8_t* xb = Xsm + (size_t)(g + 8) * p.XS;
     const bool x0_ok = g < a.m;
@@ -226,6 +249,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     // four accumulator chains per token block (piece x parity of the k16 step): two dependent
     // MMAs each, so that the tensor pipe's latency is overlapped within one warp
     float acc[2][2][MT][4];
+    float xs[2][MT][4];  // XR: sum of the activations over each 64-wide piece, by MMA with ones
     auto compute_piece = [&](const uint8_t* wrow, int xoff, auto piece_tag) {
       constexpr int H = decltype(piece_tag)::value;
       const uint4 qa = *reinterpret_cast<const uint4*>(wrow);
@@ -251,12 +275,17 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
           const uint32_t b0 = xw[i][2 * w], b1 = xw[i][2 * w + 1];
           if (w < 2) mma_16816_z(acc[H][w & 1][i], A0, A1, A2, A3, b0, b1);
           else mma_16816(acc[H][w & 1][i], A0, A1, A2, A3, b0, b1);
+          if constexpr (XR) {
+            constexpr uint32_t ONES = 0x3C003C00u;  // (1.0, 1.0)
+            if (w == 0) mma_16816_z(xs[H][i], ONES, ONES, ONES, ONES, b0, b1);
+            else mma_16816(xs[H][i], ONES, ONES, ONES, ONES, b0, b1);
+          }
         }
       }
     };
     // ---- the activation sums, once per launch: an MMA with an all-ones weight operand leaves
     // sum_k x[k][token] in the accumulator layout; warp cw takes tiles cw, cw + NCW, ...
-    {
+    if constexpr (!XR) {
       constexpr uint32_t ONES = 0x3C003C00u;  // (1.0, 1.0)
       for (int kt = cw; kt < ntiles && ok; kt += NCW) {
         float xs[2][MT][4];  // one chain per 64-wide piece
@@ -344,8 +373,12 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
 #else
         if (ok && kt < ntiles) {
 #endif
-          const uint8_t* stage = ring + (size_t)s * RING_STAGE_BYTES;
+          const uint8_t* stage = ring + (size_t)s * p.stage_bytes;
           const uint8_t* trow = stage + tile * RING_TILE_BYTES + pg * 128;
+          if constexpr (XR) {
+            xa = stage + RING_STAGE_BYTES + (size_t)g * p.xss;
+            xb = stage + RING_STAGE_BYTES + (size_t)(g + 8) * p.xss;
+          }
           const __half* stab = reinterpret_cast<const __half*>(stage + RING_W_BYTES);
           // d += s * ((acc0 + acc1) - (1024 + z) * sum x) for scale group `gi` of the stage,
           // whose activation sums are entry `xe` of the table
@@ -359,7 +392,13 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
             }
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
-              const float2 xv = *reinterpret_cast<const float2*>(xsum + (size_t)xe * TOK + i * 8 + 2 * t);
+              float2 xv;
+              if constexpr (XR) {
+                xv = make_float2(xs[h0][i][0], xs[h0][i][1]);
+                if (h0 != h1) xv.x += xs[h1][i][0], xv.y += xs[h1][i][1];
+              } else {
+                xv = *reinterpret_cast<const float2*>(xsum + (size_t)xe * TOK + i * 8 + 2 * t);
+              }
               float sum[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
@@ -374,7 +413,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
             }
           };
           // piece h: the 16 bytes at logical offset (t + 4h) * 16 of the 128-byte row
-          const int xoff = kt * 256 + t * 32;
+          const int xoff = (XR ? tile : kt) * 256 + t * 32;
           compute_piece(trow + ((t ^ pg) * 16), xoff, std::integral_constant<int, 0>{});
           compute_piece(trow + (((t + 4) ^ pg) * 16), xoff + 128, std::integral_constant<int, 1>{});
           if (per_piece) {
@@ -427,7 +466,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
 }
 
 struct RingPlan {
-  int NS, XS, gps, shift, ncw, xsum_entries, cps;
+  int NS, XS, gps, shift, ncw, xsum_entries, cps, xr, stage_bytes, xss;
   size_t smem;
 };
 
@@ -478,15 +517,39 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   }
   if (const char* e = getenv("ADR_RING_GRID")) pl.cps = atoi(e) == 2 ? 2 : 1;
 #endif
+  pl.xr = 0;
+  pl.stage_bytes = RING_STAGE_BYTES;
+  pl.xss = 0;
+  if (ns < 4) {
+    // The activations leave too little room for a ring (or none): stream them through the ring
+    // with the weights instead, 1024 k per stage and token (rows padded by 16 bytes so that the
+    // fragment loads of different tokens fall in different banks).
+    const int xss = 2048 + 16;
+    const int stage = (RING_STAGE_BYTES + a.m * xss + 1023) & ~1023;
+    const size_t fixed_xr = (size_t)(a.m > 8 ? 2 : RING_RED_BUFS) * pl.ncw * 16 * (tok + 1) * 4 +
+                            (2 * RING_MAX_STAGES + 2) * 8;
+    int ns_xr = (int)((all - fixed_xr) / stage);
+    ns_xr = std::min(ns_xr, RING_MAX_STAGES);
+    if (a.m <= 8) ns_xr = std::min(ns_xr, RING_RED_BUFS * spu - 1);
+    if (ns_xr >= 3 && ns_xr > ns) {
+      pl.xr = 1;
+      pl.cps = 1;
+      pl.stage_bytes = stage;
+      pl.xss = xss;
+      pl.NS = ns_xr;
+      pl.smem = (size_t)ns_xr * stage + fixed_xr;
+      return true;
+    }
+  }
   if (ns < 3) return false;
   pl.NS = ns;
   pl.smem = (size_t)ns * RING_STAGE_BYTES + fixed;
   return true;
 }
 
-template <int MT, bool Z, bool PDL, int NCW>
+template <int MT, bool Z, bool PDL, int NCW, bool XR>
 int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl) {
-  auto kfn = u8_ring_kernel<MT, NCW, Z, PDL>;
+  auto kfn = u8_ring_kernel<MT, NCW, Z, PDL, XR>;
   static bool configured[64] = {};
   cudaError_t e;
   const int dev = ctx->device & 63;
@@ -516,6 +579,8 @@ int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
   p.units = (a.n + 15) / 16;
   p.spu = (a.p / 128 + RING_TILES - 1) / RING_TILES;
   p.xsum_entries = pl.xsum_entries;
+  p.stage_bytes = pl.stage_bytes;
+  p.xss = pl.xss;
   p.status = ctx->d_status;
   const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
   cudaLaunchConfig_t cfg = {};
@@ -548,8 +613,11 @@ int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
   if (!plan_ring(ctx, a, pl)) return ADR_ERR_SHAPE;
   const bool z = a.zeros != nullptr, two = a.m > 8, pdl = ctx->tune_pdl != 0;
 #define ADR_RING_CASE(MT, Z)                                                       \
-  return pdl ? launch_ring_p<MT, Z, true, 8>(ctx, stream, a, pl)                   \
-             : launch_ring_p<MT, Z, false, 8>(ctx, stream, a, pl)
+  if (pl.xr)                                                                       \
+    return pdl ? launch_ring_p<MT, Z, true, 8, true>(ctx, stream, a, pl)           \
+               : launch_ring_p<MT, Z, false, 8, true>(ctx, stream, a, pl);         \
+  return pdl ? launch_ring_p<MT, Z, true, 8, false>(ctx, stream, a, pl)            \
+             : launch_ring_p<MT, Z, false, 8, false>(ctx, stream, a, pl)
   if (two) {
     if (z) { ADR_RING_CASE(2, true); }
     ADR_RING_CASE(2, false);

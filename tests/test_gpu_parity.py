@@ -191,7 +191,10 @@ def test_u8_ring_kernel(kernels, pdl):
         kernels.set_tunable("pdl", pdl)
         for m, p, n, bs, zp in ((1, 1024, 200, 128, False), (7, 1280, 333, 64, False),
                                 (16, 2048, 128, 128, True), (9, 1536, 97, 64, True),
-                                (4, 4096, 3000, 128, False), (1, 11008, 64, 128, False)):
+                                (4, 4096, 3000, 128, False), (1, 11008, 64, 128, False),
+                                # activations too large to stay resident: streamed through the ring
+                                (16, 8192, 512, 64, False), (8, 11008, 256, 128, False),
+                                (16, 11008, 272, 128, True), (12, 4224 + 4096, 300, 64, False)):
             x = rng.standard_normal((m, p)).astype(np.float16)
             q = rng.integers(0, 256, (n, p), dtype=np.uint8)
             s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
