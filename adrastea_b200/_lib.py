@@ -42,6 +42,8 @@ SIGNATURES = {
                                + [_vp, C.c_float]),
     "adr_decode_attention": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp] + [_c_int] * 6
                              + [_vp, C.c_float]),
+    "adr_allreduce_oneshot": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int,
+                                       C.c_longlong, _c_int]),
     "adr_trace_enable": (_c_int, [_vp, _c_int]),
     "adr_trace_clear": (None, [_vp]),
     "adr_trace_dump": (C.c_size_t, [_vp, C.c_char_p, C.c_size_t]),

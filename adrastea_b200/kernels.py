@@ -420,6 +420,17 @@ class GpuKernels:
             out.stride(-2), pos_dev.data_ptr(), scale)
         self._check(rc)
 
+    def allreduce_oneshot(self, out: torch.Tensor, buf_ptrs, flag_ptrs, epochs: torch.Tensor,
+                          blocks: int, rank: int, world: int, count: int, residual: bool,
+                          stream=None):
+        """adr_allreduce_oneshot: buf_ptrs / flag_ptrs are per-rank device addresses (ints)."""
+        bufs = (C.c_void_p * world)(*[int(x) for x in buf_ptrs])
+        flags = (C.c_void_p * world)(*[int(x) for x in flag_ptrs])
+        rc = self._lib.adr_allreduce_oneshot(self._ctx, _stream_handle(stream), out.data_ptr(), bufs,
+                                             flags, epochs.data_ptr(), blocks, rank, world, count,
+                                             int(residual))
+        self._check(rc)
+
     # -- library-side trace (kernel family per distinct call) -------------
     def trace_enable(self, on: bool = True):
         self._check(self._lib.adr_trace_enable(self._ctx, int(on)))

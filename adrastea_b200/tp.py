@@ -80,11 +80,56 @@ class TPContext:
             self.world = dist.get_world_size(group)
         else:
             self.group, self.rank, self.world = None, 0, 1
+        self.peer_ar = None  # a PeerAllReduce replaces the NCCL call in RowParallelU8Linear
 
     def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t
+
+
+class PeerAllReduce:
+    """Two symmetric fp16 buffers per rank, peer-mapped on every GPU of the group, and the
+    library's one-shot all-reduce kernel over them (csrc/allreduce.cu).  Row-split products are
+    written into `buffer(i)` and reduced with `all_reduce(i, out)`; the two buffers are used
+    alternately.  Unlike an NCCL call the kernel can be captured in a CUDA graph."""
+
+    BLOCKS = 64
+
+    def __init__(self, kernels, tp: "TPContext", max_elems: int, device):
+        import torch.distributed._symmetric_memory as symm
+        assert tp.world > 1
+        self.kernels, self.tp = kernels, tp
+        group = tp.group if tp.group is not None else dist.group.WORLD
+        self.bufs, self.buf_ptrs = [], []
+        for _ in range(2):
+            t = symm.empty(max_elems, dtype=torch.float16, device=device)
+            t.zero_()  # the u8 kernels read their output buffer (beta * old) even for beta = 0
+            h = symm.rendezvous(t, group)
+            self.bufs.append(t)
+            self.buf_ptrs.append([int(p) for p in h.buffer_ptrs])
+        flags = symm.empty(self.BLOCKS * tp.world, dtype=torch.int32, device=device)
+        flags.zero_()
+        fh = symm.rendezvous(flags, group)
+        self.flags, self.flag_ptrs = flags, [int(p) for p in fh.buffer_ptrs]
+        self.epochs = torch.zeros(self.BLOCKS, dtype=torch.int32, device=device)
+        self._handles = fh  # keeps the mappings alive
+        self._next = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=tp.group)  # every rank's flags are zero before anyone signals
+
+    def next_buffer(self) -> int:
+        """Index of the buffer the next row-split product must write (they alternate)."""
+        i = self._next
+        self._next ^= 1
+        return i
+
+    def buffer(self, i: int, rows: int, cols: int) -> torch.Tensor:
+        return self.bufs[i][: rows * cols].view(rows, cols)
+
+    def all_reduce(self, i: int, out: torch.Tensor, residual: bool = False):
+        self.kernels.allreduce_oneshot(out, self.buf_ptrs[i], self.flag_ptrs, self.epochs,
+                                       self.BLOCKS, self.tp.rank, self.tp.world, out.numel(), residual)
 
 
 class ColumnParallelU8Linear:
@@ -116,6 +161,13 @@ class RowParallelU8Linear:
             return out
         if self.tp.world == 1:
             self.kernels.matmul_nt_fp16u8(out, x_shard, self.w.q, self.w.scales, self.w.block, 1.0, self.w.zeros)
+            return out
+        if self.tp.peer_ar is not None:
+            ar = self.tp.peer_ar
+            i = ar.next_buffer()
+            buf = ar.buffer(i, out.shape[0], out.shape[1])
+            self.kernels.matmul_nt_fp16u8(buf, x_shard, self.w.q, self.w.scales, self.w.block, 0.0, self.w.zeros)
+            ar.all_reduce(i, out, residual)
             return out
         buf = partial if partial is not None else torch.zeros_like(out)
         self.kernels.matmul_nt_fp16u8(buf, x_shard, self.w.q, self.w.scales, self.w.block, 0.0, self.w.zeros)

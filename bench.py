@@ -372,28 +372,38 @@ def run_ours_tp(args):
     x_host = torch.randn((M, d), dtype=torch.float16).pin_memory()
     x = x_host.to(dev)
     h = torch.zeros((M, d), **f16)
-    q, kx, vx = (torch.zeros((M, dl), **f16) for _ in range(3))
-    g, u = torch.zeros((M, fl), **f16), torch.zeros((M, fl), **f16)
+    qkv, att = torch.zeros((M, 3 * dl), **f16), torch.randn((M, dl), **f16)
+    gu, g = torch.zeros((M, 2 * fl), **f16), torch.randn((M, fl), **f16)
     part = torch.zeros((M, d), **f16)
     h_host = torch.zeros((M, d), dtype=torch.float16).pin_memory()
     stream = torch.cuda.current_stream()
+    use_peer = not args.nccl
+    if use_peer:
+        from adrastea_b200.tp import PeerAllReduce
+        tp.peer_ar = PeerAllReduce(kern, tp, M * d, dev)
+        note("symmetric buffers mapped")
 
-    # The step is cut at every all-reduce: the kernels between two collectives form one
-    # segment.  Segments are captured into CUDA graphs (launching from Python costs about
-    # 14 us per kernel); the NCCL calls stay eager between the replays, because capturing
-    # them hung in this environment.
+    # q/k/v and gate/up are one matrix each (adrastea_b200/llama.py); `att` and `g` stand in for
+    # the attention output and the SiluMul output, which are not part of this workload.
+    # Default: the row-split products are reduced by the library's one-shot all-reduce over peer
+    # memory, and the whole step is ONE CUDA graph.  --nccl: the step is cut at every all-reduce,
+    # the kernels between two collectives are captured as one graph each and the NCCL calls stay
+    # eager between the replays (capturing them hung in this environment).
     def seg_attn(ly):
-        ly.wq(q, x)
-        ly.wk(kx, x)
-        ly.wv(vx, x)
-        # row-split product of this rank's slice (the attention itself is not part of this workload)
-        ly.wo.kernels.matmul_nt_fp16u8(part, q, ly.wo.w.q, ly.wo.w.scales, ly.wo.w.block)
+        ly.wqkv(qkv, x)
+        if use_peer:
+            ly.wo(h, att, residual=True)
+        else:
+            ly.wo.kernels.matmul_nt_fp16u8(part, att, ly.wo.w.q, ly.wo.w.scales, ly.wo.w.block)
 
     def seg_ffn(ly):
-        h.copy_(part)  # the reduced o-projection
-        ly.gate(g, x)
-        ly.up(u, x)
-        ly.down.kernels.matmul_nt_fp16u8(part, g, ly.down.w.q, ly.down.w.scales, ly.down.w.block)
+        if not use_peer:
+            h.copy_(part)  # the reduced o-projection
+        ly.wgu(gu, x)
+        if use_peer:
+            ly.down(h, g, residual=True)
+        else:
+            ly.down.kernels.matmul_nt_fp16u8(part, g, ly.down.w.q, ly.down.w.scales, ly.down.w.block)
 
     segments = []
     for ly in layers:
@@ -404,8 +414,10 @@ def run_ours_tp(args):
     def step():
         for seg in replay:
             seg()
-            tp.all_reduce(part)
-        h.copy_(part)
+            if not use_peer:
+                tp.all_reduce(part)
+        if not use_peer:
+            h.copy_(part)
 
     def act_bytes(ly):
         b = 0
@@ -442,14 +454,21 @@ def run_ours_tp(args):
     note("second eager step done")
     graph = None
     if not args.no_graph:
-        graphs = []
-        for seg in segments:
-            gph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gph):
-                seg()
-            graphs.append(gph)
-        replay = [gph.replay for gph in graphs]
-        graph = graphs
+        if use_peer:
+            whole = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(whole):
+                step()
+            replay = [whole.replay]
+            graph = [whole]
+        else:
+            graphs = []
+            for seg in segments:
+                gph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(gph):
+                    seg()
+                graphs.append(gph)
+            replay = [gph.replay for gph in graphs]
+            graph = graphs
     note("segments captured" if graph else "eager segments")
     run = step
     note(f"graph={'yes' if graph is not None else 'no'}")
@@ -490,8 +509,9 @@ def run_ours_tp(args):
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic",
             "config": {"workload": "configs[4]: LLaMA-65B-shape decode linears, M=16, hidden 8192, FFN 22016, "
-                                   "block 64, tensor-parallel: column-split q/k/v/gate/up, row-split o/down, "
-                                   "NCCL all-reduce after o and down",
+                                   "block 64, tensor-parallel: column-split qkv and gate/up, row-split o/down, "
+                                   + ("one-shot all-reduce over peer memory after o and down, one CUDA graph per step"
+                                      if use_peer else "NCCL all-reduce after o and down (eager, between graph segments)"),
                        "layers_per_step": TP_LAYERS, "tp": world,
                        "weight_bytes_per_step_all_ranks": int(total_bytes),
                        "all_reduces_per_step": 2 * TP_LAYERS, "all_reduce_bytes": M * d * 2,
@@ -504,7 +524,7 @@ def run_ours_tp(args):
             "gpu_launches": int(launches_per_step * args.steps),
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
-                         "kernel": "u8_ring_kernel (+ ncclAllReduce between row-split products)"},
+                         "kernel": "u8_ring_kernel + " + ("allreduce_oneshot_kernel" if use_peer else "ncclAllReduce")},
             "clocks": clocks,
         }
         print(json.dumps(line))
@@ -553,6 +573,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: do not capture the step in a CUDA graph")
+    ap.add_argument("--nccl", action="store_true",
+                    help="N > 1: reduce the row-split products with NCCL instead of the library's peer-memory kernel")
     ap.add_argument("--profile-case", default=None, choices=["u8", "f16"],
                     help="run a small fixed case of one kernel family and exit (for ncu captures)")
     ap.add_argument("--m", type=int, default=1, help="rows of the activation in --profile-case")

@@ -263,6 +263,24 @@ int adr_decode_attention(adr_ctx* ctx, adr_stream stream, void* out, const void*
                          const int32_t* pos_dev, float scale);
 
 /*
+ * No counterpart in the reference (it has no multi-GPU path, llama.rs:28-29): one-shot
+ * all-reduce (sum) of an fp16 vector over peer memory, for the row-split products of
+ * tensor-parallel decoding.  bufs[r] is rank r's partial vector and flags[r] rank r's flag array
+ * (`blocks` * world 32-bit words, zero before the first call), all addressable from this GPU
+ * (peer-mapped symmetric allocations); `epochs` is `blocks` 32-bit words of this rank's own
+ * memory, zero before the first call.  out[i] = fp16(sum_r bufs[r][i] (+ out[i] if residual)),
+ * summed in rank order in fp32, so every rank gets the same bits.  Every rank must make the same
+ * sequence of calls with the same `blocks`, and consecutive calls must alternate between two
+ * buffers (a buffer may be rewritten only after the NEXT all-reduce has been enqueued behind this
+ * one).  The wait for the peers is bounded (about a second), after which the status word is set
+ * (adr_device_status) and the call completes with a wrong result rather than hanging.
+ * count % 8 == 0, world <= 8.
+ */
+int adr_allreduce_oneshot(adr_ctx* ctx, adr_stream stream, void* out, const void* const* bufs,
+                          void* const* flags, void* epochs, int blocks, int rank, int world,
+                          long long count, int residual);
+
+/*
  * Replaces MatmulTracer (kernels.rs:231-248, 306-333).  When enabled, every
  * matmul call records (m, k, n, batches, strides, ops, kernel family) once per
  * distinct combination.  adr_trace_dump writes one JSON object per line into
