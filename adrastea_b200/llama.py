@@ -273,6 +273,7 @@ def main():
     ap.add_argument("--layers", type=int, default=0, help="use only the first N layers (0 = all)")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-pdl", action="store_true")
+    ap.add_argument("--nccl", action="store_true", help="tensor parallel: NCCL all-reduce in decode too (no graph)")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -282,7 +283,13 @@ def main():
     kern = GpuKernels(local)
     kern.set_tunable("pdl", 0 if args.no_pdl else 1)
     shape = LLAMA_7B if args.shape == "7b" else LLAMA_65B
-    model = LlamaU8(kern, shape, TPContext(), max_batch=args.batch,
+    tp = TPContext()
+    if world > 1 and not args.nccl:
+        # decode-size all-reduces go through the library's one-shot kernel over peer memory, which
+        # (unlike an NCCL call here) can be captured with the step; prefill-size ones stay on NCCL
+        from .tp import PeerAllReduce
+        tp.peer_ar = PeerAllReduce(kern, tp, args.batch * shape.dim, torch.device("cuda", local))
+    model = LlamaU8(kern, shape, tp, max_batch=args.batch,
                     max_seq=args.prefill + args.decode, n_layers=args.layers or None,
                     device=torch.device("cuda", local))
     toks = torch.randint(0, shape.vocab, (args.batch, args.prefill), device=model.device)
@@ -290,7 +297,7 @@ def main():
     e[0].record()
     model.prefill(toks)
     e[1].record()
-    if not args.no_graph:
+    if not args.no_graph and not (world > 1 and args.nccl):
         pos0, tok0 = model.pos.clone(), model.tokens.clone()
         model.capture()
         model.pos.copy_(pos0)

@@ -100,6 +100,7 @@ class PeerAllReduce:
         import torch.distributed._symmetric_memory as symm
         assert tp.world > 1
         self.kernels, self.tp = kernels, tp
+        self.max_elems = max_elems
         group = tp.group if tp.group is not None else dist.group.WORLD
         self.bufs, self.buf_ptrs = [], []
         for _ in range(2):
@@ -162,7 +163,7 @@ class RowParallelU8Linear:
         if self.tp.world == 1:
             self.kernels.matmul_nt_fp16u8(out, x_shard, self.w.q, self.w.scales, self.w.block, 1.0, self.w.zeros)
             return out
-        if self.tp.peer_ar is not None:
+        if self.tp.peer_ar is not None and out.numel() <= self.tp.peer_ar.max_elems:
             ar = self.tp.peer_ar
             i = ar.next_buffer()
             buf = ar.buffer(i, out.shape[0], out.shape[1])
