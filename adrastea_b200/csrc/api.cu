@@ -292,6 +292,35 @@ int adr_matmul_nt_f16(adr_ctx* ctx, adr_stream stream, void* out, const void* lh
   return run_matmul(ctx, (cudaStream_t)stream, a, false, true);
 }
 
+int adr_matmul_nt_fp16u8_allreduce(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                                   const uint8_t* rhs, const void* scales, const void* zeros, int m,
+                                   int p, int n, int block_size, int residual,
+                                   void* const* inboxes, void* const* flags, void* epochs,
+                                   int max_ctas, int rank, int world) {
+  if (!ctx || !out || !lhs || !rhs || !scales || !inboxes || !flags || !epochs) return ADR_ERR_INVALID;
+  if (m <= 0 || p <= 0 || n <= 0 || block_size <= 0 || max_ctas <= 0) return ADR_ERR_INVALID;
+  if (world < 2 || world > 8 || rank < 0 || rank >= world) return ADR_ERR_INVALID;
+  if (m > 16 || p % block_size != 0) return ADR_ERR_SHAPE;
+  if (!aligned16(lhs) || !aligned16(rhs)) return ADR_ERR_SHAPE;
+  U8Args a{(__half*)out, (const __half*)lhs, rhs, (const __half*)scales, (const __half*)zeros,
+           m, p, n, block_size, 0.0f};
+  if (!u8_ring_supports(ctx, a)) return ADR_ERR_SHAPE;
+  RingArFuse ar = {};
+  for (int r = 0; r < world; ++r) {
+    if (!inboxes[r] || !flags[r]) return ADR_ERR_INVALID;
+    ar.inbox[r] = static_cast<__half*>(inboxes[r]);
+    ar.flags[r] = static_cast<unsigned int*>(flags[r]);
+  }
+  ar.epochs = static_cast<unsigned int*>(epochs);
+  ar.rank = rank;
+  ar.world = world;
+  ar.residual = residual ? 1 : 0;
+  ar.max_ctas = max_ctas;
+  int rc = launch_u8_ring(ctx, (cudaStream_t)stream, a, &ar);
+  if (rc == ADR_OK) ctx->last_kernel = ADR_KERNEL_U8_RING;
+  return rc;
+}
+
 int adr_dequantize_absmax_uint8(adr_ctx* ctx, adr_stream stream, void* out, const void* scales,
                                 const void* zeros, const uint8_t* q, int rows, int k,
                                 int block_size) {

@@ -183,7 +183,15 @@ int launch_u8_gemv(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 int launch_u8_mma(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 int launch_u8_stream(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 bool u8_stream_supports(const adr_ctx* ctx, const U8Args& a);
-int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
+// Optional fusion of a tensor-parallel all-reduce into the ring kernel (u8_ring.cu): inbox[r] and
+// flags[r] are rank r's symmetric allocations as addressable from this GPU.
+struct RingArFuse {
+  __half* inbox[8];
+  unsigned int* flags[8];
+  unsigned int* epochs;
+  int rank, world, residual, max_ctas;
+};
+int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingArFuse* ar = nullptr);
 bool u8_ring_supports(const adr_ctx* ctx, const U8Args& a);
 int launch_u8_tc(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 bool u8_tc_supports(const adr_ctx* ctx, const U8Args& a);

@@ -74,6 +74,14 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
 __device__ __forceinline__ void named_bar_arrive(int id, int threads) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
+__device__ __forceinline__ void st_release_sys_u32(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
 constexpr int RING_RED_BUFS = 4;  // partial-sum buffers (and named barriers) in rotation
 
 struct RingParams {
@@ -88,6 +96,12 @@ struct RingParams {
   int stage_bytes;   // distance between ring stages
   int xss;           // XR: bytes between activation rows inside a stage
   unsigned int* status;
+  // fused all-reduce (ar_world > 1): the unit results are pushed to every rank's inbox
+  // [world][m][n] fp16 (slot = pushing rank) and summed after a flag exchange per CTA
+  __half* ar_inbox[8];         // inbox of rank p, addressable from this GPU
+  unsigned int* ar_flags[8];   // flag array of rank p: [ctas][world]
+  unsigned int* ar_epochs;     // this rank's per-CTA epoch counters
+  int ar_rank, ar_world, ar_residual;
 };
 
 // MT: 8-token column blocks.  NCW: consumer warps (a multiple of 8).
@@ -347,7 +361,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
       const bool summer = ROTATE ? (ui % NCW) == cw : true;
       constexpr int OPL = ROTATE ? 16 * TOK / 32 : 1;  // outputs per summing thread
       float old[OPL];
-      if (summer) {
+      const bool fused_ar = p.ar_world > 1;
+      if (summer && !fused_ar) {
 #pragma unroll
         for (int j = 0; j < OPL; ++j) {
           const int e = ROTATE ? lane + 32 * j : tid - 32, row = e & 15, tok = e >> 4;
@@ -456,7 +471,61 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
             float v = 0.0f;
 #pragma unroll
             for (int w = 0; w < NCW; ++w) v += rb[(size_t)w * 16 * RED_LD + row * RED_LD + tok];
-            a.out[(size_t)tok * a.n + n0 + row] = __float2half_rn(fmaf(a.beta, old[j], v));
+            if (!fused_ar) {
+              a.out[(size_t)tok * a.n + n0 + row] = __float2half_rn(fmaf(a.beta, old[j], v));
+            } else {
+              // this rank's partial result goes into slot ar_rank of every rank's inbox (peer
+              // stores; 16 lanes cover 32 contiguous bytes of one token's row)
+              const __half hv = __float2half_rn(v);
+              const size_t off = ((size_t)p.ar_rank * a.m + tok) * a.n + n0 + row;
+              for (int r = 0; r < p.ar_world; ++r) p.ar_inbox[r][off] = hv;
+            }
+          }
+        }
+      }
+    }
+    if (p.ar_world > 1) {
+      // ---- fused all-reduce.  CTA c of every rank works on the same units, so it needs only
+      // the partial results pushed by CTA c of the peers: make this CTA's pushes visible, tell
+      // CTA c of every peer, wait (bounded) for theirs, then add the world slots of this rank's
+      // own inbox in rank order (plus the residual) for the units of this CTA.
+      // (the word after the abort flag in the barrier area: no static shared memory, which
+      // would push the dynamic area past half an SM)
+      volatile unsigned int* s_ar_epoch = reinterpret_cast<volatile unsigned int*>(abort_flag + 1);
+      __threadfence_system();
+      if (tid == 32) {
+        const unsigned int e = p.ar_epochs[blockIdx.x] + 1u;
+        p.ar_epochs[blockIdx.x] = e;
+        *s_ar_epoch = e;
+      }
+      named_bar_sync(14, NCW * 32);
+      const unsigned int epoch = *s_ar_epoch;
+      const int pe = tid - 32;
+      if (pe < p.ar_world) {
+        st_release_sys_u32(p.ar_flags[pe] + (size_t)blockIdx.x * p.ar_world + p.ar_rank, epoch);
+        const unsigned int* mine = p.ar_flags[p.ar_rank] + (size_t)blockIdx.x * p.ar_world + pe;
+        const long long t0 = clock64();
+        while ((int)(ld_acquire_sys_u32(mine) - epoch) < 0) {
+          if (clock64() - t0 > kWaitLimitCycles) {
+            atomicOr(p.status, 256u);
+            break;
+          }
+        }
+        __threadfence_system();
+      }
+      named_bar_sync(14, NCW * 32);
+      const __half* box = p.ar_inbox[p.ar_rank];
+      const size_t slot = (size_t)a.m * a.n;
+      for (int ui = 0; ui < my_units; ++ui) {
+        const int n0 = ((int)blockIdx.x + ui * (int)gridDim.x) * 16;
+        for (int e = pe; e < 16 * a.m; e += NCW * 32) {
+          const int row = e & 15, tok = e >> 4;
+          if (n0 + row < a.n) {
+            const size_t off = (size_t)tok * a.n + n0 + row;
+            float v = p.ar_residual ? __half2float(a.out[off]) : 0.0f;
+            for (int r = 0; r < p.ar_world; ++r)
+              v += __half2float(__ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(box + r * slot + off))));
+            a.out[off] = __float2half_rn(v);
           }
         }
       }
@@ -548,7 +617,8 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
 }
 
 template <int MT, bool Z, bool PDL, int NCW, bool XR>
-int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl) {
+int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl,
+                  const RingArFuse* ar) {
   auto kfn = u8_ring_kernel<MT, NCW, Z, PDL, XR>;
   static bool configured[64] = {};
   cudaError_t e;
@@ -582,9 +652,22 @@ int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
   p.stage_bytes = pl.stage_bytes;
   p.xss = pl.xss;
   p.status = ctx->d_status;
+  p.ar_world = 0;
+  if (ar) {
+    for (int r = 0; r < ar->world; ++r) {
+      p.ar_inbox[r] = ar->inbox[r];
+      p.ar_flags[r] = ar->flags[r];
+    }
+    p.ar_epochs = ar->epochs;
+    p.ar_rank = ar->rank;
+    p.ar_world = ar->world;
+    p.ar_residual = ar->residual;
+  }
   const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(std::min(p.units, sms * pl.cps), 1, 1);
+  const int grid = std::min(p.units, sms * pl.cps);
+  if (ar && grid > ar->max_ctas) return ADR_ERR_SHAPE;  // the flag arrays do not cover this grid
+  cfg.gridDim = dim3(grid, 1, 1);
   cfg.blockDim = dim3((NCW + 1) * 32, 1, 1);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = stream;
@@ -608,16 +691,16 @@ bool u8_ring_supports(const adr_ctx* ctx, const U8Args& a) {
   return plan_ring(ctx, a, pl);
 }
 
-int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
+int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingArFuse* ar) {
   RingPlan pl;
   if (!plan_ring(ctx, a, pl)) return ADR_ERR_SHAPE;
   const bool z = a.zeros != nullptr, two = a.m > 8, pdl = ctx->tune_pdl != 0;
 #define ADR_RING_CASE(MT, Z)                                                       \
   if (pl.xr)                                                                       \
-    return pdl ? launch_ring_p<MT, Z, true, 8, true>(ctx, stream, a, pl)           \
-               : launch_ring_p<MT, Z, false, 8, true>(ctx, stream, a, pl);         \
-  return pdl ? launch_ring_p<MT, Z, true, 8, false>(ctx, stream, a, pl)            \
-             : launch_ring_p<MT, Z, false, 8, false>(ctx, stream, a, pl)
+    return pdl ? launch_ring_p<MT, Z, true, 8, true>(ctx, stream, a, pl, ar)       \
+               : launch_ring_p<MT, Z, false, 8, true>(ctx, stream, a, pl, ar);     \
+  return pdl ? launch_ring_p<MT, Z, true, 8, false>(ctx, stream, a, pl, ar)        \
+             : launch_ring_p<MT, Z, false, 8, false>(ctx, stream, a, pl, ar)
   if (two) {
     if (z) { ADR_RING_CASE(2, true); }
     ADR_RING_CASE(2, false);

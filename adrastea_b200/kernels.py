@@ -420,6 +420,26 @@ class GpuKernels:
             out.stride(-2), pos_dev.data_ptr(), scale)
         self._check(rc)
 
+    def matmul_nt_fp16u8_allreduce(self, output: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor,
+                                   scales: torch.Tensor, block_size: int, residual: bool,
+                                   inbox_ptrs, flag_ptrs, epochs: torch.Tensor, max_ctas: int,
+                                   rank: int, world: int, zeros: torch.Tensor | None = None,
+                                   stream=None):
+        """adr_matmul_nt_fp16u8_allreduce: the row-split u8 product with its all-reduce in the same
+        kernel; raises AdrError(ADR_ERR_SHAPE) for shapes the decode kernel does not take."""
+        m, p = lhs.shape
+        n = rhs.shape[0]
+        assert rhs.shape == (n, p) and output.shape == (m, n) and scales.shape == (n, p // block_size)
+        for t in (output, lhs, rhs, scales):
+            assert t.is_contiguous() and t.is_cuda
+        boxes = (C.c_void_p * world)(*[int(x) for x in inbox_ptrs])
+        flags = (C.c_void_p * world)(*[int(x) for x in flag_ptrs])
+        rc = self._lib.adr_matmul_nt_fp16u8_allreduce(
+            self._ctx, _stream_handle(stream), output.data_ptr(), lhs.data_ptr(), rhs.data_ptr(),
+            scales.data_ptr(), zeros.data_ptr() if zeros is not None else None, m, p, n, block_size,
+            int(residual), boxes, flags, epochs.data_ptr(), max_ctas, rank, world)
+        self._check(rc)
+
     def allreduce_oneshot(self, out: torch.Tensor, buf_ptrs, flag_ptrs, epochs: torch.Tensor,
                           blocks: int, rank: int, world: int, count: int, residual: bool,
                           stream=None):

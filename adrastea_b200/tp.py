@@ -95,6 +95,7 @@ class PeerAllReduce:
     alternately.  Unlike an NCCL call the kernel can be captured in a CUDA graph."""
 
     BLOCKS = 64
+    MAX_CTAS = 512
 
     def __init__(self, kernels, tp: "TPContext", max_elems: int, device):
         import torch.distributed._symmetric_memory as symm
@@ -116,6 +117,22 @@ class PeerAllReduce:
         self.epochs = torch.zeros(self.BLOCKS, dtype=torch.int32, device=device)
         self._handles = fh  # keeps the mappings alive
         self._next = 0
+        # for the GEMV with the all-reduce fused in: two inboxes of `world` slots, flags and epochs
+        # per CTA of the decode kernel
+        self.inboxes, self.inbox_ptrs = [], []
+        for _ in range(2):
+            t = symm.empty(tp.world * max_elems, dtype=torch.float16, device=device)
+            t.zero_()
+            h = symm.rendezvous(t, group)
+            self.inboxes.append(t)
+            self.inbox_ptrs.append([int(p) for p in h.buffer_ptrs])
+        fflags = symm.empty(self.MAX_CTAS * tp.world, dtype=torch.int32, device=device)
+        fflags.zero_()
+        ffh = symm.rendezvous(fflags, group)
+        self.fused_flags, self.fused_flag_ptrs = fflags, [int(p) for p in ffh.buffer_ptrs]
+        self.fused_epochs = torch.zeros(self.MAX_CTAS, dtype=torch.int32, device=device)
+        self._handles2 = ffh
+        self.fused = True  # RowParallelU8Linear tries the fused kernel first
         torch.cuda.synchronize(device)
         dist.barrier(group=tp.group)  # every rank's flags are zero before anyone signals
 
@@ -166,6 +183,17 @@ class RowParallelU8Linear:
         if self.tp.peer_ar is not None and out.numel() <= self.tp.peer_ar.max_elems:
             ar = self.tp.peer_ar
             i = ar.next_buffer()
+            if ar.fused and out.shape[0] <= 16 and out.is_contiguous():
+                from .kernels import AdrError
+                try:
+                    self.kernels.matmul_nt_fp16u8_allreduce(
+                        out, x_shard, self.w.q, self.w.scales, self.w.block, residual,
+                        ar.inbox_ptrs[i], ar.fused_flag_ptrs, ar.fused_epochs, ar.MAX_CTAS,
+                        self.tp.rank, self.tp.world, self.w.zeros)
+                    return out
+                except AdrError as e:
+                    if e.code != 2:  # ADR_ERR_SHAPE: a shape the decode kernel does not take
+                        raise
             buf = ar.buffer(i, out.shape[0], out.shape[1])
             self.kernels.matmul_nt_fp16u8(buf, x_shard, self.w.q, self.w.scales, self.w.block, 0.0, self.w.zeros)
             ar.all_reduce(i, out, residual)

@@ -281,6 +281,27 @@ int adr_allreduce_oneshot(adr_ctx* ctx, adr_stream stream, void* out, const void
                           long long count, int residual);
 
 /*
+ * No counterpart in the reference: the row-split product of tensor-parallel decoding with its
+ * all-reduce in the same kernel.  Each rank holds a [n, p] slice (p = K / world) of the weight and
+ * the matching slice of the activations; out[m, n] = sum over ranks of lhs_r . deq(rhs_r)^T (+ the
+ * old out if residual), the same bits on every rank.  The decode kernel pushes the result of every
+ * 16-column unit, as fp16, into slot `rank` of every rank's inbox ([world][m][n] fp16, peer-mapped:
+ * inboxes[r] is rank r's inbox as addressable from this GPU), then CTA c exchanges one flag with
+ * CTA c of every peer (flags[r]: rank r's array of max_ctas * world 32-bit words, zero before the
+ * first call; epochs: max_ctas words of this rank's own memory, zero before the first call; the
+ * wait is bounded, see adr_allreduce_oneshot) and adds the world slots of its own inbox in rank
+ * order.  Consecutive calls must alternate between two inboxes.  Every rank must make the same
+ * calls with the same shapes.  m <= 16 and a shape the persistent decode kernel takes
+ * (block_size 64 or 128, p % 128 == 0), else ADR_ERR_SHAPE: fall back to adr_matmul_nt_fp16u8 +
+ * adr_allreduce_oneshot.
+ */
+int adr_matmul_nt_fp16u8_allreduce(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                                   const uint8_t* rhs, const void* scales, const void* zeros, int m,
+                                   int p, int n, int block_size, int residual,
+                                   void* const* inboxes, void* const* flags, void* epochs,
+                                   int max_ctas, int rank, int world);
+
+/*
  * Replaces MatmulTracer (kernels.rs:231-248, 306-333).  When enabled, every
  * matmul call records (m, k, n, batches, strides, ops, kernel family) once per
  * distinct combination.  adr_trace_dump writes one JSON object per line into

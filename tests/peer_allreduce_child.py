@@ -76,12 +76,42 @@ def main():
     k.matmul_nt_fp16u8(want, x, q, sc, bs)
     tp.peer_ar = PeerAllReduce(k, tp, M * n, dev)
     lin = RowParallelU8Linear(k, U8Weight(q, sc, bs), tp)
-    got = torch.zeros((M, n), device=dev, dtype=torch.float16)
     shard = x[:, rank * kk // world:(rank + 1) * kk // world].contiguous()
-    lin(got, shard)
-    torch.cuda.synchronize()
-    rel = ((got.float() - want.float()).abs().max() / want.float().abs().max()).item()
-    assert rel < 5e-3, rel
+    scale = want.float().abs().max()
+    for fused in (False, True):  # GEMV + all-reduce kernel, then the all-reduce inside the GEMV kernel
+        tp.peer_ar.fused = fused
+        got = torch.zeros((M, n), device=dev, dtype=torch.float16)
+        lin(got, shard)
+        torch.cuda.synchronize()
+        rel = ((got.float() - want.float()).abs().max() / scale).item()
+        assert rel < 5e-3, (fused, rel)
+        # with the residual, four calls in a row (the inboxes alternate), replayed from a graph
+        acc = torch.zeros((M, n), device=dev, dtype=torch.float16)
+
+        def four():
+            for _ in range(4):
+                lin(acc, shard, residual=True)
+
+        four()
+        torch.cuda.synchronize()
+        rel = ((acc.float() - 4 * want.float()).abs().max() / (4 * scale)).item()
+        assert rel < 5e-3, (fused, "residual", rel)
+        dist.barrier()
+        gg = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gg):
+            four()
+        acc.zero_()
+        gg.replay()
+        gg.replay()
+        torch.cuda.synchronize()
+        rel = ((acc.float() - 8 * want.float()).abs().max() / (8 * scale)).item()
+        assert rel < 5e-3, (fused, "graph", rel)
+        bits = acc.view(torch.int16).to(torch.int32)
+        lo, hi = bits.clone(), bits.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        assert torch.equal(lo, hi), "ranks disagree"
+        k.device_status()
     k.device_status()
     dist.barrier()
     dist.destroy_process_group()
