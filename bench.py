@@ -381,6 +381,7 @@ def run_ours_tp(args):
     if use_peer:
         from adrastea_b200.tp import PeerAllReduce
         tp.peer_ar = PeerAllReduce(kern, tp, M * d, dev)
+        tp.peer_ar.fused = args.fused_ar
         note("symmetric buffers mapped")
 
     # q/k/v and gate/up are one matrix each (adrastea_b200/llama.py); `att` and `g` stand in for
@@ -524,7 +525,8 @@ def run_ours_tp(args):
             "gpu_launches": int(launches_per_step * args.steps),
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
-                         "kernel": "u8_ring_kernel + " + ("allreduce_oneshot_kernel" if use_peer else "ncclAllReduce")},
+                         "kernel": "u8_ring_kernel" + (" with the all-reduce fused in" if use_peer and args.fused_ar
+                                                     else " + allreduce_oneshot_kernel" if use_peer else " + ncclAllReduce")},
             "clocks": clocks,
         }
         print(json.dumps(line))
@@ -573,6 +575,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: do not capture the step in a CUDA graph")
+    ap.add_argument("--fused-ar", action="store_true",
+                    help="N > 1: all-reduce inside the row-split GEMV kernel instead of a kernel of its own")
     ap.add_argument("--nccl", action="store_true",
                     help="N > 1: reduce the row-split products with NCCL instead of the library's peer-memory kernel")
     ap.add_argument("--profile-case", default=None, choices=["u8", "f16"],
