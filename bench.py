@@ -539,6 +539,7 @@ def run_profile_case(args):
     u8 : the decode kernel over 12 distinct [--n,4096] u8 weights (201 MB at n = 4096, larger
          than L2), two passes, m = --m.
     f16: the tensor-core GEMM, [m,4096] x [4096,4096]^T over 6 distinct weights, m = --m.
+    attn: the decode-attention kernel, batch --m, 32 heads x 128, 600 of 640 cached positions.
     """
     import torch
 
@@ -554,6 +555,17 @@ def run_profile_case(args):
         for _ in range(2):
             for q, s in ws:
                 kern.matmul_nt_fp16u8(o, x, q, s, BS)
+    elif args.profile_case == "attn":
+        # decode attention at the LLaMA-7B shape: batch --m sequences, 32 heads of 128, 600 cached
+        # positions of 640 (K and V caches of 84 MB each at batch 16)
+        B, H, hd, S = m, 32, 128, 640
+        kc = torch.randn((B, S, H * hd), device="cuda").half()
+        vc = torch.randn((B, S, H * hd), device="cuda").half()
+        q = torch.randn((B, H * hd), device="cuda").half()
+        o = torch.zeros((B, H * hd), dtype=torch.float16, device="cuda")
+        pos = torch.tensor([599], dtype=torch.int32, device="cuda")
+        for _ in range(4):
+            kern.decode_attention(TensorView.of(o), TensorView.of(q), kc, vc, H, pos, 1.0 / 128 ** 0.5)
     else:
         ws = [(torch.randn(4096, K, device="cuda") * 0.02).half() for _ in range(6)]
         a = (torch.randn(m, K, device="cuda") * 0.02).half()
@@ -579,7 +591,7 @@ def main():
                     help="N > 1: all-reduce inside the row-split GEMV kernel instead of a kernel of its own")
     ap.add_argument("--nccl", action="store_true",
                     help="N > 1: reduce the row-split products with NCCL instead of the library's peer-memory kernel")
-    ap.add_argument("--profile-case", default=None, choices=["u8", "f16"],
+    ap.add_argument("--profile-case", default=None, choices=["u8", "f16", "attn"],
                     help="run a small fixed case of one kernel family and exit (for ncu captures)")
     ap.add_argument("--m", type=int, default=1, help="rows of the activation in --profile-case")
     ap.add_argument("--n", type=int, default=4096, help="weight rows in --profile-case u8")
