@@ -151,6 +151,7 @@ class LlamaU8:
         self.tokens = torch.zeros((B,), dtype=torch.int64, device=self.device)
         self.next_tokens = torch.zeros((B,), dtype=torch.int64, device=self.device)
         self._graph = None
+        self._deq = None  # fp16 scratch for one expanded weight matrix (prefill)
 
     # ------------------------------------------------------------------ sizes
     def weight_bytes_per_token(self) -> int:
@@ -210,6 +211,43 @@ class LlamaU8:
         self.pos.add_(1)
 
     # ------------------------------------------------------------- prefill
+    # ------------------------------------------------------------- prefill
+    PREFILL_DEQUANT_ROWS = 1024
+
+    def _prefill_linear(self, lin, out: torch.Tensor, x: torch.Tensor, part: torch.Tensor | None = None,
+                        residual: bool = False):
+        """A linear layer over many rows.  From PREFILL_DEQUANT_ROWS rows on, the u8 matrix is
+        first expanded to fp16 in a scratch buffer (`adr_dequantize_absmax_uint8`: the fp16-rounded
+        weights of the reference's WMMA kernel) and multiplied by the fp16 tensor-core GEMM, which
+        runs at more than twice the rate of the dequantising GEMM; the expansion costs one pass
+        over the matrix per call.  Fewer rows go through `adr_matmul_nt_fp16u8`."""
+        w = lin.w
+        rows = x.shape[0]
+        row_split = isinstance(lin, RowParallelU8Linear)
+        if rows < self.PREFILL_DEQUANT_ROWS or w.zeros is not None:
+            return lin(out, x, part, residual=residual) if row_split else lin(out, x)
+        need = w.n * w.k
+        if self._deq is None or self._deq.numel() < need:
+            self._deq = torch.empty(need, dtype=torch.float16, device=self.device)
+        wf = self._deq[:need].view(w.n, w.k)
+        self.k.dequantize_absmax_uint8(wf, w.scales, w.q)
+        wv = TensorView.of(wf).permute([1, 0])
+        if not row_split:
+            self.k.matmul_f16(TensorView.of(out), TensorView.of(x), wv)
+            return out
+        if self.tp.world == 1:
+            opts = MatmulOptions.new().store(MatmulStore.Add()) if residual else MatmulOptions.new()
+            self.k.matmul_f16(TensorView.of(out), TensorView.of(x), wv, opts)
+            return out
+        buf = part if part is not None else torch.zeros_like(out)
+        self.k.matmul_f16(TensorView.of(buf), TensorView.of(x), wv)
+        self.tp.all_reduce(buf)
+        if residual:
+            out.add_(buf)
+        else:
+            out.copy_(buf)
+        return out
+
     def prefill(self, tokens: torch.Tensor):
         """tokens: [B, S0] int64.  Fills the cache for positions [0, S0) and leaves the
         last-position argmax in self.tokens, self.pos = S0."""
@@ -230,7 +268,7 @@ class LlamaU8:
         scale = 1.0 / math.sqrt(hd)
         for li, ly in enumerate(self.layers):
             self._norm(x, h, ly.attn_norm)
-            ly.wqkv(qkv, x)
+            self._prefill_linear(ly.wqkv, qkv, x)
             for b in range(B):  # one sequence at a time, with the reference's views (llama.rs:503-554)
                 rows = qkv[b * S0:(b + 1) * S0]
                 q_b, k_b, v_b = (rows[:, i * dl:(i + 1) * dl] for i in range(3))
@@ -243,11 +281,11 @@ class LlamaU8:
                 self.k.matmul_f16(head(att[b * S0:(b + 1) * S0], [1, 0, 2]), sv, head(v_b, [1, 0, 2]))
             self.k_cache[li][:, :S0].copy_(qkv[:, dl:2 * dl].view(B, S0, dl))
             self.v_cache[li][:, :S0].copy_(qkv[:, 2 * dl:].view(B, S0, dl))
-            ly.wo(h, att, part, residual=True)
+            self._prefill_linear(ly.wo, h, att, part, residual=True)
             self._norm(x, h, ly.ffn_norm)
-            ly.wgu(gu, x)
+            self._prefill_linear(ly.wgu, gu, x)
             self._silu_mul(g, gu)
-            ly.down(h, g, part, residual=True)
+            self._prefill_linear(ly.down, h, g, part, residual=True)
         last = h.view(B, S0, d)[:, -1].contiguous()
         self._norm(self.x, last, self.out_norm)
         self.k.matmul_nt_fp16u8(self.logits, self.x, self.lm_head.q, self.lm_head.scales, self.lm_head.block)

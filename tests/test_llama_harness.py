@@ -44,13 +44,15 @@ def ref_forward(model, kernels, tokens_hist):
     return lin(last, model.lm_head)
 
 
-@pytest.mark.parametrize("graph", [False, True])
-def test_prefill_and_decode_match_full_recomputation(kernels, graph):
+@pytest.mark.parametrize("graph,expand", [(False, False), (True, False), (False, True)])
+def test_prefill_and_decode_match_full_recomputation(kernels, graph, expand):
     from adrastea_b200.llama import LlamaShape, LlamaU8
     torch.manual_seed(0)
     shape = LlamaShape(dim=256, n_heads=4, ffn=512, n_layers=2, vocab=512, block=64)
     B, S0, steps = 2, 12, 3
     model = LlamaU8(kernels, shape, max_batch=B, max_seq=S0 + steps, seed=3)
+    if expand:  # prefill through the fp16 expansion of the weights + tensor-core GEMM
+        model.PREFILL_DEQUANT_ROWS = 8
     model.embed.mul_(0.5)
     toks = torch.randint(0, shape.vocab, (B, S0), device="cuda")
     model.prefill(toks)
