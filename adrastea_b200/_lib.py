@@ -44,6 +44,8 @@ SIGNATURES = {
                              + [_vp, C.c_float]),
     "adr_allreduce_oneshot": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int,
                                        C.c_longlong, _c_int]),
+    "adr_rms_norm_matmul_nt_fp16u8": (_c_int, [_vp, _vp, _vp, _vp, _vp, C.c_float, _vp, _vp, _vp,
+                                             _c_int, _c_int, _c_int, _c_int, C.c_float]),
     "adr_matmul_nt_fp16u8_allreduce": (_c_int, [_vp] * 7 + [_c_int] * 5 + [_vp, _vp, _vp]
                                        + [_c_int] * 3),
     "adr_trace_enable": (_c_int, [_vp, _c_int]),

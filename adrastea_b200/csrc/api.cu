@@ -292,6 +292,24 @@ int adr_matmul_nt_f16(adr_ctx* ctx, adr_stream stream, void* out, const void* lh
   return run_matmul(ctx, (cudaStream_t)stream, a, false, true);
 }
 
+int adr_rms_norm_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                                  const void* norm_weights, float eps, const uint8_t* rhs,
+                                  const void* scales, const void* zeros, int m, int p, int n,
+                                  int block_size, float beta) {
+  if (!ctx || !out || !lhs || !norm_weights || !rhs || !scales) return ADR_ERR_INVALID;
+  if (m <= 0 || p <= 0 || n <= 0 || block_size <= 0) return ADR_ERR_INVALID;
+  if (m > 16 || p % block_size != 0) return ADR_ERR_SHAPE;
+  if (!aligned16(lhs) || !aligned16(rhs) || !aligned16(norm_weights)) return ADR_ERR_SHAPE;
+  U8Args a{(__half*)out, (const __half*)lhs, rhs, (const __half*)scales, (const __half*)zeros,
+           m, p, n, block_size, beta};
+  a.norm_w = (const __half*)norm_weights;
+  a.norm_eps = eps;
+  if (!u8_ring_supports(ctx, a)) return ADR_ERR_SHAPE;
+  int rc = launch_u8_ring(ctx, (cudaStream_t)stream, a);
+  if (rc == ADR_OK) ctx->last_kernel = ADR_KERNEL_U8_RING;
+  return rc;
+}
+
 int adr_matmul_nt_fp16u8_allreduce(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
                                    const uint8_t* rhs, const void* scales, const void* zeros, int m,
                                    int p, int n, int block_size, int residual,

@@ -177,6 +177,9 @@ struct U8Args {
   const __half* zeros;
   int m, p, n, block_size;
   float beta;
+  // optional: rms_norm of the rows of lhs before the product (u8 ring kernel only)
+  const __half* norm_w = nullptr;
+  float norm_eps = 0.0f;
 };
 int launch_u8_simt(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 int launch_u8_gemv(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);

@@ -102,6 +102,9 @@ struct RingParams {
   unsigned int* ar_flags[8];   // flag array of rank p: [ctas][world]
   unsigned int* ar_epochs;     // this rank's per-CTA epoch counters
   int ar_rank, ar_world, ar_residual;
+  // fused rms_norm of the activations (norm_w != nullptr; resident activations only)
+  const __half* norm_w;
+  float norm_eps;
 };
 
 // MT: 8-token column blocks.  NCW: consumer warps (a multiple of 8).
@@ -259,6 +262,58 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     bool ok = true;
     if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
     ok = mbar_wait(xbar, 0);
+
+    // ---- optional rms_norm of the activation rows, in place in shared memory, with the bits of
+    // the reference kernel (normalize.cu:7-58; rowops.cu): that kernel's thread tid sums elements
+    // tid, tid + 256, ...; here one warp takes a row and lane l keeps the eight partial sums of
+    // "threads" 8l .. 8l+7 (it reads elements 8(l + 32j) .. +7, i.e. 8l + e + 256j, in the same
+    // order), then replays the reference's xor butterfly: offsets 16 and 8 cross lanes (l^2,
+    // l^1), offsets 4, 2, 1 stay inside a lane, and the eight warp sums sit in lanes 0, 4, .., 28.
+    if constexpr (!XR) {
+      if (p.norm_w != nullptr) {
+        for (int r = cw; r < a.m && ok; r += NCW) {
+          uint8_t* xrow = Xsm + (size_t)r * p.XS;
+          float part[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) part[e] = 0.0f;
+          for (int c = lane; c * 8 < a.p; c += 32) {
+            const uint4 u = *reinterpret_cast<const uint4*>(xrow + (size_t)c * 16);
+            const __half* hv = reinterpret_cast<const __half*>(&u);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const float v = __half2float(hv[e]);
+              part[e] += v * v;
+            }
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) part[e] += __shfl_xor_sync(0xffffffffu, part[e], 2);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) part[e] += __shfl_xor_sync(0xffffffffu, part[e], 1);
+          float q4[4], q2[2];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) q4[e] = part[e] + part[e + 4];
+          q2[0] = q4[0] + q4[2];
+          q2[1] = q4[1] + q4[3];
+          const float wsum = q2[0] + q2[1];  // the sum of "warp" lane / 4
+          float W[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) W[q] = __shfl_sync(0xffffffffu, wsum, 4 * q);
+          const float total = ((W[0] + W[4]) + (W[2] + W[6])) + ((W[1] + W[5]) + (W[3] + W[7]));
+          const float rms_inv = rsqrtf((total / a.p) + p.norm_eps);
+          for (int c = lane; c * 8 < a.p; c += 32) {
+            uint4 u = *reinterpret_cast<const uint4*>(xrow + (size_t)c * 16);
+            const uint4 wv = *reinterpret_cast<const uint4*>(p.norm_w + (size_t)c * 8);
+            __half* hv = reinterpret_cast<__half*>(&u);
+            const __half* hw = reinterpret_cast<const __half*>(&wv);
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              hv[e] = __hmul(hw[e], __float2half(__half2float(hv[e]) * rms_inv));
+            *reinterpret_cast<uint4*>(xrow + (size_t)c * 16) = u;
+          }
+        }
+        named_bar_sync(13, NCW * 32);
+      }
+    }
 
     // four accumulator chains per token block (piece x parity of the k16 step): two dependent
     // MMAs each, so that the tensor pipe's latency is overlapped within one warp
@@ -589,7 +644,10 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   pl.xr = 0;
   pl.stage_bytes = RING_STAGE_BYTES;
   pl.xss = 0;
-  if (ns < 4) {
+  if (a.norm_w != nullptr) {
+    // the fused rms_norm rewrites resident activations: no streamed-activation form, 16-byte rows
+    if (ns < 3 || a.p % 8 != 0 || (reinterpret_cast<uintptr_t>(a.norm_w) & 15u)) return false;
+  } else if (ns < 4) {
     // The activations leave too little room for a ring (or none): stream them through the ring
     // with the weights instead, 1024 k per stage and token (rows padded by 16 bytes so that the
     // fragment loads of different tokens fall in different banks).
@@ -652,6 +710,8 @@ int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
   p.stage_bytes = pl.stage_bytes;
   p.xss = pl.xss;
   p.status = ctx->d_status;
+  p.norm_w = a.norm_w;
+  p.norm_eps = a.norm_eps;
   p.ar_world = 0;
   if (ar) {
     for (int r = 0; r < ar->world; ++r) {

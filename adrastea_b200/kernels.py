@@ -420,6 +420,23 @@ class GpuKernels:
             out.stride(-2), pos_dev.data_ptr(), scale)
         self._check(rc)
 
+    def rms_norm_matmul_nt_fp16u8(self, output: torch.Tensor, lhs: torch.Tensor,
+                                  norm_weight: torch.Tensor, eps: float, rhs: torch.Tensor,
+                                  scales: torch.Tensor, block_size: int, beta: float = 0.0,
+                                  zeros: torch.Tensor | None = None, stream=None):
+        """adr_rms_norm_matmul_nt_fp16u8: rms_norm of the rows of lhs, then the u8 product, in one
+        launch; raises AdrError(ADR_ERR_SHAPE) for shapes it does not take."""
+        m, p = lhs.shape
+        n = rhs.shape[0]
+        assert rhs.shape == (n, p) and output.shape == (m, n) and norm_weight.shape == (p,)
+        for t in (output, lhs, rhs, scales, norm_weight):
+            assert t.is_contiguous() and t.is_cuda
+        rc = self._lib.adr_rms_norm_matmul_nt_fp16u8(
+            self._ctx, _stream_handle(stream), output.data_ptr(), lhs.data_ptr(),
+            norm_weight.data_ptr(), eps, rhs.data_ptr(), scales.data_ptr(),
+            zeros.data_ptr() if zeros is not None else None, m, p, n, block_size, beta)
+        self._check(rc)
+
     def matmul_nt_fp16u8_allreduce(self, output: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor,
                                    scales: torch.Tensor, block_size: int, residual: bool,
                                    inbox_ptrs, flag_ptrs, epochs: torch.Tensor, max_ctas: int,

@@ -281,6 +281,20 @@ int adr_allreduce_oneshot(adr_ctx* ctx, adr_stream stream, void* out, const void
                           long long count, int residual);
 
 /*
+ * No counterpart in the reference (its layers launch rms_norm and the matmul separately,
+ * llama.rs:497-508): out = rms_norm(lhs, norm_weights, eps) . deq(rhs)^T + beta * out for decode
+ * shapes, with the bits of adr_rms_norm followed by adr_matmul_nt_fp16u8.  The decode kernel
+ * normalises the activation rows it has just copied into shared memory (every CTA does so for
+ * itself), which saves a kernel launch per norm.  lhs is contiguous [m, p]; m <= 16 and a shape the
+ * persistent decode kernel takes with the activations resident (else ADR_ERR_SHAPE: make the two
+ * calls).
+ */
+int adr_rms_norm_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                                  const void* norm_weights, float eps, const uint8_t* rhs,
+                                  const void* scales, const void* zeros, int m, int p, int n,
+                                  int block_size, float beta);
+
+/*
  * No counterpart in the reference: the row-split product of tensor-parallel decoding with its
  * all-reduce in the same kernel.  Each rank holds a [n, p] slice (p = K / world) of the weight and
  * the matching slice of the activations; out[m, n] = sum over ranks of lhs_r . deq(rhs_r)^T (+ the

@@ -199,3 +199,27 @@ def test_rowop_argument_errors(kernels):
     kc = torch.zeros((4, 12, 30), dtype=torch.float16, device="cuda")
     with pytest.raises(AdrError):  # head_dim 15 is not a multiple of 8
         kernels.decode_attention(TensorView.of(x), TensorView.of(x), kc, kc, 2, pos, 1.0)
+
+
+@pytest.mark.parametrize("m,p,n,bs", [(1, 4096, 512, 128), (5, 2048, 300, 64), (16, 4096, 256, 128),
+                                      (8, 1024, 64, 128)])
+def test_rms_norm_fused_into_the_decode_gemv(kernels, m, p, n, bs):
+    """adr_rms_norm_matmul_nt_fp16u8 gives the bits of adr_rms_norm followed by
+    adr_matmul_nt_fp16u8 (it replays the reference's reduction order inside the GEMV kernel)."""
+    from adrastea_b200 import Kernel, TensorView
+    rng = np.random.default_rng(m * 7 + n)
+    x = dev((rng.standard_normal((m, p)) * rng.uniform(0.2, 3.0, (m, 1))).astype(np.float16))
+    w = dev(rng.uniform(0.5, 1.5, p).astype(np.float16))
+    q = dev(rng.integers(0, 256, (n, p), dtype=np.uint8))
+    s = dev(rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16))
+    out0 = (rng.standard_normal((m, n)) * 0.5).astype(np.float16)
+    xn = torch.zeros_like(x)
+    kernels.rms_norm(TensorView.of(xn), TensorView.of(x), TensorView.of(w), 1e-5)
+    two = dev(out0.copy())
+    kernels.matmul_nt_fp16u8(two, xn, q, s, bs, 0.5)
+    assert kernels.last_kernel() == Kernel.U8Ring
+    one = dev(out0.copy())
+    kernels.rms_norm_matmul_nt_fp16u8(one, x, w, 1e-5, q, s, bs, 0.5)
+    torch.cuda.synchronize()
+    kernels.device_status()
+    assert torch.equal(one.view(torch.int16), two.view(torch.int16))
