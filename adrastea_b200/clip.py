@@ -5,11 +5,10 @@ Restates the call sequence of the reference's `ClipAttention::forward`,
 754-817) around this library's fp16 GEMM: q/k/v projections with `BetaBias(0.0)`,
 scores `q.k^T` with `Scale(1/sqrt(hd))`, probabilities . v, the output projection and
 fc2 with `BetaBias(1.0)` (the residual), fc1 with `QuickGeluBias`.  Layer norms, the
-softmax, the patch embedding and the head re-layout between the projections and the
-batched attention products are harness glue done with PyTorch ops; they are not part
-of this repository's kernel contract.
+softmax and the patch embedding are harness glue done with PyTorch ops; they are not
+part of this repository's kernel contract.
 
-The reference encodes one image at a time ([257, 1024]); BASELINE's config 3 asks for a
+The reference encodes one image at a time ([257, 1024]); the CLIP workload here is a
 batch of 64, which this harness runs as [B*257, 1024] linears and B*heads batched
 attention products.  Activations are kept token-major so that the per-head operands are
 strided views (no copies); the score tensor has a row pitch that is a multiple of 8

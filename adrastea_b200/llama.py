@@ -15,7 +15,7 @@ decode kernels that serve it (`decode_rope_append`, `decode_attention`), batches
 sequences, q/k/v and gate/up stored as one matrix each (one GEMV instead of three
 or two; the separate matrices remain available as row slices), tensor parallelism
 (adrastea_b200/tp.py) and CUDA-graph capture of the decode step are harness glue
-that BASELINE's configs 4 and 5 ask for.  Weights are seeded random u8 codes with
+that the LLaMA-7B and 65B-shape decode workloads need.  Weights are seeded random u8 codes with
 the config-2 distributions; there are no checkpoints in this environment.
 """
 from __future__ import annotations

@@ -1,8 +1,8 @@
 """Tensor-parallel sharding of the u8 linear layers (one process per GPU).
 
 The reference has no multi-GPU path ("bring back multi-gpu and quantization",
-adrastea_models/src/llama.rs:28-29); this is the Megatron-style split BASELINE's
-config 5 asks for, around the reference's weight layout (`[N, K]` u8 codes, fp16
+adrastea_models/src/llama.rs:28-29); this is the Megatron-style split of a 65B-shape
+model over 2, 4 or 8 GPUs, around the reference's weight layout (`[N, K]` u8 codes, fp16
 scales `[N, K/block]`, adrastea_kernels/cpp/quantize.cu:3-56):
 
   column split (q, k, v, gate, up): rank r keeps rows [r*N/t, (r+1)*N/t) of the

@@ -3,7 +3,7 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
-Workload at N=1 (BASELINE.json configs[1]): the u8-weight decode GEMV/GEMM,
+Workload at N=1 (the u8 decode configuration, configs[1] of the workload list): the u8-weight decode GEMV/GEMM,
 M in {1, 4, 16}, K = 4096, N in {4096, 11008}, block size 128, reference
 layout (zero point 127.5).  One step = for every M, one pass over LAYERS
 distinct weight sets of 4 x [4096,4096] + 2 x [11008,4096] (the decode-time
@@ -336,7 +336,7 @@ def run_ours(args):
 
 
 def run_ours_tp(args):
-    """N > 1: BASELINE configs[4], the LLaMA-65B-shape decode linears (hidden 8192, FFN 22016,
+    """N > 1: configs[4] of the workload list, the LLaMA-65B-shape decode linears (hidden 8192, FFN 22016,
     block 64), batch 16, tensor-parallel over the N ranks: column-split q/k/v/gate/up, row-split
     o/down, one NCCL all-reduce of [16, 8192] fp16 after each row-split product.  One step =
     TP_LAYERS distinct layers (6.5 GB of u8 weights in total, sharded N ways, so every launch

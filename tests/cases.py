@@ -83,7 +83,7 @@ def matmul_cases() -> list[MatmulCase]:
     m, k, n = 33, 70, 45
     add(name="rrr_tails", batches=1, m=m, k=k, n=n, out_strides=(1, n, 0), lhs_strides=(1, k, 0),
         rhs_strides=(1, n, 0), out_size=m * n, lhs_size=m * k, rhs_size=k * n, std=0.5)
-    # BASELINE config-1 distribution N(0, 0.02^2), NT, reduced size
+    # the fp16 GEMM workload's distribution N(0, 0.02^2), NT, reduced size
     m, k, n = 64, 512, 128
     add(name="c1_small", batches=1, m=m, k=k, n=n, out_strides=(1, n, 0), lhs_strides=(1, k, 0),
         rhs_strides=(k, 1, 0), out_size=m * n, lhs_size=m * k, rhs_size=n * k, std=0.02)

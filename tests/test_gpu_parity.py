@@ -2,7 +2,7 @@
 and is compared with the CPU oracle, with the golden vectors and, when the
 reference cubins travelled along, with the reference's own kernels run live.
 
-Tolerances (BASELINE north star): max relative error <= 1e-2 against the
+Tolerances (the stated goal of this path): max relative error <= 1e-2 against the
 fp32-accumulate ("ideal") oracle; u8 dequantisation bit-exact; the CUDA-core
 fp16 kernel bit-exact against the reference kernels (it keeps their
 arithmetic), up to 2 fp16 ulps where tanhf/expf sit in the epilogue.
@@ -351,7 +351,7 @@ def test_tracer_records_distinct_layouts(kernels):
     kernels.trace_enable(False)
 
 
-# ------------------------------------------------------------ full BASELINE sizes
+# ------------------------------------------------------------ full workload sizes
 def test_config1_full_size(kernels):
     """C[64,4096] = A[64,4096] . W[4096,4096], N(0, 0.02^2), both W layouts."""
     rng = np.random.default_rng(100)
@@ -442,7 +442,7 @@ def test_tc_gemm_every_tile_and_split(kernels, bn, split):
 @pytest.mark.parametrize("split", [0, 2])
 @pytest.mark.parametrize("bn", [64, 128, 256])
 def test_tc_gemm_n_contiguous_rhs(kernels, bn, split):
-    """rhs stored [K, N] row-major ("rrr", BASELINE config 1 as worded) and the
+    """rhs stored [K, N] row-major ("rrr", the fp16 GEMM workload as worded) and the
     probabilities . values product with a 16-byte-aligned score pitch (k = 257)."""
     rng = np.random.default_rng(7 * bn + split)
     try:
