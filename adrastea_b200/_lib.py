@@ -34,6 +34,7 @@ SIGNATURES = {
     "adr_matmul_nt_f16": (_c_int, [_vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, C.c_float]),
     "adr_dequantize_absmax_uint8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),
     "adr_quantize_absmax_uint8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),
+    "adr_embed_uint8": (_c_int, [_vp, _vp, _c_int, _c_int, _vp, _vp, _vp, _vp, _c_int]),
     "adr_rms_norm": (_c_int, [_vp, _vp, _vp, _vp, _vp] + [_c_int] * 6 + [C.c_float]),
     "adr_softmax_rows": (_c_int, [_vp, _vp, _vp, _vp] + [_c_int] * 4 + [C.c_float]),
     "adr_rotary": (_c_int, [_vp, _vp, _vp, _vp] + [_c_int] * 8 + [C.c_float]),

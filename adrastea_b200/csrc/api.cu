@@ -359,6 +359,17 @@ int adr_quantize_absmax_uint8(adr_ctx* ctx, adr_stream stream, uint8_t* q, void*
                             k, block_size);
 }
 
+int adr_embed_uint8(adr_ctx* ctx, adr_stream stream, int n_dim, int n_ids, const int16_t* in_ids,
+                    void* out_embeddings, const uint8_t* embeddings_table, const void* scales,
+                    int block_size) {
+  if (!ctx || !in_ids || !out_embeddings || !embeddings_table || !scales) return ADR_ERR_INVALID;
+  if (n_dim <= 0 || n_ids <= 0 || block_size <= 0) return ADR_ERR_INVALID;
+  if (n_dim % block_size != 0 || block_size % 16 != 0) return ADR_ERR_SHAPE;
+  if (!aligned16(out_embeddings) || !aligned16(embeddings_table)) return ADR_ERR_SHAPE;
+  return launch_embed_u8(ctx, (cudaStream_t)stream, n_dim, n_ids, (const short*)in_ids,
+                         (__half*)out_embeddings, embeddings_table, (const __half*)scales, block_size);
+}
+
 int adr_trace_enable(adr_ctx* ctx, int on) {
   if (!ctx) return ADR_ERR_INVALID;
   ctx->trace_on = on != 0;

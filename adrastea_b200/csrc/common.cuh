@@ -202,6 +202,8 @@ int init_u8_kernels(adr_ctx* ctx);
 
 int launch_dequantize_u8(adr_ctx* ctx, cudaStream_t stream, __half* out, const __half* scales,
                          const __half* zeros, const uint8_t* q, int rows, int k, int block_size);
+int launch_embed_u8(adr_ctx* ctx, cudaStream_t stream, int n_dim, int n_ids, const short* in_ids,
+                    __half* out, const uint8_t* table, const __half* scales, int block_size);
 int launch_quantize_u8(adr_ctx* ctx, cudaStream_t stream, uint8_t* q, __half* scales,
                        const __half* in, int rows, int k, int block_size);
 

@@ -37,6 +37,34 @@ __global__ void __launch_bounds__(256) dequantize_u8_kernel(__half* out, const _
   dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
+// embed_uint8 (adrastea_kernels/cpp/embed_uint8.cu:3-19): out[t, :] = the dequantised row
+// in_ids[t] of the table (implicit zero point 127.5).  One thread per 16 values, as above.
+__global__ void __launch_bounds__(256) embed_u8_kernel(int n_dim, int n_ids, const short* in_ids,
+                                                       __half* out, const uint8_t* table,
+                                                       const __half* scales, int block_size) {
+  const int per_row = n_dim / 16;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)n_ids * per_row) return;
+  const int t = (int)(idx / per_row);
+  const int kk = (int)(idx % per_row) * 16;
+  const int groups = n_dim / block_size;
+  const int64_t id = in_ids[t];
+  ScalePair sp = make_scale(scales[id * groups + kk / block_size], false, __half());
+  uint4 w = ldg_nc_16(table + id * n_dim + kk);
+  const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    __half2 lo, hi;
+    dequant4(ww[j], sp, lo, hi);
+    o[2 * j] = half2_as_u32(lo);
+    o[2 * j + 1] = half2_as_u32(hi);
+  }
+  uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * n_dim + kk);
+  dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+  dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
 // One warp per (row, group): absmax by shuffles, then the scale in fp16 and
 // the codes  u8(round(127.5 + x / float(scale)))  (quantize.cu:33, 42).
 __global__ void __launch_bounds__(256) quantize_u8_kernel(uint8_t* q, __half* scales,
@@ -80,6 +108,15 @@ int launch_quantize_u8(adr_ctx* ctx, cudaStream_t stream, uint8_t* q, __half* sc
   int64_t grid = (warps * 32 + 255) / 256;
   if (grid > 0x7fffffffLL) return ADR_ERR_SHAPE;
   quantize_u8_kernel<<<(unsigned)grid, 256, 0, stream>>>(q, scales, in, rows, k, block_size);
+  return after_launch(ctx);
+}
+
+int launch_embed_u8(adr_ctx* ctx, cudaStream_t stream, int n_dim, int n_ids, const short* in_ids,
+                    __half* out, const uint8_t* table, const __half* scales, int block_size) {
+  int64_t threads = (int64_t)n_ids * (n_dim / 16);
+  int64_t grid = (threads + 255) / 256;
+  if (grid > 0x7fffffffLL) return ADR_ERR_SHAPE;
+  embed_u8_kernel<<<(unsigned)grid, 256, 0, stream>>>(n_dim, n_ids, in_ids, out, table, scales, block_size);
   return after_launch(ctx);
 }
 

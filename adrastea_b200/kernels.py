@@ -468,6 +468,18 @@ class GpuKernels:
                                              int(residual))
         self._check(rc)
 
+    def embed_uint8(self, output: torch.Tensor, ids: torch.Tensor, table: torch.Tensor,
+                    scales: torch.Tensor, block_size: int, stream=None):
+        """embed_uint8 (embed_uint8.cu:3-19): rows `ids` (int16) of the u8 table, dequantised."""
+        n_ids, n_dim = output.shape
+        assert ids.dtype == torch.int16 and ids.shape == (n_ids,) and table.shape[1] == n_dim
+        assert table.dtype == torch.uint8 and output.dtype == torch.float16
+        for t in (output, ids, table, scales):
+            assert t.is_contiguous() and t.is_cuda
+        rc = self._lib.adr_embed_uint8(self._ctx, _stream_handle(stream), n_dim, n_ids, ids.data_ptr(),
+                                       output.data_ptr(), table.data_ptr(), scales.data_ptr(), block_size)
+        self._check(rc)
+
     # -- library-side trace (kernel family per distinct call) -------------
     def trace_enable(self, on: bool = True):
         self._check(self._lib.adr_trace_enable(self._ctx, int(on)))

@@ -188,6 +188,16 @@ int adr_dequantize_absmax_uint8(adr_ctx* ctx, adr_stream stream, void* out, cons
 int adr_quantize_absmax_uint8(adr_ctx* ctx, adr_stream stream, uint8_t* q, void* scales,
                               const void* in, int rows, int k, int block_size);
 
+/*
+ * Replaces kernel embed_uint8 (embed_uint8.cu:3-19; parameters in its order):
+ * out_embeddings[t, i] = fp16((float(table[in_ids[t], i]) - 127.5) *
+ *                             float(scales[in_ids[t], i / block_size])),
+ * token ids are 16-bit as in the reference kernel; contiguous operands.
+ */
+int adr_embed_uint8(adr_ctx* ctx, adr_stream stream, int n_dim, int n_ids, const int16_t* in_ids,
+                    void* out_embeddings, const uint8_t* embeddings_table, const void* scales,
+                    int block_size);
+
 /* ------------------------------------------------------------------------
  * The kernels either side of the matmuls in a decoder layer.  The first four
  * restate reference kernels with the same order of floating-point operations

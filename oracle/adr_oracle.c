@@ -641,3 +641,15 @@ void orc_decode_attention(h16* out, const h16* q, const h16* k_cache, const h16*
     }
   free(sc);
 }
+
+/* embed_uint8.cu:3-19 */
+void orc_embed_uint8(int n_dim, int n_ids, const int16_t* in_ids, h16* out, const uint8_t* table,
+                     const h16* scales, int block_size) {
+  int block_count = n_dim / block_size;
+  for (int t = 0; t < n_ids; ++t) {
+    ptrdiff_t id = in_ids[t];
+    for (int i = 0; i < n_dim; ++i)
+      out[(ptrdiff_t)t * n_dim + i] =
+          f2h(((float)table[id * n_dim + i] - 127.5f) * h2f(scales[id * block_count + i / block_size]));
+  }
+}

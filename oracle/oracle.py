@@ -261,3 +261,15 @@ def decode_attention(q: np.ndarray, k_cache: np.ndarray, v_cache: np.ndarray, n_
     f(_p(out), _p(q), _p(k_cache), _p(v_cache), B, n_heads, width // n_heads, S, width, width,
       pos, float(scale))
     return out
+
+
+def embed_uint8(ids: np.ndarray, table: np.ndarray, scales: np.ndarray, block_size: int) -> np.ndarray:
+    ids = np.ascontiguousarray(ids, dtype=np.int16)
+    out = np.zeros((ids.shape[0], table.shape[1]), np.float16)
+    _chk16(scales)
+    f = lib().orc_embed_uint8
+    f.restype = None
+    f.argtypes = [C.c_int, C.c_int] + [C.c_void_p] * 4 + [C.c_int]
+    f(table.shape[1], ids.shape[0], _p(ids), _p(out), _p(np.ascontiguousarray(table)),
+      _p(np.ascontiguousarray(scales)), block_size)
+    return out

@@ -174,3 +174,12 @@ def elementwise_binary_2d_f16(out_ptr, left_ptr, right_ptr, rows, cols, op):
     holders = [_desc2d(out_ptr, rows, cols), _desc2d(left_ptr, rows, cols),
                _desc2d(right_ptr, rows, cols), C.c_uint(op)]
     _launch(fn, (_cdiv(cols, 16), _cdiv(rows, 16), 1), (16, 16, 1), 0, holders)
+
+
+def embed_uint8(n_dim, n_ids, ids_ptr, out_ptr, table_ptr, scales_ptr, block_size):
+    """embed_uint8.cu:3-9; the kernel has no call site in the reference: launched like the fp16
+    `embed` kernel (kernels.rs:923-927), 1024 threads per block, one thread per token."""
+    fn = _function("embed_uint8", "embed_uint8")
+    holders = [C.c_int(n_dim), C.c_int(n_ids), C.c_void_p(ids_ptr), C.c_void_p(out_ptr),
+               C.c_void_p(table_ptr), C.c_void_p(scales_ptr), C.c_int(block_size)]
+    _launch(fn, (_cdiv(n_ids, 1024), 1, 1), (1024, 1, 1), 0, holders)

@@ -223,3 +223,23 @@ def test_rms_norm_fused_into_the_decode_gemv(kernels, m, p, n, bs):
     torch.cuda.synchronize()
     kernels.device_status()
     assert torch.equal(one.view(torch.int16), two.view(torch.int16))
+
+
+def test_embed_uint8_same_bits_as_reference_and_oracle(kernels):
+    rng = np.random.default_rng(31)
+    vocab, d, bs = 500, 256, 64
+    table = rng.integers(0, 256, (vocab, d), dtype=np.uint8)
+    scales = rng.uniform(0.001, 0.01, (vocab, d // bs)).astype(np.float16)
+    ids = rng.integers(0, vocab, 37).astype(np.int16)
+    want = oracle.embed_uint8(ids, table, scales, bs)
+    t, s, i = dev(table), dev(scales), dev(ids)
+    out = torch.zeros((37, d), dtype=torch.float16, device="cuda")
+    kernels.embed_uint8(out, i, t, s, bs)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), want.view(np.uint16))
+    if refcubin.available():
+        ref = torch.zeros_like(out)
+        refcubin.embed_uint8(d, 37, i.data_ptr(), ref.data_ptr(), t.data_ptr(), s.data_ptr(), bs)
+        torch.cuda.synchronize()
+        assert torch.equal(ref.view(torch.int16), out.view(torch.int16))
+    kernels.device_status()
