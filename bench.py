@@ -379,10 +379,21 @@ def run_ours_tp(args):
     stream = torch.cuda.current_stream()
     use_peer = not args.nccl
     if use_peer:
+        # peer-mapped symmetric buffers; if any rank cannot set them up, every rank falls back to
+        # the NCCL form (the ranks agree through a MIN all-reduce of a success flag)
         from adrastea_b200.tp import PeerAllReduce
-        tp.peer_ar = PeerAllReduce(kern, tp, M * d, dev)
-        tp.peer_ar.fused = args.fused_ar
-        note("symmetric buffers mapped")
+        okf = torch.ones(1, device=dev)
+        try:
+            tp.peer_ar = PeerAllReduce(kern, tp, M * d, dev)
+            tp.peer_ar.fused = args.fused_ar
+        except Exception as e:  # noqa: BLE001 - reported, then the slower path is used
+            note(f"symmetric memory unavailable: {e!r}")
+            okf.zero_()
+        dist.all_reduce(okf, op=dist.ReduceOp.MIN)
+        if float(okf.item()) < 1.0:
+            tp.peer_ar = None
+            use_peer = False
+        note("symmetric buffers mapped" if use_peer else "falling back to NCCL all-reduce")
 
     # q/k/v and gate/up are one matrix each (adrastea_b200/llama.py); `att` and `g` stand in for
     # the attention output and the SiluMul output, which are not part of this workload.
