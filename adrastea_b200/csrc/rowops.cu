@@ -410,13 +410,13 @@ __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
 }
 
 template <int HD, int CS, bool PDL>
-__global__ void __launch_bounds__(ATT2_THREADS)
+__global__ void __launch_bounds__(ATT2_THREADS, 3)
     decode_attention_wide_kernel(__half* out, const __half* q, const __half* k_cache,
                                  const __half* v_cache, int n_heads, int S, int chunk_cap, int s_q,
                                  int s_o, const int* pos_dev, float scale) {
   constexpr int LPT = HD / 8;    // lanes per position
   constexpr int TPW = 32 / LPT;  // positions per warp step
-  constexpr int U = 4;           // steps in flight
+  constexpr int U = 8;           // steps in flight
   extern __shared__ float att_smem[];
   float* sc = att_smem;                // [chunk_cap] scores, then probabilities, of this CTA's positions
   float* red = att_smem + chunk_cap;   // [ATT2_WARPS][HD] partial outputs of the warps

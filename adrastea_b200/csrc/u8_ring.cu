@@ -112,7 +112,9 @@ struct RingParams {
 // so every stage carries its own 1024-wide slice of them (m bulk copies next to the weight box);
 // the activation sums are then taken per tile by an extra MMA with an all-ones weight operand, and
 // nothing is loaded before griddepcontrol.wait.
-template <int MT, int NCW, bool HAS_ZERO, bool PDL, bool XR>
+// FUSE: compiles in the optional rms_norm of the activations and the fused all-reduce; the plain
+// product uses the instantiation without them (they cost registers and 6 % of its speed).
+template <int MT, int NCW, bool HAS_ZERO, bool PDL, bool XR, bool FUSE>
 __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     u8_ring_kernel(const __grid_constant__ CUtensorMap wmap, RingParams p) {
   constexpr int TOK = 8 * MT;
@@ -269,7 +271,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     // "threads" 8l .. 8l+7 (it reads elements 8(l + 32j) .. +7, i.e. 8l + e + 256j, in the same
     // order), then replays the reference's xor butterfly: offsets 16 and 8 cross lanes (l^2,
     // l^1), offsets 4, 2, 1 stay inside a lane, and the eight warp sums sit in lanes 0, 4, .., 28.
-    if constexpr (!XR) {
+    if constexpr (!XR && FUSE) {
       if (p.norm_w != nullptr) {
         for (int r = cw; r < a.m && ok; r += NCW) {
           uint8_t* xrow = Xsm + (size_t)r * p.XS;
@@ -416,7 +418,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
       const bool summer = ROTATE ? (ui % NCW) == cw : true;
       constexpr int OPL = ROTATE ? 16 * TOK / 32 : 1;  // outputs per summing thread
       float old[OPL];
-      const bool fused_ar = p.ar_world > 1;
+      const bool fused_ar = FUSE && p.ar_world > 1;
       if (summer && !fused_ar) {
 #pragma unroll
         for (int j = 0; j < OPL; ++j) {
@@ -539,7 +541,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
         }
       }
     }
-    if (p.ar_world > 1) {
+    if (FUSE && p.ar_world > 1) {
       // ---- fused all-reduce.  CTA c of every rank works on the same units, so it needs only
       // the partial results pushed by CTA c of the peers: make this CTA's pushes visible, tell
       // CTA c of every peer, wait (bounded) for theirs, then add the world slots of this rank's
@@ -674,10 +676,10 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   return true;
 }
 
-template <int MT, bool Z, bool PDL, int NCW, bool XR>
-int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl,
+template <int MT, bool Z, bool PDL, int NCW, bool XR, bool FUSE>
+int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl,
                   const RingArFuse* ar) {
-  auto kfn = u8_ring_kernel<MT, NCW, Z, PDL, XR>;
+  auto kfn = u8_ring_kernel<MT, NCW, Z, PDL, XR, FUSE>;
   static bool configured[64] = {};
   cudaError_t e;
   const int dev = ctx->device & 63;
@@ -742,6 +744,14 @@ int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
     return ADR_ERR_CUDA;
   }
   return after_launch(ctx);
+}
+
+template <int MT, bool Z, bool PDL, int NCW, bool XR>
+int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl,
+                  const RingArFuse* ar) {
+  if (ar != nullptr || a.norm_w != nullptr)
+    return launch_ring_f<MT, Z, PDL, NCW, XR, true>(ctx, stream, a, pl, ar);
+  return launch_ring_f<MT, Z, PDL, NCW, XR, false>(ctx, stream, a, pl, ar);
 }
 
 }  // namespace
