@@ -33,27 +33,59 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
+def _headers() -> list[Path]:
+    return list(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "adrastea_b200.h"]
+
+
 def _stale() -> bool:
     if not LIB_PATH.exists():
         return True
     t = LIB_PATH.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + [PKG_DIR.parent / "include" / "adrastea_b200.h"]
+    deps = list(CSRC.glob("*.cu")) + _headers()
     return any(d.stat().st_mtime > t for d in deps)
 
 
 def build_library(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every .cu under csrc/ into libadrastea_b200.so (sm_100a)."""
+    """Compile every .cu under csrc/ into libadrastea_b200.so (sm_100a).
+
+    Each source becomes an object file under csrc/build/ (compiled in parallel, reused while
+    neither the source nor any header is newer), then everything is linked into the library.
+    """
     if not force and not _stale():
         return LIB_PATH
-    cmd = [_nvcc(), *NVCC_FLAGS]
+    from concurrent.futures import ThreadPoolExecutor
+    obj_dir = CSRC / "build"
+    obj_dir.mkdir(exist_ok=True)
+    hdr_time = max(h.stat().st_mtime for h in _headers())
+    compile_flags = [f for f in NVCC_FLAGS if f != "-shared"]
+
+    def compile_one(src: Path):
+        obj = obj_dir / (src.stem + ".o")
+        if not force and obj.exists() and obj.stat().st_mtime > max(src.stat().st_mtime, hdr_time):
+            return obj, ""
+        cmd = [_nvcc(), *compile_flags, "-c", "-o", str(obj), str(src)]
+        if verbose:
+            cmd += ["-Xptxas", "-v"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed on {src.name}:\n" + res.stdout + res.stderr)
+        return obj, res.stderr
+
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        results = list(pool.map(compile_one, sources()))
     if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB_PATH), *map(str, sources())]
+        for _, log in results:
+            if log:
+                print(log)
+    # drop objects whose source is gone
+    keep = {o for o, _ in results}
+    for o in obj_dir.glob("*.o"):
+        if o not in keep:
+            o.unlink()
+    cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(LIB_PATH), *map(str, sorted(keep))]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
-    if verbose:
-        print(res.stderr)
+        raise RuntimeError("nvcc link failed:\n" + res.stdout + res.stderr)
     return LIB_PATH
 
 

@@ -52,7 +52,7 @@ class _Linear:
 
 class ClipVisionU:
     def __init__(self, kernels: GpuKernels, shape: ClipVisionShape = VIT_L_14, batch: int = 64,
-                 seed: int = 0, device="cuda"):
+                 seed: int = 0, device="cuda", score_pitch: int | None = None):
         self.k, self.shape, self.B = kernels, shape, batch
         self.device = torch.device(device)
         gen = torch.Generator(device=self.device).manual_seed(4242 + seed)
@@ -64,7 +64,10 @@ class ClipVisionU:
         self.cls = (torch.randn((d,), device=self.device, generator=gen) * 0.02).half()
         self.pos = (torch.randn((shape.tokens, d), device=self.device, generator=gen) * 0.02).half()
         S, H, hd, B = shape.tokens, shape.heads, shape.hidden // shape.heads, batch
-        self.Sp = (S + 7) // 8 * 8
+        # distance between score rows in elements: padded to a multiple of 8 by default;
+        # `score_pitch=S` gives the reference's own contiguous [heads, S, S] scores (clip.rs:374-388)
+        self.Sp = score_pitch or (S + 7) // 8 * 8
+        assert self.Sp >= S
         f16 = dict(dtype=torch.float16, device=self.device)
         z = lambda *s: torch.zeros(s, **f16)
         # activations are token-major, [S*B, d] (row = token * B + image): the [B*H, S, hd]

@@ -27,7 +27,6 @@ namespace {
 
 constexpr int AR_MAX_WORLD = 8;
 constexpr int AR_THREADS = 256;
-constexpr long long AR_WAIT_CYCLES = 2000000000LL;  // about a second
 
 struct ArParams {
   const __half* bufs[AR_MAX_WORLD];   // the partial vector of every rank (peer pointers)
@@ -36,6 +35,7 @@ struct ArParams {
   __half* out;
   int rank, world, residual;
   long long count;                    // elements, a multiple of 8
+  long long wait_cycles;              // bound of the wait for the peers' flags
   unsigned int* status;
 };
 
@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(AR_THREADS) allreduce_oneshot_kernel(ArParams 
     const long long t0 = clock64();
     // (epoch - seen) as a signed difference: correct across wrap-around
     while ((int)(ld_acquire_sys(mine) - epoch) < 0) {
-      if (clock64() - t0 > AR_WAIT_CYCLES) {
+      if (clock64() - t0 > p.wait_cycles) {
         atomicOr(p.status, 128u);
         break;
       }
@@ -126,6 +126,7 @@ extern "C" int adr_allreduce_oneshot(adr_ctx* ctx, adr_stream stream, void* out,
                                      int blocks, int rank, int world, long long count,
                                      int residual) {
   if (!ctx || !out || !bufs || !flags || !epochs) return ADR_ERR_INVALID;
+  DeviceGuard guard(ctx);
   if (world < 2 || world > AR_MAX_WORLD || rank < 0 || rank >= world) return ADR_ERR_INVALID;
   if (count <= 0 || blocks < 1 || blocks > 1024) return ADR_ERR_INVALID;
   if (count % 8 != 0 || (reinterpret_cast<uintptr_t>(out) & 15u)) return ADR_ERR_SHAPE;
@@ -142,6 +143,7 @@ extern "C" int adr_allreduce_oneshot(adr_ctx* ctx, adr_stream stream, void* out,
   p.residual = residual ? 1 : 0;
   p.count = count;
   p.status = ctx->d_status;
+  p.wait_cycles = peer_wait_cycles(ctx);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blocks, 1, 1);
   cfg.blockDim = dim3(AR_THREADS, 1, 1);

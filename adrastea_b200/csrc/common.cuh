@@ -6,6 +6,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <mutex>
 #include <string>
 #include <unordered_map>
@@ -42,28 +43,36 @@ struct TraceKey {
 
 }  // namespace adr
 
+// One context per device.  It may be shared by several host threads the way the reference
+// shares its kernel object behind an Arc (adrastea_models/src/llama.rs:402): the counters and
+// knobs are atomics, the trace, the tensor-map cache and the record of configured kernels
+// are guarded by `mu`.  Launches from different threads on the same stream are ordered by
+// the caller, as with any CUDA stream.
 struct adr_ctx {
   int device = 0;
   int sm_count = 0;
-  int last_cuda_error = 0;
-  int forced_kernel = ADR_KERNEL_AUTO;
-  int last_kernel = 0;
-  uint64_t launches = 0;
-  bool trace_on = false;
+  std::atomic<int> last_cuda_error{0};
+  std::atomic<int> forced_kernel{ADR_KERNEL_AUTO};
+  std::atomic<int> last_kernel{0};
+  std::atomic<uint64_t> launches{0};
+  std::atomic<bool> trace_on{false};
   std::mutex mu;
   std::vector<adr::TraceKey> trace;
+  // kernels whose dynamic shared memory limit has been raised on this context's device
+  std::unordered_map<const void*, size_t> smem_opt_in;
   // Device word written by kernels whose bounded waits ran out (0 = fine).
   unsigned int* d_status = nullptr;
   // Cache of TMA descriptors, keyed by (pointer, dims, strides, box).
   void* tma_cache = nullptr;
   void* encode_tiled_fn = nullptr;  // cuTensorMapEncodeTiled, resolved at init
   // tuning knobs (adr_set_tunable); 0 = let the planner choose
-  int tune_u8_split = 0;
-  int tune_u8_rows = 0;
-  int tune_u8_exact = 0;  // 1: fp16-rounded dequantisation in the streaming kernel
-  int tune_tc_bn = 0;
-  int tune_tc_split = 0;
-  int tune_pdl = 0;  // programmatic dependent launch of the u8 streaming kernel
+  std::atomic<int> tune_u8_split{0};
+  std::atomic<int> tune_u8_rows{0};
+  std::atomic<int> tune_u8_exact{0};  // 1: fp16-rounded dequantisation in the streaming kernel
+  std::atomic<int> tune_tc_bn{0};
+  std::atomic<int> tune_tc_split{0};
+  std::atomic<int> tune_pdl{0};      // programmatic dependent launch of the decode and row kernels
+  std::atomic<int> tune_wait_ms{0};  // limit of the peer waits in milliseconds (0: about a second)
 };
 
 namespace adr {
@@ -76,6 +85,46 @@ namespace adr {
       return ADR_ERR_CUDA;                             \
     }                                                  \
   } while (0)
+
+// Makes the context's device current for the duration of an entry point and restores the
+// caller's device afterwards (a process that drives several GPUs may call with another
+// device current).
+struct DeviceGuard {
+  int prev = -1;
+  bool switched = false;
+  explicit DeviceGuard(const adr_ctx* ctx) {
+    if (ctx && cudaGetDevice(&prev) == cudaSuccess && prev != ctx->device)
+      switched = cudaSetDevice(ctx->device) == cudaSuccess;
+  }
+  ~DeviceGuard() {
+    if (switched) cudaSetDevice(prev);
+  }
+  DeviceGuard(const DeviceGuard&) = delete;
+  DeviceGuard& operator=(const DeviceGuard&) = delete;
+};
+
+// Raises a kernel's dynamic shared memory limit once per context (the attribute is per
+// device; the context's device is current inside every entry point).
+template <typename K>
+int opt_in_smem(adr_ctx* ctx, K kfn, size_t bytes) {
+  const void* key = reinterpret_cast<const void*>(kfn);
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  auto it = ctx->smem_opt_in.find(key);
+  if (it != ctx->smem_opt_in.end() && it->second >= bytes) return ADR_OK;
+  cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) {
+    ctx->last_cuda_error = (int)e;
+    return ADR_ERR_CUDA;
+  }
+  ctx->smem_opt_in[key] = bytes;
+  return ADR_OK;
+}
+
+// Bound of a wait on a peer GPU in clock cycles (about 2 per nanosecond).
+inline long long peer_wait_cycles(const adr_ctx* ctx) {
+  const int ms = ctx->tune_wait_ms;
+  return ms > 0 ? (long long)ms * 2000000LL : 2000000000LL;
+}
 
 // Records a launch error, if any, and counts the launch.
 inline int after_launch(adr_ctx* ctx, int nlaunches = 1) {

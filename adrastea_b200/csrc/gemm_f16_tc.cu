@@ -535,20 +535,6 @@ int make_maps(adr_ctx* ctx, const MatmulArgs& a, CUtensorMap* map_a, CUtensorMap
   return ADR_OK;
 }
 
-template <typename K>
-int opt_in_smem(adr_ctx* ctx, K kfn, size_t bytes, bool* configured) {
-  const int dev = ctx->device & 63;
-  if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
-    if (e != cudaSuccess) {
-      ctx->last_cuda_error = (int)e;
-      return ADR_ERR_CUDA;
-    }
-    configured[dev] = true;
-  }
-  return ADR_OK;
-}
-
 template <int BN, bool B_MN>
 int launch_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, int S) {
   using Cfg = TcCfg<BN>;
@@ -558,9 +544,8 @@ int launch_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, int S) {
   if (rc != ADR_OK) return rc;
   const int nt = (a.n + BN - 1) / BN, mt = (a.m + BM - 1) / BM;
   if (S <= 1) {
-    static bool configured[64] = {};
     auto kfn = gemm_f16_tc_kernel<BN, B_MN>;
-    rc = opt_in_smem(ctx, kfn, Cfg::SMEM, configured);
+    rc = opt_in_smem(ctx, kfn, Cfg::SMEM);
     if (rc != ADR_OK) return rc;
     const long long tiles = (long long)nt * mt * a.batches;
     const long long sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
@@ -568,9 +553,8 @@ int launch_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, int S) {
     kfn<<<grid, TCP_THREADS, Cfg::SMEM, stream>>>(map_a, map_b, p);
     return after_launch(ctx);
   }
-  static bool configured_sk[64] = {};
   auto kfn = gemm_f16_tc_splitk_kernel<BN, B_MN>;
-  rc = opt_in_smem(ctx, kfn, Cfg::SMEM, configured_sk);
+  rc = opt_in_smem(ctx, kfn, Cfg::SMEM);
   if (rc != ADR_OK) return rc;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(S, nt, mt * a.batches);

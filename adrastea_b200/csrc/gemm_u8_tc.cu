@@ -257,16 +257,7 @@ template <int BN, bool Z>
 int launch_u8_tc_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
   using Cfg = U8Cfg<BN>;
   auto kfn = gemm_u8_tc_kernel<BN, Z>;
-  static bool configured[64] = {};
-  const int dev = ctx->device & 63;
-  if (!configured[dev]) {
-    cudaError_t e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM);
-    if (e != cudaSuccess) {
-      ctx->last_cuda_error = (int)e;
-      return ADR_ERR_CUDA;
-    }
-    configured[dev] = true;
-  }
+  if (int rc = opt_in_smem(ctx, kfn, Cfg::SMEM); rc != ADR_OK) return rc;
   CUtensorMap map_a, map_q;
   {
     const uint64_t dims[2] = {(uint64_t)a.p, (uint64_t)a.m};

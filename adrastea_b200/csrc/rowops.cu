@@ -130,33 +130,43 @@ __global__ void __launch_bounds__(ROW_THREADS)
 }
 
 // ---------------------------------------------------------------------------------------
-// rotary (rotary.cu:4-29): interleaved pairs (c, c+1) of every head
+// Rotary position embedding (the arithmetic of rotary.cu:4-29): each head is a row of
+// interleaved 2-vectors (even column, odd column); 2-vector j of a head at position t is
+// turned by t / theta^(2j / head_dim).  The turn is computed once per 2-vector as a
+// (cos, sin) pair and applied as a 2x2 rotation; the decode-time kernel below applies the
+// same pair to the query and to the key.
 // ---------------------------------------------------------------------------------------
-__device__ __forceinline__ void rotate_pair(float real, float imag, int pos, int head_c,
-                                            int head_dim, float theta, __half* o_re, __half* o_im) {
-  const float angle = pos / powf(theta, float(head_c) / head_dim);
-  const float a_cos = cosf(angle);
-  const float a_sin = sinf(angle);
-  *o_re = __float2half(real * a_cos - imag * a_sin);
-  *o_im = __float2half(real * a_sin + imag * a_cos);
+struct Turn {
+  float c, s;
+};
+__device__ __forceinline__ Turn rope_turn(int position, int col_in_head, int head_dim, float theta) {
+  const float phase = position / powf(theta, float(col_in_head) / head_dim);
+  Turn w;
+  w.c = cosf(phase);
+  w.s = sinf(phase);
+  return w;
+}
+__device__ __forceinline__ __half2 rope_apply(__half even, __half odd, Turn w) {
+  const float x = __half2float(even), y = __half2float(odd);
+  return __halves2half2(__float2half(x * w.c - y * w.s), __float2half(x * w.s + y * w.c));
 }
 
+// One thread per 2-vector; blockIdx.y / threadIdx.y walk the rows (positions pos_offset + row).
 template <bool PDL>
 __global__ void __launch_bounds__(256)
-    rotary_kernel(__half* out, const __half* in, int lx, int ly, int s_ox, int s_oy, int s_ix,
-                  int s_iy, int n_heads, int pos_offset, float theta) {
+    rope_rows_kernel(__half* out, const __half* in, int lx, int ly, int s_ox, int s_oy, int s_ix,
+                     int s_iy, int n_heads, int pos_offset, float theta) {
   pdl_enter<PDL>();
-  const int r = blockIdx.y * blockDim.y + threadIdx.y;
-  const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
+  const int row = blockIdx.y * blockDim.y + threadIdx.y;
+  const int col = 2 * (blockIdx.x * blockDim.x + threadIdx.x);
+  if (row >= ly || col >= lx) return;
   const int head_dim = lx / n_heads;
-  const int head_c = c % head_dim;
-  if (r < ly && c < lx) {
-    const float real = __half2float(in[(int64_t)r * s_iy + (int64_t)c * s_ix]);
-    const float imag = __half2float(in[(int64_t)r * s_iy + (int64_t)(c + 1) * s_ix]);
-    rotate_pair(real, imag, pos_offset + r, head_c, head_dim, theta,
-                &out[(int64_t)r * s_oy + (int64_t)c * s_ox],
-                &out[(int64_t)r * s_oy + (int64_t)(c + 1) * s_ox]);
-  }
+  const __half* src = in + (int64_t)row * s_iy + (int64_t)col * s_ix;
+  __half* dst = out + (int64_t)row * s_oy + (int64_t)col * s_ox;
+  const __half2 turned =
+      rope_apply(src[0], src[s_ix], rope_turn(pos_offset + row, col % head_dim, head_dim, theta));
+  dst[0] = __low2half(turned);
+  dst[s_ox] = __high2half(turned);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -219,15 +229,17 @@ __global__ void __launch_bounds__(256)
   const int pos = *pos_dev;
   if (pos < 0 || pos >= S) return;  // the caller's position is outside the cache: write nothing
   const int head_dim = width / n_heads;
-  const int head_c = c % head_dim;
+  const Turn w = rope_turn(pos, c % head_dim, head_dim, theta);
   __half* qrow = q + (int64_t)b * s_q;
   const __half* krow = k + (int64_t)b * s_k;
   const __half* vrow = v + (int64_t)b * s_v;
   const int64_t crow = ((int64_t)b * S + pos) * width;
-  rotate_pair(__half2float(qrow[c]), __half2float(qrow[c + 1]), pos, head_c, head_dim, theta,
-              &qrow[c], &qrow[c + 1]);
-  rotate_pair(__half2float(krow[c]), __half2float(krow[c + 1]), pos, head_c, head_dim, theta,
-              &k_cache[crow + c], &k_cache[crow + c + 1]);
+  const __half2 qt = rope_apply(qrow[c], qrow[c + 1], w);
+  qrow[c] = __low2half(qt);
+  qrow[c + 1] = __high2half(qt);
+  const __half2 kt = rope_apply(krow[c], krow[c + 1], w);
+  k_cache[crow + c] = __low2half(kt);
+  k_cache[crow + c + 1] = __high2half(kt);
   *reinterpret_cast<__half2*>(&v_cache[crow + c]) = *reinterpret_cast<const __half2*>(&vrow[c]);
 }
 
@@ -649,6 +661,7 @@ int adr_rms_norm(adr_ctx* ctx, adr_stream stream, void* out, const void* in, con
                  int length_x, int length_y, int stride_ox, int stride_oy, int stride_ix,
                  int stride_iy, float eps) {
   if (!ctx || !out || !in || !weights) return ADR_ERR_INVALID;
+  DeviceGuard guard(ctx);
   if (length_x <= 0 || length_y <= 0) return ADR_ERR_INVALID;
   if (stride_ox < 0 || stride_oy < 0 || stride_ix < 0 || stride_iy < 0) return ADR_ERR_INVALID;
   return launch_row(ctx, (cudaStream_t)stream, rms_norm_kernel<false>, rms_norm_kernel<true>,
@@ -659,6 +672,7 @@ int adr_rms_norm(adr_ctx* ctx, adr_stream stream, void* out, const void* in, con
 int adr_softmax_rows(adr_ctx* ctx, adr_stream stream, void* out, const void* in, int heads, int h,
                      int w, int pitch, float temperature) {
   if (!ctx || !out || !in) return ADR_ERR_INVALID;
+  DeviceGuard guard(ctx);
   if (heads <= 0 || h <= 0 || w <= 0 || pitch < w) return ADR_ERR_INVALID;
   if (heads > 65535) return ADR_ERR_SHAPE;
   if (!(temperature > 0.0f)) return ADR_ERR_INVALID;
@@ -671,13 +685,14 @@ int adr_rotary(adr_ctx* ctx, adr_stream stream, void* out, const void* in, int l
                int length_y, int stride_ox, int stride_oy, int stride_ix, int stride_iy, int n_heads,
                int pos_offset, float theta) {
   if (!ctx || !out || !in) return ADR_ERR_INVALID;
+  DeviceGuard guard(ctx);
   if (length_x <= 0 || length_y <= 0 || n_heads <= 0) return ADR_ERR_INVALID;
   if (length_x % n_heads != 0 || (length_x / n_heads) % 2 != 0) return ADR_ERR_SHAPE;
   if (stride_ox < 0 || stride_oy < 0 || stride_ix < 0 || stride_iy < 0) return ADR_ERR_INVALID;
   const dim3 block(64, 4);
   const dim3 grid((length_x / 2 + 63) / 64, (length_y + 3) / 4);
   if (grid.y > 65535) return ADR_ERR_SHAPE;
-  return launch_row(ctx, (cudaStream_t)stream, rotary_kernel<false>, rotary_kernel<true>, grid,
+  return launch_row(ctx, (cudaStream_t)stream, rope_rows_kernel<false>, rope_rows_kernel<true>, grid,
                     block, 0, (__half*)out, (const __half*)in, length_x, length_y, stride_ox,
                     stride_oy, stride_ix, stride_iy, n_heads, pos_offset, theta);
 }
@@ -686,6 +701,7 @@ int adr_elementwise_binary_2d_f16(adr_ctx* ctx, adr_stream stream, void* out, co
                                   const void* right, int rows, int cols, int stride_o, int stride_l,
                                   int stride_r, uint32_t op) {
   if (!ctx || !out || !left || !right) return ADR_ERR_INVALID;
+  DeviceGuard guard(ctx);
   if (rows <= 0 || cols <= 0) return ADR_ERR_INVALID;
   if (op != ADR_BINARY_ADD && op != ADR_BINARY_SILU_MUL) return ADR_ERR_UNSUPPORTED;
   if (stride_o < cols || stride_l < cols || stride_r < cols) return ADR_ERR_INVALID;
@@ -702,6 +718,7 @@ int adr_decode_rope_append(adr_ctx* ctx, adr_stream stream, void* q, const void*
                            int max_seq, int stride_q, int stride_k, int stride_v,
                            const int32_t* pos_dev, float theta) {
   if (!ctx || !q || !k || !v || !k_cache || !v_cache || !pos_dev) return ADR_ERR_INVALID;
+  DeviceGuard guard(ctx);
   if (batch <= 0 || n_heads <= 0 || head_dim <= 0 || max_seq <= 0) return ADR_ERR_INVALID;
   if (head_dim % 2 != 0 || batch > 65535) return ADR_ERR_SHAPE;
   const int width = n_heads * head_dim;
@@ -721,6 +738,7 @@ int adr_decode_attention(adr_ctx* ctx, adr_stream stream, void* out, const void*
                          int head_dim, int max_seq, int stride_q, int stride_o,
                          const int32_t* pos_dev, float scale) {
   if (!ctx || !out || !q || !k_cache || !v_cache || !pos_dev) return ADR_ERR_INVALID;
+  DeviceGuard guard(ctx);
   if (batch <= 0 || n_heads <= 0 || head_dim <= 0 || max_seq <= 0) return ADR_ERR_INVALID;
   if (head_dim % 8 != 0 || head_dim > ATT_MAX_HD || max_seq % 8 != 0 || batch > 65535)
     return ADR_ERR_SHAPE;

@@ -102,6 +102,7 @@ struct RingParams {
   unsigned int* ar_flags[8];   // flag array of rank p: [ctas][world]
   unsigned int* ar_epochs;     // this rank's per-CTA epoch counters
   int ar_rank, ar_world, ar_residual;
+  long long ar_wait_cycles;    // bound of the wait for the peers' flags
   // fused rms_norm of the activations (norm_w != nullptr; resident activations only)
   const __half* norm_w;
   float norm_eps;
@@ -215,9 +216,6 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
       if (++st == p.spu) st = 0, n0 += (int)gridDim.x * 16;
     };
     int q = 0;
-#ifdef ADR_RING_PROBE
-    if (a.beta == 124.0f) q = total_stages;  // measurement builds only: arithmetic without loads
-#endif
     if (XR) {
       // the stages carry activations: nothing may be requested before the previous kernel is done
       if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -242,9 +240,6 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
       if (lane == 0) atomicOr(p.status, 32u);
     }
     // drain: every issued stage has landed before the CTA may exit
-#ifdef ADR_RING_PROBE
-    if (a.beta == 124.0f) q = 0;
-#endif
     const int issued = q;
     for (int qq = max(0, issued - p.NS); qq < issued; ++qq)
       if (!mbar_wait(&full[qq % p.NS], (unsigned)(qq / p.NS) & 1u) && lane == 0) atomicOr(p.status, 64u);
@@ -263,7 +258,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     const bool per_piece = p.bs_shift < 7;
     bool ok = true;
     if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
-    ok = mbar_wait(xbar, 0);
+    ok = __all_sync(0xffffffffu, mbar_wait(xbar, 0));  // the same verdict in every lane
 
     // ---- optional rms_norm of the activation rows, in place in shared memory, with the bits of
     // the reference kernel (normalize.cu:7-58; rowops.cu): that kernel's thread tid sums elements
@@ -434,17 +429,9 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
         if (++cs == p.NS) cs = 0, cpar ^= 1u;
         if (NG > 1 && ++cgrp == NG) cgrp = 0;
         if (!mine) continue;  // another group's stage
-#ifdef ADR_RING_PROBE
-        if (a.beta != 124.0f)
-#endif
-        if (ok) ok = mbar_wait(&full[s], par) && !*abort_flag;
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[s], par) && !*abort_flag);
         const int kt = st * RING_TILES + tile;
-#ifdef ADR_RING_PROBE
-        // measurement builds only: beta == 123 streams the weights without the arithmetic
-        if (ok && kt < ntiles && a.beta != 123.0f) {
-#else
         if (ok && kt < ntiles) {
-#endif
           const uint8_t* stage = ring + (size_t)s * p.stage_bytes;
           const uint8_t* trow = stage + tile * RING_TILE_BYTES + pg * 128;
           if constexpr (XR) {
@@ -563,7 +550,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
         const unsigned int* mine = p.ar_flags[p.ar_rank] + (size_t)blockIdx.x * p.ar_world + pe;
         const long long t0 = clock64();
         while ((int)(ld_acquire_sys_u32(mine) - epoch) < 0) {
-          if (clock64() - t0 > kWaitLimitCycles) {
+          if (clock64() - t0 > p.ar_wait_cycles) {
             atomicOr(p.status, 256u);
             break;
           }
@@ -636,13 +623,6 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   }
   ns = std::min(ns, RING_MAX_STAGES);
   if (a.m <= 8) ns = std::min(ns, RING_RED_BUFS * spu - 1);  // keeps the rotation of partial-sum buffers safe
-#ifdef ADR_RING_PROBE
-  if (const char* e = getenv("ADR_RING_NS")) {  // measurement builds only
-    const int want = atoi(e);
-    if (want >= 3 && fixed + (size_t)want * RING_STAGE_BYTES <= all) ns = std::min(want, RING_MAX_STAGES);
-  }
-  if (const char* e = getenv("ADR_RING_GRID")) pl.cps = atoi(e) == 2 ? 2 : 1;
-#endif
   pl.xr = 0;
   pl.stage_bytes = RING_STAGE_BYTES;
   pl.xss = 0;
@@ -680,17 +660,8 @@ template <int MT, bool Z, bool PDL, int NCW, bool XR, bool FUSE>
 int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl,
                   const RingArFuse* ar) {
   auto kfn = u8_ring_kernel<MT, NCW, Z, PDL, XR, FUSE>;
-  static bool configured[64] = {};
   cudaError_t e;
-  const int dev = ctx->device & 63;
-  if (!configured[dev]) {
-    e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-    if (e != cudaSuccess) {
-      ctx->last_cuda_error = (int)e;
-      return ADR_ERR_CUDA;
-    }
-    configured[dev] = true;
-  }
+  if (int rc0 = opt_in_smem(ctx, kfn, 226 * 1024); rc0 != ADR_OK) return rc0;
   // weights as (k within tile, row, k-tile): a box of 128 x 16 x 8 lands as eight tiles of
   // [16 rows][128 bytes], each swizzled by its own row index
   CUtensorMap wmap;
@@ -715,6 +686,7 @@ int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
   p.norm_w = a.norm_w;
   p.norm_eps = a.norm_eps;
   p.ar_world = 0;
+  p.ar_wait_cycles = peer_wait_cycles(ctx);
   if (ar) {
     for (int r = 0; r < ar->world; ++r) {
       p.ar_inbox[r] = ar->inbox[r];

@@ -108,22 +108,6 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
   const int nt = te - tb;
   const int k0 = tb * 128;
   uint8_t* Xsm = Wsm + (size_t)nt * TILE_BYTES;
-#ifdef ADR_U8_TRACE
-  // Debug builds only: per-warp timestamps of the kernel's phases behind the status word.
-  unsigned long long* trbuf = reinterpret_cast<unsigned long long*>(status) + 8 +
-                              ((size_t)(blockIdx.y * gridDim.x + blockIdx.x) * NW + warp) * 64;
-#define ADR_TRACE(i)                                                    \
-  do {                                                                  \
-    if (lane == 0) {                                                    \
-      unsigned long long _t;                                            \
-      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(_t));             \
-      trbuf[i] = _t;                                                    \
-    }                                                                   \
-  } while (0)
-#else
-#define ADR_TRACE(i) do { } while (0)
-#endif
-  ADR_TRACE(0);
 
   // Request order matters: everything this CTA reads is requested at once, and requests are
   // served roughly in issue order, so the small operands that gate the first MMA (scales,
@@ -175,7 +159,6 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
       }
     }
   }
-  ADR_TRACE(1);
   if (PDL) {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -219,7 +202,6 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
     Ssm[row * NG + gi] = table_entry(a.scales[src], HAS_ZERO ? a.zeros[src] : __half(), fast);
   }
   const bool all_fast = __syncthreads_and(fast) != 0;
-  ADR_TRACE(2);
 
   // two accumulator sets for one token block, used alternately, halve the MMA dependency chain
   float d[MT][4], d2[4];
@@ -363,14 +345,12 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
   };
 
   bool ok = mbar_wait(&xbar[0], 0);
-  ADR_TRACE(3);
   auto run_tiles = [&](auto fast_tag) {
     P cur, nxt;
     int ti = kp;
     if (ti < nt) {
       ok = mbar_wait(&bars[ti], 0) && ok;
       load_piece(ti, 0, cur);
-      ADR_TRACE(4);
     }
 #pragma unroll 1
     while (ti < nt) {
@@ -430,14 +410,12 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
     if (all_fast) run_tiles(std::true_type{});
     else run_tiles(std::false_type{});
   }
-  ADR_TRACE(5);
 #pragma unroll
   for (int j = 0; j < 4; ++j) d[0][j] += d2[j];
   // every warp sees every copy land before shared memory is reused below
   for (int i = 0; i < nt; ++i) ok = mbar_wait(&bars[i], 0) && ok;
   if (!ok && lane == 0) atomicOr(status, 1u);
   __syncthreads();
-  ADR_TRACE(6);
 
   // ---- reduce the KP k-phases of each row set; the staging area is free now ----
   float* red = reinterpret_cast<float*>(Wsm);  // [NW warps][16][TOK + 1]
@@ -466,7 +444,6 @@ __global__ void __launch_bounds__(NW * 32, MT == 1 ? 3 : 2)
       __half* dst = a.out + (size_t)tok * a.n + n0 + row;
       *dst = __float2half_rn(fmaf(a.beta, __half2float(*dst), v));
     }
-    ADR_TRACE(7);
     return;
   }
   for (int e = tid; e < R * TOK; e += NT) {
@@ -568,18 +545,8 @@ template <int MT, int R, bool Z, bool PDL, bool DEFER>
 int launch_stream_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const StreamPlan& pl) {
   constexpr int NW = 8;
   auto kfn = u8_stream_kernel<MT, R, NW, Z, PDL, DEFER>;
-  // opt in to large dynamic shared memory once per device for this instantiation
-  static bool configured[64] = {};
   cudaError_t e;
-  const int dev = ctx->device & 63;
-  if (!configured[dev]) {
-    e = cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) {
-      ctx->last_cuda_error = (int)e;
-      return ADR_ERR_CUDA;
-    }
-    configured[dev] = true;
-  }
+  if (int rc0 = opt_in_smem(ctx, kfn, 200 * 1024); rc0 != ADR_OK) return rc0;
   CUtensorMap wmap;
   const uint64_t dims[2] = {(uint64_t)a.p, (uint64_t)a.n};
   const uint64_t strides[1] = {(uint64_t)a.p};

@@ -14,7 +14,17 @@ The metric is algorithmic bytes per second; the roofline is HBM bandwidth.
 One JSON line is printed by rank 0.  `value` is timed with CUDA events on the
 launching stream with all inputs resident in HBM; `e2e` is the same work
 through the public API with the activations starting in pinned host memory
-and the results read back to the host inside the timed region.
+and the results read back to the host inside the timed region.  The timed
+loop of --steps steps is repeated --repeats times; the line carries the
+median and the spread.
+
+The headline metric has three parts (u8 GB/s, fp16 GEMM TFLOP/s, LLaMA-7B
+decode tokens/s).  `value` is the first; the others are measured in the same
+process with CUDA events and reported under `extra` (skipped by --no-extra).
+
+N > 1 (under torchrun) is a DIFFERENT workload: the LLaMA-65B-shape decode
+linears, tensor-parallel, strong scaling; its tp = 1 point is in the N = 1
+line's `extra.tp1_65b`.
 """
 from __future__ import annotations
 
@@ -25,7 +35,6 @@ import subprocess
 import sys
 import tempfile
 
-NCU_TRAFFIC_RATIO = 17.08 / 17.06  # measured DRAM bytes / algorithmic bytes of the decode kernel
 import time
 from pathlib import Path
 
@@ -40,6 +49,18 @@ MS = (1, 4, 16)
 BS = 128
 LAYERS = 8
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_TFLOPS = 1590.0
+
+
+def ncu_traffic_ratio():
+    """DRAM bytes / algorithmic bytes of the decode kernel from the committed summary of an ncu
+    capture (a small case; traffic grows in proportion to the weights), or None."""
+    f = ROOT / "profiles" / "dram_traffic.json"
+    try:
+        d = json.loads(f.read_text())["u8_decode"]
+        return float(d["dram_bytes"]) / float(d["algorithmic_bytes"]), d.get("kernel")
+    except Exception:
+        return None, None
 
 
 def gemv_bytes(m, n, k=K, bs=BS):
@@ -51,14 +72,19 @@ def step_bytes():
     return sum(LAYERS * sum(gemv_bytes(m, n) for n in NS) for m in MS)
 
 
-def measured_peak():
+def measured_peak(key="hbm_gbs"):
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         try:
-            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+            return float(json.loads(p.read_text())[key]), "measured"
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback"
+    return (FALLBACK_HBM_GBS if key == "hbm_gbs" else FALLBACK_TFLOPS), "fallback"
+
+
+def spread(ms_list):
+    a = sorted(ms_list)
+    return {"n": len(a), "median_ms": float(np.median(a)), "min_ms": a[0], "max_ms": a[-1]}
 
 
 class ClockSampler:
@@ -120,8 +146,18 @@ class ClockSampler:
 # (matrixmultiply::sgemm call convention, f32, all host threads) on a bounded
 # sample of the same workload.
 # ----------------------------------------------------------------------------
+def host_threads():
+    """All the host threads this process may use (launchers such as torchrun export
+    OMP_NUM_THREADS=1 to every rank, which would pin the CPU arm to one core)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:
+        return os.cpu_count() or 1
+
+
 def cpu_sample(seconds: float = 10.0):
     from oracle import oracle
+    cores = oracle.lib().orc_set_num_threads(host_threads())
     rng = np.random.default_rng(7)
     mats = []
     for n in (4096, 11008):
@@ -148,24 +184,79 @@ def cpu_sample(seconds: float = 10.0):
         if time.perf_counter() - t0 >= seconds:
             break
     dt = time.perf_counter() - t0
-    return {"value": total / dt / 1e9, "unit": "GB/s", "cores": oracle.lib().orc_num_threads(),
+    return {"value": total / dt / 1e9, "unit": "GB/s", "cores": cores,
             "kind": "port",
             "sample": f"{passes} passes over M in {list(MS)} x N in [4096, 11008], K=4096, f32 sgemm "
                       f"on weights dequantised once outside the timed region ({dt:.1f} s)"}, dt / passes
+
+
+TP_M, TP_LAYERS, TP_DIM, TP_FFN, TP_BLOCK = 16, 8, 8192, 22016, 64
+
+
+def tp_shard_shapes(world):
+    """[n, k] of the four products of one 65B-shape layer on one rank of `world`."""
+    dl, fl = TP_DIM // world, TP_FFN // world
+    return [(3 * dl, TP_DIM), (TP_DIM, dl), (2 * fl, TP_DIM), (TP_DIM, fl)]
+
+
+def tp_workload(world, how):
+    return ("configs[4]: LLaMA-65B-shape decode linears, M=16, hidden 8192, FFN 22016, "
+            "block 64, tensor-parallel: column-split qkv and gate/up, row-split o/down, " + how)
+
+
+def cpu_sample_tp(world, seconds):
+    """The N > 1 workload on the host: the f32 sgemm over the shard shapes of all `world` ranks of
+    one layer (the same products the GPUs run, done one after another), on a bounded sample."""
+    from oracle import oracle
+    cores = oracle.lib().orc_set_num_threads(host_threads())
+    rng = np.random.default_rng(11)
+    shapes = tp_shard_shapes(world)
+    # one f32 matrix per distinct shard shape, reused for every rank's shard (values do not matter
+    # for the timing; distinct buffers per rank would need 6.5 GB x 4 bytes of host memory)
+    mats = [(n, k, rng.standard_normal((n, k), dtype=np.float32)) for n, k in shapes]
+    xs = {k: rng.standard_normal((TP_M, k), dtype=np.float32) for _, k in shapes}
+
+    def one_layer():
+        b = 0
+        for _ in range(world):
+            for n, k, w in mats:
+                oracle.sgemm(xs[k], w.T)
+                b += gemv_bytes(TP_M, n, k, TP_BLOCK)
+        return b
+    one_layer()
+    t0 = time.perf_counter()
+    total, passes = 0, 0
+    while True:
+        total += one_layer()
+        passes += 1
+        if time.perf_counter() - t0 >= seconds:
+            break
+    dt = time.perf_counter() - t0
+    return {"value": total / dt / 1e9, "unit": "GB/s", "cores": cores, "kind": "port",
+            "sample": f"{passes} passes over one 65B-shape layer (all {world} ranks' shards, M=16), f32 sgemm "
+                      f"on f32 weights ({dt:.1f} s)"}, dt / passes
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     t_budget = max(2.0, min(20.0, 1.0 * (args.steps + args.warmup)))
-    base, per_pass = cpu_sample(t_budget)
+    if world > 1:
+        base, per_pass = cpu_sample_tp(world, t_budget)
+        config = tp_config(world)
+        scaling = "strong"
+    else:
+        base, per_pass = cpu_sample(t_budget)
+        config = workload_config()
+        scaling = "weak"
     line = {
         "impl": "reference", "metric": "u8_decode_gemv_hbm_gbs", "value": base["value"],
         "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": per_pass * 1e3, "higher_is_better": True, "scaling": "weak",
+        "ms_per_step": per_pass * 1e3, "higher_is_better": True, "scaling": scaling,
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(), "cpu_baseline": base,
+        "config": config, "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "reference has no host matmul for this path except matrixmultiply::sgemm (f32); "
                 "timed: the oracle's port of that call convention on all host cores; one 'step' here "
@@ -174,11 +265,243 @@ def run_reference(args):
     print(json.dumps(line))
 
 
+def tp_rank_bytes(world):
+    """Algorithmic bytes one rank moves per step: the four fused products of TP_LAYERS layers."""
+    return TP_LAYERS * sum(gemv_bytes(TP_M, n, k, TP_BLOCK) for n, k in tp_shard_shapes(world))
+
+
+def tp_config(world, use_peer=True):
+    """The N > 1 workload description; identical in both arms (nothing measured in it)."""
+    how = ("one-shot all-reduce over peer memory after o and down, one CUDA graph per step"
+           if use_peer else "NCCL all-reduce after o and down (eager, between graph segments)")
+    return {"workload": tp_workload(world, how), "layers_per_step": TP_LAYERS, "tp": world,
+            "weight_bytes_per_step_all_ranks": world * tp_rank_bytes(world),
+            "all_reduces_per_step": 2 * TP_LAYERS, "all_reduce_bytes": TP_M * TP_DIM * 2,
+            "l2_policy": "inputs larger than L2: each rank streams its own shard of 6.5 GB of distinct "
+                         "weights per step"}
+
+
 def workload_config():
     return {"workload": "configs[1]: u8 decode GEMV, M in {1,4,16}, K=4096, N in {4096,11008}, "
                         "block 128, zero point 127.5",
             "layers_per_step": LAYERS, "distinct_weight_bytes_per_m": LAYERS * sum(n * K for n in NS),
             "l2_policy": "inputs larger than L2: 1.26 GB of distinct weights between reuses"}
+
+
+def make_timer(stream_fn, world=1):
+    """CUDA-event timing of `steps` calls of fn on the launching stream, bracketed by a barrier
+    and a device synchronisation on both sides; max over ranks when there are several."""
+    import torch
+    import torch.distributed as dist
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        stream = stream_fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(steps):
+            fn()
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+    return timed
+
+
+def graphed(fn):
+    """Run fn once eagerly, then capture it into a CUDA graph; returns the replay callable."""
+    import torch
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        fn()
+    return g.replay, g
+
+
+def decode_weights(kern, gen, with_zeros):
+    import torch
+    weights = []
+    for _ in range(LAYERS):
+        layer = []
+        for n in NS:
+            q = torch.randint(0, 256, (n, K), dtype=torch.uint8, device="cuda", generator=gen)
+            s = (torch.rand((n, K // BS), device="cuda", generator=gen) * 0.009 + 0.001).half()
+            z = ((torch.rand((n, K // BS), device="cuda", generator=gen) * 16 + 120).half()
+                 if with_zeros else None)
+            layer.append((n, q, s, z))
+        weights.append(layer)
+    return weights
+
+
+# ------------------------------------------------------------------ extras
+def extra_fp16_gemm(kern, timed, args):
+    """fp16 tensor-core GEMM at the reference's own bench shape (2048 x 4096 x 4096, rhs stored
+    [N,K] ("rrc") and [K,N] ("rrr"); adrastea/src/main.rs:555-594), a large prefill shape, and
+    the 64 x 4096 x 4096 case of configs[0] against the HBM roof."""
+    import torch
+    from adrastea_b200 import TensorView
+    peak, kind = measured_peak("bf16_tflops")
+    hbm, _ = measured_peak("hbm_gbs")
+    out = {"peak_tflops": peak, "peak_kind": f"of {kind} (cuBLAS bf16 burst)"}
+    reps = max(3, args.repeats // 2)
+
+    def case(m, k, n, layout, nw, iters):
+        a = (torch.randn(m, k, device="cuda") * 0.02).half()
+        ws = [(torch.randn((n, k) if layout == "rrc" else (k, n), device="cuda") * 0.02).half()
+              for _ in range(nw)]
+        o = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+        views = [TensorView.of(w).permute([1, 0]) if layout == "rrc" else TensorView.of(w) for w in ws]
+
+        def body():
+            for v in views:
+                kern.matmul_f16(TensorView.of(o), TensorView.of(a), v)
+        replay, g = graphed(body)
+        for _ in range(2):
+            replay()
+        ms = float(np.median([timed(replay, iters) for _ in range(reps)])) / (iters * nw)
+        return ms
+    for name, (m, k, n, layout, nw, iters) in {
+            "2048x4096x4096_rrc": (2048, 4096, 4096, "rrc", 6, 10),
+            "2048x4096x4096_rrr": (2048, 4096, 4096, "rrr", 6, 10),
+            "16384x8192x8192_rrc": (16384, 8192, 8192, "rrc", 2, 3)}.items():
+        ms = case(m, k, n, layout, nw, iters)
+        tf = 2.0 * m * k * n / (ms * 1e-3) / 1e12
+        out[name] = {"us": ms * 1e3, "tflops": tf, "frac_of_peak": tf / peak}
+    for layout in ("rrc", "rrr"):
+        ms = case(64, 4096, 4096, layout, 8, 10)  # 8 distinct weights = 268 MB between reuses
+        by = 2 * (64 * 4096 + 4096 * 4096 + 64 * 4096)
+        out[f"config1_64x4096x4096_{layout}"] = {"us": ms * 1e3, "gbs": by / (ms * 1e-3) / 1e9,
+                                                 "frac_of_hbm": by / (ms * 1e-3) / 1e9 / hbm,
+                                                 "tflops": 2.0 * 64 * 4096 * 4096 / (ms * 1e-3) / 1e12}
+    return out
+
+
+def extra_zero_points(kern, timed, args, xs, outs):
+    """The headline decode mix with fp16 zero points ~U(120,136) (configs[1] as worded)."""
+    import torch
+    gen = torch.Generator(device="cuda").manual_seed(99)
+    weights = decode_weights(kern, gen, True)
+
+    def step():
+        for m in MS:
+            for layer in weights:
+                for n, q, s, z in layer:
+                    kern.matmul_nt_fp16u8(outs[(m, n)], xs[m], q, s, BS, 0.0, z)
+    replay, g = graphed(step)
+    for _ in range(3):
+        replay()
+    ms = float(np.median([timed(replay, args.steps) for _ in range(args.repeats)])) / args.steps
+    by = sum(LAYERS * sum(gemv_bytes(m, n) + 2 * n * (K // BS) for n in NS) for m in MS)
+    hbm, _ = measured_peak()
+    return {"ms_per_step": ms, "gbs": by / (ms * 1e-3) / 1e9, "frac_of_hbm": by / (ms * 1e-3) / 1e9 / hbm,
+            "bytes_per_step": by}
+
+
+def extra_llama7b(kern, batch, prefill=512, decode=128):
+    """LLaMA-7B shape, u8 weights, KV cache: `decode` graph-replayed steps after a `prefill`-token
+    prefill; tokens/s and the fraction of the weight-stream ceiling (all weights once per step at
+    the measured HBM peak)."""
+    import torch
+    from adrastea_b200.llama import LLAMA_7B, LlamaU8
+    model = LlamaU8(kern, LLAMA_7B, max_batch=batch, max_seq=prefill + decode)
+    toks = torch.randint(0, LLAMA_7B.vocab, (batch, prefill), device="cuda")
+    e = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+    model.prefill(toks)  # warm-up (descriptor cache, allocator)
+    torch.cuda.synchronize()
+    e[0].record()
+    model.prefill(toks)
+    e[1].record()
+    pos0, tok0 = model.pos.clone(), model.tokens.clone()
+    model.capture()
+    model.pos.copy_(pos0)
+    model.tokens.copy_(tok0)
+    torch.cuda.synchronize()
+    e[2].record()
+    for _ in range(decode):
+        model.decode_step()
+    e[3].record()
+    torch.cuda.synchronize()
+    kern.device_status()
+    ms_pre, ms_dec = e[0].elapsed_time(e[1]), e[2].elapsed_time(e[3]) / decode
+    wb = model.weight_bytes_per_token()
+    hbm, _ = measured_peak()
+    ceiling = batch / (wb / (hbm * 1e9))
+    tok_s = batch / (ms_dec * 1e-3)
+    del model
+    torch.cuda.empty_cache()
+    return {"decode_ms_per_step": ms_dec, "decode_tok_s": tok_s, "weight_bytes_per_step": wb,
+            "weight_stream_ceiling_tok_s": ceiling, "frac_of_ceiling": tok_s / ceiling,
+            "prefill_tokens": batch * prefill, "prefill_ms": ms_pre,
+            "prefill_tok_s": batch * prefill / (ms_pre * 1e-3)}
+
+
+def extra_clip(kern, batch=64, iters=3):
+    """CLIP ViT-L/14 image encoder forward, fp16, random weights (configs[2])."""
+    import torch
+    from adrastea_b200.clip import VIT_L_14, ClipVisionU
+    model = ClipVisionU(kern, VIT_L_14, batch)
+    px = torch.randn((batch, 3, 224, 224), device="cuda").half()
+    model.forward(px)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(iters):
+        model.forward(px)
+    e1.record()
+    torch.cuda.synchronize()
+    kern.device_status()
+    ms = e0.elapsed_time(e1) / iters
+    peak, _ = measured_peak("bf16_tflops")
+    tf = model.flops() / (ms * 1e-3) / 1e12
+    del model
+    torch.cuda.empty_cache()
+    return {"batch": batch, "ms_per_forward": ms, "images_per_s": batch / (ms * 1e-3),
+            "matmul_tflops": tf, "frac_of_peak": tf / peak}
+
+
+def extra_tp1_65b(kern, timed, args):
+    """The N > 1 workload (8 layers of the 65B-shape decode linears, M = 16) on ONE GPU, tp = 1:
+    the base point of the strong-scaling curve (efficiency at N = this / (N x ms_per_step))."""
+    import torch
+    from adrastea_b200.llama import LLAMA_65B, LlamaU8Layer
+    from adrastea_b200.tp import TPContext
+    tp = TPContext()
+    gen = torch.Generator(device="cuda").manual_seed(4321)
+    layers = [LlamaU8Layer(kern, LLAMA_65B, tp, gen, torch.device("cuda")) for _ in range(TP_LAYERS)]
+    f16 = dict(dtype=torch.float16, device="cuda")
+    d, f, M = TP_DIM, TP_FFN, TP_M
+    x, h = torch.randn((M, d), **f16), torch.zeros((M, d), **f16)
+    qkv, att = torch.zeros((M, 3 * d), **f16), torch.randn((M, d), **f16)
+    gu, g = torch.zeros((M, 2 * f), **f16), torch.randn((M, f), **f16)
+
+    def step():
+        h.copy_(x)
+        for ly in layers:
+            ly.wqkv(qkv, x)
+            ly.wo(h, att, residual=True)
+            ly.wgu(gu, x)
+            ly.down(h, g, residual=True)
+    replay, gr = graphed(step)
+    for _ in range(3):
+        replay()
+    ms = float(np.median([timed(replay, args.steps) for _ in range(max(3, args.repeats // 2))])) / args.steps
+    by = tp_rank_bytes(1)
+    hbm, _ = measured_peak()
+    kern.device_status()
+    del layers
+    torch.cuda.empty_cache()
+    return {"ms_per_step": ms, "gbs": by / (ms * 1e-3) / 1e9, "frac_of_hbm": by / (ms * 1e-3) / 1e9 / hbm,
+            "bytes_per_step": by, "workload": tp_workload(1, "no exchange at tp = 1")}
 
 
 def run_ours(args):
@@ -199,70 +522,39 @@ def run_ours(args):
     # prefetch them while the previous launch is still running (programmatic dependent launch).
     kern.set_tunable("pdl", 0 if args.no_pdl else 1)
     gen = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    weights = []
-    for _ in range(LAYERS):
-        layer = []
-        for n in NS:
-            q = torch.randint(0, 256, (n, K), dtype=torch.uint8, device="cuda", generator=gen)
-            s = (torch.rand((n, K // BS), device="cuda", generator=gen) * 0.009 + 0.001).half()
-            layer.append((n, q, s))
-        weights.append(layer)
+    weights = decode_weights(kern, gen, False)
     xs_host = {m: torch.randn((m, K), dtype=torch.float16).pin_memory() for m in MS}
     xs = {m: xs_host[m].cuda() for m in MS}
     outs = {(m, n): torch.zeros((m, n), dtype=torch.float16, device="cuda") for m in MS for n in (4096, 11008)}
     outs_host = {key: torch.zeros(v.shape, dtype=torch.float16).pin_memory() for key, v in outs.items()}
-    stream = torch.cuda.current_stream()
 
     def step():
         for m in MS:
             x = xs[m]
             for layer in weights:
-                for n, q, s in layer:
+                for n, q, s, _ in layer:
                     kern.matmul_nt_fp16u8(outs[(m, n)], x, q, s, BS)
+
+    # The step is launch-bound when driven from Python (about 14 us per call), so the
+    # launches of one step are captured once into a CUDA graph and replayed.
+    launches0 = kern.launch_count()
+    step()
+    launches_per_step = kern.launch_count() - launches0
+    kernel_name = kern.last_kernel().name
+    replay, graph = graphed(step)
+    stream_fn = torch.cuda.current_stream
+    timed = make_timer(stream_fn, world)
 
     def step_e2e():
         for m in MS:
             xs[m].copy_(xs_host[m], non_blocking=True)
-            x = xs[m]
-            for layer in weights:
-                for n, q, s in layer:
-                    kern.matmul_nt_fp16u8(outs[(m, n)], x, q, s, BS)
-            for n in (4096, 11008):
-                outs_host[(m, n)].copy_(outs[(m, n)], non_blocking=True)
-        stream.synchronize()  # the caller reads the result on the host every step
+        replay()
+        for key in outs:
+            outs_host[key].copy_(outs[key], non_blocking=True)
+        stream_fn().synchronize()  # the caller reads the result on the host every step
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
-            fn()
-        e1.record(stream)
-        barrier()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        return ms
-
-    # The step is launch-bound when driven from Python (about 14 us per call), so the
-    # launches of one step are captured once into a CUDA graph and replayed.
-    step()
-    torch.cuda.synchronize()
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-        step()
-    eager_step = step
-    step = graph.replay
-    stream = torch.cuda.current_stream()
     for _ in range(max(args.warmup, 3)):
-        step()
+        replay()
     uuid = None
     try:
         uuid = "GPU-" + str(torch.cuda.get_device_properties(local).uuid)
@@ -271,28 +563,37 @@ def run_ours(args):
     sampler = ClockSampler(uuid)
     if rank == 0:
         sampler.start()
-    launches0 = kern.launch_count()
-    ms = timed(step, args.steps)
-    launches = kern.launch_count() - launches0
-    if launches == 0:  # graph replays do not pass through the library's counter
-        eager_step()
-        launches = (kern.launch_count() - launches0) * args.steps
-    # per-M breakdown (untimed for the headline; each is its own event pair)
+    ms_runs = [timed(replay, args.steps) for _ in range(args.repeats)]
+    ms = float(np.median(ms_runs))
+    # per-M breakdown (each its own graph and event pair)
     per_m = {}
     for m in MS:
         def one_m(m=m):
             for layer in weights:
-                for n, q, s in layer:
+                for n, q, s, _ in layer:
                     kern.matmul_nt_fp16u8(outs[(m, n)], xs[m], q, s, BS)
-        gm = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(gm):
-            one_m()
-        t = timed(gm.replay, args.steps)
+        rm, gm = graphed(one_m)
+        t = float(np.median([timed(rm, args.steps) for _ in range(max(3, args.repeats // 2))]))
         b = LAYERS * sum(gemv_bytes(m, n) for n in NS)
         per_m[f"M={m}"] = round(b * args.steps / (t * 1e-3) / 1e9, 1)
     for _ in range(2):
         step_e2e()
-    ms_e2e = timed(step_e2e, args.steps)
+    e2e_runs = [timed(step_e2e, args.steps) for _ in range(max(3, args.repeats // 2))]
+    ms_e2e = float(np.median(e2e_runs))
+    kern.device_status()
+    extra = {}
+    if rank == 0 and world == 1 and not args.no_extra:
+        for name, fn in (("fp16_gemm", lambda: extra_fp16_gemm(kern, timed, args)),
+                         ("u8_zero_points", lambda: extra_zero_points(kern, timed, args, xs, outs)),
+                         ("llama7b_decode_b1", lambda: extra_llama7b(kern, 1)),
+                         ("llama7b_decode_b16", lambda: extra_llama7b(kern, 16)),
+                         ("clip_vit_l14_b64", lambda: extra_clip(kern, 64)),
+                         ("tp1_65b", lambda: extra_tp1_65b(kern, timed, args))):
+            try:
+                extra[name] = fn()
+            except Exception as e:  # noqa: BLE001 - reported in the line; the headline stands
+                extra[name] = {"error": repr(e)}
+                torch.cuda.empty_cache()
     clocks = sampler.stop() if rank == 0 else {}
 
     if rank != 0:
@@ -306,27 +607,33 @@ def run_ours(args):
     per_gpu = value / world
     h2d = sum(m * K * 2 for m in MS)
     d2h = sum(m * n * 2 for m in MS for n in (4096, 11008))
+    ratio, ratio_kernel = ncu_traffic_ratio()
     line = {
         "metric": "u8_decode_gemv_hbm_gbs", "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
+        "repeats": spread([t / args.steps for t in ms_runs]),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic", "config": workload_config(),
         "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": ms_e2e / args.steps},
-        "gpu_launches": int(launches),
+                "ms_per_step": ms_e2e / args.steps, "repeats": spread([t / args.steps for t in e2e_runs])},
+        "gpu_launches": int(launches_per_step * args.steps),
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s",
                      "frac": per_gpu / peak,
-                     # DRAM bytes per launch: the ncu capture of one [4096,4096], M=1 launch read
-                     # 17.08 MB for 17.06 MB algorithmic (profiles/u8_ring_kernel_4096x4096.md);
-                     # traffic grows in proportion to the weights, so the average launch of the
-                     # step is scaled by that ratio
-                     "traffic": bytes_step / max(launches / args.steps, 1) * NCU_TRAFFIC_RATIO,
-                     "traffic_unit": "bytes per launch (ncu capture of a 17.06 MB launch, scaled)",
+                     # DRAM bytes per launch: an ncu capture of one small launch of the same kernel
+                     # gives measured / algorithmic bytes; traffic grows in proportion to the
+                     # weights, so the average launch of the step is scaled by that ratio
+                     "traffic": (bytes_step / max(launches_per_step, 1) * ratio) if ratio else None,
+                     "traffic_unit": "bytes per launch (ncu capture of a small launch, scaled)",
+                     "traffic_kernel": ratio_kernel,
                      "peak_kind": f"of {peak_kind}",
-                     "kernel": "u8_ring_kernel", "per_m_gbs": per_m,
-                     "bytes_per_launch_avg": bytes_step / max(launches / args.steps, 1)},
+                     "kernel": kernel_name, "per_m_gbs": per_m,
+                     "bytes_per_launch_avg": bytes_step / max(launches_per_step, 1)},
         "clocks": clocks,
+        "note": "N = 1 runs configs[1] (weak scaling: every rank its own copy); N > 1 runs configs[4] "
+                "(65B-shape, tensor-parallel, strong scaling), whose tp = 1 point is extra.tp1_65b",
     }
+    if extra:
+        line["extra"] = extra
     if world == 1 and not args.no_cpu:
         base, _ = cpu_sample(10.0)
         line["cpu_baseline"] = base
@@ -364,7 +671,8 @@ def run_ours_tp(args):
     tp = TPContext()
     kern = GpuKernels(local)
     kern.set_tunable("pdl", 0 if args.no_pdl else 1)
-    sh, M, TP_LAYERS = LLAMA_65B, 16, 8
+    sh, M = LLAMA_65B, TP_M
+    assert (sh.dim, sh.ffn, sh.block) == (TP_DIM, TP_FFN, TP_BLOCK)
     gen = torch.Generator(device=dev).manual_seed(4321 + rank)
     layers = [LlamaU8Layer(kern, sh, tp, gen, dev) for _ in range(TP_LAYERS)]
     d, dl, fl = sh.dim, sh.dim // world, sh.ffn // world
@@ -424,6 +732,8 @@ def run_ours_tp(args):
     replay = list(segments)
 
     def step():
+        if use_peer:
+            h.copy_(x)  # the residual stream starts from the step's input (it would otherwise grow without bound)
         for seg in replay:
             seg()
             if not use_peer:
@@ -431,31 +741,45 @@ def run_ours_tp(args):
         if not use_peer:
             h.copy_(part)
 
-    def act_bytes(ly):
-        b = 0
-        for lin in ly.linears():
-            b += 2 * M * lin.w.k + 2 * M * lin.w.n
-        return b
+    bytes_rank = tp_rank_bytes(world)
+    timed = make_timer(torch.cuda.current_stream, world)
 
-    bytes_rank = sum(ly.weight_bytes() + act_bytes(ly) for ly in layers)
-
-    def barrier():
-        dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(steps):
-            fn()
-        e1.record(stream)
-        barrier()
-        t = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    def tp_check():
+        """Outside the timed region: one row-split product reduced by the path under test against
+        an fp32 sum of the ranks' partial products gathered with NCCL, and the same bits on every
+        rank (MIN and MAX over ranks of the raw fp16 patterns agree)."""
+        ly = layers[0]
+        shared = torch.Generator(device=dev).manual_seed(99)  # the residual is replicated
+        h0 = torch.randn((M, d), device=dev, generator=shared).half()
+        got = h0.clone()
+        if use_peer:
+            ly.wo(got, att, residual=True)
+        else:
+            ly.wo(got, att, torch.zeros_like(got), residual=True)
+        w = ly.wo.w
+        deq = (w.q.float() - 127.5) * w.scales.float().repeat_interleave(w.block, dim=1)
+        want = att.float() @ deq.t()
+        dist.all_reduce(want)
+        want += h0.float()
+        max_rel = float(((got.float() - want).abs().max() / want.abs().max()).item())
+        bits = got.view(torch.int16).to(torch.int32)
+        lo, hi = bits.clone(), bits.clone()
+        dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+        dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+        same = bool(torch.equal(lo, hi))
+        kern.device_status()
+        return {"max_rel": max_rel, "same_bits": same, "tolerance": 1e-2,
+                "what": "layer 0 o-projection + all-reduce + residual vs fp32 sum over ranks (NCCL)"}
 
     note("weights ready")
+    check = tp_check()
+    note(f"tp_check {check}")
+    if check["max_rel"] > check["tolerance"] or not check["same_bits"]:
+        if rank == 0:
+            print(json.dumps({"metric": "u8_decode_gemv_hbm_gbs", "n_gpus": world, "tp_check": check,
+                              "error": "tensor-parallel result check failed; nothing timed"}))
+        dist.destroy_process_group()
+        sys.exit(1)
     step()
     torch.cuda.synchronize()
     note("first eager step done")
@@ -488,6 +812,7 @@ def run_ours_tp(args):
     for _ in range(max(args.warmup, 3)):
         run()
     torch.cuda.synchronize()
+    kern.device_status()  # no bounded wait ran out during warm-up
     note("warm-up done")
     uuid = None
     try:
@@ -497,7 +822,8 @@ def run_ours_tp(args):
     sampler = ClockSampler(uuid)
     if rank == 0:
         sampler.start()
-    ms = timed(run, args.steps)
+    ms_runs = [timed(run, args.steps) for _ in range(args.repeats)]
+    ms = float(np.median(ms_runs))
     note(f"timed {ms:.2f} ms")
 
     def run_e2e():
@@ -507,11 +833,12 @@ def run_ours_tp(args):
         stream.synchronize()
 
     run_e2e()
-    ms_e2e = timed(run_e2e, args.steps)
+    e2e_runs = [timed(run_e2e, args.steps) for _ in range(max(3, args.repeats // 2))]
+    ms_e2e = float(np.median(e2e_runs))
+    kern.device_status()
+    check_after = tp_check()
     clocks = sampler.stop() if rank == 0 else {}
-    tb = torch.tensor([float(bytes_rank)], device=dev, dtype=torch.float64)
-    dist.all_reduce(tb)
-    total_bytes = float(tb.item())
+    total_bytes = float(world * bytes_rank)
     if rank == 0:
         peak, peak_kind = measured_peak()
         value = total_bytes * args.steps / (ms * 1e-3) / 1e9
@@ -520,16 +847,9 @@ def run_ours_tp(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
             "data": "synthetic",
-            "config": {"workload": "configs[4]: LLaMA-65B-shape decode linears, M=16, hidden 8192, FFN 22016, "
-                                   "block 64, tensor-parallel: column-split qkv and gate/up, row-split o/down, "
-                                   + ("one-shot all-reduce over peer memory after o and down, one CUDA graph per step"
-                                      if use_peer else "NCCL all-reduce after o and down (eager, between graph segments)"),
-                       "layers_per_step": TP_LAYERS, "tp": world,
-                       "weight_bytes_per_step_all_ranks": int(total_bytes),
-                       "all_reduces_per_step": 2 * TP_LAYERS, "all_reduce_bytes": M * d * 2,
-                       "cuda_graph": graph is not None,
-                       "l2_policy": "inputs larger than L2: each rank streams its own "
-                                    f"{bytes_rank / 1e9:.2f} GB of distinct weights per step"},
+            "config": tp_config(world, use_peer), "cuda_graph": graph is not None,
+            "repeats": spread([t / args.steps for t in ms_runs]),
+            "tp_check": check, "tp_check_after_timing": check_after,
             "e2e": {"value": total_bytes * args.steps / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": M * d * 2, "d2h_bytes_per_step": M * d * 2,
                     "ms_per_step": ms_e2e / args.steps},
@@ -539,6 +859,8 @@ def run_ours_tp(args):
                          "kernel": "u8_ring_kernel" + (" with the all-reduce fused in" if use_peer and args.fused_ar
                                                      else " + allreduce_oneshot_kernel" if use_peer else " + ncclAllReduce")},
             "clocks": clocks,
+            "note": "N > 1 is configs[4] (strong scaling); its tp = 1 point is extra.tp1_65b of the N = 1 line, "
+                    "which itself runs configs[1]",
         }
         print(json.dumps(line))
     dist.destroy_process_group()
@@ -595,7 +917,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--repeats", type=int, default=10, help="repetitions of the timed loop (median reported)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the cpu_baseline leg")
+    ap.add_argument("--no-extra", action="store_true", help="skip the fp16 / zero-point / model extras")
     ap.add_argument("--no-pdl", action="store_true", help="plain stream-ordered launches")
     ap.add_argument("--no-graph", action="store_true", help="N > 1: do not capture the step in a CUDA graph")
     ap.add_argument("--fused-ar", action="store_true",

@@ -46,6 +46,10 @@ enum {
 };
 
 /* matmul.cu:26-36, kernels.rs:80-139 */
+/* ADR_LOAD_SCALE: the reference multiplies both operands by fp16(scale) in fp16 before the
+ * product (matmul.cu:45-60).  The CUDA-core kernel does the same, bit for bit; the tensor-core
+ * kernel multiplies the fp32 accumulator by fp16(scale)^2 instead: within the 1e-2 tolerance
+ * of this path, not bit-equal. */
 enum { ADR_LOAD_IDENTITY = 0, ADR_LOAD_SCALE = 1 };
 enum {
   ADR_STORE_IDENTITY = 0,
@@ -98,6 +102,8 @@ int adr_force_kernel(adr_ctx* ctx, int kernel);
  *               before on the same stream.  Activations and output are only touched after
  *               the previous kernel has completed.  The row-op kernels honour it too.
  *               Default 0.
+ *   "wait_ms":  bound, in milliseconds, of the waits on a peer GPU in adr_allreduce_oneshot and
+ *               adr_matmul_nt_fp16u8_allreduce (0 = about a second).
  *   "u8_exact": 1 = the streaming u8 kernel rounds every dequantised weight to fp16 before
  *               the product, the arithmetic of matmul_nt_wmma_16x128x256_fp16u8.cu:5-7.
  *               Default 0: weights are not rounded and scale and zero point are applied to
@@ -151,7 +157,15 @@ int adr_matmul_f16_raw(adr_ctx* ctx, adr_stream stream, void* out, const void* l
  * matmul_nt_wmma_16x128x256_fp16u8 (matmul_nt_wmma_16x128x256_fp16u8.cu:12-83),
  * same parameter list:  out[m,n] = lhs[m,p] . deq(rhs[n,p])^T + beta * out.
  * rhs is u8 [n,p] row-major, scales fp16 [n, p/block_size] row-major.
- * deq(q) = fp16((float(q) - zero) * float(scale)), bit-exact, accumulated in fp32.
+ * The reference defines the product twice, and so does this entry point:
+ *   - decode shapes (m <= 16 per pass; the default kernels) follow matmul_nt_fp16u8.cu:13-23:
+ *     the dequantised weight (float(q) - zero) * float(scale) is NOT rounded to fp16; the kernels
+ *     sum (1024 + q) * x exactly per scale group in fp32 and apply scale and zero point to the
+ *     group sums.  Against that kernel the outputs differ only by fp32 summation order.
+ *   - the prefill kernel (m > 32), and the decode kernels when the tunable "u8_exact" is 1, follow
+ *     matmul_nt_wmma_16x128x256_fp16u8.cu:5-7: deq(q) = fp16((float(q) - zero) * float(scale)),
+ *     bit-exact, products accumulated in fp32.
+ * The two forms differ by the fp16 rounding of the weights (about 1e-3 relative on an output).
  * `zeros` NULL: zero = 127.5 (the reference's layout).  `zeros` non-NULL
  * (fp16 [n, p/block_size]; an extension without counterpart in the
  * reference): zero = float(zeros[n, group]).

@@ -491,6 +491,18 @@ int orc_num_threads(void) {
 #endif
 }
 
+/* Overrides the thread count taken from the environment (launchers such as torchrun export
+ * OMP_NUM_THREADS=1 to every rank); returns the count now in force. */
+int orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+  return omp_get_max_threads();
+#else
+  (void)n;
+  return 1;
+#endif
+}
+
 /* ------------------------------------------------------------------------ */
 /* The kernels either side of the matmuls (row ops).  The reductions follow  */
 /* the reference's order: thread `tid` of 256 sums elements tid, tid+256, .. */

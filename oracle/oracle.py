@@ -43,6 +43,8 @@ def lib() -> C.CDLL:
         _lib.orc_hadd.restype = C.c_uint16
         _lib.orc_hadd.argtypes = [C.c_uint16, C.c_uint16]
         _lib.orc_num_threads.restype = C.c_int
+        _lib.orc_set_num_threads.restype = C.c_int
+        _lib.orc_set_num_threads.argtypes = [C.c_int]
     return _lib
 
 

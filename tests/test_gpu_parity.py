@@ -507,3 +507,54 @@ def test_u8_prefill_tensor_core_kernel(kernels, zp):
             res.append(o.cpu().numpy())
         assert np.array_equal(res[0].view(np.uint16), res[1].view(np.uint16))
         assert oracle.max_rel_err(res[0], want) <= TOL, (m, p, n)
+
+
+def fp16_spacing(v):
+    """Distance between neighbouring fp16 values at magnitude |v| (normal range)."""
+    v = np.maximum(np.abs(v.astype(np.float64)), 2.0 ** -14)
+    return 2.0 ** (np.floor(np.log2(v)) - 10)
+
+
+@pytest.mark.parametrize("kernel", [Kernel.U8Ring, Kernel.U8Stream, Kernel.Auto])
+def test_u8_decode_kernels_follow_the_unrounded_reference_form(kernels, kernel):
+    """The decode kernels claim the arithmetic of matmul_nt_fp16u8.cu:13-23 (weights not rounded
+    to fp16).  Held to it here: against the oracle's faithful restatement of that kernel and,
+    when the reference cubins travelled along, against the kernel itself run live.  The only
+    difference left is the order of the fp32 additions (sequential over k there, per scale
+    group here), about 1e-6 relative on a sum before the final rounding to fp16, so almost
+    every output has the same bits and none is more than one fp16 step away (steps measured
+    at max(|ref|, rms/4), since a sum that cancels to nearly zero has no meaningful ulp)."""
+    rng = np.random.default_rng(2024)
+    worst, same, total = 0.0, 0, 0
+    try:
+        kernels.force_kernel(kernel)
+        for m in (1, 4, 16):
+            for bs in (64, 128):
+                p, n = 4096, 512
+                x = rng.standard_normal((m, p)).astype(np.float16)
+                q = rng.integers(0, 256, (n, p), dtype=np.uint8)
+                s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
+                want = oracle.matmul_nt_fp16u8(x, q, s, bs, faithful=True)
+                xd, qd, sd = dev(x), dev(q), dev(s)
+                o = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+                kernels.matmul_nt_fp16u8(o, xd, qd, sd, bs)
+                kernels.device_status()
+                got = o.cpu().numpy()
+                refs = [want]
+                if refcubin.available():
+                    r = torch.zeros_like(o)
+                    refcubin.matmul_nt_fp16u8(r.data_ptr(), xd.data_ptr(), qd.data_ptr(), sd.data_ptr(),
+                                              m, p, n, bs, 0.0)
+                    torch.cuda.synchronize()
+                    refs.append(r.cpu().numpy())
+                for ref in refs:
+                    rf = ref.astype(np.float64)
+                    unit = fp16_spacing(np.maximum(np.abs(rf), np.sqrt(np.mean(rf ** 2)) / 4))
+                    steps = np.abs(got.astype(np.float64) - rf) / unit
+                    worst = max(worst, float(steps.max()))
+                    same += int(np.count_nonzero(got.view(np.uint16) == ref.view(np.uint16)))
+                    total += got.size
+    finally:
+        kernels.force_kernel(Kernel.Auto)
+    assert worst <= 1.0, worst
+    assert same / total >= 0.97, same / total
