@@ -36,6 +36,7 @@ SIGNATURES = {
     "adr_quantize_absmax_uint8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),
     "adr_embed_uint8": (_c_int, [_vp, _vp, _c_int, _c_int, _vp, _vp, _vp, _vp, _c_int]),
     "adr_rms_norm": (_c_int, [_vp, _vp, _vp, _vp, _vp] + [_c_int] * 6 + [C.c_float]),
+    "adr_layer_norm": (_c_int, [_vp] * 6 + [_c_int] * 6 + [C.c_float]),
     "adr_softmax_rows": (_c_int, [_vp, _vp, _vp, _vp] + [_c_int] * 4 + [C.c_float]),
     "adr_rotary": (_c_int, [_vp, _vp, _vp, _vp] + [_c_int] * 8 + [C.c_float]),
     "adr_elementwise_binary_2d_f16": (_c_int, [_vp, _vp, _vp, _vp, _vp] + [_c_int] * 5 + [C.c_uint32]),
@@ -43,6 +44,7 @@ SIGNATURES = {
                                + [_vp, C.c_float]),
     "adr_decode_attention": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp] + [_c_int] * 6
                              + [_vp, C.c_float]),
+    "adr_attention_f16": (_c_int, [_vp] * 6 + [_c_int] * 5 + [_vp] * 4 + [C.c_float, C.c_uint32]),
     "adr_allreduce_oneshot": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int,
                                        C.c_longlong, _c_int]),
     "adr_rms_norm_matmul_nt_fp16u8": (_c_int, [_vp, _vp, _vp, _vp, _vp, C.c_float, _vp, _vp, _vp,

@@ -82,10 +82,12 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
     for o in obj_dir.glob("*.o"):
         if o not in keep:
             o.unlink()
-    cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(LIB_PATH), *map(str, sorted(keep))]
+    tmp = LIB_PATH.with_suffix(".so.tmp")  # linked aside, then moved into place in one step
+    cmd = [_nvcc(), *NVCC_FLAGS, "-o", str(tmp), *map(str, sorted(keep))]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc link failed:\n" + res.stdout + res.stderr)
+    os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 

@@ -2,11 +2,12 @@
 
 Restates the call sequence of the reference's `ClipAttention::forward`,
 `ClipMLP::forward` and `ClipVisionTransformer` (adrastea_models/src/clip.rs:342-486,
-754-817) around this library's fp16 GEMM: q/k/v projections with `BetaBias(0.0)`,
-scores `q.k^T` with `Scale(1/sqrt(hd))`, probabilities . v, the output projection and
-fc2 with `BetaBias(1.0)` (the residual), fc1 with `QuickGeluBias`.  Layer norms, the
-softmax and the patch embedding are harness glue done with PyTorch ops; they are not
-part of this repository's kernel contract.
+754-817) around this library's kernels: layer norms through `adr_layer_norm`, q/k/v
+projections with `BetaBias(0.0)`, the attention chain (scores `q.k^T` with
+`Scale(1/sqrt(hd))`, row softmax, probabilities . v) through the fused
+`adr_attention_f16` (or, with `fused_attention=False`, as the reference's three calls),
+the output projection and fc2 with `BetaBias(1.0)` (the residual), fc1 with
+`QuickGeluBias`.  The patch embedding is harness glue done with a PyTorch op.
 
 The reference encodes one image at a time ([257, 1024]); the CLIP workload here is a
 batch of 64, which this harness runs as [B*257, 1024] linears and B*heads batched
@@ -52,8 +53,10 @@ class _Linear:
 
 class ClipVisionU:
     def __init__(self, kernels: GpuKernels, shape: ClipVisionShape = VIT_L_14, batch: int = 64,
-                 seed: int = 0, device="cuda", score_pitch: int | None = None):
+                 seed: int = 0, device="cuda", score_pitch: int | None = None,
+                 fused_attention: bool = True):
         self.k, self.shape, self.B = kernels, shape, batch
+        self.fused_attention = fused_attention and (shape.hidden // shape.heads) in (64, 128)
         self.device = torch.device(device)
         gen = torch.Generator(device=self.device).manual_seed(4242 + seed)
         d, f = shape.hidden, shape.mlp
@@ -79,6 +82,10 @@ class ClipVisionU:
         self.scores = torch.full((B * H, S, self.Sp), float("-inf"), **f16)
         self.probs = z(B * H, S, self.Sp)
         self.mid = z(S * B, f)
+        self.n1 = z(S * B, d)
+        # layer-norm scale and shift (the seeded workload uses gamma = 1, beta = 0)
+        self.ln_w = torch.ones(d, **f16)
+        self.ln_b = torch.zeros(d, **f16)
         heads = TensorLayout.new((B * H, S, hd), (hd, B * d, 1))
         self.qv, self.kv, self.vv, self.ov = (TensorView(t, heads) for t in (self.q, self.kx, self.v, self.att))
         sl = TensorLayout.new((B * H, S, S), (S * self.Sp, self.Sp, 1))
@@ -88,8 +95,27 @@ class ClipVisionU:
         self.k.matmul_f16(TensorView.of(out), TensorView.of(x), TensorView.of(lin.w).permute([1, 0]),
                           MatmulOptions.new().store(store))
 
-    def _ln(self, x):
-        return torch.nn.functional.layer_norm(x, (x.shape[-1],), eps=self.shape.eps)  # fp32 statistics inside
+    def _ln(self, out, x):
+        """layer_norm (clip.rs:431-442 / kernels.rs:652-678) of the rows of x into out."""
+        self.k.layer_norm(TensorView.of(out), TensorView.of(x), TensorView.of(self.ln_w),
+                          TensorView.of(self.ln_b), self.shape.eps)
+        return out
+
+    def _attention(self, hd):
+        scale = 1.0 / math.sqrt(hd)
+        if self.fused_attention:
+            self.k.attention_f16(self.ov, self.qv, self.kv, self.vv, scale)
+            return
+        self.k.matmul_f16(self.sv, self.qv, self.kv.permute([0, 2, 1]),
+                          MatmulOptions.new().store(MatmulStore.Scale(scale)))
+        if self.Sp == self.shape.tokens:
+            self.k.softmax_rows_inplace(self.sv, 1.0)
+            probs = self.sv
+        else:
+            # padded rows: the pad columns hold -inf, a softmax over whole rows leaves zeros there
+            torch.softmax(self.scores, dim=-1, out=self.probs)
+            probs = self.pv
+        self.k.matmul_f16(self.ov, probs, self.vv)
 
     def forward(self, pixels: torch.Tensor) -> torch.Tensor:
         """pixels: [B, 3, image, image] fp16 -> final hidden state [B, tokens, hidden]."""
@@ -99,18 +125,15 @@ class ClipVisionU:
         emb = torch.nn.functional.conv2d(pixels, self.patch_w, stride=sh.patch)  # clip.rs:767-779
         emb = emb.flatten(2).permute(2, 0, 1)                                     # [256, B, d]
         x = torch.cat([self.cls.expand(1, B, d), emb], dim=0) + self.pos[:, None, :]
-        self.h.copy_(self._ln(x).reshape(S * B, d))                               # pre-layernorm
+        self._ln(self.h, x.reshape(S * B, d).contiguous())                          # pre-layernorm
         for blk in self.blocks:
-            n1 = self._ln(self.h)
+            n1 = self._ln(self.n1, self.h)
             self._linear(self.q, n1, blk["q"], MatmulStore.BetaBias(0.0, TensorView.of(blk["q"].b)))
             self._linear(self.kx, n1, blk["k"], MatmulStore.BetaBias(0.0, TensorView.of(blk["k"].b)))
             self._linear(self.v, n1, blk["v"], MatmulStore.BetaBias(0.0, TensorView.of(blk["v"].b)))
-            self.k.matmul_f16(self.sv, self.qv, self.kv.permute([0, 2, 1]),
-                              MatmulOptions.new().store(MatmulStore.Scale(1.0 / math.sqrt(hd))))
-            torch.softmax(self.scores, dim=-1, out=self.probs)                    # fp32 inside
-            self.k.matmul_f16(self.ov, self.pv, self.vv)
+            self._attention(hd)
             self._linear(self.h, self.att, blk["o"], MatmulStore.BetaBias(1.0, TensorView.of(blk["o"].b)))
-            n2 = self._ln(self.h)
+            n2 = self._ln(self.n1, self.h)
             self._linear(self.mid, n2, blk["fc1"], MatmulStore.QuickGeluBias(TensorView.of(blk["fc1"].b)))
             self._linear(self.h, self.mid, blk["fc2"], MatmulStore.BetaBias(1.0, TensorView.of(blk["fc2"].b)))
         return self.h.view(S, B, d).transpose(0, 1)

@@ -141,7 +141,7 @@ const char* adr_strerror(int code) {
 int adr_last_cuda_error(const adr_ctx* ctx) { return ctx ? ctx->last_cuda_error.load() : 0; }
 
 int adr_force_kernel(adr_ctx* ctx, int kernel) {
-  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_U8_RING) return ADR_ERR_INVALID;
+  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_U8_TMEM) return ADR_ERR_INVALID;
   ctx->forced_kernel = kernel;
   return ADR_OK;
 }
@@ -256,6 +256,17 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
         c.lhs = a.lhs + (size_t)r0 * p;
         c.out = a.out + (size_t)r0 * n;
         rc = launch_u8_ring(ctx, st, c);
+      }
+      break;
+    }
+    case ADR_KERNEL_U8_TMEM: {
+      rc = ADR_OK;
+      for (int r0 = 0; r0 < m && rc == ADR_OK; r0 += 16) {  // one pass per 16 tokens
+        U8Args c = a;
+        c.m = (m - r0 < 16) ? m - r0 : 16;
+        c.lhs = a.lhs + (size_t)r0 * p;
+        c.out = a.out + (size_t)r0 * n;
+        rc = launch_u8_tmem(ctx, st, c);
       }
       break;
     }

@@ -107,6 +107,67 @@ __global__ void __launch_bounds__(ROW_THREADS)
 }
 
 // ---------------------------------------------------------------------------------------
+// layer_norm (normalize.cu:60-145): out[r,i] = fp16((in[r,i] - mean) / sqrt(var + eps) * w[i] + b[i])
+// with mean and the (biased) variance in fp32, each summed in the reference's order: thread t
+// adds elements t, t + 256, ..., then the butterflies of block_sum_256.  A thread keeps its
+// elements in registers over the three passes when the row has at most 16 of them per thread.
+// ---------------------------------------------------------------------------------------
+template <bool PDL>
+__global__ void __launch_bounds__(ROW_THREADS)
+    layer_norm_kernel(__half* __restrict__ out, const __half* __restrict__ in,
+                      const __half* __restrict__ w, const __half* __restrict__ b, int lx, int s_ox,
+                      int s_oy, int s_ix, int s_iy, float eps) {
+  __shared__ float s_warp[8];
+  pdl_enter<PDL>();
+  constexpr int KEEP = 16;
+  const int tid = threadIdx.x;
+  const __half* irow = in + (int64_t)blockIdx.x * s_iy;
+  __half* orow = out + (int64_t)blockIdx.x * s_oy;
+  const bool cached = lx <= KEEP * ROW_THREADS;
+  float v[KEEP];
+  float sum = 0.0f;
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+      const int i = tid + j * ROW_THREADS;
+      v[j] = i < lx ? __half2float(irow[(int64_t)i * s_ix]) : 0.0f;
+    }
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j)
+      if (tid + j * ROW_THREADS < lx) sum += v[j];
+  } else {
+    for (int i = tid; i < lx; i += ROW_THREADS) sum += __half2float(irow[(int64_t)i * s_ix]);
+  }
+  const float mean = block_sum_256(sum, s_warp) / lx;
+  float dev2 = 0.0f;
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j)
+      if (tid + j * ROW_THREADS < lx) dev2 += (v[j] - mean) * (v[j] - mean);
+  } else {
+    for (int i = tid; i < lx; i += ROW_THREADS) {
+      const float x = __half2float(irow[(int64_t)i * s_ix]);
+      dev2 += (x - mean) * (x - mean);
+    }
+  }
+  const float stddev = sqrtf(block_sum_256(dev2, s_warp) / lx + eps);
+  if (cached) {
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+      const int i = tid + j * ROW_THREADS;
+      if (i < lx)
+        orow[(int64_t)i * s_ox] =
+            __float2half((v[j] - mean) / stddev * __half2float(w[i]) + __half2float(b[i]));
+    }
+  } else {
+    for (int i = tid; i < lx; i += ROW_THREADS)
+      orow[(int64_t)i * s_ox] = __float2half((__half2float(irow[(int64_t)i * s_ix]) - mean) / stddev *
+                                                 __half2float(w[i]) +
+                                             __half2float(b[i]));
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // softmax_rows (normalize.cu:150-220), rows of `w` elements `pitch` apart
 // ---------------------------------------------------------------------------------------
 template <bool PDL>
@@ -667,6 +728,19 @@ int adr_rms_norm(adr_ctx* ctx, adr_stream stream, void* out, const void* in, con
   return launch_row(ctx, (cudaStream_t)stream, rms_norm_kernel<false>, rms_norm_kernel<true>,
                     dim3(length_y), dim3(ROW_THREADS), 0, (__half*)out, (const __half*)in,
                     (const __half*)weights, length_x, stride_ox, stride_oy, stride_ix, stride_iy, eps);
+}
+
+int adr_layer_norm(adr_ctx* ctx, adr_stream stream, void* out, const void* in, const void* weights,
+                   const void* bias, int length_x, int length_y, int stride_ox, int stride_oy,
+                   int stride_ix, int stride_iy, float eps) {
+  if (!ctx || !out || !in || !weights || !bias) return ADR_ERR_INVALID;
+  DeviceGuard guard(ctx);
+  if (length_x <= 0 || length_y <= 0) return ADR_ERR_INVALID;
+  if (stride_ox < 0 || stride_oy < 0 || stride_ix < 0 || stride_iy < 0) return ADR_ERR_INVALID;
+  return launch_row(ctx, (cudaStream_t)stream, layer_norm_kernel<false>, layer_norm_kernel<true>,
+                    dim3(length_y), dim3(ROW_THREADS), 0, (__half*)out, (const __half*)in,
+                    (const __half*)weights, (const __half*)bias, length_x, stride_ox, stride_oy,
+                    stride_ix, stride_iy, eps);
 }
 
 int adr_softmax_rows(adr_ctx* ctx, adr_stream stream, void* out, const void* in, int heads, int h,

@@ -42,16 +42,16 @@ void tma_destroy(adr_ctx* ctx) {
 int tma_get(adr_ctx* ctx, CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base,
             const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
             CUtensorMapSwizzle swizzle) {
-  if (!ctx->encode_tiled_fn || !ctx->tma_cache || rank < 2 || rank > 3) return ADR_ERR_INVALID;
+  if (!ctx->encode_tiled_fn || !ctx->tma_cache || rank < 2 || rank > 4) return ADR_ERR_INVALID;
   MapKey key;
   memset(&key, 0, sizeof(key));
   key.v[0] = (uint64_t)(uintptr_t)base;
   key.v[1] = ((uint64_t)dtype << 32) | ((uint64_t)rank << 16) | (uint64_t)swizzle;
   for (int i = 0; i < rank; ++i) {
     key.v[2 + i] = dims[i];
-    key.v[8 + i] = box[i];
+    key.v[9 + i] = box[i];
   }
-  for (int i = 0; i + 1 < rank; ++i) key.v[5 + i] = strides_bytes[i];
+  for (int i = 0; i + 1 < rank; ++i) key.v[6 + i] = strides_bytes[i];
   TmaCache* cache = static_cast<TmaCache*>(ctx->tma_cache);
   {
     std::lock_guard<std::mutex> lock(ctx->mu);
@@ -61,10 +61,10 @@ int tma_get(adr_ctx* ctx, CUtensorMap* out, CUtensorMapDataType dtype, int rank,
       return ADR_OK;
     }
   }
-  cuuint64_t gdim[3] = {1, 1, 1};
-  cuuint64_t gstride[2] = {16, 16};
-  cuuint32_t bdim[3] = {1, 1, 1};
-  cuuint32_t estride[3] = {1, 1, 1};
+  cuuint64_t gdim[4] = {1, 1, 1, 1};
+  cuuint64_t gstride[3] = {16, 16, 16};
+  cuuint32_t bdim[4] = {1, 1, 1, 1};
+  cuuint32_t estride[4] = {1, 1, 1, 1};
   for (int i = 0; i < rank; ++i) {
     gdim[i] = dims[i];
     bdim[i] = box[i];

@@ -19,7 +19,7 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 int tma_init(adr_ctx* ctx);
 void tma_destroy(adr_ctx* ctx);
 
-// A rank-`rank` (2 or 3) tiled map over `base`.  dims[0] is the innermost extent in
+// A rank-`rank` (2 to 4) tiled map over `base`.  dims[0] is the innermost extent in
 // elements, strides_bytes[i] the byte pitch of dimension i+1, box the tile in elements.
 // Cached in the context by value of all arguments.  Returns ADR_OK or an error code.
 int tma_get(adr_ctx* ctx, CUtensorMap* out, CUtensorMapDataType dtype, int rank, const void* base,
@@ -94,6 +94,14 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, i
       "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
       "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
       "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* map, int x, int y, int z,
+                                            int w, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y), "r"(z), "r"(w)
       : "memory");
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {

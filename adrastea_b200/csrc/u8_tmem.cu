@@ -1,0 +1,656 @@
+// u8-weight decode GEMV/GEMM on the 5th-generation tensor cores (m <= 16, block_size 64 or 128):
+//   out[m,n] = lhs[m,p] . deq(Q[n,p])^T + beta * out
+// (replaces adrastea_kernels/cpp/matmul_nt_fp16u8.cu:4-24 and
+// matmul_nt_wmma_16x128x256_fp16u8.cu:12-83 for decode shapes).
+//
+// The product is laid out with the WEIGHTS as the 128-row operand of tcgen05.mma and the tokens
+// as its 16-column operand, so the cost per weight byte does not depend on the number of tokens:
+//   * a stage is 128 k-bytes of up to 128 weight rows (four TMA boxes of 32 rows x 128 bytes,
+//     128-byte swizzle) in a ring of shared-memory stages, filled by a producer warp;
+//   * the consumer warps turn each byte into the fp16 value 1024 + q with one PRMT per pair
+//     (exact: the byte is put under the exponent of 1024) and write the result straight into
+//     TENSOR MEMORY with tcgen05.st: thread = weight row = TMEM lane, 8 columns per 16 bytes.
+//     The weights never exist as fp16 in shared memory;
+//   * one thread issues tcgen05.mma with the A operand read from tensor memory and the tokens
+//     (resident in shared memory as 128-byte-swizzled K-major tiles, loaded once by TMA) as B;
+//     every scale group gets an accumulator of its own (128 lanes x 16 fp32 columns);
+//   * the consumer warps read a finished group back (tcgen05.ld) and apply scale and zero point
+//     in fp32:  sum_k (q_k - z) s x_k = s * (sum_k (1024 + q_k) x_k - (1024 + z) sum_k x_k),
+//     the arithmetic of matmul_nt_fp16u8.cu:13-23 (weights not rounded to fp16);
+//   * k is split over a thread-block cluster of S CTAs (each CTA keeps only its slice of the
+//     activations); the partial sums are exchanged through distributed shared memory and added
+//     in rank order, so the result is deterministic and no scratch memory in HBM is needed.
+// A cluster walks a contiguous range of 32-row strips in chunks of up to four; the ranges are
+// equal to within one strip.  Under programmatic dependent launch the producer fills the ring
+// before griddepcontrol.wait (weights, scales and zero points are by contract not written by
+// the previous kernel); activations and output are touched only after it.  Every wait is
+// bounded; a wait that runs out sets the status word and the CTA drains its copies, frees its
+// tensor memory and returns.
+#include <algorithm>
+
+#include "tcgen05.cuh"
+#include "u8_common.cuh"
+
+namespace adr {
+
+namespace {
+
+constexpr int TM_STAGE_BYTES = 128 * 128;  // 128 rows x 128 k-bytes
+constexpr int TM_STRIP_BYTES = 32 * 128;
+constexpr int TM_MAX_STAGES = 12;
+constexpr int TM_NA = 2;        // A buffers in tensor memory (64 columns each)
+constexpr int TM_ND = 8;        // group accumulators in tensor memory (16 columns each)
+constexpr int TM_TOK = 16;      // token columns of the MMA
+constexpr uint32_t TM_COLS = 256;  // TM_NA * 64 + TM_ND * 16
+constexpr int TM_XTILE_BYTES = TM_TOK * 128;  // 16 tokens x 64 k fp16
+
+struct TmemParams {
+  U8Args a;
+  int S;          // cluster size = k-split
+  int per;        // strips per cluster
+  int strips;     // ceil(n / 32)
+  int NS;         // ring stages
+  int gps;        // scale groups per 128-k stage (1 or 2)
+  int max_tiles;  // k-tiles of the longest slice
+  unsigned int* status;
+};
+
+// ---- PTX wrappers that the other kernels do not need ----------------------------------
+__device__ __forceinline__ void tmem_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr),
+               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld_x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                 "=r"(r[7])
+               : "r"(taddr)
+               : "memory");
+}
+// D[tmem] (+)= A[tmem] . B[smem]: the A operand is read from tensor memory.
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void named_bar(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, unsigned parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, unsigned parity) {
+  if (mbar_try_wait_cluster(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (clock64() - t0 > kWaitLimitCycles) return false;
+  }
+}
+__device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
+  float v;
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(cluster_addr) : "memory");
+  return v;
+}
+
+// Warps 0 .. NCW-1 convert and drain (warp w serves TMEM lane quarter w % 4 and token part
+// w / 4), warp NCW produces, warp NCW + 1 allocates tensor memory and issues the MMAs.
+template <int NCW, bool PDL>
+__global__ void __launch_bounds__((NCW + 2) * 32, 2)
+    u8_tmem_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
+                   TmemParams p) {
+  constexpr int PARTS = NCW / 4;          // warps per lane quarter
+  constexpr int TPP = TM_TOK / PARTS;     // tokens drained per warp (8 or 4)
+  constexpr int CPP = 8 / PARTS;          // 16-byte chunks of a 128-byte row converted per warp
+  static_assert(NCW == 8, "the drain below reads eight token columns per warp");
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const U8Args& a = p.a;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const uint32_t S = (uint32_t)p.S;
+  const uint32_t rank = S > 1 ? cluster_rank() : 0u;
+  const int cluster_id = (int)(blockIdx.x / S);
+
+  // ---- this CTA's slice of k and this cluster's range of strips ----
+  const int ntiles = a.p / 128;
+  const int tb = (int)((long long)rank * ntiles / S);
+  const int te = (int)((long long)(rank + 1) * ntiles / S);
+  const int nt = te - tb;  // stages per chunk
+  const int strip_lo = cluster_id * p.per;
+  const int strip_hi = min(p.strips, strip_lo + p.per);
+  const int my_strips = max(0, strip_hi - strip_lo);
+  const int nchunks = (my_strips + 3) / 4;
+  const int total_stages = nchunks * nt;
+  const int groups = a.p / a.block_size;
+
+  // ---- shared memory ----
+  uint8_t* ring = smem_raw;
+  uint8_t* Xsm = ring + (size_t)p.NS * TM_STAGE_BYTES;                       // [2 * max_tiles][16][128 B]
+  float* partial = reinterpret_cast<float*>(Xsm + (size_t)2 * p.max_tiles * TM_XTILE_BYTES);  // [2][m][128]
+  float* xs64 = partial + (size_t)2 * a.m * 128;                             // [2 * max_tiles][16]
+  uint64_t* full = reinterpret_cast<uint64_t*>(xs64 + (size_t)2 * p.max_tiles * TM_TOK);
+  uint64_t* empty = full + TM_MAX_STAGES;
+  uint64_t* a_ready = empty + TM_MAX_STAGES;
+  uint64_t* a_free = a_ready + TM_NA;
+  uint64_t* d_ready = a_free + TM_NA;
+  uint64_t* d_free = d_ready + TM_ND;
+  uint64_t* red_ready = d_free + TM_ND;  // [2]
+  uint64_t* xfull = red_ready + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xfull + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const bool aligned = (smem_u32(smem_raw) & 1023u) == 0;  // same for every CTA of the launch
+  if (tid == 0) {
+    tma_prefetch_desc(&wmap);
+    tma_prefetch_desc(&xmap);
+    for (int s = 0; s < p.NS; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], NCW);
+    }
+    for (int i = 0; i < TM_NA; ++i) {
+      mbar_init(&a_ready[i], NCW);
+      mbar_init(&a_free[i], 1);
+    }
+    for (int i = 0; i < TM_ND; ++i) {
+      mbar_init(&d_ready[i], 1);
+      mbar_init(&d_free[i], NCW);
+    }
+    mbar_init(&red_ready[0], NCW * S);
+    mbar_init(&red_ready[1], NCW * S);
+    mbar_init(xfull, 1);
+    *abort_flag = aligned ? 0 : 1;
+    mbar_fence_init();
+    if (!aligned) atomicOr(p.status, 16u);
+  }
+  if (warp == NCW + 1) tmem_alloc(tmem_slot, TM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  if (S > 1) {
+    // the peers' barriers exist before anyone can arrive on them
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
+  if (PDL) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+  if (warp == NCW) {
+    // ------------------------------- producer -------------------------------
+    if (lane == 0 && aligned) {
+      bool ok = true;
+      int q = 0;
+      int s = 0;
+      unsigned par = 0;
+      auto issue = [&](int ci, int kt) {
+        const int strip0 = strip_lo + 4 * ci;
+        const int ns = min(4, strip_hi - strip0);
+        uint8_t* stage = ring + (size_t)s * TM_STAGE_BYTES;
+        mbar_expect_tx(&full[s], (unsigned)(ns * TM_STRIP_BYTES));
+        for (int j = 0; j < ns; ++j)
+          tma_load_2d(stage + j * TM_STRIP_BYTES, &wmap, (tb + kt) * 128, (strip0 + j) * 32, &full[s]);
+        if (++s == p.NS) s = 0, par ^= 1u;
+      };
+      int ci = 0, kt = 0;
+      auto advance = [&]() {
+        if (++kt == nt) kt = 0, ++ci;
+      };
+      // fill the ring before waiting for the previous kernel: these loads touch only weights
+      for (; q < total_stages && q < p.NS; ++q) {
+        issue(ci, kt);
+        advance();
+      }
+      if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
+      // this CTA's slice of the activations: 2 * nt tiles of [16 tokens][64 k] (rows >= m are
+      // filled with zeros by the copy engine)
+      if (my_strips > 0) {
+        mbar_expect_tx(xfull, (unsigned)(2 * nt * TM_XTILE_BYTES));
+        for (int t = 0; t < 2 * nt; ++t)
+          tma_load_2d(Xsm + (size_t)t * TM_XTILE_BYTES, &xmap, (2 * tb + t) * 64, 0, xfull);
+      } else {
+        mbar_arrive(xfull);
+      }
+      for (; q < total_stages; ++q) {
+        if (!mbar_wait(&empty[s], par ^ 1u) || *abort_flag) { ok = false; break; }
+        issue(ci, kt);
+        advance();
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicOr(p.status, 32u);
+      }
+      // drain: every issued copy has landed before the CTA may exit
+      const int issued = q;
+      for (int qq = max(0, issued - p.NS); qq < issued; ++qq)
+        if (!mbar_wait(&full[qq % p.NS], (unsigned)(qq / p.NS) & 1u)) atomicOr(p.status, 64u);
+      if (!mbar_wait(xfull, 0)) atomicOr(p.status, 64u);
+    }
+  } else if (warp == NCW + 1) {
+    // ------------------------------- MMA issue -------------------------------
+    if (lane == 0 && aligned && total_stages > 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(TM_TOK, false);
+      bool ok = mbar_wait(xfull, 0) && !*abort_flag;
+      const uint32_t xbase = smem_u32(Xsm);
+      const int kk_per_group = 8 / p.gps;
+      int q = 0;
+      for (int ci = 0; ci < nchunks && ok; ++ci) {
+        for (int kt = 0; kt < nt && ok; ++kt, ++q) {
+          const int ab = q % TM_NA;
+          if (!mbar_wait(&a_ready[ab], (unsigned)(q / TM_NA) & 1u) || *abort_flag) { ok = false; break; }
+          for (int e = 0; e < p.gps; ++e) {
+            const int gi = q * p.gps + e;
+            if (!mbar_wait(&d_free[gi % TM_ND], ((unsigned)(gi / TM_ND) & 1u) ^ 1u)) ok = false;
+          }
+          if (!ok) break;
+          tc_fence_after_sync();
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk) {
+            const int gi = q * p.gps + kk / kk_per_group;
+            const uint32_t d_addr = tmem_base + (uint32_t)(TM_NA * 64 + (gi % TM_ND) * TM_TOK);
+            const uint32_t a_addr = tmem_base + (uint32_t)(ab * 64 + kk * 8);
+            // B: tile 2 * kt + kk / 4 of the resident activations, 32 bytes further per k16
+            const uint64_t bdesc =
+                umma_desc_k_sw128(xbase + (uint32_t)((2 * kt + (kk >> 2)) * TM_XTILE_BYTES)) +
+                (uint64_t)((kk & 3) * 2);
+            umma_f16_ts(d_addr, a_addr, bdesc, idesc, (kk % kk_per_group) != 0 ? 1u : 0u);
+          }
+          umma_commit(&a_free[ab]);
+          for (int e = 0; e < p.gps; ++e) umma_commit(&d_ready[(q * p.gps + e) % TM_ND]);
+        }
+      }
+      if (!ok) {
+        *abort_flag = 1;
+        atomicOr(p.status, 8u);
+      }
+    }
+  } else {
+    // ------------------------------- consumers -------------------------------
+    const int quarter = warp & 3, part = warp >> 2;
+    const int row = quarter * 32 + lane;  // row of the chunk = TMEM lane
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const bool my_toks = part * TPP < a.m;
+    bool ok = aligned;
+    bool x_ready = false;
+    int q = 0;
+    // the stage whose accumulators are still to be drained
+    int pend_q = -1, pend_kt = 0;
+    float pend_s[2] = {0.f, 0.f}, pend_c[2] = {0.f, 0.f};
+    float d[TPP];
+
+    auto drain = [&](bool have_rows) {
+      if (!x_ready) {
+        // first drain of the launch: the activation sums per 64-wide tile and token
+        if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(xfull, 0) && !*abort_flag);
+        if (ok) {
+          for (int idx = tid; idx < 2 * nt * TM_TOK; idx += NCW * 32) {
+            const int tile = idx >> 4, tok = idx & 15;
+            const uint8_t* xr = Xsm + (size_t)tile * TM_XTILE_BYTES + tok * 128;
+            float sum = 0.0f;
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const uint4 u = *reinterpret_cast<const uint4*>(xr + c * 16);
+              const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const float2 f = __half22float2(h[j]);
+                sum += f.x;
+                sum += f.y;
+              }
+            }
+            xs64[tile * TM_TOK + tok] = sum;
+          }
+        }
+        named_bar(1, NCW * 32);
+        x_ready = true;
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        if (e >= p.gps) break;
+        const int gi = pend_q * p.gps + e;
+        const int acc = gi % TM_ND;
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&d_ready[acc], (unsigned)(gi / TM_ND) & 1u) && !*abort_flag);
+        tc_fence_after_sync();
+        if (ok && have_rows && my_toks) {
+          uint32_t v[8];
+          tmem_ld_x8(tmem_base + lane_base + (uint32_t)(TM_NA * 64 + acc * TM_TOK + part * TPP), v);
+          // sum of the activations over this scale group, per token
+          float xs[TPP];
+          const float* x0 = xs64 + (size_t)(2 * pend_kt + (p.gps == 2 ? e : 0)) * TM_TOK + part * TPP;
+#pragma unroll
+          for (int t = 0; t < TPP; t += 4) {
+            const float4 f = *reinterpret_cast<const float4*>(x0 + t);
+            xs[t] = f.x, xs[t + 1] = f.y, xs[t + 2] = f.z, xs[t + 3] = f.w;
+          }
+          if (p.gps == 1) {
+#pragma unroll
+            for (int t = 0; t < TPP; t += 4) {
+              const float4 f = *reinterpret_cast<const float4*>(x0 + TM_TOK + t);
+              xs[t] += f.x, xs[t + 1] += f.y, xs[t + 2] += f.z, xs[t + 3] += f.w;
+            }
+          }
+          tmem_ld_wait();
+          const float sc = pend_s[e], cz = pend_c[e];
+#pragma unroll
+          for (int t = 0; t < TPP; ++t) d[t] = fmaf(sc, fmaf(-cz, xs[t], __uint_as_float(v[t])), d[t]);
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&d_free[acc]);  // also on failure, so that the MMA warp can finish
+      }
+    };
+
+    for (int ci = 0; ci < nchunks; ++ci) {
+      const int strip0 = strip_lo + 4 * ci;
+      const int ns = min(4, strip_hi - strip0);
+      const bool have_rows = quarter < ns;
+      const int n_row = strip0 * 32 + row;            // this thread's weight row
+      const bool row_ok = have_rows && n_row < a.n;
+      const size_t srow = (size_t)min(n_row, a.n - 1) * groups;
+#pragma unroll
+      for (int t = 0; t < TPP; ++t) d[t] = 0.0f;
+      for (int kt = 0; kt < nt; ++kt, ++q) {
+        const int slot = q % p.NS, ab = q % TM_NA;
+        // scale and zero point of this stage's group(s) for this row, needed one stage later
+        float cur_s[2] = {0.f, 0.f}, cur_c[2] = {1151.5f, 1151.5f};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          if (e >= p.gps) break;
+          const size_t gidx = srow + (size_t)(tb + kt) * p.gps + e;
+          cur_s[e] = row_ok ? __half2float(__ldg(a.scales + gidx)) : 0.0f;
+          if (a.zeros != nullptr) cur_c[e] = 1024.0f + __half2float(__ldg(a.zeros + gidx));
+        }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[slot], (unsigned)(q / p.NS) & 1u) && !*abort_flag);
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&a_free[ab], ((unsigned)(q / TM_NA) & 1u) ^ 1u));
+        tc_fence_after_sync();
+        if (ok && have_rows) {
+          const uint8_t* wrow = ring + (size_t)slot * TM_STAGE_BYTES + quarter * TM_STRIP_BYTES + lane * 128;
+#pragma unroll
+          for (int c = 0; c < CPP; ++c) {
+            const int cc = part * CPP + c;  // logical 16-byte chunk of the row
+            const uint4 w = *reinterpret_cast<const uint4*>(wrow + ((cc ^ (lane & 7)) * 16));
+            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
+            uint32_t h[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              h[2 * j] = prmt(ww[j], 0x64646464u, 0x4140u);      // (1024 + q) for bytes 0, 1
+              h[2 * j + 1] = prmt(ww[j], 0x64646464u, 0x4342u);  // bytes 2, 3
+            }
+            tmem_st_x8(tmem_base + lane_base + (uint32_t)(ab * 64 + cc * 8), h);
+          }
+        }
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&a_ready[ab]);   // also on failure, so that nobody waits for this warp
+          mbar_arrive(&empty[slot]);
+        }
+        if (pend_q >= 0) drain(have_rows);
+        pend_q = q;
+        pend_kt = kt;
+        pend_s[0] = cur_s[0], pend_s[1] = cur_s[1];
+        pend_c[0] = cur_c[0], pend_c[1] = cur_c[1];
+      }
+      if (pend_q >= 0) drain(have_rows);
+      pend_q = -1;
+
+      // ---- finish the chunk: add the k-slices of the cluster, write the outputs ----
+      if (S == 1) {
+        if (ok && row_ok && my_toks) {
+#pragma unroll
+          for (int t = 0; t < TPP; ++t) {
+            const int tok = part * TPP + t;
+            if (tok < a.m) {
+              __half* dst = a.out + (size_t)tok * a.n + n_row;
+              *dst = __float2half_rn(fmaf(a.beta, __half2float(*dst), d[t]));
+            }
+          }
+        }
+      } else {
+        const int buf = ci & 1;
+        float* pb = partial + (size_t)buf * a.m * 128;
+        if (have_rows && my_toks) {
+#pragma unroll
+          for (int t = 0; t < TPP; ++t) {
+            const int tok = part * TPP + t;
+            if (tok < a.m) pb[tok * 128 + row] = ok ? d[t] : 0.0f;
+          }
+        }
+        asm volatile("fence.acq_rel.cluster;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          const uint32_t bar = smem_u32(&red_ready[buf]);
+          for (uint32_t r = 0; r < S; ++r) mbar_arrive_remote(map_to_rank(bar, r));
+        }
+        if (!__all_sync(0xffffffffu, mbar_wait_cluster(&red_ready[buf], (unsigned)(ci >> 1) & 1u))) {
+          ok = false;
+          if (lane == 0) atomicOr(p.status, 4u);
+        }
+        // CTA `rank` finishes rows [rank * 128 / S, (rank + 1) * 128 / S) of the chunk
+        const int rpr = 128 / (int)S;
+        const uint32_t pbase = smem_u32(pb);
+        for (int idx = tid; idx < rpr * a.m; idx += NCW * 32) {
+          const int r_in = (int)rank * rpr + idx % rpr, tok = idx / rpr;
+          const int nr = strip0 * 32 + r_in;
+          if (r_in < ns * 32 && nr < a.n && ok) {
+            float v = 0.0f;
+            for (uint32_t r = 0; r < S; ++r)
+              v += ld_cluster_f32(map_to_rank(pbase + (uint32_t)(tok * 128 + r_in) * 4u, r));
+            __half* dst = a.out + (size_t)tok * a.n + nr;
+            *dst = __float2half_rn(fmaf(a.beta, __half2float(*dst), v));
+          }
+        }
+      }
+    }
+    if (!ok && lane == 0) atomicOr(p.status, 1u);
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  __syncwarp();
+  if (S > 1) {
+    // every CTA stays resident until its peers have read its partial sums
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
+  if (warp == NCW + 1) {
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, TM_COLS);
+  }
+}
+
+struct TmemPlan {
+  int S, per, strips, clusters, NS, gps, max_tiles;
+  size_t smem;
+};
+
+}  // namespace
+
+// Number of clusters of S CTAs that can be resident at once, asked of the runtime once per
+// context and cluster size (0: such a launch is not possible).
+static int max_clusters(adr_ctx* ctx, int S, size_t smem, bool pdl);
+
+namespace {
+
+bool plan_tmem(adr_ctx* ctx, const U8Args& a, bool pdl, TmemPlan& pl) {
+  if (a.m < 1 || a.m > TM_TOK || a.p % 128 != 0 || a.n < 1) return false;
+  if (a.block_size != 64 && a.block_size != 128) return false;
+  if (a.norm_w != nullptr) return false;
+  if ((reinterpret_cast<uintptr_t>(a.rhs) & 15u) || (reinterpret_cast<uintptr_t>(a.lhs) & 15u) ||
+      (a.p % 16) != 0)
+    return false;
+  if (!ctx->encode_tiled_fn) return false;
+  const int ntiles = a.p / 128;
+  const int strips = (a.n + 31) / 32;
+  const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+  // Shared memory per CTA: half an SM's worth under programmatic dependent launch, so that
+  // the first CTAs of the next launch fit beside this one and prefetch; all of it otherwise.
+  const size_t budget = pdl ? 113 * 1024 : 224 * 1024;
+  for (int S : {4, 2, 1, 8}) {
+    if (S > ntiles) continue;
+    const int max_tiles = (ntiles + S - 1) / S;
+    const size_t fixed = (size_t)2 * max_tiles * TM_XTILE_BYTES + (size_t)2 * a.m * 128 * 4 +
+                         (size_t)2 * max_tiles * TM_TOK * 4 + 512;
+    if (fixed + 3 * TM_STAGE_BYTES > 224 * 1024) continue;
+    size_t room = budget > fixed ? budget - fixed : 0;
+    int ns = (int)(room / TM_STAGE_BYTES);
+    if (ns < 3) ns = (int)((224 * 1024 - fixed) / TM_STAGE_BYTES);  // one CTA per SM
+    ns = std::min(ns, TM_MAX_STAGES);
+    if (ns < 3) continue;
+    const size_t smem = fixed + (size_t)ns * TM_STAGE_BYTES;
+    int maxc = S == 1 ? sms : max_clusters(ctx, S, smem, pdl);
+    if (maxc <= 0) continue;
+    maxc = std::min(maxc, sms / S);
+    const int per = (strips + maxc - 1) / maxc;
+    pl.S = S;
+    pl.per = per;
+    pl.strips = strips;
+    pl.clusters = (strips + per - 1) / per;
+    pl.NS = ns;
+    pl.gps = 128 / a.block_size;
+    pl.max_tiles = max_tiles;
+    pl.smem = smem;
+    return true;
+  }
+  return false;
+}
+
+template <bool PDL>
+int launch_tmem_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const TmemPlan& pl) {
+  auto kfn = u8_tmem_kernel<8, PDL>;
+  if (int rc = opt_in_smem(ctx, kfn, 226 * 1024); rc != ADR_OK) return rc;
+  CUtensorMap wmap, xmap;
+  {
+    const uint64_t dims[2] = {(uint64_t)a.p, (uint64_t)a.n};
+    const uint64_t strides[1] = {(uint64_t)a.p};
+    const uint32_t box[2] = {128u, 32u};
+    int rc = tma_get(ctx, &wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.rhs, dims, strides, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != ADR_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)a.p, (uint64_t)a.m};
+    const uint64_t strides[1] = {(uint64_t)a.p * 2};
+    const uint32_t box[2] = {64u, (uint32_t)TM_TOK};
+    int rc = tma_get(ctx, &xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.lhs, dims, strides, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != ADR_OK) return rc;
+  }
+  TmemParams p;
+  p.a = a;
+  p.S = pl.S;
+  p.per = pl.per;
+  p.strips = pl.strips;
+  p.NS = pl.NS;
+  p.gps = pl.gps;
+  p.max_tiles = pl.max_tiles;
+  p.status = ctx->d_status;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(pl.clusters * pl.S, 1, 1);
+  cfg.blockDim = dim3((8 + 2) * 32, 1, 1);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int na = 0;
+  if (pl.S > 1) {
+    attr[na].id = cudaLaunchAttributeClusterDimension;
+    attr[na].val.clusterDim.x = pl.S;
+    attr[na].val.clusterDim.y = 1;
+    attr[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  if (PDL) {
+    attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = na;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, wmap, xmap, p);
+  if (e != cudaSuccess) {
+    ctx->last_cuda_error = (int)e;
+    return ADR_ERR_CUDA;
+  }
+  return after_launch(ctx);
+}
+
+}  // namespace
+
+static int max_clusters(adr_ctx* ctx, int S, size_t smem, bool pdl) {
+  const uint64_t key = ((uint64_t)(pdl ? 1 : 0) << 40) | ((uint64_t)S << 32) | (uint64_t)smem;
+  {
+    std::lock_guard<std::mutex> lock(ctx->mu);
+    auto it = ctx->cluster_capacity.find(key);
+    if (it != ctx->cluster_capacity.end()) return it->second;
+  }
+  int n = 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(S * 64, 1, 1);
+  cfg.blockDim = dim3((8 + 2) * 32, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e;
+  if (pdl) {
+    auto kfn = u8_tmem_kernel<8, true>;
+    if (opt_in_smem(ctx, kfn, 226 * 1024) != ADR_OK) return 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kfn, &cfg);
+  } else {
+    auto kfn = u8_tmem_kernel<8, false>;
+    if (opt_in_smem(ctx, kfn, 226 * 1024) != ADR_OK) return 0;
+    e = cudaOccupancyMaxActiveClusters(&n, kfn, &cfg);
+  }
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  std::lock_guard<std::mutex> lock(ctx->mu);
+  ctx->cluster_capacity[key] = n;
+  return n;
+}
+
+bool u8_tmem_supports(adr_ctx* ctx, const U8Args& a) {
+  TmemPlan pl;
+  return plan_tmem(ctx, a, ctx->tune_pdl != 0, pl);
+}
+
+int launch_u8_tmem(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
+  TmemPlan pl;
+  const bool pdl = ctx->tune_pdl != 0;
+  if (!plan_tmem(ctx, a, pdl, pl)) return ADR_ERR_SHAPE;
+  return pdl ? launch_tmem_p<true>(ctx, stream, a, pl) : launch_tmem_p<false>(ctx, stream, a, pl);
+}
+
+}  // namespace adr

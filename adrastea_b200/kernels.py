@@ -64,6 +64,7 @@ class Kernel(enum.IntEnum):
     U8Simt = 6
     U8Stream = 7
     U8Ring = 8
+    U8Tmem = 9
 
 
 @dataclass(frozen=True)
@@ -348,6 +349,18 @@ class GpuKernels:
                                     input.stride(-1), input.stride(-2), eps)
         self._check(rc)
 
+    def layer_norm(self, output: TensorView, input: TensorView, weight: TensorView,
+                   bias: TensorView, eps: float, stream=None):
+        """CommonKernels::layer_norm (kernels.rs:194-197, 652-678)."""
+        assert input.size(-1) == output.size(-1) and input.size(-2) == output.size(-2)
+        assert weight.stride(-1) == 1 and weight.size(-1) == output.size(-1)
+        assert bias.stride(-1) == 1 and bias.size(-1) == output.size(-1)
+        rc = self._lib.adr_layer_norm(self._ctx, _stream_handle(stream), output.data_ptr(),
+                                      input.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                                      output.size(-1), output.size(-2), output.stride(-1),
+                                      output.stride(-2), input.stride(-1), input.stride(-2), eps)
+        self._check(rc)
+
     def rotary_inplace(self, inout: TensorView, n_heads: int, pos_offset: int, theta: float,
                        stream=None):
         """CommonKernels::rotary_inplace (kernels.rs:203-205, 722-751)."""
@@ -418,6 +431,30 @@ class GpuKernels:
             self._ctx, _stream_handle(stream), out.data_ptr(), q.data_ptr(), k_cache.data_ptr(),
             v_cache.data_ptr(), B, n_heads, width // n_heads, k_cache.shape[1], q.stride(-2),
             out.stride(-2), pos_dev.data_ptr(), scale)
+        self._check(rc)
+
+    def attention_f16(self, out: TensorView, q: TensorView, k: TensorView, v: TensorView,
+                      scale: float, mask: MatmulMask = MatmulMask.None_, stream=None):
+        """adr_attention_f16: softmax(scale * q.k^T [causal]) . v in one launch, for views of rank
+        2 ([S, hd]), 3 ([heads, S, hd]) or 4 ([outer, inner, S, hd]) with unit innermost stride:
+        the reference's matmul(Scale) -> softmax_rows -> matmul chain (llama.rs:538-554,
+        clip.rs:374-388).  Raises AdrError(ADR_ERR_SHAPE) for layouts it does not take."""
+        def lower(t: TensorView):
+            self._f16(t, "attention operand")
+            nd = len(t.layout.dims)
+            assert 2 <= nd <= 4 and t.stride(-1) == 1
+            st = [t.stride(-2), t.stride(-3) if nd > 2 else 0, t.stride(-4) if nd > 3 else 0]
+            return (C.c_longlong * 3)(*st)
+        nd = len(out.layout.dims)
+        inner = out.size(-3) if nd > 2 else 1
+        outer = out.size(-4) if nd > 3 else 1
+        s_q, hd, s_k = q.size(-2), q.size(-1), k.size(-2)
+        assert out.size(-2) == s_q and out.size(-1) == hd and k.size(-1) == hd
+        assert v.size(-2) == s_k and v.size(-1) == hd
+        rc = self._lib.adr_attention_f16(self._ctx, _stream_handle(stream), out.data_ptr(),
+                                         q.data_ptr(), k.data_ptr(), v.data_ptr(), outer, inner,
+                                         s_q, s_k, hd, lower(q), lower(k), lower(v), lower(out),
+                                         float(scale), int(mask))
         self._check(rc)
 
     def rms_norm_matmul_nt_fp16u8(self, output: torch.Tensor, lhs: torch.Tensor,

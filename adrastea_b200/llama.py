@@ -150,6 +150,9 @@ class LlamaU8:
         self.pos = torch.zeros((1,), dtype=torch.int32, device=self.device)
         self.tokens = torch.zeros((B,), dtype=torch.int64, device=self.device)
         self.next_tokens = torch.zeros((B,), dtype=torch.int64, device=self.device)
+        # prefill attention in one launch (adr_attention_f16) instead of the reference's
+        # matmul(Scale, Causal) -> softmax_rows -> matmul chain per sequence
+        self.fused_attention = hd in (64, 128) and dl % 8 == 0  # what adr_attention_f16 takes
         self._graph = None
         self._deq = None  # fp16 scratch for one expanded weight matrix (prefill)
         # rms_norm inside the decode GEMV (adr_rms_norm_matmul_nt_fp16u8).  Same bits, one launch
@@ -291,11 +294,19 @@ class LlamaU8:
                 q_b, k_b, v_b = (rows[:, i * dl:(i + 1) * dl] for i in range(3))
                 self.k.rotary_inplace(TensorView.of(q_b), Hl, 0, sh.theta)
                 self.k.rotary_inplace(TensorView.of(k_b), Hl, 0, sh.theta)
+                if self.fused_attention:
+                    continue
                 head = lambda t, order: TensorView(t, TensorLayout.new((S0, Hl, hd), (t.stride(0), hd, 1))).permute(order)
                 self.k.matmul_f16(sv, head(q_b, [1, 0, 2]), head(k_b, [1, 2, 0]),
                                   MatmulOptions.new().store(MatmulStore.Scale(scale)).mask(MatmulMask.Causal))
                 self.k.softmax_rows_inplace(sv, 1.0)
                 self.k.matmul_f16(head(att[b * S0:(b + 1) * S0], [1, 0, 2]), sv, head(v_b, [1, 0, 2]))
+            if self.fused_attention:
+                # all sequences and heads at once: [B, heads, S0, hd] views of the [B*S0, 3*dl]
+                # projections and of the [B*S0, dl] output
+                hv = lambda t: TensorView(t, TensorLayout.new((B, Hl, S0, hd), (S0 * t.stride(0), hd, t.stride(0), 1)))
+                self.k.attention_f16(hv(att), hv(qkv[:, :dl]), hv(qkv[:, dl:2 * dl]), hv(qkv[:, 2 * dl:]),
+                                     scale, MatmulMask.Causal)
             self.k_cache[li][:, :S0].copy_(qkv[:, dl:2 * dl].view(B, S0, dl))
             self.v_cache[li][:, :S0].copy_(qkv[:, 2 * dl:].view(B, S0, dl))
             self._prefill_linear(ly.wo, h, att, part, residual=True)

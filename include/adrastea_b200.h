@@ -74,7 +74,9 @@ enum {
   ADR_KERNEL_U8_TC = 5,       /* m > 16: dequantise into shared memory, tcgen05.mma  */
   ADR_KERNEL_U8_SIMT = 6,     /* any m; thread-per-output restatement (slow)         */
   ADR_KERNEL_U8_STREAM = 7,   /* m <= 16: bulk-copy staged, cluster split-k, register-fed MMA */
-  ADR_KERNEL_U8_RING = 8      /* m <= 16, block 64/128: persistent CTAs, TMA ring, scale applied per group */
+  ADR_KERNEL_U8_RING = 8,     /* m <= 16, block 64/128: persistent CTAs, TMA ring, scale applied per group */
+  ADR_KERNEL_U8_TMEM = 9      /* m <= 16, block 64/128: weights converted into tensor memory, tcgen05.mma,
+                                 cluster split-k; scale applied per group */
 };
 
 /*
@@ -231,6 +233,16 @@ int adr_rms_norm(adr_ctx* ctx, adr_stream stream, void* out, const void* in, con
                  int stride_iy, float eps);
 
 /*
+ * Replaces kernel layer_norm (normalize.cu:60-145; host side kernels.rs:652-678):
+ * out[r,i] = fp16((in[r,i] - mean_r) / sqrt(var_r + eps) * weights[i] + bias[i]), mean and the
+ * biased variance of row r in fp32, summed in the reference kernel's order.  Like adr_rms_norm
+ * the output columns are addressed with stride_ox where the reference uses stride_ix.
+ */
+int adr_layer_norm(adr_ctx* ctx, adr_stream stream, void* out, const void* in, const void* weights,
+                   const void* bias, int length_x, int length_y, int stride_ox, int stride_oy,
+                   int stride_ix, int stride_iy, float eps);
+
+/*
  * Replaces kernel softmax_rows (normalize.cu:150-220; kernels.rs:892-915):
  * `heads` matrices of h rows, softmax over the first w elements of every row,
  * out = fp16(expf(x/temperature - max) / sum).  `pitch` is the distance between
@@ -285,6 +297,30 @@ int adr_decode_attention(adr_ctx* ctx, adr_stream stream, void* out, const void*
                          const void* k_cache, const void* v_cache, int batch, int n_heads,
                          int head_dim, int max_seq, int stride_q, int stride_o,
                          const int32_t* pos_dev, float scale);
+
+/*
+ * Replaces, in ONE launch, the reference's attention chain
+ *   matmul_f16(scores, q, k^T, store Scale(scale)[, mask Causal])   llama.rs:538-547, clip.rs:374-380
+ *   softmax_rows_inplace(scores)                                    llama.rs:548; normalize.cu:150-220
+ *   matmul_f16(out, scores, v)                                      llama.rs:549-554, clip.rs:381-388
+ * for batches_outer x batches_inner independent (query, key, value) matrices (heads inside
+ * sequences or images): q is [s_q, head_dim], k and v are [s_k, head_dim], out is
+ * [s_q, head_dim], each addressed as base + outer * strides[2] + inner * strides[1] +
+ * row * strides[0] + column (strides in elements, innermost stride 1; a stride of 0 broadcasts).
+ * Rounding points of the chain that are kept: score = fp16(q.k) *h fp16(scale) (the Scale store
+ * op), softmax statistics in fp32, probabilities rounded to fp16 before the product with v,
+ * output fp16.  One difference: the probabilities are exp(score - max) and the division by
+ * their sum happens after the product with v (within the 1e-2 tolerance of this path, not
+ * bit-equal to the chain).  Mask Causal hides key x from query y when x > y, as matmul.cu does.
+ * The score matrix is never written to memory.
+ * head_dim 64 or 128; pointers 16-byte aligned; every stride a multiple of 8 elements; else
+ * ADR_ERR_SHAPE (make the three calls).
+ */
+int adr_attention_f16(adr_ctx* ctx, adr_stream stream, void* out, const void* q, const void* k,
+                      const void* v, int batches_outer, int batches_inner, int s_q, int s_k,
+                      int head_dim, const long long* strides_q, const long long* strides_k,
+                      const long long* strides_v, const long long* strides_o, float scale,
+                      uint32_t mask_op);
 
 /*
  * No counterpart in the reference (it has no multi-GPU path, llama.rs:28-29): one-shot

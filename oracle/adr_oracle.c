@@ -559,6 +559,37 @@ void orc_rms_norm(h16* out, const h16* in, const h16* w, int lx, int ly, int s_o
   }
 }
 
+/* normalize.cu:60-145: two reductions in the kernel's order (thread t sums elements t, t + 256,
+ * ...; `sum += (v - mean) * (v - mean)` and `q * w + b` are contracted to fma by nvcc), output
+ * columns addressed with stride_ox. */
+void orc_layer_norm(h16* out, const h16* in, const h16* w, const h16* b, int lx, int ly, int s_ox,
+                    int s_oy, int s_ix, int s_iy, float eps) {
+  for (int r = 0; r < ly; ++r) {
+    const h16* irow = in + (ptrdiff_t)r * s_iy;
+    h16* orow = out + (ptrdiff_t)r * s_oy;
+    float part[256];
+    for (int t = 0; t < 256; ++t) {
+      float s = 0.0f;
+      for (int i = t; i < lx; i += 256) s += h2f(irow[(ptrdiff_t)i * s_ix]);
+      part[t] = s;
+    }
+    float mean = butterfly_256(part, 0) / (float)lx;
+    for (int t = 0; t < 256; ++t) {
+      float s = 0.0f;
+      for (int i = t; i < lx; i += 256) {
+        float d = h2f(irow[(ptrdiff_t)i * s_ix]) - mean;
+        s = fmaf(d, d, s);
+      }
+      part[t] = s;
+    }
+    float stddev = sqrtf(butterfly_256(part, 0) / (float)lx + eps);
+    for (int i = 0; i < lx; ++i) {
+      float q = (h2f(irow[(ptrdiff_t)i * s_ix]) - mean) / stddev;
+      orow[(ptrdiff_t)i * s_ox] = f2h(fmaf(q, h2f(w[i]), h2f(b[i])));
+    }
+  }
+}
+
 /* normalize.cu:150-220, rows `pitch` elements apart (pitch == w in the reference) */
 void orc_softmax_rows(h16* out, const h16* in, int heads, int h, int w, int pitch, float temp) {
   for (int hd = 0; hd < heads; ++hd)

@@ -208,6 +208,19 @@ def rms_norm(x: np.ndarray, w: np.ndarray, eps: float) -> np.ndarray:
     return out
 
 
+def layer_norm(x: np.ndarray, w: np.ndarray, b: np.ndarray, eps: float) -> np.ndarray:
+    ly, lx = x.shape
+    x = np.ascontiguousarray(x)
+    _chk16(x)
+    out = np.zeros_like(x)
+    f = lib().orc_layer_norm
+    f.restype = None
+    f.argtypes = [C.c_void_p] * 4 + [C.c_int] * 6 + [C.c_float]
+    f(_p(out), _p(x), _p(np.ascontiguousarray(w)), _p(np.ascontiguousarray(b)), lx, ly, 1, lx, 1, lx,
+      float(eps))
+    return out
+
+
 def softmax_rows(x: np.ndarray, w: int | None = None, temp: float = 1.0) -> np.ndarray:
     """x: [heads, h, pitch]; softmax over the first w elements of every row (others kept)."""
     heads, h, pitch = x.shape

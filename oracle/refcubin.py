@@ -151,6 +151,14 @@ def rms_norm(out_ptr, in_ptr, w_ptr, lx, ly, s_ox, s_oy, s_ix, s_iy, eps):
     _launch(fn, (ly, 1, 1), (256, 1, 1), 0, holders)
 
 
+def layer_norm(out_ptr, in_ptr, w_ptr, b_ptr, lx, ly, s_ox, s_oy, s_ix, s_iy, eps):
+    """normalize.cu:63-73 with the launch of kernels.rs:656-676 (one block of 256 per row)."""
+    fn = _function("normalize", "layer_norm")
+    holders = [C.c_void_p(out_ptr), C.c_void_p(in_ptr), C.c_void_p(w_ptr), C.c_void_p(b_ptr)]
+    holders += [C.c_int(int(v)) for v in (lx, ly, s_ox, s_oy, s_ix, s_iy)] + [C.c_float(eps)]
+    _launch(fn, (ly, 1, 1), (256, 1, 1), 0, holders)
+
+
 def softmax_rows(out_ptr, in_ptr, heads, h, w, temp):
     """normalize.cu:150-154 with the launch of kernels.rs:895-913 (contiguous rows)."""
     fn = _function("normalize", "softmax_rows")

@@ -20,10 +20,17 @@ def test_llama_7b_layer_prefill_and_decode(kernels):
     B, S0, steps = 1, 64, 2
     model = LlamaU8(kernels, shape, max_batch=B, max_seq=S0 + steps, seed=5)
     model.embed.mul_(0.5)
+    # the seeded scales ~U(0.001, 0.01) give weights of std 0.4, which at these widths overflow
+    # fp16 activations after one FFN; a tenth of that keeps every tensor finite
+    for ly in model.layers:
+        for lin in (ly.wqkv, ly.wo, ly.wgu, ly.down):  # q/k/v and gate/up are views of these
+            lin.w.scales.mul_(0.1)
+    model.lm_head.scales.mul_(0.1)
     toks = torch.randint(0, shape.vocab, (B, S0), device="cuda")
     model.prefill(toks)
     hist = toks
     want = llama_ref(model, kernels, hist)
+    assert torch.isfinite(want).all() and torch.isfinite(model.logits).all()
     rel = ((model.logits.float() - want.float()).abs().max() / want.float().abs().max()).item()
     assert rel < 3e-2, rel
     for _ in range(steps):

@@ -243,3 +243,27 @@ def test_embed_uint8_same_bits_as_reference_and_oracle(kernels):
         torch.cuda.synchronize()
         assert torch.equal(ref.view(torch.int16), out.view(torch.int16))
     kernels.device_status()
+
+
+@pytest.mark.parametrize("rows,lx", [(5, 1024), (3, 1000), (2, 4100), (4, 64), (1, 8192)])
+def test_layer_norm_same_bits_as_reference(kernels, rows, lx):
+    """adr_layer_norm against the reference kernel run live (same bits: it keeps the kernel's
+    summation order) and against the CPU oracle (one fp16 step: libm division and square root
+    against the device's)."""
+    from adrastea_b200 import TensorView
+    rng = np.random.default_rng(rows * 100 + lx)
+    x = (rng.standard_normal((rows, lx)) * rng.uniform(0.2, 3.0, (rows, 1)) + rng.uniform(-1, 1, (rows, 1))).astype(np.float16)
+    w = rng.uniform(0.5, 1.5, lx).astype(np.float16)
+    b = rng.uniform(-0.5, 0.5, lx).astype(np.float16)
+    xd, wd, bd = dev(x), dev(w), dev(b)
+    o = torch.zeros_like(xd)
+    kernels.layer_norm(TensorView.of(o), TensorView.of(xd), TensorView.of(wd), TensorView.of(bd), 1e-5)
+    kernels.device_status()
+    got = o.cpu().numpy()
+    want = oracle.layer_norm(x, w, b, 1e-5)
+    assert ulp_diff(got, want).max() <= 1
+    if refcubin.available():
+        r = torch.zeros_like(xd)
+        refcubin.layer_norm(r.data_ptr(), xd.data_ptr(), wd.data_ptr(), bd.data_ptr(), lx, rows, 1, lx, 1, lx, 1e-5)
+        torch.cuda.synchronize()
+        assert torch.equal(r.view(torch.int16), o.view(torch.int16))

@@ -288,3 +288,18 @@ def test_decode_attention_oracle_against_numpy():
     p /= p.sum(-1, keepdims=True)
     want = np.einsum("bht,bthd->bhd", p, vh).reshape(B, H * hd)
     assert np.abs(got - want).max() / np.abs(want).max() < 5e-3
+
+
+def test_layer_norm_oracle_against_float64():
+    """The layer_norm restatement (normalize.cu:60-145) against the formula in float64: the
+    fp32 reductions cost at most one fp16 step on the output."""
+    rng = np.random.default_rng(12)
+    x = (rng.standard_normal((6, 1024)) * 2 + 0.3).astype(np.float16)
+    w = rng.uniform(0.5, 1.5, 1024).astype(np.float16)
+    b = rng.uniform(-0.5, 0.5, 1024).astype(np.float16)
+    got = oracle.layer_norm(x, w, b, 1e-5).astype(np.float64)
+    xf = x.astype(np.float64)
+    mean = xf.mean(-1, keepdims=True)
+    var = ((xf - mean) ** 2).mean(-1, keepdims=True)
+    want = (xf - mean) / np.sqrt(var + 1e-5) * w.astype(np.float64) + b.astype(np.float64)
+    assert np.max(np.abs(got - want) / np.maximum(np.abs(want), 0.25)) < 2e-3
