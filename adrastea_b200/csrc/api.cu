@@ -51,15 +51,17 @@ int run_matmul(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, bool slow
   int kernel = ctx->forced_kernel;
   if (slow) kernel = ADR_KERNEL_F16_SIMT;
   if (kernel == ADR_KERNEL_AUTO)
-    kernel = gemm_f16_tc_supports(ctx, a) ? ADR_KERNEL_F16_TC : ADR_KERNEL_F16_SIMT;
+    kernel = gemm_f16_tc_supports(ctx, a) ? ADR_KERNEL_F16_TC : ADR_KERNEL_F16_TC_GATHER;
   if (kernel == ADR_KERNEL_F16_TC) {
     if (!gemm_f16_tc_supports(ctx, a)) return ADR_ERR_SHAPE;
     rc = launch_gemm_f16_tc(ctx, stream, a);
     if (rc == ADR_ERR_SHAPE && ctx->forced_kernel == ADR_KERNEL_AUTO) {
       // the view passed the static checks but the tensor map could not be encoded
-      kernel = ADR_KERNEL_F16_SIMT;
-      rc = launch_gemm_f16_simt(ctx, stream, a);
+      kernel = ADR_KERNEL_F16_TC_GATHER;
+      rc = launch_gemm_f16_gather(ctx, stream, a);
     }
+  } else if (kernel == ADR_KERNEL_F16_TC_GATHER) {
+    rc = launch_gemm_f16_gather(ctx, stream, a);
   } else if (kernel == ADR_KERNEL_F16_SIMT) {
     rc = launch_gemm_f16_simt(ctx, stream, a);
   } else {
@@ -141,7 +143,7 @@ const char* adr_strerror(int code) {
 int adr_last_cuda_error(const adr_ctx* ctx) { return ctx ? ctx->last_cuda_error.load() : 0; }
 
 int adr_force_kernel(adr_ctx* ctx, int kernel) {
-  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_U8_TMEM) return ADR_ERR_INVALID;
+  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_F16_TC_GATHER) return ADR_ERR_INVALID;
   ctx->forced_kernel = kernel;
   return ADR_OK;
 }
@@ -150,6 +152,7 @@ int adr_set_tunable(adr_ctx* ctx, const char* name, int value) {
   if (!ctx || !name || value < 0) return ADR_ERR_INVALID;
   if (!strcmp(name, "u8_split")) ctx->tune_u8_split = value;
   else if (!strcmp(name, "u8_rows")) ctx->tune_u8_rows = value;
+  else if (!strcmp(name, "u8_tiles")) ctx->tune_u8_tiles = value;
   else if (!strcmp(name, "tc_bn")) ctx->tune_tc_bn = value;
   else if (!strcmp(name, "tc_split")) ctx->tune_tc_split = value;
   else if (!strcmp(name, "pdl")) ctx->tune_pdl = value;

@@ -70,6 +70,7 @@ struct adr_ctx {
   // tuning knobs (adr_set_tunable); 0 = let the planner choose
   std::atomic<int> tune_u8_split{0};
   std::atomic<int> tune_u8_rows{0};
+  std::atomic<int> tune_u8_tiles{0};  // k-tiles per ring slot of the tensor-memory decode kernel
   std::atomic<int> tune_u8_exact{0};  // 1: fp16-rounded dequantisation in the streaming kernel
   std::atomic<int> tune_tc_bn{0};
   std::atomic<int> tune_tc_split{0};
@@ -217,6 +218,7 @@ __device__ __forceinline__ __half dequant_one_f32(uint32_t q, float scale, float
 int launch_gemm_f16_simt(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a);
 int launch_gemm_f16_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a);
 bool gemm_f16_tc_supports(const adr_ctx* ctx, const MatmulArgs& a);
+int launch_gemm_f16_gather(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a);
 int init_gemm_f16_tc(adr_ctx* ctx);
 void destroy_gemm_f16_tc(adr_ctx* ctx);
 

@@ -500,6 +500,171 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same tensor-core tile for views the copy engine cannot describe (a row pitch that is
+// not a multiple of 16 bytes, an unaligned base, neither operand dimension contiguous): the
+// [heads, 257, 257] score and probability tensors of a 257-token encoder have a 514-byte
+// pitch (adrastea_models/src/clip.rs:374-388).  Eight loader warps read the operands with
+// ordinary 2-byte loads, any strides, and write them into the 128-byte-swizzled stage
+// layout themselves (zeros outside the extents), fence.proxy.async, arrive; the MMA warp and
+// the eight epilogue warps are those of the persistent kernel.  One CTA per 128 x BN tile.
+// B_MN: rhs rows are n-contiguous ([K,N] storage): lanes run along n and the stage holds
+// chunks of [64 k][64 n], described to the tensor core as an N-major operand.
+// ---------------------------------------------------------------------------------------
+constexpr int GATHER_LOAD_WARPS = 8;
+constexpr int GATHER_THREADS = (2 + 8 + GATHER_LOAD_WARPS) * 32;
+constexpr int GATHER_STAGES = 3;
+
+struct GatherParams {
+  const __half* lhs;
+  const __half* rhs;
+  int s_lx, s_ly, s_lz, s_rx, s_ry, s_rz;
+};
+
+template <int BN, bool B_MN>
+__global__ void __launch_bounds__(GATHER_THREADS, 1)
+    gemm_f16_tc_gather_kernel(GatherParams g, TcParams p) {
+  using Cfg = TcCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* stages = smem;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + (size_t)GATHER_STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty_bar = full_bar + GATHER_STAGES;
+  uint64_t* acc_full = empty_bar + GATHER_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = (p.k + BK - 1) / BK;
+  const int n0 = blockIdx.x * BN;
+  const int mt = (p.m + BM - 1) / BM;
+  const int m0 = (blockIdx.y % mt) * BM, b = blockIdx.y / mt;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < GATHER_STAGES; ++s) {
+      mbar_init(&full_bar[s], GATHER_LOAD_WARPS);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_fence_init();
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, BN < 32 ? 32 : BN);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  if (warp == 1) {
+    if (lane == 0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % GATHER_STAGES;
+        if (!mbar_wait(&full_bar[s], (unsigned)(kb / GATHER_STAGES) & 1u)) { ok = false; break; }
+        tc_fence_after_sync();
+        mma_k_block<BN, B_MN>(tmem_base, smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES), kb == 0);
+        umma_commit(&empty_bar[s]);
+      }
+      umma_commit(acc_full);
+    }
+  } else if (warp >= 2 && warp < 10) {
+    const int quarter = warp & 3;
+    const int chunk0 = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;
+    const __half hscale = __float2half_rn(p.scale);
+    const float hs = __half2float(hscale);
+    const float pre = p.load == ADR_LOAD_SCALE ? hs * hs : 1.0f;
+    if (!mbar_wait(acc_full, 0)) ok = false;
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after_sync();
+    if (ok) {
+      const int y = m0 + row;
+      __half* orow = p.out + (int64_t)b * p.s_oz + (int64_t)y * p.s_oy;
+      epilogue_tile_rt<BN>(p, tmem_base + ((uint32_t)(quarter * 32) << 16), orow, y, n0, chunk0, pre,
+                           hscale);
+    }
+  } else if (warp >= 10) {
+    // ---------------- loaders ----------------
+    const int lt = threadIdx.x - 10 * 32;  // 0 .. 255
+    constexpr int LT = GATHER_LOAD_WARPS * 32;
+    const __half* abase = g.lhs + (p.a_bcast ? 0 : (int64_t)b * g.s_lz);
+    const __half* bbase = g.rhs + (p.b_bcast ? 0 : (int64_t)b * g.s_rz);
+    const unsigned short zero = 0;
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
+      const int s = kb % GATHER_STAGES;
+      if (!mbar_wait(&empty_bar[s], ((unsigned)(kb / GATHER_STAGES) & 1u) ^ 1u)) { ok = false; break; }
+      uint8_t* sa = stages + (size_t)s * Cfg::STAGE_BYTES;
+      uint8_t* sb = sa + Cfg::A_BYTES;
+      const int k0 = kb * BK;
+      // A: [128 rows][64 k], lanes along k
+#pragma unroll 4
+      for (int idx = lt; idx < BM * BK; idx += LT) {
+        const int r = idx >> 6, kk = idx & 63;
+        const int y = m0 + r, k = k0 + kk;
+        unsigned short v = zero;
+        if (y < p.m && k < p.k)
+          v = __half_as_ushort(abase[(int64_t)y * g.s_ly + (int64_t)k * g.s_lx]);
+        *reinterpret_cast<unsigned short*>(sa + r * 128 + ((((kk >> 3) ^ (r & 7))) << 4) + (kk & 7) * 2) = v;
+      }
+      if (B_MN) {
+        // B: chunks of [64 k][64 n], lanes along n
+#pragma unroll 4
+        for (int idx = lt; idx < BN * BK; idx += LT) {
+          const int kk = idx / BN, nn = idx % BN;
+          const int x = n0 + nn, k = k0 + kk;
+          unsigned short v = zero;
+          if (x < p.n && k < p.k)
+            v = __half_as_ushort(bbase[(int64_t)k * g.s_ry + (int64_t)x * g.s_rx]);
+          const int c = nn >> 6, ni = nn & 63;
+          *reinterpret_cast<unsigned short*>(sb + c * 8192 + kk * 128 + ((((ni >> 3) ^ (kk & 7))) << 4) +
+                                             (ni & 7) * 2) = v;
+        }
+      } else {
+        // B: [BN rows of n][64 k], lanes along k
+#pragma unroll 4
+        for (int idx = lt; idx < BN * BK; idx += LT) {
+          const int r = idx >> 6, kk = idx & 63;
+          const int x = n0 + r, k = k0 + kk;
+          unsigned short v = zero;
+          if (x < p.n && k < p.k)
+            v = __half_as_ushort(bbase[(int64_t)k * g.s_ry + (int64_t)x * g.s_rx]);
+          *reinterpret_cast<unsigned short*>(sb + r * 128 + ((((kk >> 3) ^ (r & 7))) << 4) + (kk & 7) * 2) = v;
+        }
+      }
+      // make the generic-proxy writes visible to the tensor core's async-proxy reads
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_bar[s]);
+    }
+  }
+  if (!ok) atomicOr(p.status, 2u);
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, BN < 32 ? 32 : BN);
+  }
+}
+
+template <int BN, bool B_MN>
+int launch_gather(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a) {
+  using Cfg = TcCfg<BN>;
+  auto kfn = gemm_f16_tc_gather_kernel<BN, B_MN>;
+  constexpr size_t smem = 1024 + (size_t)GATHER_STAGES * Cfg::STAGE_BYTES + 256;
+  int rc = opt_in_smem(ctx, kfn, smem);
+  if (rc != ADR_OK) return rc;
+  const bool a_bcast = a.batches > 1 && a.s_lz == 0;
+  const bool b_bcast = a.batches > 1 && a.s_rz == 0;
+  TcParams p{a.out, a.bias, a.batches, a.m, a.k, a.n, a.s_ox, a.s_oy, a.s_oz,
+             a_bcast ? 1 : 0, b_bcast ? 1 : 0, a.beta, a.scale, a.store, a.load, a.mask,
+             ctx->d_status};
+  GatherParams g{a.lhs, a.rhs, a.s_lx, a.s_ly, a.s_lz, a.s_rx, a.s_ry, a.s_rz};
+  const long long nt = (a.n + BN - 1) / BN, mt = (a.m + BM - 1) / BM;
+  if (mt * a.batches > 65535) return ADR_ERR_SHAPE;
+  kfn<<<dim3((unsigned)nt, (unsigned)(mt * a.batches)), GATHER_THREADS, smem, stream>>>(g, p);
+  return after_launch(ctx);
+}
+
 template <int BN, bool B_MN>
 int make_maps(adr_ctx* ctx, const MatmulArgs& a, CUtensorMap* map_a, CUtensorMap* map_b,
               TcParams* p) {
@@ -651,6 +816,14 @@ int launch_gemm_f16_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a) {
     case 64: return launch_tc<64, false>(ctx, stream, a, pl.S);
     default: return launch_tc<32, false>(ctx, stream, a, pl.S);
   }
+}
+
+// Tensor-core tiles behind a gathering loader: any strides, any alignment.
+int launch_gemm_f16_gather(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a) {
+  // lanes of a loader warp run along the contiguous dimension of rhs
+  const bool b_mn = a.s_rx == 1 && a.s_ry != 1;
+  if (a.n > 64) return b_mn ? launch_gather<128, true>(ctx, stream, a) : launch_gather<128, false>(ctx, stream, a);
+  return b_mn ? launch_gather<64, true>(ctx, stream, a) : launch_gather<64, false>(ctx, stream, a);
 }
 
 int init_gemm_f16_tc(adr_ctx*) { return ADR_OK; }

@@ -49,7 +49,8 @@ struct TmemParams {
   int S;          // cluster size = k-split
   int per;        // strips per cluster
   int strips;     // ceil(n / 32)
-  int NS;         // ring stages
+  int NS;         // ring slots
+  int T;          // k-tiles per ring slot (one TMA box covers T * 128 contiguous bytes of a row)
   int gps;        // scale groups per 128-k stage (1 or 2)
   int max_tiles;  // k-tiles of the longest slice
   unsigned int* status;
@@ -123,22 +124,51 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t cluster_addr) {
   return v;
 }
 
-// Warps 0 .. NCW-1 convert and drain (warp w serves TMEM lane quarter w % 4 and token part
-// w / 4), warp NCW produces, warp NCW + 1 allocates tensor memory and issues the MMAs.
-template <int NCW, bool PDL>
-__global__ void __launch_bounds__((NCW + 2) * 32, 2)
+__device__ __forceinline__ void tmem_ld_x16t(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(cluster_addr), "f"(v) : "memory");
+}
+
+// Warp roles.  Every role runs at its own pace on its own stage of the pipeline, coupled to
+// the others only through mbarriers:
+//   warps 0-3   converters, one per TMEM lane quarter: bytes -> 1024 + q -> tensor memory
+//               (A buffer q % 2 for stage q)
+//   warps 4-7   drainers, one per lane quarter: read a finished group accumulator, apply
+//               scale and zero point, keep the 16 token sums of their row in registers; at the
+//               end of a chunk push them into the shared memory of the CTA that owns the row
+//               (k-split: CTA r of the cluster owns rows [r * 128 / S, (r + 1) * 128 / S) of
+//               every chunk) and go on with the next chunk at once
+//   warp 8      finisher: adds the S partial sums of this CTA's rows in rank order, applies
+//               beta * old and writes the outputs, off the critical path
+//   warp 9      producer (TMA)
+//   warp 10     tensor memory allocation, MMA issue
+constexpr int TM_CONV_WARPS = 4;
+constexpr int TM_DRAIN_WARPS = 4;
+constexpr int TM_W_FINISH = 8, TM_W_PRODUCER = 9, TM_W_MMA = 10;
+constexpr int TM_THREADS = 11 * 32;
+constexpr int TM_SCALE_AHEAD = 8;  // scale groups requested ahead of their use
+
+template <bool PDL>
+__global__ void __launch_bounds__(TM_THREADS, PDL ? 2 : 1)
     u8_tmem_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                    TmemParams p) {
-  constexpr int PARTS = NCW / 4;          // warps per lane quarter
-  constexpr int TPP = TM_TOK / PARTS;     // tokens drained per warp (8 or 4)
-  constexpr int CPP = 8 / PARTS;          // 16-byte chunks of a 128-byte row converted per warp
-  static_assert(NCW == 8, "the drain below reads eight token columns per warp");
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const U8Args& a = p.a;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t S = (uint32_t)p.S;
   const uint32_t rank = S > 1 ? cluster_rank() : 0u;
   const int cluster_id = (int)(blockIdx.x / S);
+  const int rpr = 128 / (int)S;  // rows of a chunk owned by each CTA of the cluster
 
   // ---- this CTA's slice of k and this cluster's range of strips ----
   const int ntiles = a.p / 128;
@@ -154,8 +184,12 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 2)
 
   // ---- shared memory ----
   uint8_t* ring = smem_raw;
-  uint8_t* Xsm = ring + (size_t)p.NS * TM_STAGE_BYTES;                       // [2 * max_tiles][16][128 B]
-  float* partial = reinterpret_cast<float*>(Xsm + (size_t)2 * p.max_tiles * TM_XTILE_BYTES);  // [2][m][128]
+  const int slot_bytes = p.T * TM_STAGE_BYTES;  // [4 strips][T tiles][32 rows][128 bytes]
+  const int spc = (nt + p.T - 1) / p.T;         // ring slots per chunk
+  const int total_slots = nchunks * spc;
+  uint8_t* Xsm = ring + (size_t)p.NS * slot_bytes;                           // [2 * max_tiles][16][128 B]
+  // partial sums pushed by the cluster: [2 buffers][S sources][m tokens][rpr rows]
+  float* partial = reinterpret_cast<float*>(Xsm + (size_t)2 * p.max_tiles * TM_XTILE_BYTES);
   float* xs64 = partial + (size_t)2 * a.m * 128;                             // [2 * max_tiles][16]
   uint64_t* full = reinterpret_cast<uint64_t*>(xs64 + (size_t)2 * p.max_tiles * TM_TOK);
   uint64_t* empty = full + TM_MAX_STAGES;
@@ -163,8 +197,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 2)
   uint64_t* a_free = a_ready + TM_NA;
   uint64_t* d_ready = a_free + TM_NA;
   uint64_t* d_free = d_ready + TM_ND;
-  uint64_t* red_ready = d_free + TM_ND;  // [2]
-  uint64_t* xfull = red_ready + 2;
+  uint64_t* red_ready = d_free + TM_ND;  // [2] partial sums of a chunk have arrived
+  uint64_t* red_free = red_ready + 2;    // [2] every owner has consumed the buffer
+  uint64_t* xfull = red_free + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(xfull + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -174,24 +209,28 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 2)
     tma_prefetch_desc(&xmap);
     for (int s = 0; s < p.NS; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], NCW);
+      mbar_init(&empty[s], TM_CONV_WARPS);
     }
     for (int i = 0; i < TM_NA; ++i) {
-      mbar_init(&a_ready[i], NCW);
+      mbar_init(&a_ready[i], TM_CONV_WARPS);
       mbar_init(&a_free[i], 1);
     }
     for (int i = 0; i < TM_ND; ++i) {
       mbar_init(&d_ready[i], 1);
-      mbar_init(&d_free[i], NCW);
+      mbar_init(&d_free[i], TM_DRAIN_WARPS);
     }
-    mbar_init(&red_ready[0], NCW * S);
-    mbar_init(&red_ready[1], NCW * S);
+    // an owner hears from every drainer warp of the cluster that holds some of its rows
+    const unsigned pushers = S <= 4 ? 4u : S;
+    mbar_init(&red_ready[0], pushers);
+    mbar_init(&red_ready[1], pushers);
+    mbar_init(&red_free[0], S);
+    mbar_init(&red_free[1], S);
     mbar_init(xfull, 1);
     *abort_flag = aligned ? 0 : 1;
     mbar_fence_init();
     if (!aligned) atomicOr(p.status, 16u);
   }
-  if (warp == NCW + 1) tmem_alloc(tmem_slot, TM_COLS);
+  if (warp == TM_W_MMA) tmem_alloc(tmem_slot, TM_COLS);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -202,29 +241,32 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 2)
   }
   if (PDL) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  if (warp == NCW) {
+  if (warp == TM_W_PRODUCER) {
     // ------------------------------- producer -------------------------------
     if (lane == 0 && aligned) {
       bool ok = true;
       int q = 0;
       int s = 0;
       unsigned par = 0;
-      auto issue = [&](int ci, int kt) {
+      // one ring slot: T k-tiles of up to four strips; strip j is one 3-D box (128 bytes x 32
+      // rows x T tiles), i.e. T * 128 contiguous bytes of every row
+      auto issue = [&](int ci, int ks) {
         const int strip0 = strip_lo + 4 * ci;
         const int ns = min(4, strip_hi - strip0);
-        uint8_t* stage = ring + (size_t)s * TM_STAGE_BYTES;
-        mbar_expect_tx(&full[s], (unsigned)(ns * TM_STRIP_BYTES));
+        uint8_t* slot = ring + (size_t)s * slot_bytes;
+        mbar_expect_tx(&full[s], (unsigned)(ns * p.T * TM_STRIP_BYTES));
         for (int j = 0; j < ns; ++j)
-          tma_load_2d(stage + j * TM_STRIP_BYTES, &wmap, (tb + kt) * 128, (strip0 + j) * 32, &full[s]);
+          tma_load_3d(slot + (size_t)j * p.T * TM_STRIP_BYTES, &wmap, 0, (strip0 + j) * 32, tb + ks * p.T,
+                      &full[s]);
         if (++s == p.NS) s = 0, par ^= 1u;
       };
-      int ci = 0, kt = 0;
+      int ci = 0, ks = 0;
       auto advance = [&]() {
-        if (++kt == nt) kt = 0, ++ci;
+        if (++ks == spc) ks = 0, ++ci;
       };
       // fill the ring before waiting for the previous kernel: these loads touch only weights
-      for (; q < total_stages && q < p.NS; ++q) {
-        issue(ci, kt);
+      for (; q < total_slots && q < p.NS; ++q) {
+        issue(ci, ks);
         advance();
       }
       if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -237,9 +279,9 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 2)
       } else {
         mbar_arrive(xfull);
       }
-      for (; q < total_stages; ++q) {
+      for (; q < total_slots; ++q) {
         if (!mbar_wait(&empty[s], par ^ 1u) || *abort_flag) { ok = false; break; }
-        issue(ci, kt);
+        issue(ci, ks);
         advance();
       }
       if (!ok) {
@@ -252,7 +294,7 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 2)
         if (!mbar_wait(&full[qq % p.NS], (unsigned)(qq / p.NS) & 1u)) atomicOr(p.status, 64u);
       if (!mbar_wait(xfull, 0)) atomicOr(p.status, 64u);
     }
-  } else if (warp == NCW + 1) {
+  } else if (warp == TM_W_MMA) {
     // ------------------------------- MMA issue -------------------------------
     if (lane == 0 && aligned && total_stages > 0) {
       constexpr uint32_t idesc = umma_idesc_f16(TM_TOK, false);
@@ -290,204 +332,282 @@ __global__ void __launch_bounds__((NCW + 2) * 32, 2)
         atomicOr(p.status, 8u);
       }
     }
-  } else {
-    // ------------------------------- consumers -------------------------------
-    const int quarter = warp & 3, part = warp >> 2;
-    const int row = quarter * 32 + lane;  // row of the chunk = TMEM lane
+  } else if (warp < TM_CONV_WARPS) {
+    // ------------------------------- converters -------------------------------
+    const int quarter = warp;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    const bool my_toks = part * TPP < a.m;
     bool ok = aligned;
-    bool x_ready = false;
-    int q = 0;
-    // the stage whose accumulators are still to be drained
-    int pend_q = -1, pend_kt = 0;
-    float pend_s[2] = {0.f, 0.f}, pend_c[2] = {0.f, 0.f};
-    float d[TPP];
-
-    auto drain = [&](bool have_rows) {
-      if (!x_ready) {
-        // first drain of the launch: the activation sums per 64-wide tile and token
-        if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(xfull, 0) && !*abort_flag);
-        if (ok) {
-          for (int idx = tid; idx < 2 * nt * TM_TOK; idx += NCW * 32) {
-            const int tile = idx >> 4, tok = idx & 15;
-            const uint8_t* xr = Xsm + (size_t)tile * TM_XTILE_BYTES + tok * 128;
-            float sum = 0.0f;
+    int q = 0;   // k-tiles converted so far (A buffer q % 2)
+    int sq = 0;  // ring slots consumed so far
+    for (int ci = 0; ci < nchunks; ++ci) {
+      const int ns = min(4, strip_hi - (strip_lo + 4 * ci));
+      const bool have_rows = quarter < ns;
+      for (int ks = 0; ks < spc; ++ks, ++sq) {
+        const int slot = sq % p.NS;
+        const int tcount = min(p.T, nt - ks * p.T);
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[slot], (unsigned)(sq / p.NS) & 1u) && !*abort_flag);
+        for (int t = 0; t < tcount; ++t, ++q) {
+          const int ab = q % TM_NA;
+          uint4 w[8];
+          if (ok && have_rows) {
+            const uint8_t* wrow = ring + (size_t)slot * slot_bytes +
+                                  (size_t)(quarter * p.T + t) * TM_STRIP_BYTES + lane * 128;
+#pragma unroll
+            for (int c = 0; c < 8; ++c)  // logical 16-byte chunk c of this thread's row
+              w[c] = *reinterpret_cast<const uint4*>(wrow + ((c ^ (lane & 7)) * 16));
+          }
+          if (t == tcount - 1) {
+            // the slot is in registers: hand it back before waiting for the A buffer
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[slot]);
+          }
+          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&a_free[ab], ((unsigned)(q / TM_NA) & 1u) ^ 1u));
+          tc_fence_after_sync();
+          if (ok && have_rows) {
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
-              const uint4 u = *reinterpret_cast<const uint4*>(xr + c * 16);
-              const __half2* h = reinterpret_cast<const __half2*>(&u);
+              const uint32_t ww[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+              uint32_t h[8];
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const float2 f = __half22float2(h[j]);
-                sum += f.x;
-                sum += f.y;
+                h[2 * j] = prmt(ww[j], 0x64646464u, 0x4140u);      // (1024 + q) for bytes 0, 1
+                h[2 * j + 1] = prmt(ww[j], 0x64646464u, 0x4342u);  // bytes 2, 3
               }
-            }
-            xs64[tile * TM_TOK + tok] = sum;
-          }
-        }
-        named_bar(1, NCW * 32);
-        x_ready = true;
-      }
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        if (e >= p.gps) break;
-        const int gi = pend_q * p.gps + e;
-        const int acc = gi % TM_ND;
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&d_ready[acc], (unsigned)(gi / TM_ND) & 1u) && !*abort_flag);
-        tc_fence_after_sync();
-        if (ok && have_rows && my_toks) {
-          uint32_t v[8];
-          tmem_ld_x8(tmem_base + lane_base + (uint32_t)(TM_NA * 64 + acc * TM_TOK + part * TPP), v);
-          // sum of the activations over this scale group, per token
-          float xs[TPP];
-          const float* x0 = xs64 + (size_t)(2 * pend_kt + (p.gps == 2 ? e : 0)) * TM_TOK + part * TPP;
-#pragma unroll
-          for (int t = 0; t < TPP; t += 4) {
-            const float4 f = *reinterpret_cast<const float4*>(x0 + t);
-            xs[t] = f.x, xs[t + 1] = f.y, xs[t + 2] = f.z, xs[t + 3] = f.w;
-          }
-          if (p.gps == 1) {
-#pragma unroll
-            for (int t = 0; t < TPP; t += 4) {
-              const float4 f = *reinterpret_cast<const float4*>(x0 + TM_TOK + t);
-              xs[t] += f.x, xs[t + 1] += f.y, xs[t + 2] += f.z, xs[t + 3] += f.w;
+              tmem_st_x8(tmem_base + lane_base + (uint32_t)(ab * 64 + c * 8), h);
             }
           }
-          tmem_ld_wait();
-          const float sc = pend_s[e], cz = pend_c[e];
-#pragma unroll
-          for (int t = 0; t < TPP; ++t) d[t] = fmaf(sc, fmaf(-cz, xs[t], __uint_as_float(v[t])), d[t]);
-        }
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&d_free[acc]);  // also on failure, so that the MMA warp can finish
-      }
-    };
-
-    for (int ci = 0; ci < nchunks; ++ci) {
-      const int strip0 = strip_lo + 4 * ci;
-      const int ns = min(4, strip_hi - strip0);
-      const bool have_rows = quarter < ns;
-      const int n_row = strip0 * 32 + row;            // this thread's weight row
-      const bool row_ok = have_rows && n_row < a.n;
-      const size_t srow = (size_t)min(n_row, a.n - 1) * groups;
-#pragma unroll
-      for (int t = 0; t < TPP; ++t) d[t] = 0.0f;
-      for (int kt = 0; kt < nt; ++kt, ++q) {
-        const int slot = q % p.NS, ab = q % TM_NA;
-        // scale and zero point of this stage's group(s) for this row, needed one stage later
-        float cur_s[2] = {0.f, 0.f}, cur_c[2] = {1151.5f, 1151.5f};
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          if (e >= p.gps) break;
-          const size_t gidx = srow + (size_t)(tb + kt) * p.gps + e;
-          cur_s[e] = row_ok ? __half2float(__ldg(a.scales + gidx)) : 0.0f;
-          if (a.zeros != nullptr) cur_c[e] = 1024.0f + __half2float(__ldg(a.zeros + gidx));
-        }
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[slot], (unsigned)(q / p.NS) & 1u) && !*abort_flag);
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&a_free[ab], ((unsigned)(q / TM_NA) & 1u) ^ 1u));
-        tc_fence_after_sync();
-        if (ok && have_rows) {
-          const uint8_t* wrow = ring + (size_t)slot * TM_STAGE_BYTES + quarter * TM_STRIP_BYTES + lane * 128;
-#pragma unroll
-          for (int c = 0; c < CPP; ++c) {
-            const int cc = part * CPP + c;  // logical 16-byte chunk of the row
-            const uint4 w = *reinterpret_cast<const uint4*>(wrow + ((cc ^ (lane & 7)) * 16));
-            const uint32_t ww[4] = {w.x, w.y, w.z, w.w};
-            uint32_t h[8];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              h[2 * j] = prmt(ww[j], 0x64646464u, 0x4140u);      // (1024 + q) for bytes 0, 1
-              h[2 * j + 1] = prmt(ww[j], 0x64646464u, 0x4342u);  // bytes 2, 3
-            }
-            tmem_st_x8(tmem_base + lane_base + (uint32_t)(ab * 64 + cc * 8), h);
-          }
-        }
-        tmem_st_wait();
-        tc_fence_before_sync();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(&a_ready[ab]);   // also on failure, so that nobody waits for this warp
-          mbar_arrive(&empty[slot]);
-        }
-        if (pend_q >= 0) drain(have_rows);
-        pend_q = q;
-        pend_kt = kt;
-        pend_s[0] = cur_s[0], pend_s[1] = cur_s[1];
-        pend_c[0] = cur_c[0], pend_c[1] = cur_c[1];
-      }
-      if (pend_q >= 0) drain(have_rows);
-      pend_q = -1;
-
-      // ---- finish the chunk: add the k-slices of the cluster, write the outputs ----
-      if (S == 1) {
-        if (ok && row_ok && my_toks) {
-#pragma unroll
-          for (int t = 0; t < TPP; ++t) {
-            const int tok = part * TPP + t;
-            if (tok < a.m) {
-              __half* dst = a.out + (size_t)tok * a.n + n_row;
-              *dst = __float2half_rn(fmaf(a.beta, __half2float(*dst), d[t]));
-            }
-          }
-        }
-      } else {
-        const int buf = ci & 1;
-        float* pb = partial + (size_t)buf * a.m * 128;
-        if (have_rows && my_toks) {
-#pragma unroll
-          for (int t = 0; t < TPP; ++t) {
-            const int tok = part * TPP + t;
-            if (tok < a.m) pb[tok * 128 + row] = ok ? d[t] : 0.0f;
-          }
-        }
-        asm volatile("fence.acq_rel.cluster;" ::: "memory");
-        __syncwarp();
-        if (lane == 0) {
-          const uint32_t bar = smem_u32(&red_ready[buf]);
-          for (uint32_t r = 0; r < S; ++r) mbar_arrive_remote(map_to_rank(bar, r));
-        }
-        if (!__all_sync(0xffffffffu, mbar_wait_cluster(&red_ready[buf], (unsigned)(ci >> 1) & 1u))) {
-          ok = false;
-          if (lane == 0) atomicOr(p.status, 4u);
-        }
-        // CTA `rank` finishes rows [rank * 128 / S, (rank + 1) * 128 / S) of the chunk
-        const int rpr = 128 / (int)S;
-        const uint32_t pbase = smem_u32(pb);
-        for (int idx = tid; idx < rpr * a.m; idx += NCW * 32) {
-          const int r_in = (int)rank * rpr + idx % rpr, tok = idx / rpr;
-          const int nr = strip0 * 32 + r_in;
-          if (r_in < ns * 32 && nr < a.n && ok) {
-            float v = 0.0f;
-            for (uint32_t r = 0; r < S; ++r)
-              v += ld_cluster_f32(map_to_rank(pbase + (uint32_t)(tok * 128 + r_in) * 4u, r));
-            __half* dst = a.out + (size_t)tok * a.n + nr;
-            *dst = __float2half_rn(fmaf(a.beta, __half2float(*dst), v));
-          }
+          tmem_st_wait();
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&a_ready[ab]);  // also on failure, so that nobody waits for this warp
         }
       }
     }
     if (!ok && lane == 0) atomicOr(p.status, 1u);
+  } else if (warp < TM_CONV_WARPS + TM_DRAIN_WARPS) {
+    // ------------------------------- drainers -------------------------------
+    const int quarter = warp & 3;
+    const int dt = tid - TM_CONV_WARPS * 32;  // 0 .. 127
+    const int row = quarter * 32 + lane;      // row of the chunk = TMEM lane
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const bool wide = a.m > 8;                // tokens 8..15 exist
+    const int gshift = p.gps == 2 ? 1 : 0;
+    const unsigned short* sc16 = reinterpret_cast<const unsigned short*>(a.scales);
+    const unsigned short* zp16 = reinterpret_cast<const unsigned short*>(a.zeros);
+    const int G = nt * p.gps;                 // scale groups of a chunk in this CTA's slice
+    const int total_groups = nchunks * G;
+    bool ok = aligned;
+
+    // (chunk, group) of the scale that is requested next: TM_SCALE_AHEAD groups ahead of the
+    // one being drained, across chunk boundaries
+    int pf_ci = 0, pf_gl = 0;
+    auto scale_index = [&](int ci, int gl, bool& valid) -> size_t {
+      const int strip0 = strip_lo + 4 * ci;
+      const int nrow = strip0 * 32 + row;
+      valid = ci < nchunks && quarter < min(4, strip_hi - strip0) && nrow < a.n;
+      return (size_t)min(nrow, a.n - 1) * groups + (size_t)tb * p.gps + gl;
+    };
+    unsigned short sreg[TM_SCALE_AHEAD], zreg[TM_SCALE_AHEAD];
+#pragma unroll
+    for (int j = 0; j < TM_SCALE_AHEAD; ++j) {
+      bool valid;
+      const size_t gi = scale_index(pf_ci, pf_gl, valid);
+      sreg[j] = 0, zreg[j] = 0;
+      if (valid) {
+        sreg[j] = __ldg(sc16 + gi);
+        if (zp16 != nullptr) zreg[j] = __ldg(zp16 + gi);
+      }
+      if (++pf_gl == G) pf_gl = 0, ++pf_ci;
+    }
+
+    if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
+    // the activation sums per 64-wide tile and token (the 16-byte pieces of a row are visited
+    // in an order rotated by the token, so that the lanes of a warp read different banks)
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(xfull, 0) && !*abort_flag);
+    if (ok) {
+      for (int idx = dt; idx < 2 * nt * TM_TOK; idx += TM_DRAIN_WARPS * 32) {
+        const int tile = idx >> 4, tok = idx & 15;
+        const uint8_t* xr = Xsm + (size_t)tile * TM_XTILE_BYTES + tok * 128;
+        float sum = 0.0f;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 u = *reinterpret_cast<const uint4*>(xr + ((c + tok) & 7) * 16);
+          const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __half22float2(h[j]);
+            sum += f.x;
+            sum += f.y;
+          }
+        }
+        xs64[tile * TM_TOK + tok] = sum;
+      }
+    }
+    named_bar(1, TM_DRAIN_WARPS * 32);
+
+    float d[TM_TOK];
+#pragma unroll
+    for (int t = 0; t < TM_TOK; ++t) d[t] = 0.0f;
+    int ci = 0, gl = 0;  // chunk and group within the chunk of the group being drained
+    for (int gs0 = 0; gs0 < total_groups; gs0 += TM_SCALE_AHEAD) {
+#pragma unroll
+      for (int j = 0; j < TM_SCALE_AHEAD; ++j) {
+        const int gs = gs0 + j;
+        if (gs >= total_groups) break;
+        const int ns = min(4, strip_hi - (strip_lo + 4 * ci));
+        const bool have_rows = quarter < ns;
+        const int acc = gs % TM_ND;
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&d_ready[acc], (unsigned)(gs / TM_ND) & 1u) && !*abort_flag);
+        tc_fence_after_sync();
+        if (ok && have_rows) {
+          const int kt = gl >> gshift, e = gl & (p.gps - 1);
+          const float sc = __half2float(__ushort_as_half(sreg[j]));
+          const float cz = zp16 != nullptr ? 1024.0f + __half2float(__ushort_as_half(zreg[j])) : 1151.5f;
+          const uint32_t d_addr = tmem_base + lane_base + (uint32_t)(TM_NA * 64 + acc * TM_TOK);
+          const float* x0 = xs64 + (size_t)(2 * kt + (p.gps == 2 ? e : 0)) * TM_TOK;
+          if (wide) {
+            uint32_t v[16];
+            tmem_ld_x16t(d_addr, v);
+            float xs[16];
+#pragma unroll
+            for (int t = 0; t < 16; t += 4) {
+              const float4 f = *reinterpret_cast<const float4*>(x0 + t);
+              xs[t] = f.x, xs[t + 1] = f.y, xs[t + 2] = f.z, xs[t + 3] = f.w;
+            }
+            if (p.gps == 1) {
+#pragma unroll
+              for (int t = 0; t < 16; t += 4) {
+                const float4 f = *reinterpret_cast<const float4*>(x0 + TM_TOK + t);
+                xs[t] += f.x, xs[t + 1] += f.y, xs[t + 2] += f.z, xs[t + 3] += f.w;
+              }
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int t = 0; t < 16; ++t) d[t] = fmaf(sc, fmaf(-cz, xs[t], __uint_as_float(v[t])), d[t]);
+          } else {
+            uint32_t v[8];
+            tmem_ld_x8(d_addr, v);
+            float xs[8];
+#pragma unroll
+            for (int t = 0; t < 8; t += 4) {
+              const float4 f = *reinterpret_cast<const float4*>(x0 + t);
+              xs[t] = f.x, xs[t + 1] = f.y, xs[t + 2] = f.z, xs[t + 3] = f.w;
+            }
+            if (p.gps == 1) {
+#pragma unroll
+              for (int t = 0; t < 8; t += 4) {
+                const float4 f = *reinterpret_cast<const float4*>(x0 + TM_TOK + t);
+                xs[t] += f.x, xs[t + 1] += f.y, xs[t + 2] += f.z, xs[t + 3] += f.w;
+              }
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int t = 0; t < 8; ++t) d[t] = fmaf(sc, fmaf(-cz, xs[t], __uint_as_float(v[t])), d[t]);
+          }
+        }
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&d_free[acc]);  // also on failure, so that the MMA warp can finish
+        {  // request the scale TM_SCALE_AHEAD groups ahead into the register just used
+          bool valid;
+          const size_t gi = scale_index(pf_ci, pf_gl, valid);
+          if (valid) {
+            sreg[j] = __ldg(sc16 + gi);
+            if (zp16 != nullptr) zreg[j] = __ldg(zp16 + gi);
+          }
+          if (++pf_gl == G) pf_gl = 0, ++pf_ci;
+        }
+        if (++gl == G) {
+          // ---- end of the chunk: push this row's sums to the CTA that owns the row ----
+          const int buf = ci & 1;
+          // the owners have consumed what this buffer held two chunks ago
+          if (!__all_sync(0xffffffffu, mbar_wait_cluster(&red_free[buf], ((unsigned)(ci >> 1) & 1u) ^ 1u))) {
+            ok = false;
+            if (lane == 0) atomicOr(p.status, 4u);
+          }
+          const uint32_t owner = (uint32_t)(row / rpr);
+          const uint32_t slot_addr =
+              smem_u32(partial + ((size_t)(buf * (int)S + (int)rank) * a.m) * rpr + (row % rpr));
+          const uint32_t dst = map_to_rank(slot_addr, owner);
+          if (have_rows) {
+#pragma unroll
+            for (int t = 0; t < TM_TOK; ++t)
+              if (t < a.m) st_cluster_f32(dst + (uint32_t)(t * rpr) * 4u, ok ? d[t] : 0.0f);
+          }
+          // the lanes' stores are ordered before the release by the warp barrier
+          __syncwarp();
+          if (lane == 0 || (S == 8 && lane == 16))
+            mbar_arrive_remote(map_to_rank(smem_u32(&red_ready[buf]), owner));
+#pragma unroll
+          for (int t = 0; t < TM_TOK; ++t) d[t] = 0.0f;
+          gl = 0;
+          ++ci;
+        }
+      }
+    }
+    if (!ok && lane == 0) atomicOr(p.status, 2u);
+  } else if (warp == TM_W_FINISH) {
+    // ------------------------------- finisher -------------------------------
+    // rows [rank * rpr, (rank + 1) * rpr) of every chunk: sum of the S pushed partial sums in
+    // rank order, beta * old, store.  Output e of the chunk = token e / rpr, row e % rpr.
+    bool ok = aligned;
+    if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int ci = 0; ci < nchunks; ++ci) {
+      const int buf = ci & 1;
+      const int strip0 = strip_lo + 4 * ci;
+      const int ns = min(4, strip_hi - strip0);
+      const int nr0 = strip0 * 32 + (int)rank * rpr;  // first row of this CTA's share
+      const int outs = rpr * a.m;
+      if (!__all_sync(0xffffffffu, mbar_wait_cluster(&red_ready[buf], (unsigned)(ci >> 1) & 1u))) {
+        ok = false;
+        if (lane == 0) atomicOr(p.status, 4u);
+      }
+      const float* pb = partial + (size_t)buf * S * a.m * rpr;
+      for (int e0 = 0; e0 < outs; e0 += 128) {
+        float old[4], sum[4];
+        // four outputs per lane and round: the loads of the old values are in flight together
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int e = e0 + u * 32 + lane;
+          const int r_in = e % rpr, tok = e / rpr;
+          const bool live = e < outs && (int)rank * rpr + r_in < ns * 32 && nr0 + r_in < a.n;
+          old[u] = live ? __half2float(a.out[(size_t)tok * a.n + nr0 + r_in]) : 0.0f;
+          float v = 0.0f;
+          if (e < outs)
+            for (uint32_t r = 0; r < S; ++r) v += pb[(size_t)(r * a.m + tok) * rpr + r_in];
+          sum[u] = v;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int e = e0 + u * 32 + lane;
+          const int r_in = e % rpr, tok = e / rpr;
+          const bool live = e < outs && (int)rank * rpr + r_in < ns * 32 && nr0 + r_in < a.n;
+          if (live && ok)
+            a.out[(size_t)tok * a.n + nr0 + r_in] = __float2half_rn(fmaf(a.beta, old[u], sum[u]));
+        }
+      }
+      // the buffer may be pushed into again: tell every CTA of the cluster
+      __syncwarp();
+      if (lane == 0)
+        for (uint32_t r = 0; r < S; ++r) mbar_arrive_remote(map_to_rank(smem_u32(&red_free[buf]), r));
+    }
   }
 
   tc_fence_before_sync();
   __syncthreads();
   __syncwarp();
   if (S > 1) {
-    // every CTA stays resident until its peers have read its partial sums
+    // every CTA stays resident until its peers have stopped writing into its shared memory
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
   }
-  if (warp == NCW + 1) {
+  if (warp == TM_W_MMA) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TM_COLS);
   }
 }
 
 struct TmemPlan {
-  int S, per, strips, clusters, NS, gps, max_tiles;
+  int S, per, strips, clusters, NS, T, gps, max_tiles;
   size_t smem;
 };
 
@@ -518,13 +638,18 @@ bool plan_tmem(adr_ctx* ctx, const U8Args& a, bool pdl, TmemPlan& pl) {
     const int max_tiles = (ntiles + S - 1) / S;
     const size_t fixed = (size_t)2 * max_tiles * TM_XTILE_BYTES + (size_t)2 * a.m * 128 * 4 +
                          (size_t)2 * max_tiles * TM_TOK * 4 + 512;
-    if (fixed + 3 * TM_STAGE_BYTES > 224 * 1024) continue;
+    // k-tiles per ring slot: a copy then takes T * 128 contiguous bytes of every row
+    const int want_t = ctx->tune_u8_tiles;
+    int T = want_t > 0 ? want_t : 4;
+    T = std::max(1, std::min(T, max_tiles));
+    const size_t slot_bytes = (size_t)T * TM_STAGE_BYTES;
+    if (fixed + 2 * slot_bytes > 224 * 1024) continue;
     size_t room = budget > fixed ? budget - fixed : 0;
-    int ns = (int)(room / TM_STAGE_BYTES);
-    if (ns < 3) ns = (int)((224 * 1024 - fixed) / TM_STAGE_BYTES);  // one CTA per SM
+    int ns = (int)(room / slot_bytes);
+    if (ns < 2) ns = (int)((224 * 1024 - fixed) / slot_bytes);  // one CTA per SM
     ns = std::min(ns, TM_MAX_STAGES);
-    if (ns < 3) continue;
-    const size_t smem = fixed + (size_t)ns * TM_STAGE_BYTES;
+    if (ns < 2) continue;
+    const size_t smem = fixed + (size_t)ns * slot_bytes;
     int maxc = S == 1 ? sms : max_clusters(ctx, S, smem, pdl);
     if (maxc <= 0) continue;
     maxc = std::min(maxc, sms / S);
@@ -534,6 +659,7 @@ bool plan_tmem(adr_ctx* ctx, const U8Args& a, bool pdl, TmemPlan& pl) {
     pl.strips = strips;
     pl.clusters = (strips + per - 1) / per;
     pl.NS = ns;
+    pl.T = T;
     pl.gps = 128 / a.block_size;
     pl.max_tiles = max_tiles;
     pl.smem = smem;
@@ -544,14 +670,16 @@ bool plan_tmem(adr_ctx* ctx, const U8Args& a, bool pdl, TmemPlan& pl) {
 
 template <bool PDL>
 int launch_tmem_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const TmemPlan& pl) {
-  auto kfn = u8_tmem_kernel<8, PDL>;
+  auto kfn = u8_tmem_kernel<PDL>;
   if (int rc = opt_in_smem(ctx, kfn, 226 * 1024); rc != ADR_OK) return rc;
   CUtensorMap wmap, xmap;
   {
-    const uint64_t dims[2] = {(uint64_t)a.p, (uint64_t)a.n};
-    const uint64_t strides[1] = {(uint64_t)a.p};
-    const uint32_t box[2] = {128u, 32u};
-    int rc = tma_get(ctx, &wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.rhs, dims, strides, box,
+    // weights as (k within tile, row, k-tile): a box of 128 x 32 x T lands as T tiles of
+    // [32 rows][128 bytes], each swizzled by its own row index
+    const uint64_t dims[3] = {128u, (uint64_t)a.n, (uint64_t)(a.p / 128)};
+    const uint64_t strides[2] = {(uint64_t)a.p, 128u};
+    const uint32_t box[3] = {128u, 32u, (uint32_t)pl.T};
+    int rc = tma_get(ctx, &wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.rhs, dims, strides, box,
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != ADR_OK) return rc;
   }
@@ -569,12 +697,13 @@ int launch_tmem_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Tmem
   p.per = pl.per;
   p.strips = pl.strips;
   p.NS = pl.NS;
+  p.T = pl.T;
   p.gps = pl.gps;
   p.max_tiles = pl.max_tiles;
   p.status = ctx->d_status;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(pl.clusters * pl.S, 1, 1);
-  cfg.blockDim = dim3((8 + 2) * 32, 1, 1);
+  cfg.blockDim = dim3(TM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
@@ -613,7 +742,7 @@ static int max_clusters(adr_ctx* ctx, int S, size_t smem, bool pdl) {
   int n = 0;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(S * 64, 1, 1);
-  cfg.blockDim = dim3((8 + 2) * 32, 1, 1);
+  cfg.blockDim = dim3(TM_THREADS, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -624,11 +753,11 @@ static int max_clusters(adr_ctx* ctx, int S, size_t smem, bool pdl) {
   cfg.numAttrs = 1;
   cudaError_t e;
   if (pdl) {
-    auto kfn = u8_tmem_kernel<8, true>;
+    auto kfn = u8_tmem_kernel<true>;
     if (opt_in_smem(ctx, kfn, 226 * 1024) != ADR_OK) return 0;
     e = cudaOccupancyMaxActiveClusters(&n, kfn, &cfg);
   } else {
-    auto kfn = u8_tmem_kernel<8, false>;
+    auto kfn = u8_tmem_kernel<false>;
     if (opt_in_smem(ctx, kfn, 226 * 1024) != ADR_OK) return 0;
     e = cudaOccupancyMaxActiveClusters(&n, kfn, &cfg);
   }

@@ -65,6 +65,7 @@ class Kernel(enum.IntEnum):
     U8Stream = 7
     U8Ring = 8
     U8Tmem = 9
+    F16TcGather = 10
 
 
 @dataclass(frozen=True)

@@ -876,9 +876,11 @@ def run_profile_case(args):
     """
     import torch
 
-    from adrastea_b200 import GpuKernels, TensorView
+    from adrastea_b200 import GpuKernels, Kernel, TensorView
     torch.cuda.set_device(0)
     kern = GpuKernels(0)
+    if args.kernel:
+        kern.force_kernel(Kernel[args.kernel])
     m = args.m
     if args.profile_case == "u8":
         ws = [(torch.randint(0, 256, (args.n, K), dtype=torch.uint8, device="cuda"),
@@ -928,6 +930,7 @@ def main():
                     help="N > 1: reduce the row-split products with NCCL instead of the library's peer-memory kernel")
     ap.add_argument("--profile-case", default=None, choices=["u8", "f16", "attn"],
                     help="run a small fixed case of one kernel family and exit (for ncu captures)")
+    ap.add_argument("--kernel", default=None, help="--profile-case: pin a kernel family by name, e.g. U8Tmem")
     ap.add_argument("--m", type=int, default=1, help="rows of the activation in --profile-case")
     ap.add_argument("--n", type=int, default=4096, help="weight rows in --profile-case u8")
     args = ap.parse_args()

@@ -115,6 +115,56 @@ def test_matmul_f16_against_ideal_oracle(kernels, c):
 
 
 @pytest.mark.parametrize("c", cases.matmul_cases(), ids=lambda c: c.name)
+def test_tc_gather_kernel_takes_every_view(kernels, c):
+    """The tensor-core kernel behind gathering loader warps accepts any strides and alignment:
+    every case of the fp16 suite, forced through it, within 1e-2 of the ideal oracle."""
+    try:
+        kernels.force_kernel(Kernel.F16TcGather)
+        got = run_case(kernels, c, slow=False)
+        kernels.device_status()
+        assert kernels.last_kernel() == Kernel.F16TcGather
+        want = oracle_out(c, ideal=True)
+        err = oracle.max_rel_err(got, want)
+        assert err <= TOL, err
+        again = run_case(kernels, c, slow=False)
+        assert np.array_equal(got.view(np.uint16), again.view(np.uint16)), "not deterministic"
+    finally:
+        kernels.force_kernel(Kernel.Auto)
+
+
+def test_unaligned_score_pitch_stays_on_tensor_cores(kernels):
+    """The reference's own attention views at 257 tokens (clip.rs:374-388): scores and
+    probabilities [H, 257, 257] contiguous, i.e. a 514-byte row pitch the copy engine cannot
+    describe.  Both products are dispatched to the gathering tensor-core kernel, not to CUDA cores."""
+    rng = np.random.default_rng(99)
+    H, S, hd = 4, 257, 64
+    D = H * hd
+    q = (rng.standard_normal((S, D)) * 0.5).astype(np.float16)
+    k = (rng.standard_normal((S, D)) * 0.5).astype(np.float16)
+    v = (rng.standard_normal((S, D)) * 0.5).astype(np.float16)
+    qd, kd, vd = dev(q), dev(k), dev(v)
+    heads = TensorLayout.new((H, S, hd), (hd, D, 1))
+    scores = torch.zeros((H, S, S), dtype=torch.float16, device="cuda")
+    sv = TensorView.of(scores)
+    kernels.matmul_f16(sv, TensorView(qd, heads), TensorView(kd, heads).permute([0, 2, 1]),
+                       MatmulOptions.new().store(MatmulStore.Scale(0.125)))
+    want_s = np.zeros(H * S * S, np.float16)
+    oracle.matmul_f16(want_s, q.reshape(-1), k.reshape(-1), H, S, hd, S,
+                      (1, S, S * S, 1, D, hd, D, 1, hd), scale=0.125, store=cases.ST_SCALE, ideal=True)
+    assert oracle.max_rel_err(scores.cpu().numpy().reshape(-1), want_s) <= TOL
+    kernels.softmax_rows_inplace(sv, 1.0)
+    out = torch.zeros((S, D), dtype=torch.float16, device="cuda")
+    kernels.matmul_f16(TensorView(out, heads), sv, TensorView(vd, heads))
+    kernels.device_status()
+    assert kernels.last_kernel() == Kernel.F16TcGather
+    probs = scores.cpu().numpy()
+    want_o = np.zeros(S * D, np.float16)
+    oracle.matmul_f16(want_o, probs.reshape(-1), v.reshape(-1), H, S, S, hd,
+                      (1, D, hd, 1, S, S * S, 1, D, hd), ideal=True)
+    assert oracle.max_rel_err(out.cpu().numpy().reshape(-1), want_o) <= TOL
+
+
+@pytest.mark.parametrize("c", cases.matmul_cases(), ids=lambda c: c.name)
 def test_live_reference_kernels_agree_with_oracle(c):
     """Pins the oracle on this very GPU: matmul_f16 / matmul_f16_fast from the
     reference tree against orc_matmul_f16_ref."""
