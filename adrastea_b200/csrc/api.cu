@@ -143,7 +143,7 @@ const char* adr_strerror(int code) {
 int adr_last_cuda_error(const adr_ctx* ctx) { return ctx ? ctx->last_cuda_error.load() : 0; }
 
 int adr_force_kernel(adr_ctx* ctx, int kernel) {
-  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_F16_TC_GATHER) return ADR_ERR_INVALID;
+  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_U8_TS) return ADR_ERR_INVALID;
   ctx->forced_kernel = kernel;
   return ADR_OK;
 }
@@ -228,7 +228,8 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
   int kernel = ctx->forced_kernel;
   if (kernel == ADR_KERNEL_AUTO) {
     // up to 32 tokens two passes of the streaming kernel beat one tensor-core launch
-    if (m > 32 && u8_tc_supports(ctx, a)) kernel = ADR_KERNEL_U8_TC;
+    if (m > 32 && u8_ts_supports(ctx, a)) kernel = ADR_KERNEL_U8_TS;
+    else if (m > 32 && u8_tc_supports(ctx, a)) kernel = ADR_KERNEL_U8_TC;
     else if (p % 64 != 0) kernel = m <= 4 ? ADR_KERNEL_U8_GEMV : ADR_KERNEL_U8_SIMT;
     else if (!ctx->tune_u8_exact && !ctx->tune_u8_split && !ctx->tune_u8_rows &&
              u8_ring_supports(ctx, a16))
@@ -274,6 +275,7 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
       break;
     }
     case ADR_KERNEL_U8_TC: rc = launch_u8_tc(ctx, st, a); break;
+    case ADR_KERNEL_U8_TS: rc = launch_u8_ts(ctx, st, a); break;
     case ADR_KERNEL_U8_MMA: {
       if (p % 64 != 0) return ADR_ERR_SHAPE;
       rc = ADR_OK;

@@ -252,6 +252,8 @@ bool u8_ring_supports(const adr_ctx* ctx, const U8Args& a);
 int launch_u8_tmem(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 bool u8_tmem_supports(adr_ctx* ctx, const U8Args& a);
 int launch_u8_tc(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
+int launch_u8_ts(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
+bool u8_ts_supports(const adr_ctx* ctx, const U8Args& a);
 bool u8_tc_supports(const adr_ctx* ctx, const U8Args& a);
 int init_u8_kernels(adr_ctx* ctx);
 

@@ -1,0 +1,322 @@
+// u8-weight dequantising GEMM for prefill (m > 32), weights through TENSOR MEMORY:
+//   out[m,n] = lhs[m,p] . deq(Q[n,p])^T + beta * out
+// replacing matmul_nt_wmma_16x128x256_fp16u8 (adrastea_kernels/cpp/
+// matmul_nt_wmma_16x128x256_fp16u8.cu:12-83) beyond the decode shapes, with that kernel's
+// arithmetic: every weight is dequantised to fp16((q - zero) * scale), bit-exact, before the
+// product; products accumulate in fp32.
+//
+// The product is transposed: the 128 WEIGHT rows of a tile are the M side of tcgen05.mma and up
+// to 256 TOKENS its N side, so a weight is dequantised once per 256 tokens and the tensor core
+// runs its widest instruction.
+//   * producer warp: per 64-wide k-step one TMA box of the weights (128 rows x 64 bytes of u8)
+//     and one of the activations (BT tokens x 64 fp16, 128-byte swizzle, K-major) into a ring;
+//   * eight converter warps (warp w: TMEM lane quarter w % 4, k-steps of parity w / 4): thread =
+//     weight row; 16 bytes -> 16 fp16 in registers (u8_common.cuh) -> tcgen05.st into one of
+//     four A buffers in tensor memory.  The dequantised weights never touch shared memory;
+//   * one thread issues tcgen05.mma (A from tensor memory, B = activations from shared memory,
+//     M = 128, N = BT, K = 16) into one accumulator of BT columns;
+//   * after the last k-step the converter warps turn into the epilogue: tcgen05.ld, beta * old,
+//     fp16 stores (thread = weight row, so a warp writes 32 consecutive outputs of one token).
+// Persistent CTAs walk the tiles with the token blocks of one weight block next to each
+// other, so that a weight block is read from HBM once and then from L2.
+// Needs p % 64 == 0 and block_size % 64 == 0 (one scale group per k-step); other shapes take
+// the kernel that stages the dequantised operand in shared memory (gemm_u8_tc.cu).
+#include <algorithm>
+
+#include "tcgen05.cuh"
+#include "u8_common.cuh"
+
+namespace adr {
+
+namespace {
+
+constexpr int TS_BK = 64;            // k per step
+constexpr int TS_ROWS = 128;         // weight rows per tile
+constexpr int TS_NA = 4;             // A buffers in tensor memory (32 columns each)
+constexpr int TS_CONV_WARPS = 8;
+constexpr int TS_W_PRODUCER = 8, TS_W_MMA = 9;
+constexpr int TS_THREADS = 10 * 32;
+
+template <int BT>
+struct TsCfg {
+  static constexpr int W_BYTES = TS_ROWS * TS_BK;      // u8
+  static constexpr int X_BYTES = BT * TS_BK * 2;       // fp16
+  static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
+  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
+  static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + 512;
+  static constexpr uint32_t A_COL0 = BT;
+  static constexpr uint32_t TMEM_COLS = BT + TS_NA * 32 <= 256 ? 256 : 512;
+};
+
+struct TsParams {
+  __half* out;
+  const __half* scales;
+  const __half* zeros;
+  int m, p, n, block_size;
+  float beta;
+  unsigned int* status;
+};
+
+__device__ __forceinline__ void ts_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr),
+               "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+               : "memory");
+}
+__device__ __forceinline__ void ts_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+template <bool ACCUMULATE>
+__device__ __forceinline__ void ts_mma(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc) {
+  if (ACCUMULATE)
+    asm volatile("tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, 1;" ::"r"(tmem_d), "r"(tmem_a),
+                 "l"(bdesc), "r"(idesc)
+                 : "memory");
+  else
+    asm volatile("tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, 0;" ::"r"(tmem_d), "r"(tmem_a),
+                 "l"(bdesc), "r"(idesc)
+                 : "memory");
+}
+
+template <int BT>
+__global__ void __launch_bounds__(TS_THREADS, 1)
+    gemm_u8_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                      TsParams p) {
+  using Cfg = TsCfg<BT>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* stages = smem;  // per stage: activations (1024-aligned), then weights
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint64_t* empty = full + Cfg::STAGES;      // 4 converter warps + the MMA commit
+  uint64_t* a_ready = empty + Cfg::STAGES;   // [TS_NA]
+  uint64_t* a_free = a_ready + TS_NA;        // [TS_NA]
+  uint64_t* acc_full = a_free + TS_NA;
+  uint64_t* acc_empty = acc_full + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_kb = p.p / TS_BK;
+  const int nb = (p.n + TS_ROWS - 1) / TS_ROWS, tt = (p.m + BT - 1) / BT;
+  const int total_tiles = nb * tt;
+  const int groups = p.p / p.block_size;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&map_w);
+    tma_prefetch_desc(&map_x);
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 5);
+    }
+    for (int i = 0; i < TS_NA; ++i) {
+      mbar_init(&a_ready[i], 4);
+      mbar_init(&a_free[i], 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, TS_CONV_WARPS);
+    mbar_fence_init();
+  }
+  if (warp == TS_W_MMA) tmem_alloc(tmem_slot, Cfg::TMEM_COLS);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  bool ok = true;
+
+  // tiles: the token blocks of one weight block follow one another
+  auto tile_n0 = [&](int t) { return (t / tt) * TS_ROWS; };
+  auto tile_t0 = [&](int t) { return (t % tt) * BT; };
+
+  if (warp == TS_W_PRODUCER) {
+    if (lane == 0) {
+      int it = 0;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+        const int n0 = tile_n0(t), t0 = tile_t0(t);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % Cfg::STAGES;
+          if (!mbar_wait(&empty[s], ((unsigned)(it / Cfg::STAGES) & 1u) ^ 1u)) { ok = false; break; }
+          uint8_t* st = stages + (size_t)s * Cfg::STAGE_BYTES;
+          mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
+          tma_load_2d(st, &map_x, kb * TS_BK, t0, &full[s]);
+          tma_load_2d(st + Cfg::X_BYTES, &map_w, kb * TS_BK, n0, &full[s]);
+        }
+      }
+      if (!ok) atomicOr(p.status, 8u);
+    }
+  } else if (warp == TS_W_MMA) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = umma_idesc_f16(BT, false);
+      int it = 0, local = 0;
+      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+        // the single accumulator is free once the epilogue of the previous tile has read it
+        if (!mbar_wait(acc_empty, ((unsigned)local & 1u) ^ 1u)) { ok = false; break; }
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % Cfg::STAGES, ab = it & (TS_NA - 1);
+          if (!mbar_wait(&full[s], (unsigned)(it / Cfg::STAGES) & 1u)) { ok = false; break; }
+          if (!mbar_wait(&a_ready[ab], (unsigned)(it / TS_NA) & 1u)) { ok = false; break; }
+          tc_fence_after_sync();
+          const uint64_t xdesc = umma_desc_k_sw128(smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES));
+          const uint32_t a_addr = tmem_base + Cfg::A_COL0 + (uint32_t)(ab * 32);
+          if (kb == 0) ts_mma<false>(tmem_base, a_addr, xdesc, idesc);
+          else ts_mma<true>(tmem_base, a_addr, xdesc, idesc);
+          ts_mma<true>(tmem_base, a_addr + 8, xdesc + 2, idesc);
+          ts_mma<true>(tmem_base, a_addr + 16, xdesc + 4, idesc);
+          ts_mma<true>(tmem_base, a_addr + 24, xdesc + 6, idesc);
+          umma_commit(&a_free[ab]);
+          umma_commit(&empty[s]);
+        }
+        umma_commit(acc_full);
+      }
+      if (!ok) atomicOr(p.status, 8u);
+    }
+  } else {
+    // ---------------- converters, then epilogue ----------------
+    const int quarter = warp & 3, phase = warp >> 2;
+    const int row = quarter * 32 + lane;  // weight row of the tile = TMEM lane
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    const bool has_zero = p.zeros != nullptr;
+    int it = 0, local = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+      const int n0 = tile_n0(t), t0 = tile_t0(t);
+      const int n_row = n0 + row;
+      const size_t srow = (size_t)min(n_row, p.n - 1) * groups;
+      // scale of this warp's first k-step of the tile; the next one is requested a step ahead
+      int kb_mine = ((it & 1) == phase) ? 0 : 1;
+      __half sc = __float2half(0.f), zp = __float2half(0.f);
+      if (kb_mine < num_kb) {
+        const int g = (kb_mine * TS_BK) / p.block_size;
+        sc = p.scales[srow + g];
+        if (has_zero) zp = p.zeros[srow + g];
+      }
+      for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        if ((it & 1) != phase) continue;
+        const int s = it % Cfg::STAGES, ab = it & (TS_NA - 1);
+        const ScalePair sp = make_scale(sc, has_zero, zp);
+        if (kb + 2 < num_kb) {  // this warp's next k-step
+          const int g = ((kb + 2) * TS_BK) / p.block_size;
+          sc = p.scales[srow + g];
+          if (has_zero) zp = p.zeros[srow + g];
+        }
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[s], (unsigned)(it / Cfg::STAGES) & 1u));
+        uint4 w[4];
+        if (ok) {
+          const uint8_t* wrow = stages + (size_t)s * Cfg::STAGE_BYTES + Cfg::X_BYTES + row * TS_BK;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) w[c] = *reinterpret_cast<const uint4*>(wrow + c * 16);
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);  // the weights of the stage are in registers
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&a_free[ab], ((unsigned)(it / TS_NA) & 1u) ^ 1u));
+        tc_fence_after_sync();
+        if (ok) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            const uint32_t ww[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+            uint32_t h[8];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              __half2 lo, hi;
+              dequant4(ww[j], sp, lo, hi);
+              h[2 * j] = half2_as_u32(lo);
+              h[2 * j + 1] = half2_as_u32(hi);
+            }
+            ts_st_x8(tmem_base + lane_base + Cfg::A_COL0 + (uint32_t)(ab * 32 + c * 8), h);
+          }
+        }
+        ts_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&a_ready[ab]);
+      }
+      // ---- epilogue of the tile: this warp's lane quarter, token half `phase` ----
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, (unsigned)local & 1u));
+      tc_fence_after_sync();
+      if (ok) {
+        constexpr int HALF = BT / 2;
+#pragma unroll 1
+        for (int c = 0; c < HALF / 32; ++c) {
+          const int tok0 = t0 + phase * HALF + c * 32;
+          if (tok0 >= p.m) break;  // uniform across the warp
+          uint32_t acc[32];
+          tmem_ld_32x32(tmem_base + lane_base + (uint32_t)(phase * HALF + c * 32), acc);
+          unsigned short old[32];
+          const bool row_ok = n_row < p.n;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tok = tok0 + j;
+            old[j] = (row_ok && tok < p.m)
+                         ? reinterpret_cast<const unsigned short*>(p.out)[(size_t)tok * p.n + n_row]
+                         : (unsigned short)0;
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int tok = tok0 + j;
+            if (row_ok && tok < p.m)
+              p.out[(size_t)tok * p.n + n_row] = __float2half_rn(
+                  fmaf(p.beta, __half2float(__ushort_as_half(old[j])), __uint_as_float(acc[j])));
+          }
+        }
+      }
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);
+    }
+    if (!ok && lane == 0) atomicOr(p.status, 8u);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == TS_W_MMA) {
+    __syncwarp();
+    tc_fence_after_sync();
+    tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+  }
+}
+
+template <int BT>
+int launch_u8_ts_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
+  using Cfg = TsCfg<BT>;
+  auto kfn = gemm_u8_ts_kernel<BT>;
+  if (int rc = opt_in_smem(ctx, kfn, Cfg::SMEM); rc != ADR_OK) return rc;
+  CUtensorMap map_w, map_x;
+  {
+    const uint64_t dims[2] = {(uint64_t)a.p, (uint64_t)a.n};
+    const uint64_t strides[1] = {(uint64_t)a.p};
+    const uint32_t box[2] = {TS_BK, TS_ROWS};
+    int rc = tma_get(ctx, &map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.rhs, dims, strides, box,
+                     CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc != ADR_OK) return rc;
+  }
+  {
+    const uint64_t dims[2] = {(uint64_t)a.p, (uint64_t)a.m};
+    const uint64_t strides[1] = {(uint64_t)a.p * 2};
+    const uint32_t box[2] = {TS_BK, (uint32_t)BT};
+    int rc = tma_get(ctx, &map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.lhs, dims, strides, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != ADR_OK) return rc;
+  }
+  TsParams p{a.out, a.scales, a.zeros, a.m, a.p, a.n, a.block_size, a.beta, ctx->d_status};
+  const long long tiles = (long long)((a.n + TS_ROWS - 1) / TS_ROWS) * ((a.m + BT - 1) / BT);
+  const long long sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+  const unsigned grid = (unsigned)std::min<long long>(tiles, sms);
+  kfn<<<grid, TS_THREADS, Cfg::SMEM, stream>>>(map_w, map_x, p);
+  return after_launch(ctx);
+}
+
+}  // namespace
+
+bool u8_ts_supports(const adr_ctx* ctx, const U8Args& a) {
+  if (!ctx->encode_tiled_fn) return false;
+  if (a.p % TS_BK != 0 || a.block_size % TS_BK != 0 || a.p % a.block_size != 0) return false;
+  if ((reinterpret_cast<uintptr_t>(a.lhs) & 15u) || (reinterpret_cast<uintptr_t>(a.rhs) & 15u))
+    return false;
+  return true;
+}
+
+int launch_u8_ts(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
+  if (!u8_ts_supports(ctx, a)) return ADR_ERR_SHAPE;
+  // 256 tokens per tile unless that would leave more than half of a tile empty
+  if (a.m > 128) return launch_u8_ts_t<256>(ctx, stream, a);
+  return launch_u8_ts_t<128>(ctx, stream, a);
+}
+
+}  // namespace adr

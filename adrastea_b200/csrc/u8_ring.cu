@@ -353,6 +353,38 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     // sum_k x[k][token] in the accumulator layout; warp cw takes tiles cw, cw + NCW, ...
     if constexpr (!XR) {
       constexpr uint32_t ONES = 0x3C003C00u;  // (1.0, 1.0)
+      if (MT == 1 && a.m <= 4) {
+        // few tokens: plain sums are quicker than the chain of MMAs.  Eight lanes share one
+        // (token, scale-group unit) pair; the columns of the absent tokens are zeroed.
+        const int ctid = tid - 32, sub = ctid & 7;
+        const int entries = p.xsum_entries;
+        for (int idx = ctid; idx < entries * TOK; idx += NCW * 32)
+          if ((idx & (TOK - 1)) >= a.m) xsum[idx] = 0.0f;
+        const int halves = per_piece ? 8 : 16;  // elements per lane
+        const int pairs = entries * a.m;
+        // (the trip count is the same for all lanes of a warp: the shuffles below need them all)
+        for (int base = (ctid >> 5) * 4; base < pairs && ok; base += NCW * 4) {
+          const int pr = base + ((ctid >> 3) & 3);
+          const bool live = pr < pairs;
+          const int r = live ? pr % a.m : 0, e = live ? pr / a.m : 0;
+          const uint8_t* xr = Xsm + (size_t)r * p.XS + (size_t)(e * 8 + sub) * halves * 2;
+          float sum = 0.0f;
+          for (int c = 0; c < (live ? halves / 8 : 0); ++c) {
+            const uint4 u = *reinterpret_cast<const uint4*>(xr + c * 16);
+            const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = __half22float2(h[j]);
+              sum += f.x;
+              sum += f.y;
+            }
+          }
+          sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+          sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+          if (sub == 0 && live) xsum[(size_t)e * TOK + r] = sum;
+        }
+      } else
       for (int kt = cw; kt < ntiles && ok; kt += NCW) {
         float xs[2][MT][4];  // one chain per 64-wide piece
 #pragma unroll
@@ -412,14 +444,17 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
       constexpr bool ROTATE = MT == 1 && NG == 1;
       const bool summer = ROTATE ? (ui % NCW) == cw : true;
       constexpr int OPL = ROTATE ? 16 * TOK / 32 : 1;  // outputs per summing thread
-      float old[OPL];
+      // (kept as loaded: a conversion here would make the warp wait for the loads at once,
+      // and with it the seven warps that share its ring stages)
+      unsigned short old[OPL];
       const bool fused_ar = FUSE && p.ar_world > 1;
       if (summer && !fused_ar) {
 #pragma unroll
         for (int j = 0; j < OPL; ++j) {
           const int e = ROTATE ? lane + 32 * j : tid - 32, row = e & 15, tok = e >> 4;
           old[j] = (tok < a.m && n0 + row < a.n)
-                       ? __half2float(a.out[(size_t)tok * a.n + n0 + row]) : 0.0f;
+                       ? reinterpret_cast<const unsigned short*>(a.out)[(size_t)tok * a.n + n0 + row]
+                       : (unsigned short)0;
         }
       }
       for (int st = 0; st < p.spu; ++st) {
@@ -516,7 +551,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
 #pragma unroll
             for (int w = 0; w < NCW; ++w) v += rb[(size_t)w * 16 * RED_LD + row * RED_LD + tok];
             if (!fused_ar) {
-              a.out[(size_t)tok * a.n + n0 + row] = __float2half_rn(fmaf(a.beta, old[j], v));
+              a.out[(size_t)tok * a.n + n0 + row] =
+                  __float2half_rn(fmaf(a.beta, __half2float(__ushort_as_half(old[j])), v));
             } else {
               // this rank's partial result goes into slot ar_rank of every rank's inbox (peer
               // stores; 16 lanes cover 32 contiguous bytes of one token's row)

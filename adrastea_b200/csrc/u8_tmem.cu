@@ -38,8 +38,8 @@ namespace {
 constexpr int TM_STAGE_BYTES = 128 * 128;  // 128 rows x 128 k-bytes
 constexpr int TM_STRIP_BYTES = 32 * 128;
 constexpr int TM_MAX_STAGES = 12;
-constexpr int TM_NA = 2;        // A buffers in tensor memory (64 columns each)
-constexpr int TM_ND = 8;        // group accumulators in tensor memory (16 columns each)
+constexpr int TM_NA = 2;        // A buffers in tensor memory (64 columns each); a power of two
+constexpr int TM_ND = 8;        // group accumulators in tensor memory (16 columns each); a power of two
 constexpr int TM_TOK = 16;      // token columns of the MMA
 constexpr uint32_t TM_COLS = 256;  // TM_NA * 64 + TM_ND * 16
 constexpr int TM_XTILE_BYTES = TM_TOK * 128;  // 16 tokens x 64 k fp16
@@ -81,6 +81,19 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(tmem_d),
       "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
+}
+// The same with the accumulate flag known at compile time (no predicate to set up).
+template <bool ACCUMULATE>
+__device__ __forceinline__ void umma_f16_ts_c(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc,
+                                              uint32_t idesc) {
+  if (ACCUMULATE)
+    asm volatile("tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, 1;" ::"r"(tmem_d), "r"(tmem_a),
+                 "l"(bdesc), "r"(idesc)
+                 : "memory");
+  else
+    asm volatile("tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, 0;" ::"r"(tmem_d), "r"(tmem_a),
+                 "l"(bdesc), "r"(idesc)
+                 : "memory");
 }
 __device__ __forceinline__ void named_bar(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -151,17 +164,19 @@ __device__ __forceinline__ void st_cluster_f32(uint32_t cluster_addr, float v) {
 //   warp 8      finisher: adds the S partial sums of this CTA's rows in rank order, applies
 //               beta * old and writes the outputs, off the critical path
 //   warp 9      producer (TMA)
-//   warp 10     tensor memory allocation, MMA issue
+//   warps 10-11 MMA issue, k-tiles of even and of odd index (issuing an MMA costs the thread
+//               tens of nanoseconds; two threads alternate so that one waits for its operands
+//               while the other issues); warp 10 also allocates the tensor memory
 constexpr int TM_CONV_WARPS = 4;
 constexpr int TM_DRAIN_WARPS = 4;
-constexpr int TM_W_FINISH = 8, TM_W_PRODUCER = 9, TM_W_MMA = 10;
-constexpr int TM_THREADS = 11 * 32;
+constexpr int TM_W_FINISH = 8, TM_W_PRODUCER = 9, TM_W_MMA = 10;  // and TM_W_MMA + 1
+constexpr int TM_THREADS = 12 * 32;
 constexpr int TM_SCALE_AHEAD = 8;  // scale groups requested ahead of their use
 
 template <bool PDL>
 __global__ void __launch_bounds__(TM_THREADS, PDL ? 2 : 1)
-    u8_tmem_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-                   TmemParams p) {
+    u8_tmem_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap wmap_strip,
+                   const __grid_constant__ CUtensorMap xmap, TmemParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const U8Args& a = p.a;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -206,6 +221,7 @@ __global__ void __launch_bounds__(TM_THREADS, PDL ? 2 : 1)
   const bool aligned = (smem_u32(smem_raw) & 1023u) == 0;  // same for every CTA of the launch
   if (tid == 0) {
     tma_prefetch_desc(&wmap);
+    tma_prefetch_desc(&wmap_strip);
     tma_prefetch_desc(&xmap);
     for (int s = 0; s < p.NS; ++s) {
       mbar_init(&full[s], 1);
@@ -248,16 +264,22 @@ __global__ void __launch_bounds__(TM_THREADS, PDL ? 2 : 1)
       int q = 0;
       int s = 0;
       unsigned par = 0;
-      // one ring slot: T k-tiles of up to four strips; strip j is one 3-D box (128 bytes x 32
-      // rows x T tiles), i.e. T * 128 contiguous bytes of every row
+      // One ring slot: T k-tiles of up to four strips.  A full chunk is ONE 3-D box (128 bytes
+      // x 128 rows x T tiles); the last chunk of a range may hold fewer strips and is loaded
+      // strip by strip (128 bytes x 32 rows x T tiles each).  Issuing a copy costs this thread
+      // tens of nanoseconds, so the number of copies matters.
       auto issue = [&](int ci, int ks) {
         const int strip0 = strip_lo + 4 * ci;
         const int ns = min(4, strip_hi - strip0);
         uint8_t* slot = ring + (size_t)s * slot_bytes;
         mbar_expect_tx(&full[s], (unsigned)(ns * p.T * TM_STRIP_BYTES));
-        for (int j = 0; j < ns; ++j)
-          tma_load_3d(slot + (size_t)j * p.T * TM_STRIP_BYTES, &wmap, 0, (strip0 + j) * 32, tb + ks * p.T,
-                      &full[s]);
+        if (ns == 4 && p.T == 1) {
+          tma_load_3d(slot, &wmap, 0, strip0 * 32, tb + ks, &full[s]);
+        } else {
+          for (int j = 0; j < ns; ++j)
+            tma_load_3d(slot + (size_t)j * p.T * TM_STRIP_BYTES, &wmap_strip, 0, (strip0 + j) * 32,
+                        tb + ks * p.T, &full[s]);
+        }
         if (++s == p.NS) s = 0, par ^= 1u;
       };
       int ci = 0, ks = 0;
@@ -273,9 +295,10 @@ __global__ void __launch_bounds__(TM_THREADS, PDL ? 2 : 1)
       // this CTA's slice of the activations: 2 * nt tiles of [16 tokens][64 k] (rows >= m are
       // filled with zeros by the copy engine)
       if (my_strips > 0) {
-        mbar_expect_tx(xfull, (unsigned)(2 * nt * TM_XTILE_BYTES));
-        for (int t = 0; t < 2 * nt; ++t)
-          tma_load_2d(Xsm + (size_t)t * TM_XTILE_BYTES, &xmap, (2 * tb + t) * 64, 0, xfull);
+        // one box: 64 k x 16 tokens x all 64-wide tiles of the longest slice (a shorter slice
+        // reads one or two tiles beyond its own, which nobody uses)
+        mbar_expect_tx(xfull, (unsigned)(2 * p.max_tiles * TM_XTILE_BYTES));
+        tma_load_3d(Xsm, &xmap, 0, 0, 2 * tb, xfull);
       } else {
         mbar_arrive(xfull);
       }
@@ -294,37 +317,47 @@ __global__ void __launch_bounds__(TM_THREADS, PDL ? 2 : 1)
         if (!mbar_wait(&full[qq % p.NS], (unsigned)(qq / p.NS) & 1u)) atomicOr(p.status, 64u);
       if (!mbar_wait(xfull, 0)) atomicOr(p.status, 64u);
     }
-  } else if (warp == TM_W_MMA) {
+  } else if (warp >= TM_W_MMA) {
     // ------------------------------- MMA issue -------------------------------
+    const int mma_phase = warp - TM_W_MMA;  // this warp issues the k-tiles with q % 2 == mma_phase
     if (lane == 0 && aligned && total_stages > 0) {
       constexpr uint32_t idesc = umma_idesc_f16(TM_TOK, false);
       bool ok = mbar_wait(xfull, 0) && !*abort_flag;
-      const uint32_t xbase = smem_u32(Xsm);
-      const int kk_per_group = 8 / p.gps;
-      int q = 0;
+      // One thread issues everything, so the loop is kept free of divisions and of address
+      // arithmetic that can be folded: per k-tile one descriptor base, per MMA constant offsets.
+      const uint64_t xdesc0 = umma_desc_k_sw128(smem_u32(Xsm));
+      const bool two_groups = p.gps == 2;
+      int q = 0;    // k-tiles issued so far
+      int gi = 0;   // scale groups issued so far
       for (int ci = 0; ci < nchunks && ok; ++ci) {
-        for (int kt = 0; kt < nt && ok; ++kt, ++q) {
-          const int ab = q % TM_NA;
+        for (int kt = 0; kt < nt && ok; ++kt, ++q, gi += two_groups ? 2 : 1) {
+          if ((q & 1) != mma_phase) continue;
+          const int ab = q & (TM_NA - 1);
           if (!mbar_wait(&a_ready[ab], (unsigned)(q / TM_NA) & 1u) || *abort_flag) { ok = false; break; }
-          for (int e = 0; e < p.gps; ++e) {
-            const int gi = q * p.gps + e;
-            if (!mbar_wait(&d_free[gi % TM_ND], ((unsigned)(gi / TM_ND) & 1u) ^ 1u)) ok = false;
-          }
+          const int acc0 = gi & (TM_ND - 1), acc1 = (gi + 1) & (TM_ND - 1);
+          if (!mbar_wait(&d_free[acc0], ((unsigned)(gi / TM_ND) & 1u) ^ 1u)) ok = false;
+          if (two_groups && !mbar_wait(&d_free[acc1], ((unsigned)((gi + 1) / TM_ND) & 1u) ^ 1u)) ok = false;
           if (!ok) break;
           tc_fence_after_sync();
-#pragma unroll
-          for (int kk = 0; kk < 8; ++kk) {
-            const int gi = q * p.gps + kk / kk_per_group;
-            const uint32_t d_addr = tmem_base + (uint32_t)(TM_NA * 64 + (gi % TM_ND) * TM_TOK);
-            const uint32_t a_addr = tmem_base + (uint32_t)(ab * 64 + kk * 8);
-            // B: tile 2 * kt + kk / 4 of the resident activations, 32 bytes further per k16
-            const uint64_t bdesc =
-                umma_desc_k_sw128(xbase + (uint32_t)((2 * kt + (kk >> 2)) * TM_XTILE_BYTES)) +
-                (uint64_t)((kk & 3) * 2);
-            umma_f16_ts(d_addr, a_addr, bdesc, idesc, (kk % kk_per_group) != 0 ? 1u : 0u);
-          }
+          const uint32_t a_addr = tmem_base + (uint32_t)(ab * 64);
+          const uint32_t d0 = tmem_base + (uint32_t)(TM_NA * 64 + acc0 * TM_TOK);
+          const uint32_t d1 = two_groups ? tmem_base + (uint32_t)(TM_NA * 64 + acc1 * TM_TOK) : d0;
+          // B: tiles 2 * kt and 2 * kt + 1 of the resident activations (2 KB = 128 sixteen-byte
+          // units apart), 32 bytes (2 units) further per k16 step
+          const uint64_t xdesc = xdesc0 + (uint64_t)(2 * kt) * (TM_XTILE_BYTES >> 4);
+          constexpr uint64_t T1 = TM_XTILE_BYTES >> 4;  // the second 64-wide tile of the k-tile
+          umma_f16_ts_c<false>(d0, a_addr, xdesc, idesc);
+          umma_f16_ts_c<true>(d0, a_addr + 8, xdesc + 2, idesc);
+          umma_f16_ts_c<true>(d0, a_addr + 16, xdesc + 4, idesc);
+          umma_f16_ts_c<true>(d0, a_addr + 24, xdesc + 6, idesc);
+          if (two_groups) umma_f16_ts_c<false>(d1, a_addr + 32, xdesc + T1, idesc);
+          else umma_f16_ts_c<true>(d1, a_addr + 32, xdesc + T1, idesc);
+          umma_f16_ts_c<true>(d1, a_addr + 40, xdesc + T1 + 2, idesc);
+          umma_f16_ts_c<true>(d1, a_addr + 48, xdesc + T1 + 4, idesc);
+          umma_f16_ts_c<true>(d1, a_addr + 56, xdesc + T1 + 6, idesc);
           umma_commit(&a_free[ab]);
-          for (int e = 0; e < p.gps; ++e) umma_commit(&d_ready[(q * p.gps + e) % TM_ND]);
+          umma_commit(&d_ready[acc0]);
+          if (two_groups) umma_commit(&d_ready[acc1]);
         }
       }
       if (!ok) {
@@ -558,48 +591,52 @@ __global__ void __launch_bounds__(TM_THREADS, PDL ? 2 : 1)
       const int ns = min(4, strip_hi - strip0);
       const int nr0 = strip0 * 32 + (int)rank * rpr;  // first row of this CTA's share
       const int outs = rpr * a.m;
-      if (!__all_sync(0xffffffffu, mbar_wait_cluster(&red_ready[buf], (unsigned)(ci >> 1) & 1u))) {
-        ok = false;
-        if (lane == 0) atomicOr(p.status, 4u);
-      }
       const float* pb = partial + (size_t)buf * S * a.m * rpr;
-      for (int e0 = 0; e0 < outs; e0 += 128) {
-        float old[4], sum[4];
-        // four outputs per lane and round: the loads of the old values are in flight together
+      const int rshift = 31 - __clz(rpr);  // rpr is a power of two
+      constexpr int FB = 16;               // outputs per lane and round: their loads are in flight together
+      bool arrived = false;
+      for (int e0 = 0; e0 < outs; e0 += 32 * FB) {
+        float old[FB];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < FB; ++u) {
           const int e = e0 + u * 32 + lane;
-          const int r_in = e % rpr, tok = e / rpr;
+          const int r_in = e & (rpr - 1), tok = e >> rshift;
           const bool live = e < outs && (int)rank * rpr + r_in < ns * 32 && nr0 + r_in < a.n;
           old[u] = live ? __half2float(a.out[(size_t)tok * a.n + nr0 + r_in]) : 0.0f;
-          float v = 0.0f;
-          if (e < outs)
-            for (uint32_t r = 0; r < S; ++r) v += pb[(size_t)(r * a.m + tok) * rpr + r_in];
-          sum[u] = v;
+        }
+        // the old values of the first round are requested before the partial sums are awaited
+        if (!arrived) {
+          if (!__all_sync(0xffffffffu, mbar_wait_cluster(&red_ready[buf], (unsigned)(ci >> 1) & 1u))) {
+            ok = false;
+            if (lane == 0) atomicOr(p.status, 4u);
+          }
+          arrived = true;
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
+        for (int u = 0; u < FB; ++u) {
           const int e = e0 + u * 32 + lane;
-          const int r_in = e % rpr, tok = e / rpr;
+          const int r_in = e & (rpr - 1), tok = e >> rshift;
           const bool live = e < outs && (int)rank * rpr + r_in < ns * 32 && nr0 + r_in < a.n;
-          if (live && ok)
-            a.out[(size_t)tok * a.n + nr0 + r_in] = __float2half_rn(fmaf(a.beta, old[u], sum[u]));
+          if (live && ok) {
+            float v = 0.0f;
+            for (uint32_t r = 0; r < S; ++r) v += pb[(size_t)(r * a.m + tok) * rpr + r_in];
+            a.out[(size_t)tok * a.n + nr0 + r_in] = __float2half_rn(fmaf(a.beta, old[u], v));
+          }
         }
       }
-      // the buffer may be pushed into again: tell every CTA of the cluster
+      // The buffer may be pushed into again: tell every CTA of the cluster - unless nobody will
+      // (the last two chunks): a CTA that has finished must not be signalled any more.
       __syncwarp();
-      if (lane == 0)
+      if (lane == 0 && ci + 2 < nchunks)
         for (uint32_t r = 0; r < S; ++r) mbar_arrive_remote(map_to_rank(smem_u32(&red_free[buf]), r));
     }
   }
 
+  // No cluster barrier at the end: a CTA's finisher returns only after every peer's partial
+  // sums for its rows have arrived, and nothing else is ever written into its shared memory
+  // (the buffer-free signals above stop two chunks before the end).
   tc_fence_before_sync();
   __syncthreads();
-  __syncwarp();
-  if (S > 1) {
-    // every CTA stays resident until its peers have stopped writing into its shared memory
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-  }
   if (warp == TM_W_MMA) {
     tc_fence_after_sync();
     tmem_dealloc(tmem_base, TM_COLS);
@@ -636,11 +673,12 @@ bool plan_tmem(adr_ctx* ctx, const U8Args& a, bool pdl, TmemPlan& pl) {
   for (int S : {4, 2, 1, 8}) {
     if (S > ntiles) continue;
     const int max_tiles = (ntiles + S - 1) / S;
+    if (2 * max_tiles > 256) continue;  // one copy brings the whole activation slice
     const size_t fixed = (size_t)2 * max_tiles * TM_XTILE_BYTES + (size_t)2 * a.m * 128 * 4 +
                          (size_t)2 * max_tiles * TM_TOK * 4 + 512;
     // k-tiles per ring slot: a copy then takes T * 128 contiguous bytes of every row
     const int want_t = ctx->tune_u8_tiles;
-    int T = want_t > 0 ? want_t : 4;
+    int T = want_t > 0 ? want_t : 1;
     T = std::max(1, std::min(T, max_tiles));
     const size_t slot_bytes = (size_t)T * TM_STAGE_BYTES;
     if (fixed + 2 * slot_bytes > 224 * 1024) continue;
@@ -672,22 +710,28 @@ template <bool PDL>
 int launch_tmem_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const TmemPlan& pl) {
   auto kfn = u8_tmem_kernel<PDL>;
   if (int rc = opt_in_smem(ctx, kfn, 226 * 1024); rc != ADR_OK) return rc;
-  CUtensorMap wmap, xmap;
+  CUtensorMap wmap, wmap_strip, xmap;
   {
-    // weights as (k within tile, row, k-tile): a box of 128 x 32 x T lands as T tiles of
-    // [32 rows][128 bytes], each swizzled by its own row index
+    // weights as (k within tile, row, k-tile): a box of 128 x R x T lands as T tiles of
+    // [R rows][128 bytes], each row swizzled by its own index; R = 128 for a whole chunk,
+    // 32 for one strip
     const uint64_t dims[3] = {128u, (uint64_t)a.n, (uint64_t)(a.p / 128)};
     const uint64_t strides[2] = {(uint64_t)a.p, 128u};
-    const uint32_t box[3] = {128u, 32u, (uint32_t)pl.T};
+    const uint32_t box[3] = {128u, 128u, 1u};
     int rc = tma_get(ctx, &wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.rhs, dims, strides, box,
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != ADR_OK) return rc;
+    const uint32_t sbox[3] = {128u, 32u, (uint32_t)pl.T};
+    rc = tma_get(ctx, &wmap_strip, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.rhs, dims, strides, sbox,
+                 CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != ADR_OK) return rc;
   }
   {
-    const uint64_t dims[2] = {(uint64_t)a.p, (uint64_t)a.m};
-    const uint64_t strides[1] = {(uint64_t)a.p * 2};
-    const uint32_t box[2] = {64u, (uint32_t)TM_TOK};
-    int rc = tma_get(ctx, &xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, a.lhs, dims, strides, box,
+    // activations as (k within a 64-wide tile, token, tile): one box brings a CTA's whole slice
+    const uint64_t dims[3] = {64u, (uint64_t)a.m, (uint64_t)(a.p / 64)};
+    const uint64_t strides[2] = {(uint64_t)a.p * 2, 128u};
+    const uint32_t box[3] = {64u, (uint32_t)TM_TOK, (uint32_t)(2 * pl.max_tiles)};
+    int rc = tma_get(ctx, &xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, a.lhs, dims, strides, box,
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != ADR_OK) return rc;
   }
@@ -722,7 +766,7 @@ int launch_tmem_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Tmem
   }
   cfg.attrs = attr;
   cfg.numAttrs = na;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, wmap, xmap, p);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, wmap, wmap_strip, xmap, p);
   if (e != cudaSuccess) {
     ctx->last_cuda_error = (int)e;
     return ADR_ERR_CUDA;

@@ -66,6 +66,7 @@ class Kernel(enum.IntEnum):
     U8Ring = 8
     U8Tmem = 9
     F16TcGather = 10
+    U8Ts = 11
 
 
 @dataclass(frozen=True)

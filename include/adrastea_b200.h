@@ -77,8 +77,10 @@ enum {
   ADR_KERNEL_U8_RING = 8,     /* m <= 16, block 64/128: persistent CTAs, TMA ring, scale applied per group */
   ADR_KERNEL_U8_TMEM = 9,     /* m <= 16, block 64/128: weights converted into tensor memory, tcgen05.mma,
                                  cluster split-k; scale applied per group */
-  ADR_KERNEL_F16_TC_GATHER = 10 /* tcgen05.mma behind loader warps that gather operands of any stride
-                                   or alignment into the swizzled stage layout (views TMA cannot describe) */
+  ADR_KERNEL_F16_TC_GATHER = 10, /* tcgen05.mma behind loader warps that gather operands of any stride
+                                    or alignment into the swizzled stage layout (views TMA cannot describe) */
+  ADR_KERNEL_U8_TS = 11       /* m > 32, p % 64 == 0, block % 64 == 0: weights dequantised into tensor
+                                 memory (A operand), 256 tokens per tcgen05.mma */
 };
 
 /*

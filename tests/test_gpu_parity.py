@@ -194,6 +194,8 @@ def u8_kernels_for(c):
                 ks.append(Kernel.U8Ring)
     if c.p % 16 == 0:
         ks.append(Kernel.U8Tc)
+    if c.p % 64 == 0 and c.block_size % 64 == 0:
+        ks.append(Kernel.U8Ts)
     return ks
 
 
@@ -580,25 +582,37 @@ def test_tc_gemm_n_contiguous_rhs(kernels, bn, split):
 
 @pytest.mark.parametrize("zp", [False, True])
 def test_u8_prefill_tensor_core_kernel(kernels, zp):
-    """m > 16 takes the dequantising tensor-core kernel: ragged m/n, several k-blocks
-    and tiles per CTA, beta, zero points; checked against the ideal oracle."""
+    """m > 32 takes a dequantising tensor-core kernel: the one that dequantises into tensor
+    memory when p and the block size are multiples of 64, else the one that stages the
+    dequantised operand in shared memory; both forced in turn on the shapes they take.  Ragged
+    m/n, several k-steps and tiles per CTA, both tile widths, beta, zero points; against the
+    ideal oracle (fp16-rounded weights, exact products)."""
     rng = np.random.default_rng(31 + zp)
-    for m, p, n, bs, beta in ((130, 1088, 300, 64, 0.5), (512, 512, 1024, 128, 0.0), (40, 256, 192, 128, 1.0)):
-        x = rng.standard_normal((m, p)).astype(np.float16)
-        q = rng.integers(0, 256, (n, p), dtype=np.uint8)
-        s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
-        z = rng.uniform(120, 136, (n, p // bs)).astype(np.float16) if zp else None
-        out0 = (rng.standard_normal((m, n)) * 0.5).astype(np.float16)
-        want = oracle.matmul_nt_fp16u8(x, q, s, bs, beta, out0, z)
-        res = []
-        for _ in range(2):
-            o = dev(out0.copy())
-            kernels.matmul_nt_fp16u8(o, dev(x), dev(q), dev(s), bs, beta, dev(z) if zp else None)
-            kernels.device_status()
-            assert kernels.last_kernel() == Kernel.U8Tc
-            res.append(o.cpu().numpy())
-        assert np.array_equal(res[0].view(np.uint16), res[1].view(np.uint16))
-        assert oracle.max_rel_err(res[0], want) <= TOL, (m, p, n)
+    try:
+        for m, p, n, bs, beta in ((130, 1088, 300, 64, 0.5), (512, 512, 1024, 128, 0.0),
+                                  (40, 256, 192, 128, 1.0), (300, 4096, 260, 128, 0.5),
+                                  (700, 832, 520, 64, 0.0), (33, 1040, 100, 16, 0.5)):
+            x = rng.standard_normal((m, p)).astype(np.float16)
+            q = rng.integers(0, 256, (n, p), dtype=np.uint8)
+            s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
+            z = rng.uniform(120, 136, (n, p // bs)).astype(np.float16) if zp else None
+            out0 = (rng.standard_normal((m, n)) * 0.5).astype(np.float16)
+            want = oracle.matmul_nt_fp16u8(x, q, s, bs, beta, out0, z)
+            takes_ts = p % 64 == 0 and bs % 64 == 0
+            for kern in ([Kernel.Auto, Kernel.U8Ts, Kernel.U8Tc] if takes_ts else [Kernel.Auto, Kernel.U8Tc]):
+                kernels.force_kernel(kern)
+                res = []
+                for _ in range(2):
+                    o = dev(out0.copy())
+                    kernels.matmul_nt_fp16u8(o, dev(x), dev(q), dev(s), bs, beta, dev(z) if zp else None)
+                    kernels.device_status()
+                    res.append(o.cpu().numpy())
+                expect = kern if kern != Kernel.Auto else (Kernel.U8Ts if takes_ts else Kernel.U8Tc)
+                assert kernels.last_kernel() == expect
+                assert np.array_equal(res[0].view(np.uint16), res[1].view(np.uint16))
+                assert oracle.max_rel_err(res[0], want) <= TOL, (kern, m, p, n)
+    finally:
+        kernels.force_kernel(Kernel.Auto)
 
 
 def fp16_spacing(v):
