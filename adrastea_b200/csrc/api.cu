@@ -152,7 +152,6 @@ int adr_set_tunable(adr_ctx* ctx, const char* name, int value) {
   if (!ctx || !name || value < 0) return ADR_ERR_INVALID;
   if (!strcmp(name, "u8_split")) ctx->tune_u8_split = value;
   else if (!strcmp(name, "u8_rows")) ctx->tune_u8_rows = value;
-  else if (!strcmp(name, "u8_tiles")) ctx->tune_u8_tiles = value;
   else if (!strcmp(name, "tc_bn")) ctx->tune_tc_bn = value;
   else if (!strcmp(name, "tc_split")) ctx->tune_tc_split = value;
   else if (!strcmp(name, "pdl")) ctx->tune_pdl = value;
@@ -260,17 +259,6 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
         c.lhs = a.lhs + (size_t)r0 * p;
         c.out = a.out + (size_t)r0 * n;
         rc = launch_u8_ring(ctx, st, c);
-      }
-      break;
-    }
-    case ADR_KERNEL_U8_TMEM: {
-      rc = ADR_OK;
-      for (int r0 = 0; r0 < m && rc == ADR_OK; r0 += 16) {  // one pass per 16 tokens
-        U8Args c = a;
-        c.m = (m - r0 < 16) ? m - r0 : 16;
-        c.lhs = a.lhs + (size_t)r0 * p;
-        c.out = a.out + (size_t)r0 * n;
-        rc = launch_u8_tmem(ctx, st, c);
       }
       break;
     }

@@ -60,8 +60,6 @@ struct adr_ctx {
   std::vector<adr::TraceKey> trace;
   // kernels whose dynamic shared memory limit has been raised on this context's device
   std::unordered_map<const void*, size_t> smem_opt_in;
-  // clusters of the decode kernel that fit the device at once, by (pdl, cluster size, smem)
-  std::unordered_map<uint64_t, int> cluster_capacity;
   // Device word written by kernels whose bounded waits ran out (0 = fine).
   unsigned int* d_status = nullptr;
   // Cache of TMA descriptors, keyed by (pointer, dims, strides, box).
@@ -70,7 +68,6 @@ struct adr_ctx {
   // tuning knobs (adr_set_tunable); 0 = let the planner choose
   std::atomic<int> tune_u8_split{0};
   std::atomic<int> tune_u8_rows{0};
-  std::atomic<int> tune_u8_tiles{0};  // k-tiles per ring slot of the tensor-memory decode kernel
   std::atomic<int> tune_u8_exact{0};  // 1: fp16-rounded dequantisation in the streaming kernel
   std::atomic<int> tune_tc_bn{0};
   std::atomic<int> tune_tc_split{0};
@@ -249,8 +246,6 @@ struct RingArFuse {
 };
 int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingArFuse* ar = nullptr);
 bool u8_ring_supports(const adr_ctx* ctx, const U8Args& a);
-int launch_u8_tmem(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
-bool u8_tmem_supports(adr_ctx* ctx, const U8Args& a);
 int launch_u8_tc(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 int launch_u8_ts(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 bool u8_ts_supports(const adr_ctx* ctx, const U8Args& a);

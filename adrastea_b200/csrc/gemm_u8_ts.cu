@@ -10,13 +10,17 @@
 // runs its widest instruction.
 //   * producer warp: per 64-wide k-step one TMA box of the weights (128 rows x 64 bytes of u8)
 //     and one of the activations (BT tokens x 64 fp16, 128-byte swizzle, K-major) into a ring;
-//   * eight converter warps (warp w: TMEM lane quarter w % 4, k-steps of parity w / 4): thread =
-//     weight row; 16 bytes -> 16 fp16 in registers (u8_common.cuh) -> tcgen05.st into one of
-//     four A buffers in tensor memory.  The dequantised weights never touch shared memory;
+//   * sixteen converter warps (warp w: TMEM lane quarter w % 4, k-steps with index % 4 ==
+//     w / 4): thread = weight row; 16 bytes -> 16 fp16 in registers (u8_common.cuh) ->
+//     tcgen05.st into one of eight A buffers in tensor memory.  The dequantised weights never
+//     touch shared memory.  (Converting a k-step takes a warp about half a microsecond, the
+//     tensor core needs a quarter: four phases keep it fed);
 //   * one thread issues tcgen05.mma (A from tensor memory, B = activations from shared memory,
-//     M = 128, N = BT, K = 16) into one accumulator of BT columns;
-//   * after the last k-step the converter warps turn into the epilogue: tcgen05.ld, beta * old,
-//     fp16 stores (thread = weight row, so a warp writes 32 consecutive outputs of one token).
+//     M = 128, N = BT, K = 16) into one accumulator of BT columns (one issuer: the order of
+//     MMAs into one accumulator is only defined within a thread);
+//   * after the last k-step the converter warps turn into the epilogue: tcgen05.ld, a
+//     transposition of 32 rows x 8 tokens (fp32) through a small shared-memory tile so that
+//     old outputs are read and new ones written as 16-byte vectors, fp16(acc + beta * old).
 // Persistent CTAs walk the tiles with the token blocks of one weight block next to each
 // other, so that a weight block is read from HBM once and then from L2.
 // Needs p % 64 == 0 and block_size % 64 == 0 (one scale group per k-step); other shapes take
@@ -32,18 +36,24 @@ namespace {
 
 constexpr int TS_BK = 64;            // k per step
 constexpr int TS_ROWS = 128;         // weight rows per tile
-constexpr int TS_NA = 4;             // A buffers in tensor memory (32 columns each)
-constexpr int TS_CONV_WARPS = 8;
-constexpr int TS_W_PRODUCER = 8, TS_W_MMA = 9;
-constexpr int TS_THREADS = 10 * 32;
+constexpr int TS_NA = 8;             // A buffers in tensor memory (32 columns each)
+constexpr int TS_PHASES = 4;         // converter phases (k-step index % 4)
+constexpr int TS_CONV_WARPS = 4 * TS_PHASES;
+constexpr int TS_W_PRODUCER = 16, TS_W_MMA = 17;
+constexpr int TS_THREADS = 18 * 32;
+constexpr int TS_EPI_TOK = 8;        // tokens per transposition pass
+constexpr int TS_EPI_LD = 36;        // floats between token rows of the tile (16 bytes more than 32:
+                                     // the eight token rows then start in different bank groups)
+constexpr int TS_EPI_BYTES = TS_EPI_TOK * TS_EPI_LD * 4;  // per converter warp
 
 template <int BT>
 struct TsCfg {
   static constexpr int W_BYTES = TS_ROWS * TS_BK;      // u8
   static constexpr int X_BYTES = BT * TS_BK * 2;       // fp16
   static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
-  static constexpr int STAGES = (200 * 1024) / STAGE_BYTES > 8 ? 8 : (200 * 1024) / STAGE_BYTES;
-  static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + 512;
+  static constexpr int STAGES = (204 * 1024) / STAGE_BYTES > 8 ? 8 : (204 * 1024) / STAGE_BYTES;
+  static constexpr size_t EPI_BYTES = (size_t)TS_CONV_WARPS * TS_EPI_BYTES;
+  static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + EPI_BYTES + 512;
   static constexpr uint32_t A_COL0 = BT;
   static constexpr uint32_t TMEM_COLS = BT + TS_NA * 32 <= 256 ? 256 : 512;
 };
@@ -86,7 +96,8 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* stages = smem;  // per stage: activations (1024-aligned), then weights
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES);
+  uint8_t* epi = smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES;  // [warp][16 tokens][32 rows] fp16
+  uint64_t* full = reinterpret_cast<uint64_t*>(epi + Cfg::EPI_BYTES);
   uint64_t* empty = full + Cfg::STAGES;      // 4 converter warps + the MMA commit
   uint64_t* a_ready = empty + Cfg::STAGES;   // [TS_NA]
   uint64_t* a_free = a_ready + TS_NA;        // [TS_NA]
@@ -105,7 +116,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
     tma_prefetch_desc(&map_x);
     for (int s = 0; s < Cfg::STAGES; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 5);
+      mbar_init(&empty[s], 5);  // the four converter warps of the step's phase + the MMA commit
     }
     for (int i = 0; i < TS_NA; ++i) {
       mbar_init(&a_ready[i], 4);
@@ -149,20 +160,30 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
         // the single accumulator is free once the epilogue of the previous tile has read it
         if (!mbar_wait(acc_empty, ((unsigned)local & 1u) ^ 1u)) { ok = false; break; }
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % Cfg::STAGES, ab = it & (TS_NA - 1);
-          if (!mbar_wait(&full[s], (unsigned)(it / Cfg::STAGES) & 1u)) { ok = false; break; }
-          if (!mbar_wait(&a_ready[ab], (unsigned)(it / TS_NA) & 1u)) { ok = false; break; }
+        // two k-steps per round: the waits and the bookkeeping of this single thread are the
+        // tensor core's idle time, so they are paid once per eight MMAs where possible
+        for (int kb = 0; kb < num_kb && ok; kb += 2) {
+          const int steps = min(2, num_kb - kb);
+          // (the converters waited for a stage's copies before they converted, so the
+          // activations of the stage have landed too)
+          for (int u = 0; u < steps; ++u) {
+            const int ab = (it + u) & (TS_NA - 1);
+            if (!mbar_wait(&a_ready[ab], (unsigned)((it + u) / TS_NA) & 1u)) ok = false;
+          }
+          if (!ok) break;
           tc_fence_after_sync();
-          const uint64_t xdesc = umma_desc_k_sw128(smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES));
-          const uint32_t a_addr = tmem_base + Cfg::A_COL0 + (uint32_t)(ab * 32);
-          if (kb == 0) ts_mma<false>(tmem_base, a_addr, xdesc, idesc);
-          else ts_mma<true>(tmem_base, a_addr, xdesc, idesc);
-          ts_mma<true>(tmem_base, a_addr + 8, xdesc + 2, idesc);
-          ts_mma<true>(tmem_base, a_addr + 16, xdesc + 4, idesc);
-          ts_mma<true>(tmem_base, a_addr + 24, xdesc + 6, idesc);
-          umma_commit(&a_free[ab]);
-          umma_commit(&empty[s]);
+          for (int u = 0; u < steps; ++u, ++it) {
+            const int s = it % Cfg::STAGES, ab = it & (TS_NA - 1);
+            const uint64_t xdesc = umma_desc_k_sw128(smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES));
+            const uint32_t a_addr = tmem_base + Cfg::A_COL0 + (uint32_t)(ab * 32);
+            if (kb + u == 0) ts_mma<false>(tmem_base, a_addr, xdesc, idesc);
+            else ts_mma<true>(tmem_base, a_addr, xdesc, idesc);
+            ts_mma<true>(tmem_base, a_addr + 8, xdesc + 2, idesc);
+            ts_mma<true>(tmem_base, a_addr + 16, xdesc + 4, idesc);
+            ts_mma<true>(tmem_base, a_addr + 24, xdesc + 6, idesc);
+            umma_commit(&a_free[ab]);
+            umma_commit(&empty[s]);
+          }
         }
         umma_commit(acc_full);
       }
@@ -180,7 +201,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
       const int n_row = n0 + row;
       const size_t srow = (size_t)min(n_row, p.n - 1) * groups;
       // scale of this warp's first k-step of the tile; the next one is requested a step ahead
-      int kb_mine = ((it & 1) == phase) ? 0 : 1;
+      int kb_mine = (phase - (it & (TS_PHASES - 1)) + TS_PHASES) & (TS_PHASES - 1);
       __half sc = __float2half(0.f), zp = __float2half(0.f);
       if (kb_mine < num_kb) {
         const int g = (kb_mine * TS_BK) / p.block_size;
@@ -188,11 +209,11 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
         if (has_zero) zp = p.zeros[srow + g];
       }
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        if ((it & 1) != phase) continue;
+        if ((it & (TS_PHASES - 1)) != phase) continue;
         const int s = it % Cfg::STAGES, ab = it & (TS_NA - 1);
         const ScalePair sp = make_scale(sc, has_zero, zp);
-        if (kb + 2 < num_kb) {  // this warp's next k-step
-          const int g = ((kb + 2) * TS_BK) / p.block_size;
+        if (kb + TS_PHASES < num_kb) {  // this warp's next k-step
+          const int g = ((kb + TS_PHASES) * TS_BK) / p.block_size;
           sc = p.scales[srow + g];
           if (has_zero) zp = p.zeros[srow + g];
         }
@@ -227,33 +248,71 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(&a_ready[ab]);
       }
-      // ---- epilogue of the tile: this warp's lane quarter, token half `phase` ----
+      // ---- epilogue of the tile: this warp's lane quarter (32 weight rows), token quarter
+      // `phase`.  Passes of 8 tokens: the thread (= weight row) writes its 8 fp32 results into
+      // the warp's [8 tokens][32 rows] tile, then every lane takes one piece (8 consecutive rows
+      // of one token): old outputs read and new ones written as 16-byte vectors.
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, (unsigned)local & 1u));
       tc_fence_after_sync();
       if (ok) {
-        constexpr int HALF = BT / 2;
+        constexpr int QT = BT / TS_PHASES;  // tokens per warp
+        float* tile = reinterpret_cast<float*>(epi + (size_t)warp * TS_EPI_BYTES);
+        const int nq0 = n0 + quarter * 32;  // first output column of this warp
+        const bool vec = (p.n % 8 == 0) && nq0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0;
+        const int tk = lane >> 2, seg = lane & 3;  // this lane's piece of a pass
 #pragma unroll 1
-        for (int c = 0; c < HALF / 32; ++c) {
-          const int tok0 = t0 + phase * HALF + c * 32;
+        for (int c = 0; c < QT / TS_EPI_TOK; ++c) {
+          const int tok0 = t0 + phase * QT + c * TS_EPI_TOK;
           if (tok0 >= p.m) break;  // uniform across the warp
-          uint32_t acc[32];
-          tmem_ld_32x32(tmem_base + lane_base + (uint32_t)(phase * HALF + c * 32), acc);
-          unsigned short old[32];
-          const bool row_ok = n_row < p.n;
+          uint32_t acc[8];
+          asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                       : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]),
+                         "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7])
+                       : "r"(tmem_base + lane_base + (uint32_t)(phase * QT + c * TS_EPI_TOK))
+                       : "memory");
+          if (vec) {
+            // old outputs of this lane's piece, requested before the accumulator is awaited
+            uint4 oldv = make_uint4(0, 0, 0, 0);
+            __half* optr = p.out + (size_t)(tok0 + tk) * p.n + nq0 + seg * 8;
+            const bool live = tok0 + tk < p.m;
+            if (live) oldv = *reinterpret_cast<const uint4*>(optr);
+            tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int tok = tok0 + j;
-            old[j] = (row_ok && tok < p.m)
-                         ? reinterpret_cast<const unsigned short*>(p.out)[(size_t)tok * p.n + n_row]
-                         : (unsigned short)0;
-          }
-          tmem_ld_wait();
+            for (int j = 0; j < TS_EPI_TOK; ++j) tile[j * TS_EPI_LD + lane] = __uint_as_float(acc[j]);
+            __syncwarp();
+            if (live) {
+              const float4 a0 = *reinterpret_cast<const float4*>(tile + tk * TS_EPI_LD + seg * 8);
+              const float4 a1 = *reinterpret_cast<const float4*>(tile + tk * TS_EPI_LD + seg * 8 + 4);
+              const __half2* o2 = reinterpret_cast<const __half2*>(&oldv);
+              const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+              uint4 res;
+              __half2* r2 = reinterpret_cast<__half2*>(&res);
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int tok = tok0 + j;
-            if (row_ok && tok < p.m)
-              p.out[(size_t)tok * p.n + n_row] = __float2half_rn(
-                  fmaf(p.beta, __half2float(__ushort_as_half(old[j])), __uint_as_float(acc[j])));
+              for (int e = 0; e < 4; ++e) {
+                const float2 ov = __half22float2(o2[e]);
+                r2[e] = __floats2half2_rn(fmaf(p.beta, ov.x, av[2 * e]), fmaf(p.beta, ov.y, av[2 * e + 1]));
+              }
+              *reinterpret_cast<uint4*>(optr) = res;
+            }
+            __syncwarp();
+          } else {
+            const bool row_ok = n_row < p.n;
+            unsigned short old[TS_EPI_TOK];
+#pragma unroll
+            for (int j = 0; j < TS_EPI_TOK; ++j) {
+              const int tok = tok0 + j;
+              old[j] = (row_ok && tok < p.m)
+                           ? reinterpret_cast<const unsigned short*>(p.out)[(size_t)tok * p.n + n_row]
+                           : (unsigned short)0;
+            }
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < TS_EPI_TOK; ++j) {
+              const int tok = tok0 + j;
+              if (row_ok && tok < p.m)
+                p.out[(size_t)tok * p.n + n_row] = __float2half_rn(
+                    fmaf(p.beta, __half2float(__ushort_as_half(old[j])), __uint_as_float(acc[j])));
+            }
           }
         }
       }

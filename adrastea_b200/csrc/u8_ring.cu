@@ -95,6 +95,7 @@ struct RingParams {
   int xsum_entries;  // k-units of the activation-sum table
   int stage_bytes;   // distance between ring stages
   int xss;           // XR: bytes between activation rows inside a stage
+  int rbufs;         // partial-sum buffers in rotation (2 or 4)
   unsigned int* status;
   // fused all-reduce (ar_world > 1): the unit results are pushed to every rank's inbox
   // [world][m][n] fp16 (slot = pushing rank) and summed after a flag exchange per CTA
@@ -132,7 +133,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
   float* red = reinterpret_cast<float*>(Xsm + (XR ? 0 : (size_t)a.m * p.XS));  // [RBUFS][NCW][16][RED_LD]
   // sum of the activations over every scale-group unit (a tile, or a 64-wide piece when
   // block_size is 64), per token: [units of k][TOK]
-  constexpr int RBUFS = (MT == 1 && NG == 1) ? RING_RED_BUFS : 2;  // the all-sync form needs two
+  const int RBUFS = p.rbufs;  // four in rotation, or two (the all-sync form, or to save room)
   float* xsum = red + RBUFS * NCW * 16 * RED_LD;
   uint64_t* full = reinterpret_cast<uint64_t*>(xsum + (XR ? 0 : (size_t)p.xsum_entries * TOK));
   uint64_t* empty = full + RING_MAX_STAGES;
@@ -525,7 +526,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
       // and barrier `ui % RING_RED_BUFS` are reused four units later; a warp cannot be that
       // far ahead of the summing warp, because the ring (at most 4 * spu - 1 stages, see
       // plan_ring) refills a stage only after all eight warps have released it.
-      const int rbuf = ui % RBUFS;
+      const int rbuf = ui & (RBUFS - 1);
       float* rb = red + (size_t)rbuf * NCW * 16 * RED_LD;
       {
         float* rw = rb + (size_t)cw * 16 * RED_LD;
@@ -615,7 +616,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
 }
 
 struct RingPlan {
-  int NS, XS, gps, shift, ncw, xsum_entries, cps, xr, stage_bytes, xss;
+  int NS, XS, gps, shift, ncw, xsum_entries, cps, xr, stage_bytes, xss, rbufs;
   size_t smem;
 };
 
@@ -635,8 +636,12 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   pl.gps = 1024 / a.block_size;
   pl.shift = a.block_size == 64 ? 6 : 7;
   pl.xsum_entries = (a.p / 128) * (a.block_size == 64 ? 2 : 1);
-  const size_t fixed = (size_t)a.m * pl.XS + (size_t)(a.m > 8 ? 2 : RING_RED_BUFS) * pl.ncw * 16 * (tok + 1) * 4 +
-                       (size_t)pl.xsum_entries * tok * 4 + (2 * RING_MAX_STAGES + 2) * 8;
+  auto fixed_for = [&](int rbufs) {
+    return (size_t)a.m * pl.XS + (size_t)rbufs * pl.ncw * 16 * (tok + 1) * 4 +
+           (size_t)pl.xsum_entries * tok * 4 + (2 * RING_MAX_STAGES + 2) * 8;
+  };
+  pl.rbufs = a.m > 8 ? 2 : RING_RED_BUFS;
+  size_t fixed = fixed_for(pl.rbufs);
   const int spu = (a.p / 128 + RING_TILES - 1) / RING_TILES;
   const int sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
   const int units = (a.n + 15) / 16;
@@ -646,19 +651,33 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   // CTA (sixteen consumer warps per SM hide the latency of the arithmetic better than eight),
   // else the first CTAs of the next launch, started early under programmatic dependent
   // launch.  When half an SM leaves fewer than five stages, one CTA takes all of it.
-  const int ns_half = fixed < half ? (int)((half - fixed) / RING_STAGE_BYTES) : 0;
+  int ns_half = fixed < half ? (int)((half - fixed) / RING_STAGE_BYTES) : 0;
+  int half_min = 5;
+  if (a.m > 2 && a.m <= 8 && ns_half < 5) {
+    // A few tokens more and the activations crowd the ring out of half an SM.  Two partial-sum
+    // buffers instead of four win a stage back, and four stages beside an early successor
+    // measured better than ten without one.
+    const size_t f2 = fixed_for(2);
+    const int nh2 = f2 < half ? (int)((half - f2) / RING_STAGE_BYTES) : 0;
+    if (nh2 >= 4 && nh2 <= 2 * spu - 1) {
+      pl.rbufs = 2;
+      fixed = f2;
+      ns_half = nh2;
+      half_min = 4;
+    }
+  }
   int ns;
   pl.cps = 1;
   if (a.m <= 2 && units >= 4 * sms && ns_half >= 4) {
     pl.cps = 2;
     ns = ns_half;
-  } else if (ns_half >= 5) {
+  } else if (ns_half >= half_min) {
     ns = ns_half;
   } else {
     ns = fixed < all ? (int)((all - fixed) / RING_STAGE_BYTES) : 0;
   }
   ns = std::min(ns, RING_MAX_STAGES);
-  if (a.m <= 8) ns = std::min(ns, RING_RED_BUFS * spu - 1);  // keeps the rotation of partial-sum buffers safe
+  if (a.m <= 8) ns = std::min(ns, pl.rbufs * spu - 1);  // keeps the rotation of partial-sum buffers safe
   pl.xr = 0;
   pl.stage_bytes = RING_STAGE_BYTES;
   pl.xss = 0;
@@ -671,12 +690,14 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
     // fragment loads of different tokens fall in different banks).
     const int xss = 2048 + 16;
     const int stage = (RING_STAGE_BYTES + a.m * xss + 1023) & ~1023;
-    const size_t fixed_xr = (size_t)(a.m > 8 ? 2 : RING_RED_BUFS) * pl.ncw * 16 * (tok + 1) * 4 +
+    const int rb_xr = a.m > 8 ? 2 : RING_RED_BUFS;
+    const size_t fixed_xr = (size_t)rb_xr * pl.ncw * 16 * (tok + 1) * 4 +
                             (2 * RING_MAX_STAGES + 2) * 8;
     int ns_xr = (int)((all - fixed_xr) / stage);
     ns_xr = std::min(ns_xr, RING_MAX_STAGES);
     if (a.m <= 8) ns_xr = std::min(ns_xr, RING_RED_BUFS * spu - 1);
     if (ns_xr >= 3 && ns_xr > ns) {
+      pl.rbufs = rb_xr;
       pl.xr = 1;
       pl.cps = 1;
       pl.stage_bytes = stage;
@@ -718,6 +739,7 @@ int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
   p.xsum_entries = pl.xsum_entries;
   p.stage_bytes = pl.stage_bytes;
   p.xss = pl.xss;
+  p.rbufs = pl.rbufs;
   p.status = ctx->d_status;
   p.norm_w = a.norm_w;
   p.norm_eps = a.norm_eps;

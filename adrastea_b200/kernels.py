@@ -64,9 +64,8 @@ class Kernel(enum.IntEnum):
     U8Simt = 6
     U8Stream = 7
     U8Ring = 8
-    U8Tmem = 9
-    F16TcGather = 10
-    U8Ts = 11
+    F16TcGather = 9
+    U8Ts = 10
 
 
 @dataclass(frozen=True)

@@ -232,15 +232,15 @@ class LlamaU8:
 
     # ------------------------------------------------------------- prefill
     # ------------------------------------------------------------- prefill
-    PREFILL_DEQUANT_ROWS = 1024
+    PREFILL_DEQUANT_ROWS = 4096
 
     def _prefill_linear(self, lin, out: torch.Tensor, x: torch.Tensor, part: torch.Tensor | None = None,
                         residual: bool = False):
-        """A linear layer over many rows.  From PREFILL_DEQUANT_ROWS rows on, the u8 matrix is
-        first expanded to fp16 in a scratch buffer (`adr_dequantize_absmax_uint8`: the fp16-rounded
-        weights of the reference's WMMA kernel) and multiplied by the fp16 tensor-core GEMM, which
-        runs at more than twice the rate of the dequantising GEMM; the expansion costs one pass
-        over the matrix per call.  Fewer rows go through `adr_matmul_nt_fp16u8`."""
+        """A linear layer over many rows.  Up to PREFILL_DEQUANT_ROWS rows go through
+        `adr_matmul_nt_fp16u8` (the kernel that dequantises into tensor memory).  From there on
+        the u8 matrix is first expanded to fp16 in a scratch buffer (`adr_dequantize_absmax_uint8`:
+        the same fp16-rounded weights) and multiplied by the fp16 tensor-core GEMM: with that
+        many rows the fp16 GEMM's higher rate outweighs one extra pass over the matrix."""
         w = lin.w
         rows = x.shape[0]
         row_split = isinstance(lin, RowParallelU8Linear)

@@ -870,7 +870,9 @@ def run_profile_case(args):
     """Small, self-terminating cases for `ncu` captures (a few hundred MB on the device).
 
     u8 : the decode kernel over 12 distinct [--n,4096] u8 weights (201 MB at n = 4096, larger
-         than L2), two passes, m = --m.
+         than L2), two passes, m = --m (m > 32 reaches the prefill kernel).
+    fattn: the fused attention kernel, 1024 heads of 257 x 64 (the CLIP encoder's shape at batch
+         64) when --m is 64, else --m heads of 512 x 128 with the causal mask (LLaMA prefill).
     f16: the tensor-core GEMM, [m,4096] x [4096,4096]^T over 6 distinct weights, m = --m.
     attn: the decode-attention kernel, batch --m, 32 heads x 128, 600 of 640 cached positions.
     """
@@ -890,6 +892,23 @@ def run_profile_case(args):
         for _ in range(2):
             for q, s in ws:
                 kern.matmul_nt_fp16u8(o, x, q, s, BS)
+    elif args.profile_case == "fattn":
+        import math
+        if m == 64:
+            B, S, H, hd = 64, 257, 16, 64
+            t = [torch.randn((S * B, H * hd), device="cuda").half() for _ in range(4)]
+            from adrastea_b200 import TensorLayout
+            lay = TensorLayout.new((B * H, S, hd), (hd, B * H * hd, 1))
+            v = [TensorView(x, lay) for x in t]
+            for _ in range(3):
+                kern.attention_f16(v[3], v[0], v[1], v[2], 1.0 / math.sqrt(hd))
+        else:
+            H, S, hd = m, 512, 128
+            t = [torch.randn((H, S, hd), device="cuda").half() for _ in range(4)]
+            from adrastea_b200 import MatmulMask
+            for _ in range(3):
+                kern.attention_f16(TensorView.of(t[3]), TensorView.of(t[0]), TensorView.of(t[1]),
+                                   TensorView.of(t[2]), 1.0 / math.sqrt(hd), MatmulMask.Causal)
     elif args.profile_case == "attn":
         # decode attention at the LLaMA-7B shape: batch --m sequences, 32 heads of 128, 600 cached
         # positions of 640 (K and V caches of 84 MB each at batch 16)
@@ -928,9 +947,9 @@ def main():
                     help="N > 1: all-reduce inside the row-split GEMV kernel instead of a kernel of its own")
     ap.add_argument("--nccl", action="store_true",
                     help="N > 1: reduce the row-split products with NCCL instead of the library's peer-memory kernel")
-    ap.add_argument("--profile-case", default=None, choices=["u8", "f16", "attn"],
+    ap.add_argument("--profile-case", default=None, choices=["u8", "f16", "attn", "fattn"],
                     help="run a small fixed case of one kernel family and exit (for ncu captures)")
-    ap.add_argument("--kernel", default=None, help="--profile-case: pin a kernel family by name, e.g. U8Tmem")
+    ap.add_argument("--kernel", default=None, help="--profile-case: pin a kernel family by name, e.g. U8Ring")
     ap.add_argument("--m", type=int, default=1, help="rows of the activation in --profile-case")
     ap.add_argument("--n", type=int, default=4096, help="weight rows in --profile-case u8")
     args = ap.parse_args()

@@ -75,11 +75,9 @@ enum {
   ADR_KERNEL_U8_SIMT = 6,     /* any m; thread-per-output restatement (slow)         */
   ADR_KERNEL_U8_STREAM = 7,   /* m <= 16: bulk-copy staged, cluster split-k, register-fed MMA */
   ADR_KERNEL_U8_RING = 8,     /* m <= 16, block 64/128: persistent CTAs, TMA ring, scale applied per group */
-  ADR_KERNEL_U8_TMEM = 9,     /* m <= 16, block 64/128: weights converted into tensor memory, tcgen05.mma,
-                                 cluster split-k; scale applied per group */
-  ADR_KERNEL_F16_TC_GATHER = 10, /* tcgen05.mma behind loader warps that gather operands of any stride
-                                    or alignment into the swizzled stage layout (views TMA cannot describe) */
-  ADR_KERNEL_U8_TS = 11       /* m > 32, p % 64 == 0, block % 64 == 0: weights dequantised into tensor
+  ADR_KERNEL_F16_TC_GATHER = 9, /* tcgen05.mma behind loader warps that gather operands of any stride
+                                   or alignment into the swizzled stage layout (views TMA cannot describe) */
+  ADR_KERNEL_U8_TS = 10       /* m > 32, p % 64 == 0, block % 64 == 0: weights dequantised into tensor
                                  memory (A operand), 256 tokens per tcgen05.mma */
 };
 
@@ -99,8 +97,6 @@ int adr_force_kernel(adr_ctx* ctx, int kernel);
 /* Tuning knobs for A/B runs; value 0 restores the planner's own choice.
  *   "u8_split": cluster size (k-split) of the streaming u8 kernel, 1/2/4/8
  *   "u8_rows":  weight rows per CTA of the streaming u8 kernel, 32/64
- *   "u8_tiles": k-tiles (of 128) per ring slot of the tensor-memory u8 decode kernel, 1/2/4/8: one
- *               copy then takes that many times 128 contiguous bytes of every weight row
  *   "tc_bn":    N-tile of the tensor-core fp16 kernel, 32/64/128/256
  *   "tc_split": cluster size (k-split) of the tensor-core fp16 kernel, 1/2/4/8
  *   "pdl":      1 = launch the u8 streaming kernel with programmatic dependent launch: it
