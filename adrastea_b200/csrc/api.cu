@@ -157,6 +157,9 @@ int adr_set_tunable(adr_ctx* ctx, const char* name, int value) {
   else if (!strcmp(name, "pdl")) ctx->tune_pdl = value;
   else if (!strcmp(name, "u8_exact")) ctx->tune_u8_exact = value;
   else if (!strcmp(name, "wait_ms")) ctx->tune_wait_ms = value;
+  else if (!strcmp(name, "pdl_guard")) ctx->tune_pdl_guard = value;
+  else if (!strcmp(name, "u8_cps_m")) ctx->tune_u8_cps_m = value;
+  else if (!strcmp(name, "u8_cps_x4")) ctx->tune_u8_cps_x4 = value;
   else return ADR_ERR_INVALID;
   return ADR_OK;
 }

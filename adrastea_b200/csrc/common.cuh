@@ -73,6 +73,11 @@ struct adr_ctx {
   std::atomic<int> tune_tc_split{0};
   std::atomic<int> tune_pdl{0};      // programmatic dependent launch of the decode and row kernels
   std::atomic<int> tune_wait_ms{0};  // limit of the peer waits in milliseconds (0: about a second)
+  std::atomic<int> tune_u8_cps_m{2}, tune_u8_cps_x4{16};
+  std::atomic<int> tune_pdl_guard{3};  // which SM-filling launches end a chain of early starts (bit 0: two CTAs per SM, bit 1: one large CTA)
+  // the last launch whose CTAs left no room beside them on an SM: its number and its stream
+  std::atomic<unsigned long long> fill_launch{~0ull};
+  std::atomic<uintptr_t> fill_stream{0};
 };
 
 namespace adr {

@@ -116,7 +116,7 @@ struct RingParams {
 // nothing is loaded before griddepcontrol.wait.
 // FUSE: compiles in the optional rms_norm of the activations and the fused all-reduce; the plain
 // product uses the instantiation without them (they cost registers and 6 % of its speed).
-template <int MT, int NCW, bool HAS_ZERO, bool PDL, bool XR, bool FUSE>
+template <int MT, int NCW, bool HAS_ZERO, bool PDL, bool XR, bool FUSE, bool SUMS_IN_LOOP>
 __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     u8_ring_kernel(const __grid_constant__ CUtensorMap wmap, RingParams p) {
   constexpr int TOK = 8 * MT;
@@ -225,6 +225,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     } else {
       // fill the ring before waiting for the previous kernel: these loads touch only weights
       for (; q < total_stages && q < p.NS; ++q) issue();
+      // (Asking here for the next stages to be brought into L2 while the ring is full was tried
+      // and lost 1-7 %: the requests compete with the launch before, which is still streaming.)
       if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
       if (lane == 0) mbar_expect_tx(xbar, (unsigned)(a.m * a.p * 2));
       __syncwarp();
@@ -316,7 +318,13 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     // four accumulator chains per token block (piece x parity of the k16 step): two dependent
     // MMAs each, so that the tensor pipe's latency is overlapped within one warp
     float acc[2][2][MT][4];
-    float xs[2][MT][4];  // XR: sum of the activations over each 64-wide piece, by MMA with ones
+    // Sums of the activations over each 64-wide piece, by an MMA with an all-ones weight operand
+    // next to every weight MMA, when they are not taken from the table made once per launch.
+    // The table costs less arithmetic, but making it stands between the arrival of the
+    // activations and the first stage; which way wins depends on the token count (see the
+    // launcher).
+    constexpr bool XS_INLINE = XR || SUMS_IN_LOOP;
+    float xs[2][MT][4];
     auto compute_piece = [&](const uint8_t* wrow, int xoff, auto piece_tag) {
       constexpr int H = decltype(piece_tag)::value;
       const uint4 qa = *reinterpret_cast<const uint4*>(wrow);
@@ -342,7 +350,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
           const uint32_t b0 = xw[i][2 * w], b1 = xw[i][2 * w + 1];
           if (w < 2) mma_16816_z(acc[H][w & 1][i], A0, A1, A2, A3, b0, b1);
           else mma_16816(acc[H][w & 1][i], A0, A1, A2, A3, b0, b1);
-          if constexpr (XR) {
+          if constexpr (XS_INLINE) {
             constexpr uint32_t ONES = 0x3C003C00u;  // (1.0, 1.0)
             if (w == 0) mma_16816_z(xs[H][i], ONES, ONES, ONES, ONES, b0, b1);
             else mma_16816(xs[H][i], ONES, ONES, ONES, ONES, b0, b1);
@@ -352,7 +360,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     };
     // ---- the activation sums, once per launch: an MMA with an all-ones weight operand leaves
     // sum_k x[k][token] in the accumulator layout; warp cw takes tiles cw, cw + NCW, ...
-    if constexpr (!XR) {
+    if constexpr (!XS_INLINE) {
       constexpr uint32_t ONES = 0x3C003C00u;  // (1.0, 1.0)
       if (MT == 1 && a.m <= 4) {
         // few tokens: plain sums are quicker than the chain of MMAs.  Eight lanes share one
@@ -488,7 +496,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
 #pragma unroll
             for (int i = 0; i < MT; ++i) {
               float2 xv;
-              if constexpr (XR) {
+              if constexpr (XS_INLINE) {
                 xv = make_float2(xs[h0][i][0], xs[h0][i][1]);
                 if (h0 != h1) xv.x += xs[h1][i][0], xv.y += xs[h1][i][1];
               } else {
@@ -668,7 +676,8 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   }
   int ns;
   pl.cps = 1;
-  if (a.m <= 2 && units >= 4 * sms && ns_half >= 4) {
+  const int cps_m = ctx->tune_u8_cps_m.load(), cps_x4 = ctx->tune_u8_cps_x4.load();
+  if (a.m <= cps_m && units * 4 >= cps_x4 * sms && ns_half >= 4) {
     pl.cps = 2;
     ns = ns_half;
   } else if (ns_half >= half_min) {
@@ -713,10 +722,10 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   return true;
 }
 
-template <int MT, bool Z, bool PDL, int NCW, bool XR, bool FUSE>
+template <int MT, bool Z, bool PDL, int NCW, bool XR, bool FUSE, bool XSI>
 int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl,
                   const RingArFuse* ar) {
-  auto kfn = u8_ring_kernel<MT, NCW, Z, PDL, XR, FUSE>;
+  auto kfn = u8_ring_kernel<MT, NCW, Z, PDL, XR, FUSE, XSI>;
   cudaError_t e;
   if (int rc0 = opt_in_smem(ctx, kfn, 226 * 1024); rc0 != ADR_OK) return rc0;
   // weights as (k within tile, row, k-tile): a box of 128 x 16 x 8 lands as eight tiles of
@@ -767,21 +776,48 @@ int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = PDL ? 1 : 0;
+  // CTAs of half an SM's size rely on landing one per SM, each beside a CTA of the launch
+  // before.  Behind a launch that filled whole SMs (two CTAs each, or one large CTA) they would
+  // start as those SMs drain, two to an SM on the first half of the SMs to finish, and every
+  // later launch of the chain would inherit that placement: each one running on half the SMs,
+  // a quarter slower.  So the first such launch behind a filling launch gives up its early
+  // start and begins on an empty GPU, which spreads its CTAs one per SM again.
+  const int guard = ctx->tune_pdl_guard.load();
+  const int fill_kind = pl.cps == 2 ? 1 : (pl.smem > 114 * 1024 ? 2 : 0);
+  bool early = PDL;
+  if (PDL && fill_kind == 0 && ctx->fill_launch.load() == ctx->launches.load() &&
+      ctx->fill_stream.load() == reinterpret_cast<uintptr_t>(stream))
+    early = false;
+  cfg.numAttrs = early ? 1 : 0;
   e = cudaLaunchKernelEx(&cfg, kfn, wmap, p);
   if (e != cudaSuccess) {
     ctx->last_cuda_error = (int)e;
     return ADR_ERR_CUDA;
   }
-  return after_launch(ctx);
+  const int rc2 = after_launch(ctx);
+  if (fill_kind & guard) {
+    ctx->fill_launch = ctx->launches.load();
+    ctx->fill_stream = reinterpret_cast<uintptr_t>(stream);
+  }
+  return rc2;
 }
 
 template <int MT, bool Z, bool PDL, int NCW, bool XR>
 int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl,
                   const RingArFuse* ar) {
+  // Two to eight tokens: the activation sums ride along in the main loop (measured 3-9 %
+  // quicker than making the table first); one token, or more than eight, make the table (3 %
+  // quicker: the loop is the bottleneck there).
+  if constexpr (MT == 1 && !XR) {
+    if (a.m >= 2) {
+      if (ar != nullptr || a.norm_w != nullptr)
+        return launch_ring_f<MT, Z, PDL, NCW, XR, true, true>(ctx, stream, a, pl, ar);
+      return launch_ring_f<MT, Z, PDL, NCW, XR, false, true>(ctx, stream, a, pl, ar);
+    }
+  }
   if (ar != nullptr || a.norm_w != nullptr)
-    return launch_ring_f<MT, Z, PDL, NCW, XR, true>(ctx, stream, a, pl, ar);
-  return launch_ring_f<MT, Z, PDL, NCW, XR, false>(ctx, stream, a, pl, ar);
+    return launch_ring_f<MT, Z, PDL, NCW, XR, true, false>(ctx, stream, a, pl, ar);
+  return launch_ring_f<MT, Z, PDL, NCW, XR, false, false>(ctx, stream, a, pl, ar);
 }
 
 }  // namespace

@@ -304,6 +304,22 @@ class GpuKernels:
                                             m, p, n, block_size, beta)
         self._check(rc)
 
+    def matmul_nt_fp16u8_ws(self, output: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor,
+                            scales: torch.Tensor, block_size: int, workspace: torch.Tensor,
+                            beta: float = 0.0, zeros: torch.Tensor | None = None, stream=None):
+        """adr_matmul_nt_fp16u8_ws: the same product with a scratch buffer to expand weight panels
+        into (any contiguous CUDA tensor; its bytes are clobbered)."""
+        m, p = lhs.shape
+        n = rhs.shape[0]
+        assert rhs.shape == (n, p) and output.shape == (m, n) and scales.shape == (n, p // block_size)
+        for t in (output, lhs, rhs, scales, workspace) + ((zeros,) if zeros is not None else ()):
+            assert t.is_contiguous() and t.is_cuda
+        rc = self._lib.adr_matmul_nt_fp16u8_ws(
+            self._ctx, _stream_handle(stream), output.data_ptr(), lhs.data_ptr(), rhs.data_ptr(),
+            scales.data_ptr(), zeros.data_ptr() if zeros is not None else None, m, p, n, block_size,
+            beta, workspace.data_ptr(), workspace.numel() * workspace.element_size())
+        self._check(rc)
+
     def matmul_nt_f16(self, output: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor,
                       beta: float = 0.0, stream=None):
         """matmul_nt_wmma_128x64x64 / matmul_nt_wmma_16x128x256

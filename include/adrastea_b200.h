@@ -182,6 +182,22 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
                          int n, int block_size, float beta);
 
 /*
+ * The same product as adr_matmul_nt_fp16u8 for callers with scratch memory to lend (no
+ * counterpart in the reference, whose kernels take none): from a few thousand rows on, panels
+ * of weight rows are dequantised to fp16 (the bit-exact fp16-rounded weights of
+ * matmul_nt_wmma_16x128x256_fp16u8.cu:5-7) into `workspace` and multiplied by the fp16
+ * tensor-core GEMM, which at that size outruns the dequantising GEMM by about a third.
+ * `workspace` is device memory of `workspace_bytes` bytes, 16-byte aligned, at least 256 * p
+ * bytes (128 weight rows as fp16); 32 MiB or more lets every panel be as large as the kernel
+ * wants.  Its contents are scratch: undefined before and after the call.  With fewer rows, or a
+ * NULL or too small workspace, the call is adr_matmul_nt_fp16u8.
+ */
+int adr_matmul_nt_fp16u8_ws(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                            const uint8_t* rhs, const void* scales, const void* zeros, int m, int p,
+                            int n, int block_size, float beta, void* workspace,
+                            size_t workspace_bytes);
+
+/*
  * Replaces kernels matmul_nt_wmma_128x64x64 (matmul_nt_wmma_128x64x64.cu:8-78)
  * and matmul_nt_wmma_16x128x256 (matmul_nt_wmma_16x128x256.cu:8-68), same
  * parameter list:  out[m,n] = lhs[m,p] . rhs[n,p]^T + beta * out, contiguous
