@@ -33,6 +33,8 @@ SIGNATURES = {
                                       _c_int, C.c_float]),
     "adr_matmul_nt_fp16u8_ws": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int,
                                          _c_int, C.c_float, _vp, C.c_size_t]),
+    "adr_matmul_nt_fp16u8_noalloc": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int,
+                                              _c_int, _c_int, C.c_float]),
     "adr_matmul_nt_f16": (_c_int, [_vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, C.c_float]),
     "adr_dequantize_absmax_uint8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),
     "adr_quantize_absmax_uint8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),

@@ -136,6 +136,7 @@ const char* adr_strerror(int code) {
     case ADR_ERR_CUDA: return "CUDA call failed";
     case ADR_ERR_DEVICE: return "a kernel's bounded wait ran out";
     case ADR_ERR_NCCL: return "NCCL call failed";
+    case ADR_ERR_TOO_LARGE: return "operands exceed the entry point's built-in scratch buffer";
     default: return "unknown error";
   }
 }

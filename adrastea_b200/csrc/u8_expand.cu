@@ -7,6 +7,8 @@
 //   out[m,n] = lhs[m,p] . deq(rhs[n,p])^T + beta * out
 #include "tma.cuh"
 
+#include <mutex>
+
 namespace adr {
 
 namespace {
@@ -50,6 +52,34 @@ int check_u8(const adr_ctx* ctx, const void* out, const void* lhs, const void* r
   return ADR_OK;
 }
 
+// Scratch for the entry point that may not allocate: one array per device, part of the loaded
+// module, so it exists without any allocation call.  16 MiB holds 128 weight rows (the smallest
+// panel) of up to 65536 columns as fp16.
+constexpr size_t BUILTIN_SCRATCH_BYTES = 16u << 20;
+constexpr int BUILTIN_MAX_P = (int)(BUILTIN_SCRATCH_BYTES / 2 / 128);
+static __device__ __align__(256) unsigned char g_builtin_scratch[BUILTIN_SCRATCH_BYTES];
+
+constexpr int MAX_DEVICES = 64;
+std::mutex g_builtin_mu;
+void* g_builtin_ptr[MAX_DEVICES] = {};
+
+// The array's device address, looked up once per device (the current device is the context's).
+int builtin_scratch(adr_ctx* ctx, __half** ptr) {
+  if (ctx->device < 0 || ctx->device >= MAX_DEVICES) return ADR_ERR_INVALID;
+  std::lock_guard<std::mutex> lock(g_builtin_mu);
+  if (!g_builtin_ptr[ctx->device]) {
+    void* a = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&a, g_builtin_scratch);
+    if (e != cudaSuccess || !a) {
+      ctx->last_cuda_error = (int)e;
+      return ADR_ERR_CUDA;
+    }
+    g_builtin_ptr[ctx->device] = a;
+  }
+  *ptr = static_cast<__half*>(g_builtin_ptr[ctx->device]);
+  return ADR_OK;
+}
+
 }  // namespace
 
 }  // namespace adr
@@ -73,6 +103,25 @@ extern "C" int adr_matmul_nt_fp16u8_ws(adr_ctx* ctx, adr_stream stream, void* ou
   U8Args a{(__half*)out, (const __half*)lhs, rhs, (const __half*)scales, (const __half*)zeros,
            m, p, n, block_size, beta};
   rc = expand_matmul(ctx, (cudaStream_t)stream, a, (__half*)workspace, workspace_bytes / 2);
+  if (rc == ADR_OK) ctx->last_kernel = ADR_KERNEL_F16_TC;
+  return rc;
+}
+
+extern "C" int adr_matmul_nt_fp16u8_noalloc(adr_ctx* ctx, adr_stream stream, void* out,
+                                            const void* lhs, const uint8_t* rhs, const void* scales,
+                                            const void* zeros, int m, int p, int n, int block_size,
+                                            float beta) {
+  int rc = check_u8(ctx, out, lhs, rhs, scales, m, p, n, block_size);
+  if (rc != ADR_OK) return rc;
+  if (p > BUILTIN_MAX_P) return ADR_ERR_TOO_LARGE;  // 128 rows of p columns exceed the array
+  if (p % 8 != 0 || n % 8 != 0 || (reinterpret_cast<uintptr_t>(out) & 15u)) return ADR_ERR_SHAPE;
+  DeviceGuard guard(ctx);
+  __half* scratch = nullptr;
+  rc = builtin_scratch(ctx, &scratch);
+  if (rc != ADR_OK) return rc;
+  U8Args a{(__half*)out, (const __half*)lhs, rhs, (const __half*)scales, (const __half*)zeros,
+           m, p, n, block_size, beta};
+  rc = expand_matmul(ctx, (cudaStream_t)stream, a, scratch, BUILTIN_SCRATCH_BYTES / 2);
   if (rc == ADR_OK) ctx->last_kernel = ADR_KERNEL_F16_TC;
   return rc;
 }

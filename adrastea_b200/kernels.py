@@ -320,6 +320,22 @@ class GpuKernels:
             beta, workspace.data_ptr(), workspace.numel() * workspace.element_size())
         self._check(rc)
 
+    def matmul_nt_fp16u8_noalloc(self, output: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor,
+                                 scales: torch.Tensor, block_size: int, beta: float = 0.0,
+                                 zeros: torch.Tensor | None = None, stream=None):
+        """adr_matmul_nt_fp16u8_noalloc: the product of matmul_nt_fp16u8_ws over the library's
+        built-in 16 MiB scratch array (one per device: calls that overlap in time race on it)."""
+        m, p = lhs.shape
+        n = rhs.shape[0]
+        assert rhs.shape == (n, p) and output.shape == (m, n) and scales.shape == (n, p // block_size)
+        for t in (output, lhs, rhs, scales) + ((zeros,) if zeros is not None else ()):
+            assert t.is_contiguous() and t.is_cuda
+        rc = self._lib.adr_matmul_nt_fp16u8_noalloc(
+            self._ctx, _stream_handle(stream), output.data_ptr(), lhs.data_ptr(), rhs.data_ptr(),
+            scales.data_ptr(), zeros.data_ptr() if zeros is not None else None, m, p, n, block_size,
+            beta)
+        self._check(rc)
+
     def matmul_nt_f16(self, output: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor,
                       beta: float = 0.0, stream=None):
         """matmul_nt_wmma_128x64x64 / matmul_nt_wmma_16x128x256

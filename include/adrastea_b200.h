@@ -42,7 +42,8 @@ enum {
   ADR_ERR_UNSUPPORTED = 3, /* op the reference has no device code for         */
   ADR_ERR_CUDA = 4,        /* a CUDA call failed; see adr_last_cuda_error     */
   ADR_ERR_DEVICE = 5,      /* a kernel reported a bounded wait that ran out   */
-  ADR_ERR_NCCL = 6
+  ADR_ERR_NCCL = 6,
+  ADR_ERR_TOO_LARGE = 7    /* operands exceed a fixed built-in buffer (see the entry point) */
 };
 
 /* matmul.cu:26-36, kernels.rs:80-139 */
@@ -196,6 +197,29 @@ int adr_matmul_nt_fp16u8_ws(adr_ctx* ctx, adr_stream stream, void* out, const vo
                             const uint8_t* rhs, const void* scales, const void* zeros, int m, int p,
                             int n, int block_size, float beta, void* workspace,
                             size_t workspace_bytes);
+
+/*
+ * adr_matmul_nt_fp16u8_ws without a workspace argument and without any allocation: the weight
+ * panels are expanded into a 16 MiB array that is part of the library itself (one per device
+ * and process).  No counterpart in the reference.  It is for callers that have no device
+ * memory of their own to lend and may not ask for any at this point: every byte of the device
+ * belongs to another allocator, or the call sits in a loop where cudaMalloc and cudaFree
+ * (which synchronise the whole device) are not acceptable.  The call issues no allocating or
+ * freeing CUDA call.  It always takes the expansion path (dequantise a panel of weight rows,
+ * fp16 tensor-core GEMM), whatever m is, so it pays off from a few thousand rows on.
+ *   - p <= 65536 (128 weight rows of p fp16 columns must fit the array), else
+ *     ADR_ERR_TOO_LARGE, and nothing is launched.  p % 8 == 0, n % 8 == 0 and `out`, `lhs`,
+ *     `rhs` 16-byte aligned, else ADR_ERR_SHAPE.  A panel is 16 MiB / (2 p) weight rows, so
+ *     long rows mean many small GEMMs: with 32 MiB to lend, adr_matmul_nt_fp16u8_ws is faster.
+ *   - The first call on a device looks up the array's address (cudaGetSymbolAddress): make
+ *     that first call before any stream capture begins.
+ *   - The array is shared by all calls on the device.  It keeps the last call's panels, and
+ *     two calls in flight at the same time (other streams, other threads) overwrite each
+ *     other's panels: keep the calls on one stream or order them with events.
+ */
+int adr_matmul_nt_fp16u8_noalloc(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                                 const uint8_t* rhs, const void* scales, const void* zeros,
+                                 int m, int p, int n, int block_size, float beta);
 
 /*
  * Replaces kernels matmul_nt_wmma_128x64x64 (matmul_nt_wmma_128x64x64.cu:8-78)
