@@ -144,7 +144,7 @@ const char* adr_strerror(int code) {
 int adr_last_cuda_error(const adr_ctx* ctx) { return ctx ? ctx->last_cuda_error.load() : 0; }
 
 int adr_force_kernel(adr_ctx* ctx, int kernel) {
-  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_U8_TS) return ADR_ERR_INVALID;
+  if (!ctx || kernel < ADR_KERNEL_AUTO || kernel > ADR_KERNEL_U8_KSPLIT) return ADR_ERR_INVALID;
   ctx->forced_kernel = kernel;
   return ADR_OK;
 }
@@ -159,6 +159,8 @@ int adr_set_tunable(adr_ctx* ctx, const char* name, int value) {
   else if (!strcmp(name, "u8_exact")) ctx->tune_u8_exact = value;
   else if (!strcmp(name, "wait_ms")) ctx->tune_wait_ms = value;
   else if (!strcmp(name, "pdl_guard")) ctx->tune_pdl_guard = value;
+  else if (!strcmp(name, "ks_clusters")) ctx->tune_ks_clusters = value;
+  else if (!strcmp(name, "ks_stages")) ctx->tune_ks_stages = value;
   else if (!strcmp(name, "u8_cps_m")) ctx->tune_u8_cps_m = value;
   else if (!strcmp(name, "u8_cps_x4")) ctx->tune_u8_cps_x4 = value;
   else return ADR_ERR_INVALID;
@@ -235,6 +237,9 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
     else if (m > 32 && u8_tc_supports(ctx, a)) kernel = ADR_KERNEL_U8_TC;
     else if (p % 64 != 0) kernel = m <= 4 ? ADR_KERNEL_U8_GEMV : ADR_KERNEL_U8_SIMT;
     else if (!ctx->tune_u8_exact && !ctx->tune_u8_split && !ctx->tune_u8_rows &&
+             (a16.m >= 5 || (a16.m >= 4 && p >= 8192)) && u8_ksplit_supports(ctx, a16))
+      kernel = ADR_KERNEL_U8_KSPLIT;  // from five tokens on (four at k = 8192) the cluster split wins
+    else if (!ctx->tune_u8_exact && !ctx->tune_u8_split && !ctx->tune_u8_rows &&
              u8_ring_supports(ctx, a16))
       kernel = ADR_KERNEL_U8_RING;
     else if (u8_stream_supports(ctx, a16)) kernel = ADR_KERNEL_U8_STREAM;
@@ -263,6 +268,17 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
         c.lhs = a.lhs + (size_t)r0 * p;
         c.out = a.out + (size_t)r0 * n;
         rc = launch_u8_ring(ctx, st, c);
+      }
+      break;
+    }
+    case ADR_KERNEL_U8_KSPLIT: {
+      rc = ADR_OK;
+      for (int r0 = 0; r0 < m && rc == ADR_OK; r0 += 16) {  // one pass per 16 tokens
+        U8Args c = a;
+        c.m = (m - r0 < 16) ? m - r0 : 16;
+        c.lhs = a.lhs + (size_t)r0 * p;
+        c.out = a.out + (size_t)r0 * n;
+        rc = launch_u8_ksplit(ctx, st, c);
       }
       break;
     }

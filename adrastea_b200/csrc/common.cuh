@@ -74,6 +74,7 @@ struct adr_ctx {
   std::atomic<int> tune_pdl{0};      // programmatic dependent launch of the decode and row kernels
   std::atomic<int> tune_wait_ms{0};  // limit of the peer waits in milliseconds (0: about a second)
   std::atomic<int> tune_u8_cps_m{2}, tune_u8_cps_x4{16};
+  std::atomic<int> tune_ks_clusters{0}, tune_ks_stages{0};  // cluster k-split kernel: clusters in the grid, ring stages
   std::atomic<int> tune_pdl_guard{3};  // which SM-filling launches end a chain of early starts (bit 0: two CTAs per SM, bit 1: one large CTA)
   // the last launch whose CTAs left no room beside them on an SM: its number and its stream
   std::atomic<unsigned long long> fill_launch{~0ull};
@@ -251,6 +252,8 @@ struct RingArFuse {
 };
 int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingArFuse* ar = nullptr);
 bool u8_ring_supports(const adr_ctx* ctx, const U8Args& a);
+int launch_u8_ksplit(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
+bool u8_ksplit_supports(const adr_ctx* ctx, const U8Args& a);
 int launch_u8_tc(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 int launch_u8_ts(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 bool u8_ts_supports(const adr_ctx* ctx, const U8Args& a);

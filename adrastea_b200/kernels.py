@@ -66,6 +66,7 @@ class Kernel(enum.IntEnum):
     U8Ring = 8
     F16TcGather = 9
     U8Ts = 10
+    U8KSplit = 11
 
 
 @dataclass(frozen=True)

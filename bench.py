@@ -566,13 +566,14 @@ def run_ours(args):
     ms_runs = [timed(replay, args.steps) for _ in range(args.repeats)]
     ms = float(np.median(ms_runs))
     # per-M breakdown (each its own graph and event pair)
-    per_m = {}
+    per_m, per_m_kernel = {}, {}
     for m in MS:
         def one_m(m=m):
             for layer in weights:
                 for n, q, s, _ in layer:
                     kern.matmul_nt_fp16u8(outs[(m, n)], xs[m], q, s, BS)
         rm, gm = graphed(one_m)
+        per_m_kernel[f"M={m}"] = kern.last_kernel().name
         t = float(np.median([timed(rm, args.steps) for _ in range(max(3, args.repeats // 2))]))
         b = LAYERS * sum(gemv_bytes(m, n) for n in NS)
         per_m[f"M={m}"] = round(b * args.steps / (t * 1e-3) / 1e9, 1)
@@ -626,7 +627,8 @@ def run_ours(args):
                      "traffic_unit": "bytes per launch (ncu capture of a small launch, scaled)",
                      "traffic_kernel": ratio_kernel,
                      "peak_kind": f"of {peak_kind}",
-                     "kernel": kernel_name, "per_m_gbs": per_m,
+                     "kernel": "+".join(sorted(set(per_m_kernel.values()))) or kernel_name,
+                     "per_m_gbs": per_m, "per_m_kernel": per_m_kernel,
                      "bytes_per_launch_avg": bytes_step / max(launches_per_step, 1)},
         "clocks": clocks,
         "note": "N = 1 runs configs[1] (weak scaling: every rank its own copy); N > 1 runs configs[4] "

@@ -78,8 +78,11 @@ enum {
   ADR_KERNEL_U8_RING = 8,     /* m <= 16, block 64/128: persistent CTAs, TMA ring, scale applied per group */
   ADR_KERNEL_F16_TC_GATHER = 9, /* tcgen05.mma behind loader warps that gather operands of any stride
                                    or alignment into the swizzled stage layout (views TMA cannot describe) */
-  ADR_KERNEL_U8_TS = 10       /* m > 32, p % 64 == 0, block % 64 == 0: weights dequantised into tensor
+  ADR_KERNEL_U8_TS = 10,      /* m > 32, p % 64 == 0, block % 64 == 0: weights dequantised into tensor
                                  memory (A operand), 256 tokens per tcgen05.mma */
+  ADR_KERNEL_U8_KSPLIT = 11   /* m <= 16, p = 1024 * (2..8), block 64/128: k split over a thread-block
+                                 cluster, activations in registers, partial sums through
+                                 distributed shared memory */
 };
 
 /*

@@ -192,6 +192,8 @@ def u8_kernels_for(c):
             ks.append(Kernel.U8Stream)
             if c.block_size in (64, 128) and c.n >= 16 and (c.p // c.block_size) % 2 == 0:
                 ks.append(Kernel.U8Ring)
+                if c.p % 1024 == 0 and 2 <= c.p // 1024 <= 8:
+                    ks.append(Kernel.U8KSplit)
     if c.p % 16 == 0:
         ks.append(Kernel.U8Tc)
     if c.p % 64 == 0 and c.block_size % 64 == 0:
@@ -267,8 +269,12 @@ def test_u8_ring_kernel(kernels, pdl):
             kernels.force_kernel(Kernel.Auto)
             o = dev(out0.copy())
             kernels.matmul_nt_fp16u8(o, xd, qd, sd, bs, 0.5, zd)
-            assert kernels.last_kernel() == Kernel.U8Ring
-            assert np.array_equal(o.cpu().numpy().view(np.uint16), res[0].view(np.uint16))
+            if p % 1024 == 0 and 2 <= p // 1024 <= 8 and (m >= 5 or (m >= 4 and p >= 8192)):
+                assert kernels.last_kernel() == Kernel.U8KSplit  # the cluster split takes these
+                assert oracle.max_rel_err(o.cpu().numpy(), want) <= 2e-3
+            else:
+                assert kernels.last_kernel() == Kernel.U8Ring
+                assert np.array_equal(o.cpu().numpy().view(np.uint16), res[0].view(np.uint16))
             kernels.set_tunable("u8_exact", 1)
             o = dev(out0.copy())
             kernels.matmul_nt_fp16u8(o, xd, qd, sd, bs, 0.5, zd)
@@ -279,6 +285,49 @@ def test_u8_ring_kernel(kernels, pdl):
     finally:
         kernels.set_tunable("pdl", 0)
         kernels.set_tunable("u8_exact", 0)
+        kernels.force_kernel(Kernel.Auto)
+
+
+@pytest.mark.parametrize("pdl", [0, 1])
+def test_u8_cluster_ksplit_kernel(kernels, pdl):
+    """The cluster k-split kernel: every cluster size it takes (k = 2048 .. 8192), ragged n, fewer
+    units than clusters and many more, both block sizes, both token blocks, zero points, beta,
+    several launches back to back (inbox slots and credits in rotation); thrice for determinism."""
+    rng = np.random.default_rng(177 + pdl)
+    try:
+        kernels.set_tunable("pdl", pdl)
+        kernels.force_kernel(Kernel.U8KSplit)
+        for m, p, n, bs, zp in ((1, 4096, 200, 128, False), (7, 2048, 333, 64, False),
+                                (16, 4096, 4096, 128, True), (9, 8192, 97, 64, True),
+                                (4, 4096, 11008, 128, False), (16, 8192, 1000, 128, False),
+                                (3, 3072, 16, 64, False), (16, 5120, 2500, 64, True),
+                                (12, 7168, 640, 128, False)):
+            x = rng.standard_normal((m, p)).astype(np.float16)
+            q = rng.integers(0, 256, (n, p), dtype=np.uint8)
+            s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
+            z = rng.uniform(120, 136, (n, p // bs)).astype(np.float16) if zp else None
+            out0 = (rng.standard_normal((m, n)) * 0.5).astype(np.float16)
+            want = oracle.matmul_nt_fp16u8(x, q, s, bs, 0.5, out0, z)
+            xd, qd, sd, zd = dev(x), dev(q), dev(s), dev(z) if zp else None
+            res = []
+            for _ in range(3):
+                o = dev(out0.copy())
+                kernels.matmul_nt_fp16u8(o, xd, qd, sd, bs, 0.5, zd)
+                kernels.device_status()
+                res.append(o.cpu().numpy())
+            assert kernels.last_kernel() == Kernel.U8KSplit
+            assert np.array_equal(res[0].view(np.uint16), res[1].view(np.uint16))
+            assert np.array_equal(res[0].view(np.uint16), res[2].view(np.uint16))
+            assert oracle.max_rel_err(res[0], want) <= 2e-3, (m, p, n, oracle.max_rel_err(res[0], want))
+        # shapes it does not take are refused, not mangled
+        x = torch.zeros((1, 1024), dtype=torch.float16, device="cuda")
+        q = torch.zeros((64, 1024), dtype=torch.uint8, device="cuda")
+        s = torch.ones((64, 8), dtype=torch.float16, device="cuda")
+        o = torch.zeros((1, 64), dtype=torch.float16, device="cuda")
+        with pytest.raises(AdrError):
+            kernels.matmul_nt_fp16u8(o, x, q, s, 128)
+    finally:
+        kernels.set_tunable("pdl", 0)
         kernels.force_kernel(Kernel.Auto)
 
 
@@ -579,7 +628,7 @@ def fp16_spacing(v):
     return 2.0 ** (np.floor(np.log2(v)) - 10)
 
 
-@pytest.mark.parametrize("kernel", [Kernel.U8Ring, Kernel.U8Stream, Kernel.Auto])
+@pytest.mark.parametrize("kernel", [Kernel.U8Ring, Kernel.U8Stream, Kernel.U8KSplit, Kernel.Auto])
 def test_u8_decode_kernels_follow_the_unrounded_reference_form(kernels, kernel):
     """The decode kernels claim the arithmetic of matmul_nt_fp16u8.cu:13-23 (weights not rounded
     to fp16).  Held to it here: against the oracle's faithful restatement of that kernel and,

@@ -216,7 +216,11 @@ def test_rms_norm_fused_into_the_decode_gemv(kernels, m, p, n, bs):
     xn = torch.zeros_like(x)
     kernels.rms_norm(TensorView.of(xn), TensorView.of(x), TensorView.of(w), 1e-5)
     two = dev(out0.copy())
-    kernels.matmul_nt_fp16u8(two, xn, q, s, bs, 0.5)
+    kernels.force_kernel(Kernel.U8Ring)  # the fused form lives in the ring kernel: same bits as its plain form
+    try:
+        kernels.matmul_nt_fp16u8(two, xn, q, s, bs, 0.5)
+    finally:
+        kernels.force_kernel(Kernel.Auto)
     assert kernels.last_kernel() == Kernel.U8Ring
     one = dev(out0.copy())
     kernels.rms_norm_matmul_nt_fp16u8(one, x, w, 1e-5, q, s, bs, 0.5)
