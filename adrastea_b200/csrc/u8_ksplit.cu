@@ -37,6 +37,7 @@ constexpr int KS_TILE_BYTES = 16 * 128;               // 16 rows x 128 k
 constexpr int KS_W_BYTES = 8 * KS_TILE_BYTES;         // 16 KB: eight tiles, one per consumer warp
 constexpr int KS_STAGE_BYTES = KS_W_BYTES + 1024;     // + scales and zero points
 constexpr int KS_MAX_STAGES = 6;
+constexpr int KS_NR = 2;                              // partial-sum buffers in rotation
 constexpr int KS_INB = 2;                             // inbox slots per owner
 constexpr int KS_MAX_S = 8;
 constexpr int KS_THREADS = 10 * 32;                   // producer, eight consumers, reducer
@@ -162,13 +163,14 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
     return;
   }
   uint8_t* ring = smem_raw;
-  float* red = reinterpret_cast<float*>(ring + (size_t)p.NS * KS_STAGE_BYTES);  // [NS][8][TOK][KS_RLD]
-  float* inbox = red + (size_t)p.NS * 8 * TOK * KS_RLD;                           // [KS_INB][S][16 * TOK]
+  float* red = reinterpret_cast<float*>(ring + (size_t)p.NS * KS_STAGE_BYTES);  // [KS_NR][8][TOK][KS_RLD]
+  float* inbox = red + (size_t)KS_NR * 8 * TOK * KS_RLD;                          // [KS_INB][S][16 * TOK]
   uint64_t* full = reinterpret_cast<uint64_t*>(inbox + (size_t)KS_INB * S * 16 * TOK);
   uint64_t* empty = full + KS_MAX_STAGES;
   uint64_t* inbox_full = empty + KS_MAX_STAGES;         // [KS_INB]: S partial results (as bytes) per use
   uint64_t* credit = inbox_full + KS_INB;               // [KS_MAX_S][KS_INB]: owner o took my push
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(credit + KS_MAX_S * KS_INB);
+  uint64_t* red_free = credit + KS_MAX_S * KS_INB;      // [KS_NR]: the reducer has read the buffer
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(red_free + KS_NR);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rank = (int)cluster_rank();
@@ -181,7 +183,7 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
     tma_prefetch_desc(&wmap);
     for (int s = 0; s < p.NS; ++s) {
       mbar_init(&full[s], 33);  // expect_tx arrival + one cp.async arrival per producer lane
-      mbar_init(&empty[s], 9);  // the eight consumer warps and the reducer
+      mbar_init(&empty[s], 8);  // the eight consumer warps
     }
     for (int i = 0; i < KS_INB; ++i) {
       // one arrival per use, by this CTA's reducer, which also states the bytes to expect: S
@@ -190,6 +192,7 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
       if (rank + i * S < J) mbar_expect_tx(&inbox_full[i], (unsigned)(S * 16 * TOK * 4));
     }
     for (int i = 0; i < KS_MAX_S * KS_INB; ++i) mbar_init(&credit[i], 1);
+    for (int i = 0; i < KS_NR; ++i) mbar_init(&red_free[i], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -367,9 +370,16 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
           correct(cw, 0, 1);
         }
       }
-      // ---- the partial sums go into the stage's own buffer, [token][row] with rows padded to 20
-      // floats (conflict-free stores, 16-byte loads for the reducing warp), and the warp moves on
-      float* rw = red + ((size_t)s * 8 + cw) * TOK * KS_RLD;
+      // the stage is read: it may be refilled (also on failure, so that the producer can finish)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[s]);
+      // ---- the partial sums go into buffer j % KS_NR, once the reducer has read what unit
+      // j - KS_NR left there: [token][row] with rows padded to 20 floats (conflict-free stores,
+      // 16-byte loads for the reducing warp); then the warp moves on
+      const int b = j % KS_NR;
+      if (j >= KS_NR && ok)
+        ok = __all_sync(0xffffffffu, mbar_wait(&red_free[b], (unsigned)(j / KS_NR - 1) & 1u) && !*abort_flag);
+      float* rw = red + ((size_t)b * 8 + cw) * TOK * KS_RLD;
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
         rw[(i * 8 + 2 * t) * KS_RLD + pg] = d[i][0];
@@ -379,8 +389,7 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
       }
       __threadfence_block();  // the partial sums are visible before the arrival is counted
       __syncwarp();
-      ks_bar_arrive(1 + s, 9 * 32);
-      if (lane == 0) mbar_arrive(&empty[s]);  // also on failure, so that the producer can finish
+      ks_bar_arrive(1 + b, 9 * 32);
       if (++s == p.NS) s = 0, par ^= 1u;
     }
     if (!ok && lane == 0) atomicOr(p.status, 1u);
@@ -478,13 +487,13 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
     };
     int fin_j = rank;  // the next owned unit to finish
     load_old(fin_j);
-    int s = 0;
     for (int j = 0; j < J; ++j) {
-      ks_bar_sync(1 + s, 9 * 32);
+      const int b = j % KS_NR;
+      ks_bar_sync(1 + b, 9 * 32);
       float v[OPL];
 #pragma unroll
       for (int e = 0; e < OPL; ++e) v[e] = 0.0f;
-      const float* rb = red + (size_t)s * 8 * TOK * KS_RLD + tok * KS_RLD + row0;
+      const float* rb = red + (size_t)b * 8 * TOK * KS_RLD + tok * KS_RLD + row0;
 #pragma unroll
       for (int w = 0; w < 8; ++w) {
 #pragma unroll
@@ -494,7 +503,7 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
         }
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[s]);  // the buffer is read: the stage may be refilled
+      if (lane == 0) mbar_arrive(&red_free[b]);  // the buffer is read: unit j + KS_NR may use it
       const int owner = j % S, k = j / S, slot = k % KS_INB, use = k / KS_INB;
       // Own units that the cluster may be waiting for (their slots are due for reuse) first:
       // every owner does this before it waits for a slot itself, so the oldest unfinished unit
@@ -520,7 +529,6 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
       for (int e = 0; e < OPL; e += 4) st_async_f32x4(dst + e * 4, v[e], v[e + 1], v[e + 2], v[e + 3], dbar);
       // owned units whose pushes happen to be complete
       while (fin_j <= j && finish(fin_j, false)) fin_j += S;
-      if (++s == p.NS) s = 0;
     }
     for (; fin_j < J; fin_j += S) finish(fin_j, true);
     if (!ok && lane == 0) atomicOr(p.status, 1u);
@@ -548,9 +556,9 @@ bool plan_ksplit(const adr_ctx* ctx, const U8Args& a, KsPlan& pl) {
   pl.S = a.p / 1024;
   pl.Q = 0;  // chosen by the launcher, which knows how many clusters the GPU holds at once
   const size_t half = 113 * 1024;
-  const size_t per_stage = KS_STAGE_BYTES + (size_t)8 * tok * KS_RLD * 4;
-  const size_t fixed = (size_t)KS_INB * pl.S * 16 * tok * 4 +
-                       (2 * KS_MAX_STAGES + KS_INB + KS_MAX_S * KS_INB + 1) * 8;
+  const size_t per_stage = KS_STAGE_BYTES;
+  const size_t fixed = (size_t)KS_NR * 8 * tok * KS_RLD * 4 + (size_t)KS_INB * pl.S * 16 * tok * 4 +
+                       (2 * KS_MAX_STAGES + KS_INB + KS_MAX_S * KS_INB + KS_NR + 1) * 8;
   int ns = fixed < half ? (int)((half - fixed) / per_stage) : 0;
   ns = std::min(ns, KS_MAX_STAGES);
   const int tune_ns = ctx->tune_ks_stages.load();
@@ -587,10 +595,10 @@ int launch_ksplit_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ks
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   // As many clusters as the GPU holds at the same time (a cluster needs its S CTAs on one GPC, so
-  // this is less than SMs x 2 / S), asked once per configuration, less a sixteenth: measured, a
-  // grid of exactly the number the runtime names already runs a third longer with clusters of
-  // 8 (32 are fine, 33 are not), and a grid of more than fit runs in two waves.  The units are
-  // then spread evenly over as few rounds as that allows.
+  // this is less than SMs x 2 / S: 71 clusters of 4, 33 of 8 on a B200), asked once per
+  // configuration, less one: measured, a grid of exactly the number the runtime names runs a
+  // third longer with clusters of 8 (32 are fine, 33 are not), and a grid of more than fit runs
+  // in two waves.  The units are then spread evenly over as few rounds as that allows.
   int qmax = ctx->tune_ks_clusters.load();
   if (qmax <= 0) {
     static std::mutex mu;
@@ -606,7 +614,7 @@ int launch_ksplit_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ks
         cudaGetLastError();
         nc = std::max(1, (ctx->sm_count > 0 ? ctx->sm_count : 148) / pl.S);
       }
-      it = known.emplace(key, std::max(1, nc - nc / 16)).first;
+      it = known.emplace(key, std::max(1, nc - 1)).first;
     }
     qmax = it->second;
   }

@@ -858,7 +858,7 @@ def run_ours_tp(args):
             "gpu_launches": int(launches_per_step * args.steps),
             "roofline": {"bound": "hbm", "achieved": value / world, "peak": peak, "unit": "GB/s",
                          "frac": value / world / peak, "traffic": None, "peak_kind": f"of {peak_kind}",
-                         "kernel": "u8_ring_kernel" + (" with the all-reduce fused in" if use_peer and args.fused_ar
+                         "kernel": "u8_ksplit_kernel (k = 8192) / u8_ring_kernel" + (" with the all-reduce fused in" if use_peer and args.fused_ar
                                                      else " + allreduce_oneshot_kernel" if use_peer else " + ncclAllReduce")},
             "clocks": clocks,
             "note": "N > 1 is configs[4] (strong scaling); its tp = 1 point is extra.tp1_65b of the N = 1 line, "

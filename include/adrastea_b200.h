@@ -110,6 +110,12 @@ int adr_force_kernel(adr_ctx* ctx, int kernel);
  *               before on the same stream.  Activations and output are only touched after
  *               the previous kernel has completed.  The row-op kernels honour it too.
  *               Default 0.
+ *   "pdl_guard": with "pdl" on, which launches of the persistent decode kernel end a chain of
+ *               early starts (the launch behind them begins on an empty GPU): bit 0 = launches
+ *               with two CTAs per SM, bit 1 = launches whose CTAs take a whole SM.  Default 3;
+ *               0 shows what the guard is worth (CTAs then land two to an SM on half the SMs).
+ *   "ks_clusters", "ks_stages": clusters in the grid / ring stages of the cluster k-split
+ *               decode kernel (0 = the planner's choice).
  *   "wait_ms":  bound, in milliseconds, of the waits on a peer GPU in adr_allreduce_oneshot and
  *               adr_matmul_nt_fp16u8_allreduce (0 = about a second).
  *   "u8_exact": 1 = the streaming u8 kernel rounds every dequantised weight to fp16 before
