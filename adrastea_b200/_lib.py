@@ -28,6 +28,9 @@ SIGNATURES = {
     "adr_launch_count": (C.c_uint64, [_vp]),
     "adr_matmul_f16": (_c_int, _MATMUL_F16_ARGS),
     "adr_matmul_f16_slow": (_c_int, _MATMUL_F16_ARGS),
+    # (ctx, stream, out, lhs, rhs) + outer batches + (batches, m, k, n) + 12 strides + bias + ...
+    "adr_matmul_f16_b2": (_c_int, [_vp] * 5 + [_c_int] * 17 + [_vp, C.c_float, C.c_float, C.c_uint32,
+                                                         C.c_uint32, C.c_uint32]),
     "adr_matmul_f16_raw": (_c_int, [_vp, _vp, _vp, _vp, _vp] + [_c_int] * 13),
     "adr_matmul_nt_fp16u8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int,
                                       _c_int, C.c_float]),

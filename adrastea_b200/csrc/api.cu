@@ -195,6 +195,38 @@ int adr_matmul_f16(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs, 
   return run_matmul(ctx, (cudaStream_t)stream, a, false);
 }
 
+int adr_matmul_f16_b2(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs, const void* rhs,
+                      int batches_outer, int batches, int m, int k, int n, int stride_ox,
+                      int stride_oy, int stride_oz, int stride_ow, int stride_lx, int stride_ly,
+                      int stride_lz, int stride_lw, int stride_rx, int stride_ry, int stride_rz,
+                      int stride_rw, const void* bias, float beta, float scale, uint32_t store_op,
+                      uint32_t load_op, uint32_t mask_op) {
+  if (batches_outer <= 0 || batches <= 0) return ADR_ERR_INVALID;
+  if (stride_ow < 0 || stride_lw < 0 || stride_rw < 0) return ADR_ERR_INVALID;
+  // The two batch dimensions of an operand fold into one when its outer stride is `batches`
+  // inner strides (or both are 0: broadcast); if that holds for all three, one launch does it.
+  auto folds = [&](int sz, int sw) { return (long long)sw == (long long)sz * batches; };
+  const long long total = (long long)batches_outer * batches;
+  if (batches_outer == 1 ||
+      (total <= 0x7fffffff && folds(stride_oz, stride_ow) && folds(stride_lz, stride_lw) &&
+       folds(stride_rz, stride_rw)))
+    return adr_matmul_f16(ctx, stream, out, lhs, rhs, (int)total, m, k, n, stride_ox, stride_oy,
+                          stride_oz, stride_lx, stride_ly, stride_lz, stride_rx, stride_ry,
+                          stride_rz, bias, beta, scale, store_op, load_op, mask_op);
+  if (!out || !lhs || !rhs) return ADR_ERR_INVALID;
+  // otherwise one launch per outer index, each over the inner batch
+  for (int w = 0; w < batches_outer; ++w) {
+    const int rc = adr_matmul_f16(
+        ctx, stream, static_cast<__half*>(out) + (size_t)w * stride_ow,
+        static_cast<const __half*>(lhs) + (size_t)w * stride_lw,
+        static_cast<const __half*>(rhs) + (size_t)w * stride_rw, batches, m, k, n, stride_ox,
+        stride_oy, stride_oz, stride_lx, stride_ly, stride_lz, stride_rx, stride_ry, stride_rz, bias,
+        beta, scale, store_op, load_op, mask_op);
+    if (rc != ADR_OK) return rc;
+  }
+  return ADR_OK;
+}
+
 int adr_matmul_f16_slow(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
                         const void* rhs, int batches, int m, int k, int n, int stride_ox,
                         int stride_oy, int stride_oz, int stride_lx, int stride_ly, int stride_lz,
@@ -237,8 +269,10 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
     else if (m > 32 && u8_tc_supports(ctx, a)) kernel = ADR_KERNEL_U8_TC;
     else if (p % 64 != 0) kernel = m <= 4 ? ADR_KERNEL_U8_GEMV : ADR_KERNEL_U8_SIMT;
     else if (!ctx->tune_u8_exact && !ctx->tune_u8_split && !ctx->tune_u8_rows &&
-             (a16.m >= 5 || (a16.m >= 4 && p >= 8192)) && u8_ksplit_supports(ctx, a16))
-      kernel = ADR_KERNEL_U8_KSPLIT;  // from five tokens on (four at k = 8192) the cluster split wins
+             (p <= 8192 ? (a16.m >= 5 || (a16.m >= 4 && p == 8192))
+                        : (a16.m >= 7 || (a16.m >= 4 && p >= 16384))) &&
+             u8_ksplit_supports(ctx, a16))
+      kernel = ADR_KERNEL_U8_KSPLIT;  // measured: from these token counts on the cluster split wins
     else if (!ctx->tune_u8_exact && !ctx->tune_u8_split && !ctx->tune_u8_rows &&
              u8_ring_supports(ctx, a16))
       kernel = ADR_KERNEL_U8_RING;

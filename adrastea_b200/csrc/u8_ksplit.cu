@@ -1,5 +1,6 @@
 // u8-weight decode GEMV/GEMM, k split over a thread-block cluster (m <= 16, block_size 64 or
-// 128, p = 1024 * S with S = 2..8 CTAs per cluster):
+// 128, p a multiple of 128 from 2048 on; a cluster of S <= 8 CTAs covers 1024 * S of k, a longer k
+// goes out as several launches over consecutive k ranges):
 //   out[m,n] = lhs[m,p] . deq(Q[n,p])^T + beta * out
 // (replaces adrastea_kernels/cpp/matmul_nt_fp16u8.cu:4-24 for decode shapes; same arithmetic as
 // the persistent ring kernel: one PRMT per weight pair makes 1024 + q, mma.sync.m16n8k16 sums
@@ -145,6 +146,8 @@ struct KsParams {
   int units;     // ceil(n / 16)
   int S;         // CTAs per cluster = k slices
   int Q;         // clusters in the grid
+  int t0;        // first 128-wide k tile of this launch (a long k goes out as several launches)
+  float beta;    // of this launch: the caller's for the first k range, 1 for the ranges after it
   long long wait_cycles;
   unsigned int* status;
 };
@@ -206,7 +209,11 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
     // Weights, scales and zero points only: by contract not written by the kernel before, so
     // nothing here waits for it.
     bool ok = true;
-    const bool wide = (groups % 8) == 0 && (reinterpret_cast<uintptr_t>(a.scales) & 15u) == 0 &&
+    // (a slice that reaches past the end of k copies its scales in 4-byte pieces, each checked)
+    const int tiles_total = a.p / 128;
+    const int tile0 = p.t0 + rank * 8;  // this CTA's first tile
+    const bool whole = tile0 + 8 <= tiles_total;
+    const bool wide = whole && (groups % 8) == 0 && (reinterpret_cast<uintptr_t>(a.scales) & 15u) == 0 &&
                       (!HAS_ZERO || (reinterpret_cast<uintptr_t>(a.zeros) & 15u) == 0);
     const int per = wide ? 8 : 2;          // halves per copy
     const int per_row = p.gps / per;       // copies per row
@@ -218,7 +225,7 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
       c_row[u] = c < copies ? c / per_row : -1;
       c_col[u] = c < copies ? (c % per_row) * per : 0;
     }
-    const int g0 = rank * p.gps;
+    const int g0 = (tile0 * 128) >> p.bs_shift;
     int s = 0;
     unsigned par = 0;
     for (int j = 0; j < J && ok; ++j) {
@@ -230,12 +237,12 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
       uint8_t* stage = ring + (size_t)s * KS_STAGE_BYTES;
       if (lane == 0) {
         mbar_expect_tx(&full[s], (unsigned)KS_W_BYTES);
-        tma_load_3d(stage, &wmap, 0, n0, rank * 8, &full[s]);
+        tma_load_3d(stage, &wmap, 0, n0, tile0, &full[s]);  // tiles past the end of k arrive as zeros
       }
       __half* stab = reinterpret_cast<__half*>(stage + KS_W_BYTES);
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        if (c_row[u] >= 0) {
+        if (c_row[u] >= 0 && g0 + c_col[u] < groups) {
           const size_t src = (size_t)min(n0 + c_row[u], a.n - 1) * groups + g0 + c_col[u];
           __half* dst = stab + c_row[u] * p.gps + c_col[u];
           if (wide) {
@@ -268,16 +275,19 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
     if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
     // ---- this warp's activations, for the whole launch: tokens g (and g + 8) of the 128 k of
     // its tile, 32 bytes per 64-wide piece, in the order the weight bytes are consumed in
+    // (a tile past the end of k: zero activations, and its stages are not computed at all: the
+    // scales were not copied for it)
+    const bool tile_ok = p.t0 + rank * 8 + cw < a.p / 128;
     uint32_t xw[MT][2][8];
     {
-      const size_t koff = (size_t)(rank * 8 + cw) * 256 + (size_t)t * 32;  // bytes into a row
+      const size_t koff = (size_t)(p.t0 + rank * 8 + cw) * 256 + (size_t)t * 32;  // bytes into a row
 #pragma unroll
       for (int i = 0; i < MT; ++i) {
         const int tok = i * 8 + g;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           uint4 v0 = make_uint4(0, 0, 0, 0), v1 = v0;
-          if (tok < a.m) {
+          if (tok < a.m && tile_ok) {
             const uint8_t* src = reinterpret_cast<const uint8_t*>(a.lhs) + (size_t)tok * a.p * 2 + koff + h * 128;
             v0 = *reinterpret_cast<const uint4*>(src);
             v1 = *reinterpret_cast<const uint4*>(src + 16);
@@ -312,7 +322,7 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
 #pragma unroll
         for (int e = 0; e < 4; ++e) d[i][e] = 0.0f;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[s], par) && !*abort_flag);
-      if (ok) {
+      if (ok && tile_ok) {
         const uint8_t* stage = ring + (size_t)s * KS_STAGE_BYTES;
         const uint8_t* trow = stage + cw * KS_TILE_BYTES + pg * 128;
         const __half* stab = reinterpret_cast<const __half*>(stage + KS_W_BYTES);
@@ -362,7 +372,7 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
         using F = std::false_type;
         compute_piece(trow + ((t ^ pg) * 16), std::integral_constant<int, 0>{}, T{});
         if (per_piece) {
-          correct(2 * cw, 0, 0);
+          correct(2 * cw, 0, 0);  // (group indices are relative to the stage)
           compute_piece(trow + (((t + 4) ^ pg) * 16), std::integral_constant<int, 1>{}, T{});
           correct(2 * cw + 1, 1, 1);
         } else {
@@ -472,7 +482,7 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
 #pragma unroll
         for (int e = 0; e < OPL; ++e)
           res[e] = __half_as_ushort(
-              __float2half_rn(fmaf(a.beta, __half2float(__ushort_as_half(old[e])), v[e])));
+              __float2half_rn(fmaf(p.beta, __half2float(__ushort_as_half(old[e])), v[e])));
         if (vec && n0 + 16 <= a.n) {
           if (OPL == 8) *reinterpret_cast<uint4*>(optr) = *reinterpret_cast<const uint4*>(res);
           else *reinterpret_cast<uint2*>(optr) = *reinterpret_cast<const uint2*>(res);
@@ -542,10 +552,13 @@ struct KsPlan {
   size_t smem;
 };
 
-bool plan_ksplit(const adr_ctx* ctx, const U8Args& a, KsPlan& pl) {
+// Plan for the k range of `kc` elements (at most 8192) of a product; the range may end inside
+// a CTA's slice.
+bool plan_ksplit(const adr_ctx* ctx, const U8Args& a, int kc, KsPlan& pl) {
   if (a.m < 1 || a.m > 16 || a.n < 16) return false;
   if (a.block_size != 64 && a.block_size != 128) return false;
-  if (a.p % 1024 != 0 || a.p / 1024 < 2 || a.p / 1024 > KS_MAX_S) return false;
+  if (a.p % 128 != 0 || a.p < 2048 || ((a.p / a.block_size) & 1)) return false;  // 4-byte scale copies
+  if (kc < 128 || kc > 1024 * KS_MAX_S) return false;
   if (a.norm_w != nullptr) return false;
   if ((reinterpret_cast<uintptr_t>(a.rhs) & 15u) || (reinterpret_cast<uintptr_t>(a.lhs) & 15u) ||
       (reinterpret_cast<uintptr_t>(a.scales) & 3u) ||
@@ -553,7 +566,7 @@ bool plan_ksplit(const adr_ctx* ctx, const U8Args& a, KsPlan& pl) {
     return false;
   if (!ctx->encode_tiled_fn) return false;
   const int tok = a.m > 8 ? 16 : 8;
-  pl.S = a.p / 1024;
+  pl.S = (kc + 1023) / 1024;
   pl.Q = 0;  // chosen by the launcher, which knows how many clusters the GPU holds at once
   const size_t half = 113 * 1024;
   const size_t per_stage = KS_STAGE_BYTES;
@@ -570,7 +583,8 @@ bool plan_ksplit(const adr_ctx* ctx, const U8Args& a, KsPlan& pl) {
 }
 
 template <int MT, bool Z, bool PDL>
-int launch_ksplit_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const KsPlan& pl) {
+int launch_ksplit_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const KsPlan& pl, int t0,
+                    float beta) {
   auto kfn = u8_ksplit_kernel<MT, Z, PDL>;
   if (int rc0 = opt_in_smem(ctx, kfn, 226 * 1024); rc0 != ADR_OK) return rc0;
   // weights as (k within tile, row, k-tile): a box of 128 x 16 x 8 lands as eight tiles of
@@ -628,6 +642,8 @@ int launch_ksplit_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ks
   p.bs_shift = a.block_size == 64 ? 6 : 7;
   p.units = (a.n + 15) / 16;
   p.S = pl.S;
+  p.t0 = t0;
+  p.beta = beta;
   p.Q = Q;
   p.wait_cycles = peer_wait_cycles(ctx);
   p.status = ctx->d_status;
@@ -643,25 +659,49 @@ int launch_ksplit_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ks
 
 }  // namespace
 
+// A cluster covers at most 8192 of k, so a longer k goes out as several launches over
+// consecutive k ranges, the later ones adding to what the earlier ones wrote (beta = 1; the
+// output passes through fp16 between them).  The ranges are cut evenly in units of 1024.
+namespace {
+int ksplit_ranges(int p) { return (p + 1024 * KS_MAX_S - 1) / (1024 * KS_MAX_S); }
+int ksplit_range_len(int p) {
+  const int slices = (p + 1023) / 1024, r = ksplit_ranges(p);
+  return ((slices + r - 1) / r) * 1024;
+}
+}  // namespace
+
 bool u8_ksplit_supports(const adr_ctx* ctx, const U8Args& a) {
+  if (a.p < 2048) return false;
   KsPlan pl;
-  return plan_ksplit(ctx, a, pl);
+  const int len = ksplit_range_len(a.p);
+  for (int k0 = 0; k0 < a.p; k0 += len)
+    if (!plan_ksplit(ctx, a, std::min(len, a.p - k0), pl)) return false;
+  return true;
 }
 
 int launch_u8_ksplit(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
-  KsPlan pl;
-  if (!plan_ksplit(ctx, a, pl)) return ADR_ERR_SHAPE;
+  if (!u8_ksplit_supports(ctx, a)) return ADR_ERR_SHAPE;
   const bool z = a.zeros != nullptr, two = a.m > 8, pdl = ctx->tune_pdl != 0;
-#define ADR_KS_CASE(MT, Z)                                                    \
-  return pdl ? launch_ksplit_t<MT, Z, true>(ctx, stream, a, pl)               \
-             : launch_ksplit_t<MT, Z, false>(ctx, stream, a, pl)
-  if (two) {
-    if (z) { ADR_KS_CASE(2, true); }
-    ADR_KS_CASE(2, false);
+  const int len = ksplit_range_len(a.p);
+  for (int k0 = 0; k0 < a.p; k0 += len) {
+    KsPlan pl;
+    if (!plan_ksplit(ctx, a, std::min(len, a.p - k0), pl)) return ADR_ERR_SHAPE;
+    const int t0 = k0 / 128;
+    const float beta = k0 == 0 ? a.beta : 1.0f;
+    int rc;
+    if (two)
+      rc = z ? (pdl ? launch_ksplit_t<2, true, true>(ctx, stream, a, pl, t0, beta)
+                    : launch_ksplit_t<2, true, false>(ctx, stream, a, pl, t0, beta))
+             : (pdl ? launch_ksplit_t<2, false, true>(ctx, stream, a, pl, t0, beta)
+                    : launch_ksplit_t<2, false, false>(ctx, stream, a, pl, t0, beta));
+    else
+      rc = z ? (pdl ? launch_ksplit_t<1, true, true>(ctx, stream, a, pl, t0, beta)
+                    : launch_ksplit_t<1, true, false>(ctx, stream, a, pl, t0, beta))
+             : (pdl ? launch_ksplit_t<1, false, true>(ctx, stream, a, pl, t0, beta)
+                    : launch_ksplit_t<1, false, false>(ctx, stream, a, pl, t0, beta));
+    if (rc != ADR_OK) return rc;
   }
-  if (z) { ADR_KS_CASE(1, true); }
-  ADR_KS_CASE(1, false);
-#undef ADR_KS_CASE
+  return ADR_OK;
 }
 
 }  // namespace adr

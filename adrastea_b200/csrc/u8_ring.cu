@@ -226,7 +226,9 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
       // fill the ring before waiting for the previous kernel: these loads touch only weights
       for (; q < total_stages && q < p.NS; ++q) issue();
       // (Asking here for the next stages to be brought into L2 while the ring is full was tried
-      // and lost 1-7 %: the requests compete with the launch before, which is still streaming.)
+      // and lost 1-7 %: the requests compete with the launch before, which is still streaming.
+      // So was, on the consumer side, taking the next stage's weight bytes into registers while
+      // the current stage's MMAs run: 10-20 % slower.)
       if (PDL) asm volatile("griddepcontrol.wait;" ::: "memory");
       if (lane == 0) mbar_expect_tx(xbar, (unsigned)(a.m * a.p * 2));
       __syncwarp();

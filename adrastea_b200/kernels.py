@@ -276,6 +276,33 @@ class GpuKernels:
         self._matmul(self._lib.adr_matmul_f16, output, left, right, options or MatmulOptions(),
                      stream)
 
+    def matmul_f16_b2(self, output: TensorView, left: TensorView, right: TensorView,
+                      options: MatmulOptions | None = None, stream=None):
+        """adr_matmul_f16_b2: matmul_f16 for rank-4 views (two batch dimensions; an operand of
+        lower rank is broadcast), which the reference's launch cannot take (kernels.rs:858)."""
+        options = options or MatmulOptions()
+        for v, w in ((output, "output"), (left, "left"), (right, "right")):
+            self._f16(v, w)
+        assert len(output.layout.dims) == 4
+        (batches, m, k, n, sox, soy, soz, slx, sly, slz, srx, sry, srz,
+         bias, beta, scale, store, load, mask) = lower_matmul(output, left, right, options)
+
+        def wstride(v: TensorView) -> int:
+            return v.stride(-4) if len(v.layout.dims) > 3 else 0
+
+        for v in (left, right):
+            if len(v.layout.dims) > 3:
+                assert v.size(-4) == output.size(-4), "outer batch mismatch"
+        bias_ptr = None
+        if bias is not None:
+            self._f16(bias, "bias")
+            bias_ptr = bias.data_ptr()
+        rc = self._lib.adr_matmul_f16_b2(
+            self._ctx, _stream_handle(stream), output.data_ptr(), left.data_ptr(), right.data_ptr(),
+            output.size(-4), batches, m, k, n, sox, soy, soz, wstride(output), slx, sly, slz,
+            wstride(left), srx, sry, srz, wstride(right), bias_ptr, beta, scale, store, load, mask)
+        self._check(rc)
+
     def matmul_f16_slow(self, output: TensorView, left: TensorView, right: TensorView,
                         options: MatmulOptions | None = None, stream=None):
         """CommonKernels::matmul_f16_slow (kernels.rs:206-209, 753-819)."""

@@ -148,6 +148,22 @@ int adr_matmul_f16(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs, 
                    uint32_t load_op, uint32_t mask_op);
 
 /*
+ * adr_matmul_f16 with a second, outer batch dimension `w` (4th-last; its element strides follow
+ * each operand's z stride), for operands that are rank-4 views such as the [B, H, S, hd] views of
+ * [B, S, H*hd] storage that a batched attention block multiplies (clip.rs:374-388 at batch > 1).
+ * No counterpart in the reference, whose launch takes its batch count from out.size(-3) only
+ * (kernels.rs:858, 868-880).  When the two batch dimensions of every operand fold into one
+ * (outer stride == batches * z stride, or both 0) this is one launch over batches_outer * batches;
+ * otherwise it is one launch per outer index.  The bias is shared by all batches.
+ */
+int adr_matmul_f16_b2(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs, const void* rhs,
+                      int batches_outer, int batches, int m, int k, int n, int stride_ox,
+                      int stride_oy, int stride_oz, int stride_ow, int stride_lx, int stride_ly,
+                      int stride_lz, int stride_lw, int stride_rx, int stride_ry, int stride_rz,
+                      int stride_rw, const void* bias, float beta, float scale, uint32_t store_op,
+                      uint32_t load_op, uint32_t mask_op);
+
+/*
  * Replaces CommonKernels::matmul_f16_slow -> kernel matmul_f16
  * (kernels.rs:206-209, 753-819; matmul.cu:493-502).  Same contract; always
  * takes the CUDA-core kernel that accepts any strides.

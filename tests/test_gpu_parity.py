@@ -182,6 +182,14 @@ def test_live_reference_kernels_agree_with_oracle(c):
         assert np.abs(d).max() <= (0 if c.exact_vs_reference else 2), kern
 
 
+def ksplit_takes(m, p, bs):
+    """Shapes the cluster k-split kernel takes, and whether the dispatcher picks it."""
+    ok = p % 128 == 0 and p >= 2048 and bs in (64, 128) and (p // bs) % 2 == 0
+    if p <= 8192:
+        return ok, ok and (m >= 5 or (m >= 4 and p == 8192))
+    return ok, ok and (m >= 7 or (m >= 4 and p >= 16384))
+
+
 def u8_kernels_for(c):
     ks = [Kernel.U8Simt]
     if c.m <= 4:
@@ -192,7 +200,7 @@ def u8_kernels_for(c):
             ks.append(Kernel.U8Stream)
             if c.block_size in (64, 128) and c.n >= 16 and (c.p // c.block_size) % 2 == 0:
                 ks.append(Kernel.U8Ring)
-                if c.p % 1024 == 0 and 2 <= c.p // 1024 <= 8:
+                if ksplit_takes(c.m, c.p, c.block_size)[0]:
                     ks.append(Kernel.U8KSplit)
     if c.p % 16 == 0:
         ks.append(Kernel.U8Tc)
@@ -269,7 +277,7 @@ def test_u8_ring_kernel(kernels, pdl):
             kernels.force_kernel(Kernel.Auto)
             o = dev(out0.copy())
             kernels.matmul_nt_fp16u8(o, xd, qd, sd, bs, 0.5, zd)
-            if p % 1024 == 0 and 2 <= p // 1024 <= 8 and (m >= 5 or (m >= 4 and p >= 8192)):
+            if ksplit_takes(m, p, bs)[1]:
                 assert kernels.last_kernel() == Kernel.U8KSplit  # the cluster split takes these
                 assert oracle.max_rel_err(o.cpu().numpy(), want) <= 2e-3
             else:
@@ -290,7 +298,7 @@ def test_u8_ring_kernel(kernels, pdl):
 
 @pytest.mark.parametrize("pdl", [0, 1])
 def test_u8_cluster_ksplit_kernel(kernels, pdl):
-    """The cluster k-split kernel: every cluster size it takes (k = 2048 .. 8192), ragged n, fewer
+    """The cluster k-split kernel: every cluster size (k = 2048 .. 8192 and beyond), ragged n, fewer
     units than clusters and many more, both block sizes, both token blocks, zero points, beta,
     several launches back to back (inbox slots and credits in rotation); thrice for determinism."""
     rng = np.random.default_rng(177 + pdl)
@@ -301,7 +309,12 @@ def test_u8_cluster_ksplit_kernel(kernels, pdl):
                                 (16, 4096, 4096, 128, True), (9, 8192, 97, 64, True),
                                 (4, 4096, 11008, 128, False), (16, 8192, 1000, 128, False),
                                 (3, 3072, 16, 64, False), (16, 5120, 2500, 64, True),
-                                (12, 7168, 640, 128, False)):
+                                (12, 7168, 640, 128, False),
+                                # k that ends inside a CTA's slice; k beyond one cluster's reach
+                                # (two and three launches over consecutive k ranges)
+                                (6, 2304, 100, 128, False), (16, 11008, 272, 128, True),
+                                (8, 11008, 256, 128, False), (12, 8320, 300, 64, False),
+                                (5, 22016, 64, 64, False)):
             x = rng.standard_normal((m, p)).astype(np.float16)
             q = rng.integers(0, 256, (n, p), dtype=np.uint8)
             s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
@@ -671,3 +684,50 @@ def test_u8_decode_kernels_follow_the_unrounded_reference_form(kernels, kernel):
         kernels.force_kernel(Kernel.Auto)
     assert worst <= 1.0, worst
     assert same / total >= 0.97, same / total
+
+
+def test_matmul_f16_second_batch_dimension(kernels):
+    """adr_matmul_f16_b2 on the [B, H, S, hd] views of [B, S, H*hd] storage that a batched attention
+    block multiplies: the same bits as one matmul_f16 call per outer index; operands whose two
+    batch dimensions fold go out as one launch; a rank-3 operand is broadcast over the outer one."""
+    B, H, S, hd = 3, 4, 72, 64
+    g = torch.Generator(device="cuda").manual_seed(5)
+    q = torch.randn((B, S, H * hd), device="cuda", generator=g).half()
+    k = torch.randn((B, S, H * hd), device="cuda", generator=g).half()
+    lay4 = TensorLayout.new((B, H, S, hd), (S * H * hd, hd, H * hd, 1))
+    qv, kv = TensorView(q, lay4), TensorView(k, lay4)
+    opts = MatmulOptions.new().store(MatmulStore.Scale(0.125)).mask(MatmulMask.Causal)
+    out = torch.zeros((B, H, S, S), dtype=torch.float16, device="cuda")
+    n0 = kernels.launch_count()
+    kernels.matmul_f16_b2(TensorView.of(out), qv, kv.permute([0, 1, 3, 2]), opts)
+    assert kernels.launch_count() - n0 == B  # the outer stride of q and k does not fold
+    want = torch.zeros_like(out)
+    lay3 = TensorLayout.new((H, S, hd), (hd, H * hd, 1))
+    for b in range(B):
+        kernels.matmul_f16(TensorView.of(want[b]), TensorView(q[b], lay3),
+                           TensorView(k[b], lay3).permute([0, 2, 1]), opts)
+    kernels.device_status()
+    assert torch.equal(out.view(torch.int16), want.view(torch.int16))
+    ref = torch.einsum("bhsd,bhtd->bhst", q.view(B, S, H, hd).permute(0, 2, 1, 3).float(),
+                       k.view(B, S, H, hd).permute(0, 2, 1, 3).float()) * 0.125
+    mask = torch.ones((S, S), dtype=torch.bool, device="cuda").tril()
+    got = out.float()
+    assert torch.all(torch.isinf(got[..., ~mask]) & (got[..., ~mask] < 0))
+    err = (got[..., mask] - ref[..., mask]).abs().max() / ref[..., mask].abs().max()
+    assert err.item() <= TOL
+    # contiguous [B, H, S, hd] operands fold into one launch; the rhs is a rank-3 view shared by all b
+    a = torch.randn((B, H, S, hd), device="cuda", generator=g).half()
+    w = torch.randn((H, hd, 48), device="cuda", generator=g).half()
+    o2 = torch.zeros((B, H, S, 48), dtype=torch.float16, device="cuda")
+    n0 = kernels.launch_count()
+    kernels.matmul_f16_b2(TensorView.of(o2), TensorView.of(a), TensorView.of(w))
+    assert kernels.launch_count() - n0 == B  # the broadcast operand's strides (z != 0, w == 0) do not fold
+    w4 = w.unsqueeze(0).expand(B, H, hd, 48).contiguous()
+    o3 = torch.zeros_like(o2)
+    n0 = kernels.launch_count()
+    kernels.matmul_f16_b2(TensorView.of(o3), TensorView.of(a), TensorView.of(w4))
+    assert kernels.launch_count() - n0 == 1
+    kernels.device_status()
+    assert torch.equal(o2.view(torch.int16), o3.view(torch.int16))
+    ref2 = torch.einsum("bhsd,hdn->bhsn", a.float(), w.float())
+    assert ((o2.float() - ref2).abs().max() / ref2.abs().max()).item() <= TOL
