@@ -38,6 +38,10 @@ SIGNATURES = {
                                          _c_int, C.c_float, _vp, C.c_size_t]),
     "adr_matmul_nt_fp16u8_noalloc": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int,
                                               _c_int, _c_int, C.c_float]),
+    "adr_matmul_nt_fp16u8_grouped": (_c_int, [_vp, _vp, _c_int, C.POINTER(_vp), _vp, C.POINTER(_vp),
+                                              C.POINTER(_vp), C.POINTER(_vp), _c_int, _c_int,
+                                              C.POINTER(_c_int), _c_int, C.c_float]),
+    "adr_silu_mul_matmul_nt_fp16u8": (_c_int, [_vp] * 10 + [_c_int] * 4),
     "adr_matmul_nt_f16": (_c_int, [_vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, C.c_float]),
     "adr_dequantize_absmax_uint8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),
     "adr_quantize_absmax_uint8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),

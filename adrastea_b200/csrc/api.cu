@@ -161,6 +161,8 @@ int adr_set_tunable(adr_ctx* ctx, const char* name, int value) {
   else if (!strcmp(name, "pdl_guard")) ctx->tune_pdl_guard = value;
   else if (!strcmp(name, "ks_clusters")) ctx->tune_ks_clusters = value;
   else if (!strcmp(name, "ks_stages")) ctx->tune_ks_stages = value;
+  else if (!strcmp(name, "ks_off")) ctx->tune_ks_off = value;
+  else if (!strcmp(name, "ks_pdl")) ctx->tune_ks_pdl = value;
   else if (!strcmp(name, "u8_cps_m")) ctx->tune_u8_cps_m = value;
   else if (!strcmp(name, "u8_cps_x4")) ctx->tune_u8_cps_x4 = value;
   else return ADR_ERR_INVALID;
@@ -268,7 +270,7 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
     if (m > 32 && u8_ts_supports(ctx, a)) kernel = ADR_KERNEL_U8_TS;
     else if (m > 32 && u8_tc_supports(ctx, a)) kernel = ADR_KERNEL_U8_TC;
     else if (p % 64 != 0) kernel = m <= 4 ? ADR_KERNEL_U8_GEMV : ADR_KERNEL_U8_SIMT;
-    else if (!ctx->tune_u8_exact && !ctx->tune_u8_split && !ctx->tune_u8_rows &&
+    else if (!ctx->tune_u8_exact && !ctx->tune_u8_split && !ctx->tune_u8_rows && !ctx->tune_ks_off &&
              (p <= 8192 ? (a16.m >= 5 || (a16.m >= 4 && p == 8192))
                         : (a16.m >= 7 || (a16.m >= 4 && p >= 16384))) &&
              u8_ksplit_supports(ctx, a16))
@@ -334,6 +336,69 @@ int adr_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void*
     default: return ADR_ERR_INVALID;
   }
   if (rc == ADR_OK) ctx->last_kernel = kernel;
+  return rc;
+}
+
+int adr_matmul_nt_fp16u8_grouped(adr_ctx* ctx, adr_stream stream, int count, void* const* outs,
+                                 const void* lhs, const uint8_t* const* rhss,
+                                 const void* const* scaless, const void* const* zeross, int m,
+                                 int p, const int* ns, int block_size, float beta) {
+  if (!ctx || !outs || !lhs || !rhss || !scaless || !ns || count < 1) return ADR_ERR_INVALID;
+  for (int i = 0; i < count; ++i)
+    if (!outs[i] || !rhss[i] || !scaless[i] || ns[i] <= 0) return ADR_ERR_INVALID;
+  DeviceGuard guard(ctx);
+  cudaStream_t st = (cudaStream_t)stream;
+  // Up to four matrices per launch of the persistent decode kernel when it takes them (m <= 16,
+  // activations resident); otherwise, and for what is left, one call per matrix.
+  int i = 0;
+  if (ctx->forced_kernel == ADR_KERNEL_AUTO || ctx->forced_kernel == ADR_KERNEL_U8_RING) {
+    while (count - i >= 2 && m <= 16) {
+      RingGroup g = {};
+      g.count = count - i < 4 ? count - i : 4;
+      for (int j = 0; j < g.count; ++j) {
+        g.rhs[j] = rhss[i + j];
+        g.scales[j] = (const __half*)scaless[i + j];
+        g.zeros[j] = zeross ? (const __half*)zeross[i + j] : nullptr;
+        g.out[j] = (__half*)outs[i + j];
+        g.n[j] = ns[i + j];
+      }
+      U8Args common{nullptr, (const __half*)lhs, nullptr, nullptr, nullptr, m, p, 0, block_size, beta};
+      const int rc = launch_u8_ring_grouped(ctx, st, common, g);
+      if (rc == ADR_ERR_SHAPE) break;  // not a shape for the grouped form: separate calls below
+      if (rc != ADR_OK) return rc;
+      ctx->last_kernel = ADR_KERNEL_U8_RING;
+      i += g.count;
+    }
+  }
+  for (; i < count; ++i) {
+    const int rc = adr_matmul_nt_fp16u8(ctx, stream, outs[i], lhs, rhss[i], scaless[i],
+                                        zeross ? zeross[i] : nullptr, m, p, ns[i], block_size, beta);
+    if (rc != ADR_OK) return rc;
+  }
+  return ADR_OK;
+}
+
+int adr_silu_mul_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                                  const uint8_t* rhs_gate, const void* scales_gate,
+                                  const void* zeros_gate, const uint8_t* rhs_up,
+                                  const void* scales_up, const void* zeros_up, int m, int p, int n,
+                                  int block_size) {
+  if (!ctx || !out || !lhs || !rhs_gate || !scales_gate || !rhs_up || !scales_up) return ADR_ERR_INVALID;
+  if (m <= 0 || p <= 0 || n <= 0 || block_size <= 0) return ADR_ERR_INVALID;
+  if ((zeros_gate != nullptr) != (zeros_up != nullptr)) return ADR_ERR_INVALID;
+  if (m > 16) return ADR_ERR_SHAPE;
+  DeviceGuard guard(ctx);
+  RingGroup g = {};
+  g.count = 2;
+  g.pair = 1;
+  g.rhs[0] = rhs_gate, g.rhs[1] = rhs_up;
+  g.scales[0] = (const __half*)scales_gate, g.scales[1] = (const __half*)scales_up;
+  g.zeros[0] = (const __half*)zeros_gate, g.zeros[1] = (const __half*)zeros_up;
+  g.out[0] = g.out[1] = (__half*)out;
+  g.n[0] = g.n[1] = n;
+  U8Args common{nullptr, (const __half*)lhs, nullptr, nullptr, nullptr, m, p, 0, block_size, 0.0f};
+  const int rc = launch_u8_ring_grouped(ctx, (cudaStream_t)stream, common, g);
+  if (rc == ADR_OK) ctx->last_kernel = ADR_KERNEL_U8_RING;
   return rc;
 }
 

@@ -74,10 +74,11 @@ struct adr_ctx {
   std::atomic<int> tune_pdl{0};      // programmatic dependent launch of the decode and row kernels
   std::atomic<int> tune_wait_ms{0};  // limit of the peer waits in milliseconds (0: about a second)
   std::atomic<int> tune_u8_cps_m{2}, tune_u8_cps_x4{16};
-  std::atomic<int> tune_ks_clusters{0}, tune_ks_stages{0};  // cluster k-split kernel: clusters in the grid, ring stages
-  std::atomic<int> tune_pdl_guard{3};  // which SM-filling launches end a chain of early starts (bit 0: two CTAs per SM, bit 1: one large CTA)
+  std::atomic<int> tune_ks_clusters{0}, tune_ks_stages{0}, tune_ks_off{0};  // cluster k-split kernel: clusters in the grid, ring stages
+  std::atomic<int> tune_pdl_guard{7};
+  std::atomic<int> tune_ks_pdl{1};  // the cluster k-split kernel may start early under "pdl"  // which SM-filling launches end a chain of early starts (bit 0: two CTAs per SM, bit 1: one large CTA)
   // the last launch whose CTAs left no room beside them on an SM: its number and its stream
-  std::atomic<unsigned long long> fill_launch{~0ull};
+  std::atomic<int> fill_flag{0};
   std::atomic<uintptr_t> fill_stream{0};
 };
 
@@ -127,6 +128,21 @@ int opt_in_smem(adr_ctx* ctx, K kfn, size_t bytes) {
 }
 
 // Bound of a wait on a peer GPU in clock cycles (about 2 per nanosecond).
+// Bookkeeping for chains of early starts (programmatic dependent launch).  A launch whose CTAs
+// fill whole SMs leaves a mark on its stream; the persistent decode kernel's half-SM form reads
+// it (it must not start as those SMs drain, see u8_ring.cu) and clears it once a launch with a
+// full dependency has let the GPU run empty.  Small kernels in between do not clear it: they
+// start early themselves and pass the early start on.
+inline void note_filling_launch(adr_ctx* ctx, cudaStream_t stream, int kind_bit) {
+  if (ctx->tune_pdl.load() && (ctx->tune_pdl_guard.load() & kind_bit)) {
+    ctx->fill_stream = reinterpret_cast<uintptr_t>(stream);
+    ctx->fill_flag = 1;
+  }
+}
+inline bool behind_filling_launch(const adr_ctx* ctx, cudaStream_t stream) {
+  return ctx->fill_flag.load() != 0 && ctx->fill_stream.load() == reinterpret_cast<uintptr_t>(stream);
+}
+
 inline long long peer_wait_cycles(const adr_ctx* ctx) {
   const int ms = ctx->tune_wait_ms;
   return ms > 0 ? (long long)ms * 2000000LL : 2000000000LL;
@@ -251,6 +267,17 @@ struct RingArFuse {
   int rank, world, residual, max_ctas;
 };
 int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingArFuse* ar = nullptr);
+// up to four weight matrices multiplied by the same activations in one launch
+struct RingGroup {
+  int count;
+  const uint8_t* rhs[4];
+  const __half* scales[4];
+  const __half* zeros[4];
+  __half* out[4];
+  int n[4];
+  int pair = 0;  // 1: two matrices of equal n (gate, up); out[0] receives SiluMul(gate, up), out[1] is unused
+};
+int launch_u8_ring_grouped(adr_ctx* ctx, cudaStream_t stream, const U8Args& common, const RingGroup& grp);
 bool u8_ring_supports(const adr_ctx* ctx, const U8Args& a);
 int launch_u8_ksplit(adr_ctx* ctx, cudaStream_t stream, const U8Args& a);
 bool u8_ksplit_supports(const adr_ctx* ctx, const U8Args& a);

@@ -666,6 +666,8 @@ int launch_attention_wide(adr_ctx* ctx, cudaStream_t stream, __half* out, const 
     ctx->last_cuda_error = (int)e;
     return ADR_ERR_CUDA;
   }
+  if ((long long)n_heads * CS * batch >= (ctx->sm_count > 0 ? ctx->sm_count : 148))
+    note_filling_launch(ctx, stream, 4);  // (see launch_row)
   return after_launch(ctx);
 }
 
@@ -705,6 +707,10 @@ int launch_row(adr_ctx* ctx, cudaStream_t stream, void (*plain)(KArgs...), void 
     ctx->last_cuda_error = (int)e;
     return ADR_ERR_CUDA;
   }
+  // a row kernel with at least one CTA per SM (decode attention over many heads) fills the GPU
+  // like a large product does: the decode kernel's half-SM form must not start as it drains
+  if ((long long)grid.x * grid.y * grid.z >= (ctx->sm_count > 0 ? ctx->sm_count : 148))
+    note_filling_launch(ctx, stream, 4);
   return after_launch(ctx);
 }
 

@@ -648,12 +648,13 @@ int launch_ksplit_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ks
   p.wait_cycles = peer_wait_cycles(ctx);
   p.status = ctx->d_status;
   cfg.gridDim = dim3(Q * pl.S, 1, 1);
-  cfg.numAttrs = PDL ? 2 : 1;
+  cfg.numAttrs = (PDL && ctx->tune_ks_pdl.load()) ? 2 : 1;
   cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, wmap, p);
   if (e != cudaSuccess) {
     ctx->last_cuda_error = (int)e;
     return ADR_ERR_CUDA;
   }
+  note_filling_launch(ctx, stream, 1);  // two CTAs per SM: a half-SM launch must not start as they drain
   return after_launch(ctx);
 }
 

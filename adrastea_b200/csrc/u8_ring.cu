@@ -84,8 +84,30 @@ __device__ __forceinline__ unsigned int ld_acquire_sys_u32(const unsigned int* p
 }
 constexpr int RING_RED_BUFS = 4;  // partial-sum buffers (and named barriers) in rotation
 
+constexpr int RING_MAX_PROBLEMS = 4;
+// The grouped form: several weight matrices (same k, block size and activations; q/k/v or
+// gate/up of a decoder layer) walked by one launch.  Units are numbered across the problems.
+struct RingProblem {
+  const __half* scales;
+  const __half* zeros;
+  __half* out;
+  int n;      // rows of this matrix
+  int unit0;  // number of the first unit of this matrix
+};
+struct RingMaps {
+  CUtensorMap m[RING_MAX_PROBLEMS];
+};
+
 struct RingParams {
   U8Args a;
+  int nprob;  // grouped form: number of problems (a.rhs/scales/zeros/out/n are then unused)
+  // Paired form (two problems of equal n: the gate and up projections): a CTA takes the gate unit
+  // and the up unit of the same 16 rows one after the other and writes SiluMul(gate, up), each
+  // rounded to fp16 first as the separate kernels would (elementwise.cu:28-33), to prob[0].out.
+  // `units` then counts pairs.
+  int pair;
+  int wide_ok;  // grouped form: every scale (and zero point) matrix allows 16-byte copies
+  RingProblem prob[RING_MAX_PROBLEMS];
   int NS;        // stages in the ring
   int XS;        // bytes between activation rows in shared memory
   int gps;       // scale groups per stage (1024 / block_size)
@@ -116,9 +138,19 @@ struct RingParams {
 // nothing is loaded before griddepcontrol.wait.
 // FUSE: compiles in the optional rms_norm of the activations and the fused all-reduce; the plain
 // product uses the instantiation without them (they cost registers and 6 % of its speed).
-template <int MT, int NCW, bool HAS_ZERO, bool PDL, bool XR, bool FUSE, bool SUMS_IN_LOOP>
+// The problem that unit `gu` belongs to (grouped form).
+__device__ __forceinline__ int ring_locate(const RingParams& p, int gu) {
+  int i = 0;
+#pragma unroll
+  for (int j = 1; j < RING_MAX_PROBLEMS; ++j)
+    if (j < p.nprob && gu >= p.prob[j].unit0) i = j;
+  return i;
+}
+
+template <int MT, int NCW, bool HAS_ZERO, bool PDL, bool XR, bool FUSE, bool SUMS_IN_LOOP, bool GROUPED>
 __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
-    u8_ring_kernel(const __grid_constant__ CUtensorMap wmap, RingParams p) {
+    u8_ring_kernel(const __grid_constant__ RingMaps maps, RingParams p) {
+  static_assert(!GROUPED || (!XR && !FUSE), "the grouped form keeps the activations resident and fuses nothing");
   constexpr int TOK = 8 * MT;
   constexpr int NG = NCW / 8;  // consumer groups
   constexpr int RED_LD = TOK + 1;
@@ -144,11 +176,14 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
   const int ntiles = a.p / 128;
   const int groups = a.p >> p.bs_shift;
   // units of this CTA: blockIdx.x, blockIdx.x + gridDim.x, ...
-  const int my_units = (p.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const bool paired = GROUPED && p.pair != 0;
+  const int my_units = ((p.units - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x) * (paired ? 2 : 1);
+  // paired form: the gate results of a pair, as fp16, for the warp that finishes the pair
+  unsigned short* pairbuf = reinterpret_cast<unsigned short*>(xbar + 2);  // [2][16 * TOK]
   const int total_stages = my_units * p.spu;
 
   if (tid == 0) {
-    tma_prefetch_desc(&wmap);
+    tma_prefetch_desc(&maps.m[0]);
     for (int s = 0; s < p.NS; ++s) {
       mbar_init(&full[s], 33);  // expect_tx arrival + one cp.async arrival per producer lane
       mbar_init(&empty[s], 8);  // the eight warps of the group that consumed the stage
@@ -166,8 +201,9 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     // scales of a stage: 16 rows x gps halves, copied in 16-byte pieces when every row of the
     // scale matrix starts on a 16-byte boundary, else in 4-byte pieces.  A lane's share of the
     // copies (row, position in the row) is the same for every stage and is worked out once.
-    const bool wide = (groups % 8) == 0 && (reinterpret_cast<uintptr_t>(a.scales) & 15u) == 0 &&
-                      (!HAS_ZERO || (reinterpret_cast<uintptr_t>(a.zeros) & 15u) == 0);
+    const bool wide = GROUPED ? (groups % 8) == 0 && p.wide_ok != 0
+                              : (groups % 8) == 0 && (reinterpret_cast<uintptr_t>(a.scales) & 15u) == 0 &&
+                                    (!HAS_ZERO || (reinterpret_cast<uintptr_t>(a.zeros) & 15u) == 0);
     const int per = wide ? 8 : 2;          // halves per copy
     const int per_row = p.gps / per;       // copies per row
     const int copies = 16 * per_row;       // per stage and table (16..128)
@@ -179,16 +215,28 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
       c_col[u] = c < copies ? (c % per_row) * per : 0;
     }
     // stage counters, advanced without divisions: ring slot s, k-position st within the unit,
-    // first row n0 of the unit
-    int s = 0, st = 0, n0 = (int)blockIdx.x * 16;
+    // first row n0 of the unit (grouped form: unit number gu, from which the matrix and the row)
+    int s = 0, st = 0, n0 = (int)blockIdx.x * 16, gu = (int)blockIdx.x, uq = 0;
     unsigned par = 0;  // parity of the current pass over the ring
     auto issue = [&]() {
+      const CUtensorMap* wm = &maps.m[0];
+      const __half* scales = a.scales;
+      const __half* zeros = a.zeros;
+      int rows = a.n;
+      if constexpr (GROUPED) {
+        const int pi = paired ? (uq & 1) : ring_locate(p, gu);
+        wm = &maps.m[pi];
+        scales = p.prob[pi].scales;
+        zeros = p.prob[pi].zeros;
+        rows = p.prob[pi].n;
+        n0 = paired ? gu * 16 : (gu - p.prob[pi].unit0) * 16;
+      }
       uint8_t* stage = ring + (size_t)s * p.stage_bytes;
       // XR: this stage's slice of every activation row (the last stage of a unit may be short)
       const int xbytes = XR ? min(2048, (a.p - st * 1024) * 2) : 0;
       if (lane == 0) {
         mbar_expect_tx(&full[s], (unsigned)(RING_W_BYTES + a.m * xbytes));
-        tma_load_3d(stage, &wmap, 0, n0, st * RING_TILES, &full[s]);
+        tma_load_3d(stage, wm, 0, n0, st * RING_TILES, &full[s]);
       }
       if (XR) {
         __syncwarp();  // the transaction count is posted before any of the copies can complete
@@ -201,20 +249,24 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
         if (c_row[u] >= 0 && g0 + c_col[u] < groups) {
-          const size_t src = (size_t)min(n0 + c_row[u], a.n - 1) * groups + g0 + c_col[u];
+          const size_t src = (size_t)min(n0 + c_row[u], rows - 1) * groups + g0 + c_col[u];
           __half* dst = stab + c_row[u] * p.gps + c_col[u];
           if (wide) {
-            cp_async_16(dst, a.scales + src);
-            if (HAS_ZERO) cp_async_16(dst + 16 * p.gps, a.zeros + src);
+            cp_async_16(dst, scales + src);
+            if (HAS_ZERO) cp_async_16(dst + 16 * p.gps, zeros + src);
           } else {
-            cp_async_4(dst, a.scales + src);
-            if (HAS_ZERO) cp_async_4(dst + 16 * p.gps, a.zeros + src);
+            cp_async_4(dst, scales + src);
+            if (HAS_ZERO) cp_async_4(dst + 16 * p.gps, zeros + src);
           }
         }
       }
       cp_async_arrive(&full[s]);
       if (++s == p.NS) s = 0, par ^= 1u;
-      if (++st == p.spu) st = 0, n0 += (int)gridDim.x * 16;
+      if (++st == p.spu) {
+        st = 0, n0 += (int)gridDim.x * 16;
+        ++uq;
+        if (!paired || !(uq & 1)) gu += (int)gridDim.x;  // paired: the same rows twice (gate, up)
+      }
     };
     int q = 0;
     if (XR) {
@@ -441,7 +493,21 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
     unsigned cpar = 0;   // parity of the current pass over the ring
     int cgrp = 0;        // consumer group whose turn it is
     for (int ui = 0; ui < my_units; ++ui) {
-      const int n0 = ((int)blockIdx.x + ui * (int)gridDim.x) * 16;
+      int n0 = ((int)blockIdx.x + ui * (int)gridDim.x) * 16;
+      __half* out = a.out;
+      int rows = a.n;
+      if constexpr (GROUPED) {
+        if (paired) {
+          n0 = ((int)blockIdx.x + (ui >> 1) * (int)gridDim.x) * 16;
+          out = p.prob[0].out;
+          rows = p.prob[0].n;
+        } else {
+          const int gu = (int)blockIdx.x + ui * (int)gridDim.x, pi = ring_locate(p, gu);
+          n0 = (gu - p.prob[pi].unit0) * 16;
+          out = p.prob[pi].out;
+          rows = p.prob[pi].n;
+        }
+      }
       float d[MT][4];
 #pragma unroll
       for (int i = 0; i < MT; ++i)
@@ -463,8 +529,8 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
 #pragma unroll
         for (int j = 0; j < OPL; ++j) {
           const int e = ROTATE ? lane + 32 * j : tid - 32, row = e & 15, tok = e >> 4;
-          old[j] = (tok < a.m && n0 + row < a.n)
-                       ? reinterpret_cast<const unsigned short*>(a.out)[(size_t)tok * a.n + n0 + row]
+          old[j] = (tok < a.m && n0 + row < rows && !paired)
+                       ? reinterpret_cast<const unsigned short*>(out)[(size_t)tok * rows + n0 + row]
                        : (unsigned short)0;
         }
       }
@@ -557,12 +623,25 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
 #pragma unroll
         for (int j = 0; j < OPL; ++j) {
           const int e = ROTATE ? lane + 32 * j : tid - 32, row = e & 15, tok = e >> 4;
-          if (tok < a.m && n0 + row < a.n) {
+          if (tok < a.m && n0 + row < rows) {
             float v = 0.0f;
 #pragma unroll
             for (int w = 0; w < NCW; ++w) v += rb[(size_t)w * 16 * RED_LD + row * RED_LD + tok];
-            if (!fused_ar) {
-              a.out[(size_t)tok * a.n + n0 + row] =
+            if (GROUPED && paired) {
+              // gate unit: keep fp16(gate) for the warp that finishes the up unit (it cannot get
+              // there before this warp has announced its partial sums of the up unit, which it
+              // does after these stores); up unit: SiluMul with the arithmetic of the
+              // elementwise kernel
+              unsigned short* pb = pairbuf + ((ui >> 1) & 1) * 16 * TOK;
+              if (!(ui & 1)) {
+                pb[e] = __half_as_ushort(__float2half_rn(v));
+              } else {
+                const float gf = __half2float(__ushort_as_half(pb[e]));
+                const float uf = __half2float(__float2half_rn(v));
+                out[(size_t)tok * rows + n0 + row] = __float2half(gf / (1.0f + expf(-gf)) * uf);
+              }
+            } else if (!fused_ar) {
+              out[(size_t)tok * rows + n0 + row] =
                   __float2half_rn(fmaf(a.beta, __half2float(__ushort_as_half(old[j])), v));
             } else {
               // this rank's partial result goes into slot ar_rank of every rank's inbox (peer
@@ -630,7 +709,8 @@ struct RingPlan {
   size_t smem;
 };
 
-bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
+// `extra`: bytes of shared memory the launch needs beyond the usual areas (paired form).
+bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl, size_t extra = 0) {
   if (a.m < 1 || a.m > 16 || a.p % 128 != 0 || a.n < 16) return false;
   if (a.block_size != 64 && a.block_size != 128) return false;
   if (a.p % a.block_size != 0 || ((a.p / a.block_size) & 1)) return false;  // 4-byte scale copies
@@ -648,7 +728,7 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   pl.xsum_entries = (a.p / 128) * (a.block_size == 64 ? 2 : 1);
   auto fixed_for = [&](int rbufs) {
     return (size_t)a.m * pl.XS + (size_t)rbufs * pl.ncw * 16 * (tok + 1) * 4 +
-           (size_t)pl.xsum_entries * tok * 4 + (2 * RING_MAX_STAGES + 2) * 8;
+           (size_t)pl.xsum_entries * tok * 4 + (2 * RING_MAX_STAGES + 2) * 8 + extra;
   };
   pl.rbufs = a.m > 8 ? 2 : RING_RED_BUFS;
   size_t fixed = fixed_for(pl.rbufs);
@@ -724,28 +804,62 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl) {
   return true;
 }
 
-template <int MT, bool Z, bool PDL, int NCW, bool XR, bool FUSE, bool XSI>
+// `grp` (grouped form): the matrices of the launch; `a` then carries the common arguments and
+// n = 16 x the total number of units.
+template <int MT, bool Z, bool PDL, int NCW, bool XR, bool FUSE, bool XSI, bool G = false>
 int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl,
-                  const RingArFuse* ar) {
-  auto kfn = u8_ring_kernel<MT, NCW, Z, PDL, XR, FUSE, XSI>;
+                  const RingArFuse* ar, const RingGroup* grp = nullptr) {
+  auto kfn = u8_ring_kernel<MT, NCW, Z, PDL, XR, FUSE, XSI, G>;
   cudaError_t e;
   if (int rc0 = opt_in_smem(ctx, kfn, 226 * 1024); rc0 != ADR_OK) return rc0;
   // weights as (k within tile, row, k-tile): a box of 128 x 16 x 8 lands as eight tiles of
   // [16 rows][128 bytes], each swizzled by its own row index
-  CUtensorMap wmap;
-  const uint64_t dims[3] = {128u, (uint64_t)a.n, (uint64_t)(a.p / 128)};
+  RingMaps maps;
+  RingParams p;
+  p.nprob = 1;
+  p.wide_ok = 1;
+  p.pair = 0;
   const uint64_t strides[2] = {(uint64_t)a.p, 128u};
   const uint32_t box[3] = {128u, 16u, (uint32_t)RING_TILES};
-  int rc = tma_get(ctx, &wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.rhs, dims, strides, box,
-                   CU_TENSOR_MAP_SWIZZLE_128B);
-  if (rc != ADR_OK) return rc;
-  RingParams p;
+  int units_total = (a.n + 15) / 16;
+  if (G) {
+    units_total = 0;
+    p.nprob = grp->count;
+    for (int i = 0; i < grp->count; ++i) {
+      const uint64_t dims[3] = {128u, (uint64_t)grp->n[i], (uint64_t)(a.p / 128)};
+      int rc = tma_get(ctx, &maps.m[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, grp->rhs[i], dims, strides,
+                       box, CU_TENSOR_MAP_SWIZZLE_128B);
+      if (rc != ADR_OK) return rc;
+      p.prob[i] = RingProblem{grp->scales[i], Z ? grp->zeros[i] : nullptr, grp->out[i], grp->n[i],
+                              units_total};
+      units_total += (grp->n[i] + 15) / 16;
+      if ((reinterpret_cast<uintptr_t>(grp->scales[i]) & 15u) ||
+          (Z && (reinterpret_cast<uintptr_t>(grp->zeros[i]) & 15u)))
+        p.wide_ok = 0;
+    }
+    for (int i = grp->count; i < RING_MAX_PROBLEMS; ++i) {
+      maps.m[i] = maps.m[0];
+      p.prob[i] = p.prob[0];
+    }
+    if (grp->pair) {
+      p.pair = 1;
+      units_total = (grp->n[0] + 15) / 16;  // pairs
+    }
+  } else {
+    const uint64_t dims[3] = {128u, (uint64_t)a.n, (uint64_t)(a.p / 128)};
+    int rc = tma_get(ctx, &maps.m[0], CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, a.rhs, dims, strides, box,
+                     CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc != ADR_OK) return rc;
+    for (int i = 1; i < RING_MAX_PROBLEMS; ++i) maps.m[i] = maps.m[0];
+    for (int i = 0; i < RING_MAX_PROBLEMS; ++i)
+      p.prob[i] = RingProblem{a.scales, a.zeros, a.out, a.n, 0};
+  }
   p.a = a;
   p.NS = pl.NS;
   p.XS = pl.XS;
   p.gps = pl.gps;
   p.bs_shift = pl.shift;
-  p.units = (a.n + 15) / 16;
+  p.units = units_total;
   p.spu = (a.p / 128 + RING_TILES - 1) / RING_TILES;
   p.xsum_entries = pl.xsum_entries;
   p.stage_bytes = pl.stage_bytes;
@@ -784,23 +898,20 @@ int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
   // later launch of the chain would inherit that placement: each one running on half the SMs,
   // a quarter slower.  So the first such launch behind a filling launch gives up its early
   // start and begins on an empty GPU, which spreads its CTAs one per SM again.
-  const int guard = ctx->tune_pdl_guard.load();
+  // (Other kernels of this library that fill the SMs — the cluster k-split kernel, decode
+  // attention over many heads — leave the same mark; small kernels in between pass it on.)
   const int fill_kind = pl.cps == 2 ? 1 : (pl.smem > 114 * 1024 ? 2 : 0);
   bool early = PDL;
-  if (PDL && fill_kind == 0 && ctx->fill_launch.load() == ctx->launches.load() &&
-      ctx->fill_stream.load() == reinterpret_cast<uintptr_t>(stream))
-    early = false;
+  if (PDL && fill_kind == 0 && behind_filling_launch(ctx, stream)) early = false;
+  if (PDL && !early) ctx->fill_flag = 0;  // this launch waits for everything before it: the GPU runs empty
   cfg.numAttrs = early ? 1 : 0;
-  e = cudaLaunchKernelEx(&cfg, kfn, wmap, p);
+  e = cudaLaunchKernelEx(&cfg, kfn, maps, p);
   if (e != cudaSuccess) {
     ctx->last_cuda_error = (int)e;
     return ADR_ERR_CUDA;
   }
   const int rc2 = after_launch(ctx);
-  if (fill_kind & guard) {
-    ctx->fill_launch = ctx->launches.load();
-    ctx->fill_stream = reinterpret_cast<uintptr_t>(stream);
-  }
+  if (fill_kind) note_filling_launch(ctx, stream, fill_kind);
   return rc2;
 }
 
@@ -823,6 +934,48 @@ int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
 }
 
 }  // namespace
+
+// Several matrices with the same activations in one launch; ADR_ERR_SHAPE when the ring kernel
+// does not take them with the activations resident (the caller then makes separate calls).
+int launch_u8_ring_grouped(adr_ctx* ctx, cudaStream_t stream, const U8Args& common,
+                           const RingGroup& grp) {
+  if (grp.count < 1 || grp.count > RING_MAX_PROBLEMS) return ADR_ERR_INVALID;
+  int units = 0;
+  bool z = grp.zeros[0] != nullptr;
+  for (int i = 0; i < grp.count; ++i) {
+    if (!grp.rhs[i] || !grp.scales[i] || !grp.out[i] || grp.n[i] < 16) return ADR_ERR_SHAPE;
+    if ((grp.zeros[i] != nullptr) != z) return ADR_ERR_INVALID;  // all with zero points, or none
+    if ((reinterpret_cast<uintptr_t>(grp.rhs[i]) & 15u) || (reinterpret_cast<uintptr_t>(grp.scales[i]) & 3u) ||
+        (z && (reinterpret_cast<uintptr_t>(grp.zeros[i]) & 3u)))
+      return ADR_ERR_SHAPE;
+    units += (grp.n[i] + 15) / 16;
+  }
+  U8Args a = common;
+  a.rhs = grp.rhs[0];
+  a.scales = grp.scales[0];
+  a.zeros = grp.zeros[0];
+  a.out = grp.out[0];
+  a.n = units * 16;
+  a.norm_w = nullptr;
+  if (grp.pair && (grp.count != 2 || grp.n[0] != grp.n[1] || common.beta != 0.0f)) return ADR_ERR_INVALID;
+  RingPlan pl;
+  if (!plan_ring(ctx, a, pl, grp.pair ? 2 * 16 * 16 * 2 + 16 : 0) || pl.xr) return ADR_ERR_SHAPE;
+  const bool two = a.m > 8, pdl = ctx->tune_pdl != 0, xsi = !two && a.m >= 2;
+#define ADR_RING_G(MT, Z, XSI)                                                                        \
+  return pdl ? launch_ring_f<MT, Z, true, 8, false, false, XSI, true>(ctx, stream, a, pl, nullptr, &grp) \
+             : launch_ring_f<MT, Z, false, 8, false, false, XSI, true>(ctx, stream, a, pl, nullptr, &grp)
+  if (two) {
+    if (z) { ADR_RING_G(2, true, false); }
+    ADR_RING_G(2, false, false);
+  }
+  if (xsi) {
+    if (z) { ADR_RING_G(1, true, true); }
+    ADR_RING_G(1, false, true);
+  }
+  if (z) { ADR_RING_G(1, true, false); }
+  ADR_RING_G(1, false, false);
+#undef ADR_RING_G
+}
 
 bool u8_ring_supports(const adr_ctx* ctx, const U8Args& a) {
   RingPlan pl;

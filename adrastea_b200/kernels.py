@@ -332,6 +332,48 @@ class GpuKernels:
                                             m, p, n, block_size, beta)
         self._check(rc)
 
+    def matmul_nt_fp16u8_grouped(self, outputs, lhs: torch.Tensor, rhss, scaless, block_size: int,
+                                 beta: float = 0.0, zeross=None, stream=None):
+        """adr_matmul_nt_fp16u8_grouped: several u8 products over the same activations (q/k/v,
+        gate/up), as one launch of the decode kernel where it takes them."""
+        import ctypes as C
+        count = len(outputs)
+        m, p = lhs.shape
+        assert len(rhss) == count and len(scaless) == count and (zeross is None or len(zeross) == count)
+        for o, q, s in zip(outputs, rhss, scaless):
+            assert q.shape[1] == p and o.shape == (m, q.shape[0]) and s.shape == (q.shape[0], p // block_size)
+            for t in (o, q, s):
+                assert t.is_contiguous() and t.is_cuda
+        assert lhs.is_contiguous() and lhs.dtype == torch.float16
+
+        def arr(ts):
+            return (C.c_void_p * count)(*[t.data_ptr() for t in ts])
+
+        ns = (C.c_int * count)(*[q.shape[0] for q in rhss])
+        rc = self._lib.adr_matmul_nt_fp16u8_grouped(
+            self._ctx, _stream_handle(stream), count, arr(outputs), lhs.data_ptr(), arr(rhss),
+            arr(scaless), arr(zeross) if zeross is not None else None, m, p, ns, block_size, beta)
+        self._check(rc)
+
+    def silu_mul_matmul_nt_fp16u8(self, output: torch.Tensor, lhs: torch.Tensor, rhs_gate: torch.Tensor,
+                                  scales_gate: torch.Tensor, rhs_up: torch.Tensor,
+                                  scales_up: torch.Tensor, block_size: int,
+                                  zeros_gate: torch.Tensor | None = None,
+                                  zeros_up: torch.Tensor | None = None, stream=None):
+        """adr_silu_mul_matmul_nt_fp16u8: SiluMul(lhs . gate^T, lhs . up^T) in one launch of the
+        decode kernel (raises AdrError code 2 for shapes it does not take)."""
+        m, p = lhs.shape
+        n = rhs_gate.shape[0]
+        assert rhs_gate.shape == (n, p) and rhs_up.shape == (n, p) and output.shape == (m, n)
+        for t in (output, lhs, rhs_gate, rhs_up, scales_gate, scales_up):
+            assert t.is_contiguous() and t.is_cuda
+        rc = self._lib.adr_silu_mul_matmul_nt_fp16u8(
+            self._ctx, _stream_handle(stream), output.data_ptr(), lhs.data_ptr(), rhs_gate.data_ptr(),
+            scales_gate.data_ptr(), zeros_gate.data_ptr() if zeros_gate is not None else None,
+            rhs_up.data_ptr(), scales_up.data_ptr(),
+            zeros_up.data_ptr() if zeros_up is not None else None, m, p, n, block_size)
+        self._check(rc)
+
     def matmul_nt_fp16u8_ws(self, output: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor,
                             scales: torch.Tensor, block_size: int, workspace: torch.Tensor,
                             beta: float = 0.0, zeros: torch.Tensor | None = None, stream=None):

@@ -160,6 +160,10 @@ class LlamaU8:
         # against 4.30 at batch 16: every CTA normalises the rows for itself before its first MMA,
         # while the separate kernel overlaps the GEMV's prologue), so it is off by default.
         self.fuse_norm = False
+        # gate/up products + SiluMul in one launch of the decode kernel
+        # (adr_silu_mul_matmul_nt_fp16u8: same bits as the three kernels, one launch instead of two
+        # and no [tokens, 2 * ffn] round trip); used for decode batches the kernel takes
+        self.fuse_silu = True
 
     # ------------------------------------------------------------------ sizes
     def weight_bytes_per_token(self) -> int:
@@ -185,6 +189,23 @@ class LlamaU8:
         self._norm(self.x, h, norm_w)
         self.k.matmul_nt_fp16u8(out, self.x, w.q, w.scales, w.block, 0.0, w.zeros)
 
+    def _norm_gate_up_silu(self, ly) -> bool:
+        """self.g = SiluMul(gate, up) of rms_norm(self.h) in two launches (norm, fused product);
+        False if the decode kernel does not take the shape."""
+        from .kernels import AdrError
+        w, fl = ly.wgu.w, self.fl
+        self._norm(self.x, self.h, ly.ffn_norm)
+        try:
+            self.k.silu_mul_matmul_nt_fp16u8(
+                self.g, self.x, w.q[:fl], w.scales[:fl], w.q[fl:], w.scales[fl:], w.block,
+                w.zeros[:fl] if w.zeros is not None else None,
+                w.zeros[fl:] if w.zeros is not None else None)
+            return True
+        except AdrError as e:
+            if e.code != 2:  # anything but "shape not taken"
+                raise
+            return False
+
     def _silu_mul(self, out: torch.Tensor, gu: torch.Tensor):
         """out = SiluMul(gate, up), the two halves of the fused gate/up product."""
         fl = self.fl
@@ -203,8 +224,9 @@ class LlamaU8:
             self.k.decode_attention(TensorView.of(self.att), qv, self.k_cache[li], self.v_cache[li],
                                     self.Hl, self.pos, scale)
             ly.wo(self.h, self.att, self.partial, residual=True)       # store = Add, llama.rs:555-560
-            self._norm_linear(self.gu, self.h, ly.ffn_norm, ly.wgu.w)
-            self._silu_mul(self.g, self.gu)
+            if not (self.fuse_silu and self._norm_gate_up_silu(ly)):
+                self._norm_linear(self.gu, self.h, ly.ffn_norm, ly.wgu.w)
+                self._silu_mul(self.g, self.gu)
             ly.down(self.h, self.g, self.partial, residual=True)       # llama.rs:584-589
         self._norm_linear(self.logits, self.h, self.out_norm, self.lm_head)
         torch.argmax(self.logits, dim=-1, out=self.next_tokens)

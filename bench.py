@@ -407,6 +407,40 @@ def extra_zero_points(kern, timed, args, xs, outs):
             "bytes_per_step": by}
 
 
+def extra_grouped(kern, timed, args, weights, xs, outs_by):
+    """The same decode mix through adr_matmul_nt_fp16u8_grouped: per layer the four [4096,4096]
+    products as one launch and the two [11008,4096] products as another (they share their
+    activations in this workload, as q/k/v and gate/up do in a decoder layer).  Its own line:
+    the headline stays the per-launch figure."""
+    import torch
+    per_m = {}
+    total_ms = 0.0
+    for m in MS:
+        groups = []
+        for layer in weights:
+            by_n = {}
+            for n, q, s, _ in layer:
+                by_n.setdefault(n, []).append((q, s))
+            for n, lst in by_n.items():
+                o = [torch.zeros((m, n), dtype=torch.float16, device="cuda") for _ in lst]
+                groups.append((o, [q for q, _ in lst], [s for _, s in lst]))
+
+        def run(groups=groups, m=m):
+            for o, qs, ss in groups:
+                kern.matmul_nt_fp16u8_grouped(o, xs[m], qs, ss, BS)
+        rm, gm = graphed(run)
+        t = float(np.median([timed(rm, args.steps) for _ in range(max(3, args.repeats // 2))]))
+        b = LAYERS * sum(gemv_bytes(m, n) for n in NS)
+        per_m[f"M={m}"] = round(b * args.steps / (t * 1e-3) / 1e9, 1)
+        total_ms += t / args.steps
+        del gm
+    hbm, _ = measured_peak()
+    gbs = step_bytes() / (total_ms * 1e-3) / 1e9
+    return {"ms_per_step": total_ms, "gbs": gbs, "frac_of_hbm": gbs / hbm, "per_m_gbs": per_m,
+            "launches_per_step": 2 * LAYERS * len(MS),
+            "what": "adr_matmul_nt_fp16u8_grouped: 2 launches per layer instead of 6"}
+
+
 def extra_llama7b(kern, batch, prefill=512, decode=128):
     """LLaMA-7B shape, u8 weights, KV cache: `decode` graph-replayed steps after a `prefill`-token
     prefill; tokens/s and the fraction of the weight-stream ceiling (all weights once per step at
@@ -586,6 +620,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_extra:
         for name, fn in (("fp16_gemm", lambda: extra_fp16_gemm(kern, timed, args)),
                          ("u8_zero_points", lambda: extra_zero_points(kern, timed, args, xs, outs)),
+                         ("u8_grouped", lambda: extra_grouped(kern, timed, args, weights, xs, outs)),
                          ("llama7b_decode_b1", lambda: extra_llama7b(kern, 1)),
                          ("llama7b_decode_b16", lambda: extra_llama7b(kern, 16)),
                          ("clip_vit_l14_b64", lambda: extra_clip(kern, 64)),

@@ -247,6 +247,38 @@ int adr_matmul_nt_fp16u8_noalloc(adr_ctx* ctx, adr_stream stream, void* out, con
                                  int m, int p, int n, int block_size, float beta);
 
 /*
+ * `count` u8 products over the SAME activations, out_i[m, n_i] = lhs[m, p] . deq(rhs_i[n_i, p])^T +
+ * beta * out_i, for callers that keep q/k/v or gate/up as separate matrices the way the reference
+ * does (llama.rs:503-527, 565-577).  No counterpart in the reference, which launches them one by
+ * one.  For decode shapes (m <= 16, activations that fit the kernel's shared memory, block 64/128,
+ * p % 128 == 0) up to four matrices go out as ONE launch of the persistent decode kernel, whose
+ * CTAs walk the rows of all of them: one launch-to-launch gap and one load of the activations
+ * instead of one per matrix.  Results are bit-identical to separate adr_matmul_nt_fp16u8 calls
+ * with the persistent kernel.  Shapes that kernel does not take are served by separate calls.
+ * `zeross` is NULL, or an array without NULL entries.  All matrices share p, block_size and beta.
+ */
+int adr_matmul_nt_fp16u8_grouped(adr_ctx* ctx, adr_stream stream, int count, void* const* outs,
+                                 const void* lhs, const uint8_t* const* rhss,
+                                 const void* const* scaless, const void* const* zeross, int m,
+                                 int p, const int* ns, int block_size, float beta);
+
+/*
+ * out[m, n] = SiluMul(lhs . deq(rhs_gate)^T, lhs . deq(rhs_up)^T): the gate and up products of a
+ * feed-forward block (llama.rs:565-577) and the elementwise kernel that follows them
+ * (elementwise.cu:28-33) as ONE launch of the persistent decode kernel.  A CTA takes the gate unit
+ * and the up unit of the same 16 rows one after the other; both results are rounded to fp16 as
+ * the separate kernels would before fp16(g / (1 + expf(-g)) * u) is written, so the bits equal
+ * two adr_matmul_nt_fp16u8 calls (persistent kernel) followed by adr_elementwise_binary_2d_f16
+ * (SiluMul).  Decode shapes only (m <= 16, activations resident, block 64/128, p % 128 == 0), else
+ * ADR_ERR_SHAPE: make the three calls.  The two matrices may be halves of one [2n, p] matrix.
+ */
+int adr_silu_mul_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
+                                  const uint8_t* rhs_gate, const void* scales_gate,
+                                  const void* zeros_gate, const uint8_t* rhs_up,
+                                  const void* scales_up, const void* zeros_up, int m, int p, int n,
+                                  int block_size);
+
+/*
  * Replaces kernels matmul_nt_wmma_128x64x64 (matmul_nt_wmma_128x64x64.cu:8-78)
  * and matmul_nt_wmma_16x128x256 (matmul_nt_wmma_16x128x256.cu:8-68), same
  * parameter list:  out[m,n] = lhs[m,p] . rhs[n,p]^T + beta * out, contiguous

@@ -731,3 +731,52 @@ def test_matmul_f16_second_batch_dimension(kernels):
     assert torch.equal(o2.view(torch.int16), o3.view(torch.int16))
     ref2 = torch.einsum("bhsd,hdn->bhsn", a.float(), w.float())
     assert ((o2.float() - ref2).abs().max() / ref2.abs().max()).item() <= TOL
+
+
+@pytest.mark.parametrize("pdl", [0, 1])
+def test_u8_grouped_products_equal_separate_calls(kernels, pdl):
+    """adr_matmul_nt_fp16u8_grouped: q/k/v-like and gate/up-like groups over the same activations
+    give the bits of separate calls of the persistent kernel (ragged n, zero points, beta, more
+    than four matrices, both token blocks); a shape the grouped form does not take still works."""
+    rng = np.random.default_rng(311 + pdl)
+    try:
+        kernels.set_tunable("pdl", pdl)
+        for m, p, ns, bs, zp, beta in ((1, 4096, (4096, 4096, 4096), 128, False, 0.0),
+                                       (4, 4096, (11008, 11008), 128, False, 0.5),
+                                       (16, 2048, (200, 1000, 48, 333, 640), 64, True, 0.5),
+                                       (3, 1280, (64, 4000), 64, False, 0.0),
+                                       (16, 11008, (256, 272), 128, False, 0.0)):  # activations too large: separate calls
+            x = dev(rng.standard_normal((m, p)).astype(np.float16))
+            qs = [dev(rng.integers(0, 256, (n, p), dtype=np.uint8)) for n in ns]
+            ss = [dev(rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)) for n in ns]
+            zs = [dev(rng.uniform(120, 136, (n, p // bs)).astype(np.float16)) for n in ns] if zp else None
+            o0 = [(rng.standard_normal((m, n)) * 0.5).astype(np.float16) for n in ns]
+            want = []
+            kernels.force_kernel(Kernel.U8Ring)
+            for i, n in enumerate(ns):
+                o = dev(o0[i].copy())
+                kernels.matmul_nt_fp16u8(o, x, qs[i], ss[i], bs, beta, zs[i] if zp else None)
+                want.append(o)
+            kernels.force_kernel(Kernel.Auto)
+            outs = [dev(a.copy()) for a in o0]
+            n0 = kernels.launch_count()
+            kernels.matmul_nt_fp16u8_grouped(outs, x, qs, ss, bs, beta, zs)
+            launches = kernels.launch_count() - n0
+            kernels.device_status()
+            if p <= 4096:
+                assert launches == (len(ns) + 3) // 4  # four matrices per launch, a lone last one by itself
+                for i, (got, ref) in enumerate(zip(outs, want)):
+                    if len(ns) % 4 == 1 and i == len(ns) - 1:  # served by a separate call: any decode kernel
+                        w = oracle.matmul_nt_fp16u8(x.cpu().numpy(), qs[i].cpu().numpy(), ss[i].cpu().numpy(),
+                                                    bs, beta, o0[i], zs[i].cpu().numpy() if zp else None)
+                        assert oracle.max_rel_err(got.cpu().numpy(), w) <= 2e-3
+                    else:
+                        assert torch.equal(got.view(torch.int16), ref.view(torch.int16)), (m, p, ns, i)
+            else:
+                assert launches >= len(ns)
+                for got, q, s_, a0 in zip(outs, qs, ss, o0):
+                    w = oracle.matmul_nt_fp16u8(x.cpu().numpy(), q.cpu().numpy(), s_.cpu().numpy(), bs, beta, a0)
+                    assert oracle.max_rel_err(got.cpu().numpy(), w) <= 2e-3
+    finally:
+        kernels.set_tunable("pdl", 0)
+        kernels.force_kernel(Kernel.Auto)

@@ -271,3 +271,41 @@ def test_layer_norm_same_bits_as_reference(kernels, rows, lx):
         refcubin.layer_norm(r.data_ptr(), xd.data_ptr(), wd.data_ptr(), bd.data_ptr(), lx, rows, 1, lx, 1, lx, 1e-5)
         torch.cuda.synchronize()
         assert torch.equal(r.view(torch.int16), o.view(torch.int16))
+
+
+@pytest.mark.parametrize("m,p,n,bs,zp", [(1, 4096, 11008, 128, False), (4, 4096, 1000, 64, False),
+                                          (16, 2048, 333, 128, True), (7, 1280, 4000, 64, True),
+                                          (2, 4096, 16, 128, False)])
+def test_silu_mul_fused_into_the_gate_and_up_products(kernels, m, p, n, bs, zp):
+    """adr_silu_mul_matmul_nt_fp16u8 gives the bits of two adr_matmul_nt_fp16u8 calls (persistent
+    kernel) followed by the SiluMul elementwise kernel; the two matrices are the halves of one
+    [2n, p] matrix, as a harness that fuses gate and up at load time holds them."""
+    from adrastea_b200 import BinaryOp, Kernel, TensorView
+    rng = np.random.default_rng(m * 11 + n)
+    x = dev(rng.standard_normal((m, p)).astype(np.float16))
+    q = dev(rng.integers(0, 256, (2 * n, p), dtype=np.uint8))
+    s = dev(rng.uniform(0.001, 0.01, (2 * n, p // bs)).astype(np.float16))
+    z = dev(rng.uniform(120, 136, (2 * n, p // bs)).astype(np.float16)) if zp else None
+    g = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+    u = torch.zeros((m, n), dtype=torch.float16, device="cuda")
+    kernels.force_kernel(Kernel.U8Ring)
+    try:
+        kernels.matmul_nt_fp16u8(g, x, q[:n], s[:n], bs, 0.0, z[:n] if zp else None)
+        kernels.matmul_nt_fp16u8(u, x, q[n:], s[n:], bs, 0.0, z[n:] if zp else None)
+    finally:
+        kernels.force_kernel(Kernel.Auto)
+    want = torch.zeros_like(g)
+    kernels.elementwise_binary_2d_f16(TensorView.of(want), TensorView.of(g), TensorView.of(u), BinaryOp.SiluMul)
+    for pdl in (0, 1):
+        kernels.set_tunable("pdl", pdl)
+        try:
+            for _ in range(2):
+                got = torch.full((m, n), 7.0, dtype=torch.float16, device="cuda")
+                n0 = kernels.launch_count()
+                kernels.silu_mul_matmul_nt_fp16u8(got, x, q[:n], s[:n], q[n:], s[n:], bs,
+                                                  z[:n] if zp else None, z[n:] if zp else None)
+                assert kernels.launch_count() - n0 == 1
+                kernels.device_status()
+                assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (m, p, n, pdl)
+        finally:
+            kernels.set_tunable("pdl", 0)
