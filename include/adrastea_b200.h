@@ -112,8 +112,12 @@ int adr_force_kernel(adr_ctx* ctx, int kernel);
  *               Default 0.
  *   "pdl_guard": with "pdl" on, which launches of the persistent decode kernel end a chain of
  *               early starts (the launch behind them begins on an empty GPU): bit 0 = launches
- *               with two CTAs per SM, bit 1 = launches whose CTAs take a whole SM.  Default 3;
- *               0 shows what the guard is worth (CTAs then land two to an SM on half the SMs).
+ *               with two CTAs per SM (the cluster k-split kernel included), bit 1 = launches
+ *               whose CTAs take a whole SM, bit 2 = row kernels with at least one CTA per SM
+ *               (decode attention over many heads).  Default 7; 0 shows what the guard is worth
+ *               (CTAs then land two to an SM on half the SMs).
+ *   "ks_pdl":   0 = the cluster k-split kernel never starts early under "pdl" (default 1).
+ *   "ks_off":   1 = the dispatcher never picks the cluster k-split kernel (A/B runs).
  *   "ks_clusters", "ks_stages": clusters in the grid / ring stages of the cluster k-split
  *               decode kernel (0 = the planner's choice).
  *   "wait_ms":  bound, in milliseconds, of the waits on a peer GPU in adr_allreduce_oneshot and
