@@ -75,10 +75,11 @@ struct adr_ctx {
   std::atomic<int> tune_wait_ms{0};  // limit of the peer waits in milliseconds (0: about a second)
   std::atomic<int> tune_u8_cps_m{2}, tune_u8_cps_x4{16};
   std::atomic<int> tune_ks_clusters{0}, tune_ks_stages{0}, tune_ks_off{0};  // cluster k-split kernel: clusters in the grid, ring stages
-  std::atomic<int> tune_pdl_guard{7};
+  std::atomic<int> tune_pdl_guard{15};
   std::atomic<int> tune_ks_pdl{1};  // the cluster k-split kernel may start early under "pdl"  // which SM-filling launches end a chain of early starts (bit 0: two CTAs per SM, bit 1: one large CTA)
   // the last launch whose CTAs left no room beside them on an SM: its number and its stream
   std::atomic<int> fill_flag{0};
+  std::atomic<unsigned long long> fill_launch{0};
   std::atomic<uintptr_t> fill_stream{0};
 };
 
@@ -137,10 +138,15 @@ inline void note_filling_launch(adr_ctx* ctx, cudaStream_t stream, int kind_bit)
   if (ctx->tune_pdl.load() && (ctx->tune_pdl_guard.load() & kind_bit)) {
     ctx->fill_stream = reinterpret_cast<uintptr_t>(stream);
     ctx->fill_flag = 1;
+    ctx->fill_launch = ctx->launches.load() + 1;  // the number this launch is about to get
   }
 }
 inline bool behind_filling_launch(const adr_ctx* ctx, cudaStream_t stream) {
-  return ctx->fill_flag.load() != 0 && ctx->fill_stream.load() == reinterpret_cast<uintptr_t>(stream);
+  if (ctx->fill_flag.load() == 0 || ctx->fill_stream.load() != reinterpret_cast<uintptr_t>(stream))
+    return false;
+  // bit 3 of the guard: the mark survives small kernels launched in between; without it only
+  // the launch directly behind the filling one is held back
+  return (ctx->tune_pdl_guard.load() & 8) != 0 || ctx->fill_launch.load() == ctx->launches.load();
 }
 
 inline long long peer_wait_cycles(const adr_ctx* ctx) {

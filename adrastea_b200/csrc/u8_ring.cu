@@ -910,9 +910,8 @@ int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
     ctx->last_cuda_error = (int)e;
     return ADR_ERR_CUDA;
   }
-  const int rc2 = after_launch(ctx);
   if (fill_kind) note_filling_launch(ctx, stream, fill_kind);
-  return rc2;
+  return after_launch(ctx);
 }
 
 template <int MT, bool Z, bool PDL, int NCW, bool XR>
