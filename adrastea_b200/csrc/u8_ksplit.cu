@@ -94,10 +94,11 @@ __device__ __forceinline__ void st_async_f32x4(uint32_t addr, float a, float b, 
       "f"(a), "f"(b), "f"(c), "f"(d), "r"(remote_bar)
       : "memory");
 }
-// One arrival on an mbarrier of another CTA of the cluster; orders this thread's earlier
-// stores (to that CTA's shared memory included) before it.
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t remote_bar) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar)
+// One arrival on an mbarrier of another CTA of the cluster, without ordering anything: for a
+// signal whose only precondition the sender has
+// already made sure of by other means.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t remote_bar) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote_bar)
                : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, unsigned parity) {
@@ -466,14 +467,29 @@ __global__ void __launch_bounds__(KS_THREADS, 2)
           v[e] += f.x, v[e + 1] += f.y, v[e + 2] += f.z, v[e + 3] += f.w;
         }
       }
-      // if the slot has another use: announce it, then tell every CTA of the cluster that it may
+      // If the slot has another use: announce it, then tell every CTA of the cluster that it may
       // push again (every such arrival is waited for by its receiver before that push, so none
-      // can reach a CTA that has already left)
+      // can reach a CTA that has already left).  The arrival carries no fence (a release at
+      // cluster scope here cost 6-9 % of the whole launch); what it must follow is only this
+      // warp's own reads of the slot, and it does: its address is made to depend on the sums of
+      // everything read, so it cannot issue before those loads have returned their data.
       __syncwarp();
       if (j + S * KS_INB < J) {
         if (lane == 0) mbar_expect_tx(&inbox_full[slot], (unsigned)(S * 16 * TOK * 4));
         __syncwarp();
-        if (lane < S) mbar_arrive_cluster(map_to_rank(smem_u32(&credit[rank * KS_INB + slot]), (uint32_t)lane));
+        float all = 0.0f;
+#pragma unroll
+        for (int e = 0; e < OPL; ++e) all += v[e];
+        all += __shfl_xor_sync(0xffffffffu, all, 16);
+        all += __shfl_xor_sync(0xffffffffu, all, 8);
+        all += __shfl_xor_sync(0xffffffffu, all, 4);
+        all += __shfl_xor_sync(0xffffffffu, all, 2);
+        all += __shfl_xor_sync(0xffffffffu, all, 1);
+        uint32_t nothing;
+        asm volatile("and.b32 %0, %1, 0;" : "=r"(nothing) : "r"(__float_as_uint(all)));
+        if (lane < S)
+          mbar_arrive_cluster_relaxed(
+              map_to_rank(smem_u32(&credit[rank * KS_INB + slot]), (uint32_t)lane) + nothing);
       }
       const int n0 = (q + j * p.Q) * 16;
       __half* optr = a.out + (size_t)tok * a.n + n0 + row0;
