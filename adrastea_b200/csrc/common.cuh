@@ -78,6 +78,7 @@ struct adr_ctx {
   std::atomic<int> tune_pdl_guard{15};
   std::atomic<int> tune_ks_pdl{1};  // the cluster k-split kernel may start early under "pdl"  // which SM-filling launches end a chain of early starts (bit 0: two CTAs per SM, bit 1: one large CTA)
   // the last launch whose CTAs left no room beside them on an SM: its number and its stream
+  std::atomic<int> small_before{0};  // the last launch through this context was a small row kernel
   std::atomic<int> fill_flag{0};
   std::atomic<unsigned long long> fill_launch{0};
   std::atomic<uintptr_t> fill_stream{0};

@@ -711,6 +711,8 @@ int launch_row(adr_ctx* ctx, cudaStream_t stream, void (*plain)(KArgs...), void 
   // like a large product does: the decode kernel's half-SM form must not start as it drains
   if ((long long)grid.x * grid.y * grid.z >= (ctx->sm_count > 0 ? ctx->sm_count : 148))
     note_filling_launch(ctx, stream, 4);
+  else
+    ctx->small_before = 1;
   return after_launch(ctx);
 }
 

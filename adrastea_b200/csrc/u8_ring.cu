@@ -911,6 +911,7 @@ int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
     return ADR_ERR_CUDA;
   }
   if (fill_kind) note_filling_launch(ctx, stream, fill_kind);
+  ctx->small_before = 0;
   return after_launch(ctx);
 }
 

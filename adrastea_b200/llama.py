@@ -224,7 +224,8 @@ class LlamaU8:
             self.k.decode_attention(TensorView.of(self.att), qv, self.k_cache[li], self.v_cache[li],
                                     self.Hl, self.pos, scale)
             ly.wo(self.h, self.att, self.partial, residual=True)       # store = Add, llama.rs:555-560
-            if not (self.fuse_silu and self._norm_gate_up_silu(ly)):
+            # (from five tokens on the cluster kernel + the elementwise kernel are as fast or faster)
+            if not (self.fuse_silu and self.h.shape[0] <= 4 and self._norm_gate_up_silu(ly)):
                 self._norm_linear(self.gu, self.h, ly.ffn_norm, ly.wgu.w)
                 self._silu_mul(self.g, self.gu)
             ly.down(self.h, self.g, self.partial, residual=True)       # llama.rs:584-589
