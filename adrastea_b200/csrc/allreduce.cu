@@ -159,5 +159,6 @@ extern "C" int adr_allreduce_oneshot(adr_ctx* ctx, adr_stream stream, void* out,
     ctx->last_cuda_error = (int)e;
     return ADR_ERR_CUDA;
   }
+  ctx->small_before = 1;  // a small kernel that holds its CTA slots while it waits for the peers
   return after_launch(ctx);
 }
