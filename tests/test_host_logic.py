@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from adrastea_b200 import (MatmulLoad, MatmulMask, MatmulOptions, MatmulStore, MatmulStoreOp,
-                           TensorView, lower_matmul)
+                           TensorLayout, TensorView, lower_matmul)
 
 ROOT = Path(__file__).resolve().parents[1]
 
@@ -98,3 +98,41 @@ def test_strerror_needs_no_gpu():
     lib = _lib.load()
     assert lib.adr_strerror(0) == b"ok"
     assert b"shape" in lib.adr_strerror(2)
+
+
+def test_every_error_code_has_its_own_text():
+    from adrastea_b200 import _lib
+    lib = _lib.load()
+    texts = [lib.adr_strerror(c) for c in range(8)]
+    assert len(set(texts)) == 8 and b"unknown" not in b" ".join(texts)
+    assert b"built-in scratch" in lib.adr_strerror(7)
+    assert lib.adr_strerror(99) == b"unknown error"
+
+
+def test_entry_points_refuse_a_missing_context_before_touching_a_gpu():
+    """Argument checks come first: with no context (and no GPU) the calls return ADR_ERR_INVALID."""
+    import ctypes as C
+    from adrastea_b200 import _lib
+    lib = _lib.load()
+    buf = C.create_string_buffer(64)
+    p = C.cast(buf, C.c_void_p)
+    ptrs = (C.c_void_p * 2)(p, p)
+    ns = (C.c_int * 2)(16, 16)
+    assert lib.adr_matmul_nt_fp16u8(None, None, p, p, p, p, None, 1, 128, 16, 128, 0.0) == 1
+    assert lib.adr_matmul_nt_fp16u8_ws(None, None, p, p, p, p, None, 1, 128, 16, 128, 0.0, p, 64) == 1
+    assert lib.adr_matmul_nt_fp16u8_noalloc(None, None, p, p, p, p, None, 1, 128, 16, 128, 0.0) == 1
+    assert lib.adr_matmul_nt_fp16u8_grouped(None, None, 2, ptrs, p, ptrs, ptrs, None, 1, 128, ns, 128, 0.0) == 1
+    assert lib.adr_silu_mul_matmul_nt_fp16u8(None, None, p, p, p, p, None, p, p, None, 1, 128, 16, 128) == 1
+    assert lib.adr_set_tunable(None, b"pdl", 1) != 0
+
+
+def test_lowering_of_rank_four_views_keeps_the_inner_batch():
+    """A rank-4 output lowers to the inner batch count and z strides; the outer dimension's
+    stride is what adr_matmul_f16_b2 takes next to them."""
+    o = TensorView(None, TensorLayout.new((3, 4, 72, 72), (4 * 72 * 72, 72 * 72, 72, 1)))
+    q = TensorView(None, TensorLayout.new((3, 4, 72, 64), (72 * 256, 64, 256, 1)))
+    k = TensorView(None, TensorLayout.new((3, 4, 64, 72), (72 * 256, 64, 1, 256)))
+    low = lower_matmul(o, q, k, MatmulOptions.new())
+    assert low[:4] == (4, 72, 64, 72)
+    assert low[4:13] == (1, 72, 72 * 72, 1, 256, 64, 256, 1, 64)
+    assert (o.stride(-4), q.stride(-4), k.stride(-4)) == (4 * 72 * 72, 72 * 256, 72 * 256)
