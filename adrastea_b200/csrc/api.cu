@@ -163,6 +163,7 @@ int adr_set_tunable(adr_ctx* ctx, const char* name, int value) {
   else if (!strcmp(name, "ks_stages")) ctx->tune_ks_stages = value;
   else if (!strcmp(name, "ks_off")) ctx->tune_ks_off = value;
   else if (!strcmp(name, "ks_pdl")) ctx->tune_ks_pdl = value;
+  else if (!strcmp(name, "ks_slack")) ctx->tune_ks_slack = value;
   else if (!strcmp(name, "u8_cps_m")) ctx->tune_u8_cps_m = value;
   else if (!strcmp(name, "u8_cps_x4")) ctx->tune_u8_cps_x4 = value;
   else return ADR_ERR_INVALID;

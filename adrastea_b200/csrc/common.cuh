@@ -74,7 +74,7 @@ struct adr_ctx {
   std::atomic<int> tune_pdl{0};      // programmatic dependent launch of the decode and row kernels
   std::atomic<int> tune_wait_ms{0};  // limit of the peer waits in milliseconds (0: about a second)
   std::atomic<int> tune_u8_cps_m{2}, tune_u8_cps_x4{16};
-  std::atomic<int> tune_ks_clusters{0}, tune_ks_stages{0}, tune_ks_off{0};  // cluster k-split kernel: clusters in the grid, ring stages
+  std::atomic<int> tune_ks_clusters{0}, tune_ks_stages{0}, tune_ks_off{0}, tune_ks_slack{1};  // cluster k-split kernel: clusters in the grid, ring stages
   std::atomic<int> tune_pdl_guard{15};
   std::atomic<int> tune_ks_pdl{1};  // the cluster k-split kernel may start early under "pdl"  // which SM-filling launches end a chain of early starts (bit 0: two CTAs per SM, bit 1: one large CTA)
   // the last launch whose CTAs left no room beside them on an SM: its number and its stream

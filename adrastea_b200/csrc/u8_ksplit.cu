@@ -647,13 +647,16 @@ int launch_ksplit_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ks
       it = known.emplace(key, std::max(1, nc - 1)).first;
     }
     qmax = it->second;
-    // Behind a small kernel of this library that started early (a norm, an elementwise op) some
-    // of its CTAs still hold a slot each when this launch's clusters are placed, and with the
-    // registers of an SM fully taken by two CTAs of the 16-token form, a cluster that finds no
-    // room runs as a second wave.  Leave room for about sixteen such CTAs then (measured in a
-    // LLaMA-7B decode step at batch 16: 4.37 -> 3.99 ms; in chains of products alone the full
-    // grid is 10 % quicker on some shapes, so it stays there).
-    if (PDL && MT == 2 && ctx->small_before.load() != 0) qmax = std::max(1, qmax - (16 + pl.S - 1) / pl.S);
+    // Behind a small kernel of this library that started early (a norm, an elementwise op, the
+    // all-reduce) some of its CTAs still hold a slot each when this launch's clusters are
+    // placed, and a cluster that finds no room runs as a second wave.  Leave room for about
+    // sixteen such CTAs then (tunable "ks_slack", default on; measured in a LLaMA-7B decode
+    // step: 4.37 -> 3.99 ms at batch 16, 3.14 -> 2.70 ms at batch 5; in chains of products
+    // alone the full grid is 10 % quicker on some shapes, so it stays there).  Capping the kernel at 88
+    // registers so that such a CTA fits beside two of this kernel's was tried instead: 7-10 %
+    // slower in chains of products, and no cure.
+    if (PDL && ctx->tune_ks_slack.load() != 0 && ctx->small_before.load() != 0)
+      qmax = std::max(1, qmax - (16 + pl.S - 1) / pl.S);
   }
   ctx->small_before = 0;
   const int units = (a.n + 15) / 16;

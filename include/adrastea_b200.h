@@ -121,6 +121,9 @@ int adr_force_kernel(adr_ctx* ctx, int kernel);
  *               faster at batch 4 and 1 % slower at batch 1.
  *   "ks_pdl":   0 = the cluster k-split kernel never starts early under "pdl" (default 1).
  *   "ks_off":   1 = the dispatcher never picks the cluster k-split kernel (A/B runs).
+ *   "ks_slack": 1 (default) = behind a small kernel of this library the cluster k-split kernel
+ *               leaves about sixteen CTA slots of its grid unused, so that none of its clusters
+ *               is pushed into a second wave by CTAs that started early and are still waiting.
  *   "ks_clusters", "ks_stages": clusters in the grid / ring stages of the cluster k-split
  *               decode kernel (0 = the planner's choice).
  *   "wait_ms":  bound, in milliseconds, of the waits on a peer GPU in adr_allreduce_oneshot and
