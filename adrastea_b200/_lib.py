@@ -42,6 +42,9 @@ SIGNATURES = {
                                               C.POINTER(_vp), C.POINTER(_vp), _c_int, _c_int,
                                               C.POINTER(_c_int), _c_int, C.c_float]),
     "adr_silu_mul_matmul_nt_fp16u8": (_c_int, [_vp] * 10 + [_c_int] * 4),
+    "adr_qkv_rope_append_matmul_nt_fp16u8": (_c_int, [_vp, _vp, _vp, _c_int, _vp, _vp, C.c_float, _vp,
+                                                      _vp, _vp, _c_int, _c_int, _c_int, _c_int,
+                                                      _c_int, _vp, _vp, _c_int, _vp, C.c_float]),
     "adr_matmul_nt_f16": (_c_int, [_vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int, C.c_float]),
     "adr_dequantize_absmax_uint8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),
     "adr_quantize_absmax_uint8": (_c_int, [_vp, _vp, _vp, _vp, _vp, _c_int, _c_int, _c_int]),

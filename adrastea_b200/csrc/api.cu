@@ -437,6 +437,33 @@ int adr_rms_norm_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, co
   return rc;
 }
 
+int adr_qkv_rope_append_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* q_out,
+                                         int stride_q, const void* lhs, const void* norm_weights,
+                                         float eps, const uint8_t* rhs, const void* scales,
+                                         const void* zeros, int m, int p, int width, int n_heads,
+                                         int block_size, void* k_cache, void* v_cache, int max_seq,
+                                         const int32_t* pos_dev, float theta) {
+  if (!ctx || !q_out || !lhs || !rhs || !scales || !k_cache || !v_cache || !pos_dev) return ADR_ERR_INVALID;
+  DeviceGuard guard(ctx);
+  if (m <= 0 || p <= 0 || width <= 0 || n_heads <= 0 || block_size <= 0 || max_seq <= 0)
+    return ADR_ERR_INVALID;
+  if (m > 16 || p % block_size != 0) return ADR_ERR_SHAPE;
+  // units of 16 columns must lie inside one of the q, k, v sections; heads hold whole pairs
+  if (width % 16 != 0 || width % n_heads != 0 || (width / n_heads) % 2 != 0 || stride_q < width)
+    return ADR_ERR_SHAPE;
+  if (!aligned16(lhs) || !aligned16(rhs) || (norm_weights && !aligned16(norm_weights))) return ADR_ERR_SHAPE;
+  U8Args a{(__half*)q_out, (const __half*)lhs, rhs, (const __half*)scales, (const __half*)zeros,
+           m, p, 3 * width, block_size, 0.0f};
+  a.norm_w = (const __half*)norm_weights;
+  a.norm_eps = eps;
+  if (!u8_ring_supports(ctx, a)) return ADR_ERR_SHAPE;
+  RingRope rope{(__half*)k_cache, (__half*)v_cache, width, n_heads, max_seq, stride_q,
+                (const int*)pos_dev, theta};
+  int rc = launch_u8_ring(ctx, (cudaStream_t)stream, a, nullptr, &rope);
+  if (rc == ADR_OK) ctx->last_kernel = ADR_KERNEL_U8_RING;
+  return rc;
+}
+
 int adr_matmul_nt_fp16u8_allreduce(adr_ctx* ctx, adr_stream stream, void* out, const void* lhs,
                                    const uint8_t* rhs, const void* scales, const void* zeros, int m,
                                    int p, int n, int block_size, int residual,

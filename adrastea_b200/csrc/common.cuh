@@ -172,6 +172,27 @@ inline int after_launch(adr_ctx* ctx, int nlaunches = 1) {
 // __half; SCALE and ADD then compute in fp16, the bias/gelu/beta forms in
 // fp32 with `inner + beta * old` contracted to one fma.
 // ---------------------------------------------------------------------------
+// The rotation of rotary.cu:4-29 for one (even, odd) pair: shared by the row kernel, the
+// decode-time append kernel and the decode product's fused epilogue, so that they agree to the bit.
+struct Turn {
+  float c, s;
+};
+__device__ __forceinline__ Turn rope_turn(int position, int col_in_head, int head_dim, float theta) {
+  const float phase = position / powf(theta, float(col_in_head) / head_dim);
+  Turn w;
+  w.c = cosf(phase);
+  w.s = sinf(phase);
+  return w;
+}
+__device__ __forceinline__ __half2 rope_apply(__half even, __half odd, Turn w) {
+  const float x = __half2float(even), y = __half2float(odd);
+  // The contraction is written out (second product rounded, first one fused into the sum: what
+  // the compiler makes of `x * c - y * s` in the reference kernel), so that every caller gets the
+  // same bits whatever code surrounds the call.
+  return __halves2half2(__float2half(__fmaf_rn(x, w.c, -__fmul_rn(y, w.s))),
+                        __float2half(__fmaf_rn(x, w.s, __fmul_rn(y, w.c))));
+}
+
 __device__ __forceinline__ float gelu_tanh(float t) {
   return 0.5f * t * (1.0f + tanhf(0.7978845608028654f * (t + 0.044715f * t * t * t)));
 }
@@ -273,7 +294,17 @@ struct RingArFuse {
   unsigned int* epochs;
   int rank, world, residual, max_ctas;
 };
-int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingArFuse* ar = nullptr);
+// Optional epilogue of the ring kernel for a fused q/k/v projection at decode time: rotary
+// embedding of q and k, k and v appended to the cache at position *pos.
+struct RingRope {
+  __half* k_cache;
+  __half* v_cache;
+  int width, n_heads, max_seq, q_pitch;
+  const int* pos;
+  float theta;
+};
+int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingArFuse* ar = nullptr,
+                   const RingRope* rope = nullptr);
 // up to four weight matrices multiplied by the same activations in one launch
 struct RingGroup {
   int count;

@@ -197,21 +197,6 @@ __global__ void __launch_bounds__(ROW_THREADS)
 // (cos, sin) pair and applied as a 2x2 rotation; the decode-time kernel below applies the
 // same pair to the query and to the key.
 // ---------------------------------------------------------------------------------------
-struct Turn {
-  float c, s;
-};
-__device__ __forceinline__ Turn rope_turn(int position, int col_in_head, int head_dim, float theta) {
-  const float phase = position / powf(theta, float(col_in_head) / head_dim);
-  Turn w;
-  w.c = cosf(phase);
-  w.s = sinf(phase);
-  return w;
-}
-__device__ __forceinline__ __half2 rope_apply(__half even, __half odd, Turn w) {
-  const float x = __half2float(even), y = __half2float(odd);
-  return __halves2half2(__float2half(x * w.c - y * w.s), __float2half(x * w.s + y * w.c));
-}
-
 // One thread per 2-vector; blockIdx.y / threadIdx.y walk the rows (positions pos_offset + row).
 template <bool PDL>
 __global__ void __launch_bounds__(256)

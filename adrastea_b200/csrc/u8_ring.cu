@@ -129,6 +129,14 @@ struct RingParams {
   // fused rms_norm of the activations (norm_w != nullptr; resident activations only)
   const __half* norm_w;
   float norm_eps;
+  // fused rotary embedding + KV-cache append (the product is a fused q/k/v projection of 3 x
+  // rope_width columns): q is rotated and written to out with row pitch rope_q_pitch, k is rotated
+  // into k_cache[token][*rope_pos], v copied into v_cache[token][*rope_pos]
+  int rope_width, rope_heads, rope_max_seq, rope_q_pitch;
+  const int* rope_pos;
+  float rope_theta;
+  __half* rope_k_cache;
+  __half* rope_v_cache;
 };
 
 // MT: 8-token column blocks.  NCW: consumer warps (a multiple of 8).
@@ -529,7 +537,7 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
 #pragma unroll
         for (int j = 0; j < OPL; ++j) {
           const int e = ROTATE ? lane + 32 * j : tid - 32, row = e & 15, tok = e >> 4;
-          old[j] = (tok < a.m && n0 + row < rows && !paired)
+          old[j] = (tok < a.m && n0 + row < rows && !paired && !(FUSE && p.rope_width > 0))
                        ? reinterpret_cast<const unsigned short*>(out)[(size_t)tok * rows + n0 + row]
                        : (unsigned short)0;
         }
@@ -620,6 +628,38 @@ __global__ void __launch_bounds__((NCW + 1) * 32, (NCW == 8 && MT == 1) ? 2 : 1)
         named_bar_arrive(1 + rbuf, NCW * 32);
       } else {
         named_bar_sync(1 + rbuf, NCW * 32);
+        if (FUSE && p.rope_width > 0) {
+          // ---- rotary embedding + cache append on the way out (decode_rope_append's arithmetic on
+          // the fp16-rounded products).  Columns come in (even, odd) pairs held by neighbouring
+          // lanes; a unit of 16 columns lies inside one of the q, k, v sections.
+          const int pos = *p.rope_pos;
+          const int sect = n0 / p.rope_width, c0 = n0 - sect * p.rope_width;
+          const int head_dim = p.rope_width / p.rope_heads;
+#pragma unroll
+          for (int j = 0; j < OPL; ++j) {
+            const int e = ROTATE ? lane + 32 * j : tid - 32, row = e & 15, tok = e >> 4;
+            float v = 0.0f;
+            if (tok < a.m) {
+#pragma unroll
+              for (int w = 0; w < NCW; ++w) v += rb[(size_t)w * 16 * RED_LD + row * RED_LD + tok];
+            }
+            const __half mine = __float2half_rn(v);
+            const __half other = __ushort_as_half(
+                (unsigned short)__shfl_xor_sync(0xffffffffu, (unsigned int)__half_as_ushort(mine), 1));
+            if (tok < a.m && pos >= 0 && pos < p.rope_max_seq) {
+              const int col = c0 + row;
+              __half res = mine;
+              if (sect < 2) {
+                const __half2 turned = (row & 1) ? rope_apply(other, mine, rope_turn(pos, (col - 1) % head_dim, head_dim, p.rope_theta))
+                                                 : rope_apply(mine, other, rope_turn(pos, col % head_dim, head_dim, p.rope_theta));
+                res = (row & 1) ? __high2half(turned) : __low2half(turned);
+              }
+              if (sect == 0) out[(size_t)tok * p.rope_q_pitch + col] = res;
+              else if (sect == 1) p.rope_k_cache[((size_t)tok * p.rope_max_seq + pos) * p.rope_width + col] = res;
+              else p.rope_v_cache[((size_t)tok * p.rope_max_seq + pos) * p.rope_width + col] = res;
+            }
+          }
+        } else
 #pragma unroll
         for (int j = 0; j < OPL; ++j) {
           const int e = ROTATE ? lane + 32 * j : tid - 32, row = e & 15, tok = e >> 4;
@@ -808,7 +848,7 @@ bool plan_ring(const adr_ctx* ctx, const U8Args& a, RingPlan& pl, size_t extra =
 // n = 16 x the total number of units.
 template <int MT, bool Z, bool PDL, int NCW, bool XR, bool FUSE, bool XSI, bool G = false>
 int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl,
-                  const RingArFuse* ar, const RingGroup* grp = nullptr) {
+                  const RingArFuse* ar, const RingGroup* grp = nullptr, const RingRope* rope = nullptr) {
   auto kfn = u8_ring_kernel<MT, NCW, Z, PDL, XR, FUSE, XSI, G>;
   cudaError_t e;
   if (int rc0 = opt_in_smem(ctx, kfn, 226 * 1024); rc0 != ADR_OK) return rc0;
@@ -868,6 +908,17 @@ int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
   p.status = ctx->d_status;
   p.norm_w = a.norm_w;
   p.norm_eps = a.norm_eps;
+  p.rope_width = 0;
+  if (rope) {
+    p.rope_width = rope->width;
+    p.rope_heads = rope->n_heads;
+    p.rope_max_seq = rope->max_seq;
+    p.rope_q_pitch = rope->q_pitch;
+    p.rope_pos = rope->pos;
+    p.rope_theta = rope->theta;
+    p.rope_k_cache = rope->k_cache;
+    p.rope_v_cache = rope->v_cache;
+  }
   p.ar_world = 0;
   p.ar_wait_cycles = peer_wait_cycles(ctx);
   if (ar) {
@@ -917,19 +968,19 @@ int launch_ring_f(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const Ring
 
 template <int MT, bool Z, bool PDL, int NCW, bool XR>
 int launch_ring_p(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingPlan& pl,
-                  const RingArFuse* ar) {
+                  const RingArFuse* ar, const RingRope* rope) {
   // Two to eight tokens: the activation sums ride along in the main loop (measured 3-9 %
   // quicker than making the table first); one token, or more than eight, make the table (3 %
   // quicker: the loop is the bottleneck there).
   if constexpr (MT == 1 && !XR) {
     if (a.m >= 2) {
-      if (ar != nullptr || a.norm_w != nullptr)
-        return launch_ring_f<MT, Z, PDL, NCW, XR, true, true>(ctx, stream, a, pl, ar);
+      if (ar != nullptr || a.norm_w != nullptr || rope != nullptr)
+        return launch_ring_f<MT, Z, PDL, NCW, XR, true, true>(ctx, stream, a, pl, ar, nullptr, rope);
       return launch_ring_f<MT, Z, PDL, NCW, XR, false, true>(ctx, stream, a, pl, ar);
     }
   }
-  if (ar != nullptr || a.norm_w != nullptr)
-    return launch_ring_f<MT, Z, PDL, NCW, XR, true, false>(ctx, stream, a, pl, ar);
+  if (ar != nullptr || a.norm_w != nullptr || rope != nullptr)
+    return launch_ring_f<MT, Z, PDL, NCW, XR, true, false>(ctx, stream, a, pl, ar, nullptr, rope);
   return launch_ring_f<MT, Z, PDL, NCW, XR, false, false>(ctx, stream, a, pl, ar);
 }
 
@@ -982,16 +1033,18 @@ bool u8_ring_supports(const adr_ctx* ctx, const U8Args& a) {
   return plan_ring(ctx, a, pl);
 }
 
-int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingArFuse* ar) {
+int launch_u8_ring(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, const RingArFuse* ar,
+                   const RingRope* rope) {
   RingPlan pl;
   if (!plan_ring(ctx, a, pl)) return ADR_ERR_SHAPE;
+  if (rope && (pl.xr || a.beta != 0.0f)) return ADR_ERR_SHAPE;
   const bool z = a.zeros != nullptr, two = a.m > 8, pdl = ctx->tune_pdl != 0;
 #define ADR_RING_CASE(MT, Z)                                                       \
   if (pl.xr)                                                                       \
-    return pdl ? launch_ring_p<MT, Z, true, 8, true>(ctx, stream, a, pl, ar)       \
-               : launch_ring_p<MT, Z, false, 8, true>(ctx, stream, a, pl, ar);     \
-  return pdl ? launch_ring_p<MT, Z, true, 8, false>(ctx, stream, a, pl, ar)        \
-             : launch_ring_p<MT, Z, false, 8, false>(ctx, stream, a, pl, ar)
+    return pdl ? launch_ring_p<MT, Z, true, 8, true>(ctx, stream, a, pl, ar, rope)       \
+               : launch_ring_p<MT, Z, false, 8, true>(ctx, stream, a, pl, ar, rope);     \
+  return pdl ? launch_ring_p<MT, Z, true, 8, false>(ctx, stream, a, pl, ar, rope)        \
+             : launch_ring_p<MT, Z, false, 8, false>(ctx, stream, a, pl, ar, rope)
   if (two) {
     if (z) { ADR_RING_CASE(2, true); }
     ADR_RING_CASE(2, false);

@@ -374,6 +374,26 @@ class GpuKernels:
             zeros_up.data_ptr() if zeros_up is not None else None, m, p, n, block_size)
         self._check(rc)
 
+    def qkv_rope_append_matmul_nt_fp16u8(self, q_out: torch.Tensor, lhs: torch.Tensor,
+                                         rhs: torch.Tensor, scales: torch.Tensor, block_size: int,
+                                         n_heads: int, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                                         pos: torch.Tensor, theta: float,
+                                         norm_weights: torch.Tensor | None = None, eps: float = 0.0,
+                                         zeros: torch.Tensor | None = None, stream=None):
+        """adr_qkv_rope_append_matmul_nt_fp16u8: fused q/k/v product (+ rms_norm) + rotary + cache
+        append in one launch; q_out is a [m, width] view (row pitch q_out.stride(0))."""
+        m, p = lhs.shape
+        width = rhs.shape[0] // 3
+        assert rhs.shape == (3 * width, p) and q_out.shape == (m, width) and q_out.stride(1) == 1
+        assert k_cache.shape[2] == width and v_cache.shape == k_cache.shape and k_cache.shape[0] >= m
+        assert pos.dtype == torch.int32 and pos.is_cuda
+        rc = self._lib.adr_qkv_rope_append_matmul_nt_fp16u8(
+            self._ctx, _stream_handle(stream), q_out.data_ptr(), q_out.stride(0), lhs.data_ptr(),
+            norm_weights.data_ptr() if norm_weights is not None else None, eps, rhs.data_ptr(),
+            scales.data_ptr(), zeros.data_ptr() if zeros is not None else None, m, p, width, n_heads,
+            block_size, k_cache.data_ptr(), v_cache.data_ptr(), k_cache.shape[1], pos.data_ptr(), theta)
+        self._check(rc)
+
     def matmul_nt_fp16u8_ws(self, output: torch.Tensor, lhs: torch.Tensor, rhs: torch.Tensor,
                             scales: torch.Tensor, block_size: int, workspace: torch.Tensor,
                             beta: float = 0.0, zeros: torch.Tensor | None = None, stream=None):

@@ -164,6 +164,13 @@ class LlamaU8:
         # (adr_silu_mul_matmul_nt_fp16u8: same bits as the three kernels, one launch instead of two
         # and no [tokens, 2 * ffn] round trip); used for decode batches the kernel takes
         self.fuse_silu = True
+        # q/k/v product + rotary + cache append (+ rms_norm with fuse_norm) in one launch of the
+        # decode kernel (adr_qkv_rope_append_matmul_nt_fp16u8: same bits as the separate kernels).
+        # One or two launches fewer per layer, but measured slower (2.18 -> 2.25 ms per step at
+        # batch 1, 2.90 -> 3.25 at batch 4): the kernel's form with fused ops is slower than the
+        # plain one by more than the small kernels cost when they overlap their neighbours under
+        # programmatic dependent launch.  Off by default.
+        self.fuse_rope = False
 
     # ------------------------------------------------------------------ sizes
     def weight_bytes_per_token(self) -> int:
@@ -188,6 +195,26 @@ class LlamaU8:
                     raise
         self._norm(self.x, h, norm_w)
         self.k.matmul_nt_fp16u8(out, self.x, w.q, w.scales, w.block, 0.0, w.zeros)
+
+    def _norm_qkv_rope(self, ly, li: int) -> bool:
+        """q (rotated) into self.qkv[:, :dl], k (rotated) and v into the caches of layer li, from
+        rms_norm(self.h), in one launch; False if the decode kernel does not take the shape."""
+        from .kernels import AdrError
+        w = ly.wqkv.w
+        src = self.h
+        if not self.fuse_norm:
+            self._norm(self.x, self.h, ly.attn_norm)
+            src = self.x
+        try:
+            self.k.qkv_rope_append_matmul_nt_fp16u8(
+                self.qkv[:, :self.dl], src, w.q, w.scales, w.block, self.Hl, self.k_cache[li],
+                self.v_cache[li], self.pos, self.shape.theta,
+                ly.attn_norm if self.fuse_norm else None, self.shape.norm_eps, w.zeros)
+            return True
+        except AdrError as e:
+            if e.code != 2:  # anything but "shape not taken"
+                raise
+            return False
 
     def _norm_gate_up_silu(self, ly) -> bool:
         """self.g = SiluMul(gate, up) of rms_norm(self.h) in two launches (norm, fused product);
@@ -218,9 +245,10 @@ class LlamaU8:
         qv, kv, vv = (TensorView.of(self.qkv[:, i * dl:(i + 1) * dl]) for i in range(3))
         scale = 1.0 / math.sqrt(sh.head_dim)
         for li, ly in enumerate(self.layers):
-            self._norm_linear(self.qkv, self.h, ly.attn_norm, ly.wqkv.w)
-            self.k.decode_rope_append(qv, kv, vv, self.k_cache[li], self.v_cache[li], self.Hl,
-                                      self.pos, sh.theta)
+            if not (self.fuse_rope and self.h.shape[0] <= 4 and self._norm_qkv_rope(ly, li)):
+                self._norm_linear(self.qkv, self.h, ly.attn_norm, ly.wqkv.w)
+                self.k.decode_rope_append(qv, kv, vv, self.k_cache[li], self.v_cache[li], self.Hl,
+                                          self.pos, sh.theta)
             self.k.decode_attention(TensorView.of(self.att), qv, self.k_cache[li], self.v_cache[li],
                                     self.Hl, self.pos, scale)
             ly.wo(self.h, self.att, self.partial, residual=True)       # store = Add, llama.rs:555-560

@@ -289,6 +289,24 @@ int adr_silu_mul_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* out, co
                                   int block_size);
 
 /*
+ * The fused q/k/v projection of a decode step together with what follows it: rhs is [3 * width, p]
+ * (q rows, then k rows, then v rows); q is rotated (adr_rotary's formula at position *pos_dev) and
+ * written to q_out[m, width] with row pitch stride_q, k is rotated into k_cache[token, pos, :],
+ * v is copied into v_cache[token, pos, :] (caches [m or more, max_seq, width] fp16).  With
+ * norm_weights non-NULL the rows of lhs are rms-normalised first (adr_rms_norm's bits).  One
+ * launch of the persistent decode kernel instead of adr_(rms_norm +) matmul_nt_fp16u8 +
+ * adr_decode_rope_append, same bits.  No counterpart in the reference (no KV cache there).
+ * Decode shapes only (m <= 16, activations resident, block 64/128, p % 128 == 0, width % 16 == 0),
+ * else ADR_ERR_SHAPE: make the separate calls.  A position outside [0, max_seq) writes nothing.
+ */
+int adr_qkv_rope_append_matmul_nt_fp16u8(adr_ctx* ctx, adr_stream stream, void* q_out,
+                                         int stride_q, const void* lhs, const void* norm_weights,
+                                         float eps, const uint8_t* rhs, const void* scales,
+                                         const void* zeros, int m, int p, int width, int n_heads,
+                                         int block_size, void* k_cache, void* v_cache, int max_seq,
+                                         const int32_t* pos_dev, float theta);
+
+/*
  * Replaces kernels matmul_nt_wmma_128x64x64 (matmul_nt_wmma_128x64x64.cu:8-78)
  * and matmul_nt_wmma_16x128x256 (matmul_nt_wmma_16x128x256.cu:8-68), same
  * parameter list:  out[m,n] = lhs[m,p] . rhs[n,p]^T + beta * out, contiguous

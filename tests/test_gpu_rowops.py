@@ -309,3 +309,63 @@ def test_silu_mul_fused_into_the_gate_and_up_products(kernels, m, p, n, bs, zp):
                 assert torch.equal(got.view(torch.int16), want.view(torch.int16)), (m, p, n, pdl)
         finally:
             kernels.set_tunable("pdl", 0)
+
+
+@pytest.mark.parametrize("m,p,width,heads,bs,with_norm", [(1, 4096, 4096, 32, 128, False), (4, 4096, 4096, 32, 128, True),
+                                                          (2, 1024, 512, 4, 64, True), (16, 2048, 256, 2, 128, False),
+                                                          (3, 1280, 192, 3, 64, False)])
+def test_qkv_product_with_rotary_and_cache_append_fused(kernels, m, p, width, heads, bs, with_norm):
+    """adr_qkv_rope_append_matmul_nt_fp16u8 gives the bits of (adr_rms_norm +) adr_matmul_nt_fp16u8
+    (persistent kernel) followed by adr_decode_rope_append: rotated q, and the rows of the key and
+    value caches at the position; every other cache row stays untouched."""
+    from adrastea_b200 import Kernel, TensorView
+    rng = np.random.default_rng(m * 13 + width)
+    S, pos_val, theta, eps = 24, 17, 10000.0, 1e-5
+    x = dev((rng.standard_normal((m, p)) * rng.uniform(0.5, 2.0, (m, 1))).astype(np.float16))
+    nw = dev(rng.uniform(0.5, 1.5, p).astype(np.float16))
+    q = dev(rng.integers(0, 256, (3 * width, p), dtype=np.uint8))
+    s = dev(rng.uniform(0.001, 0.01, (3 * width, p // bs)).astype(np.float16))
+    pos = torch.tensor([pos_val], dtype=torch.int32, device="cuda")
+    fill = 0.25
+    # the separate kernels
+    xin = x
+    if with_norm:
+        xin = torch.zeros_like(x)
+        kernels.rms_norm(TensorView.of(xin), TensorView.of(x), TensorView.of(nw), eps)
+    qkv = torch.zeros((m, 3 * width), dtype=torch.float16, device="cuda")
+    kernels.force_kernel(Kernel.U8Ring)
+    try:
+        kernels.matmul_nt_fp16u8(qkv, xin, q, s, bs)
+    finally:
+        kernels.force_kernel(Kernel.Auto)
+    kc = torch.full((m, S, width), fill, dtype=torch.float16, device="cuda")
+    vc = torch.full((m, S, width), fill, dtype=torch.float16, device="cuda")
+    qv, kv, vv = (TensorView.of(qkv[:, i * width:(i + 1) * width]) for i in range(3))
+    kernels.decode_rope_append(qv, kv, vv, kc, vc, heads, pos, theta)
+    kernels.device_status()
+    for pdl in (0, 1):
+        kernels.set_tunable("pdl", pdl)
+        try:
+            out = torch.full((m, 3 * width), 9.0, dtype=torch.float16, device="cuda")
+            kc2 = torch.full((m, S, width), fill, dtype=torch.float16, device="cuda")
+            vc2 = torch.full((m, S, width), fill, dtype=torch.float16, device="cuda")
+            n0 = kernels.launch_count()
+            kernels.qkv_rope_append_matmul_nt_fp16u8(out[:, :width], x, q, s, bs, heads, kc2, vc2, pos, theta,
+                                                     nw if with_norm else None, eps)
+            assert kernels.launch_count() - n0 == 1
+            kernels.device_status()
+            assert torch.equal(out[:, :width].contiguous().view(torch.int16),
+                               qkv[:, :width].contiguous().view(torch.int16)), (m, p, width, pdl)
+            assert torch.all(out[:, width:] == 9.0)
+            assert torch.equal(kc2.view(torch.int16), kc.view(torch.int16))
+            assert torch.equal(vc2.view(torch.int16), vc.view(torch.int16))
+        finally:
+            kernels.set_tunable("pdl", 0)
+    # a position outside the cache writes nothing
+    bad = torch.tensor([S], dtype=torch.int32, device="cuda")
+    out = torch.full((m, 3 * width), 9.0, dtype=torch.float16, device="cuda")
+    kc2 = torch.full((m, S, width), fill, dtype=torch.float16, device="cuda")
+    vc2 = kc2.clone()
+    kernels.qkv_rope_append_matmul_nt_fp16u8(out[:, :width], x, q, s, bs, heads, kc2, vc2, bad, theta)
+    kernels.device_status()
+    assert torch.all(out == 9.0) and torch.all(kc2 == fill) and torch.all(vc2 == fill)
