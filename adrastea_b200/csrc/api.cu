@@ -166,6 +166,7 @@ int adr_set_tunable(adr_ctx* ctx, const char* name, int value) {
   else if (!strcmp(name, "ks_slack")) ctx->tune_ks_slack = value;
   else if (!strcmp(name, "u8_cps_m")) ctx->tune_u8_cps_m = value;
   else if (!strcmp(name, "u8_cps_x4")) ctx->tune_u8_cps_x4 = value;
+  else if (!strcmp(name, "ts_bt")) ctx->tune_ts_bt = value;
   else return ADR_ERR_INVALID;
   return ADR_OK;
 }

@@ -41,6 +41,7 @@ constexpr int TS_PHASES = 4;         // converter phases (k-step index % 4)
 constexpr int TS_CONV_WARPS = 4 * TS_PHASES;
 constexpr int TS_W_PRODUCER = 16, TS_W_MMA = 17;
 constexpr int TS_THREADS = 18 * 32;
+constexpr int TS_SCALE_AHEAD = 4;    // k-steps of a warp whose scales are requested in advance
 constexpr int TS_EPI_TOK = 8;        // tokens per transposition pass
 constexpr int TS_EPI_LD = 36;        // floats between token rows of the tile (16 bytes more than 32:
                                      // the eight token rows then start in different bank groups)
@@ -194,35 +195,50 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
     const int quarter = warp & 3, phase = warp >> 2;
     const int row = quarter * 32 + lane;  // weight row of the tile = TMEM lane
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    // the weight tile is stored with the 64-byte swizzle (16-byte piece ^ bits 7-8 of the
+    // address), so that the eight rows a quarter-warp reads at once lie in different banks
+    const int wswz = (row >> 1) & 3;
     const bool has_zero = p.zeros != nullptr;
     int it = 0, local = 0;
     for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
       const int n0 = tile_n0(t), t0 = tile_t0(t);
       const int n_row = n0 + row;
       const size_t srow = (size_t)min(n_row, p.n - 1) * groups;
-      // scale of this warp's first k-step of the tile; the next one is requested a step ahead
-      int kb_mine = (phase - (it & (TS_PHASES - 1)) + TS_PHASES) & (TS_PHASES - 1);
-      __half sc = __float2half(0.f), zp = __float2half(0.f);
-      if (kb_mine < num_kb) {
-        const int g = (kb_mine * TS_BK) / p.block_size;
-        sc = p.scales[srow + g];
-        if (has_zero) zp = p.zeros[srow + g];
+      // Scales (and zero points) of this warp's next TS_SCALE_AHEAD k-steps wait in registers:
+      // the 2-byte loads (one row per lane, a row's groups apart) take longer than a k-step's
+      // conversion, so requesting only one step ahead left every warp waiting for its scale.
+      const int kb_mine = (phase - (it & (TS_PHASES - 1)) + TS_PHASES) & (TS_PHASES - 1);
+      __half scq[TS_SCALE_AHEAD], zpq[TS_SCALE_AHEAD];
+#pragma unroll
+      for (int d = 0; d < TS_SCALE_AHEAD; ++d) {
+        scq[d] = zpq[d] = __float2half(0.f);
+        const int kq = kb_mine + d * TS_PHASES;
+        if (kq < num_kb) {
+          const int g = (kq * TS_BK) / p.block_size;
+          scq[d] = p.scales[srow + g];
+          if (has_zero) zpq[d] = p.zeros[srow + g];
+        }
       }
       for (int kb = 0; kb < num_kb; ++kb, ++it) {
         if ((it & (TS_PHASES - 1)) != phase) continue;
         const int s = it % Cfg::STAGES, ab = it & (TS_NA - 1);
-        const ScalePair sp = make_scale(sc, has_zero, zp);
-        if (kb + TS_PHASES < num_kb) {  // this warp's next k-step
-          const int g = ((kb + TS_PHASES) * TS_BK) / p.block_size;
-          sc = p.scales[srow + g];
-          if (has_zero) zp = p.zeros[srow + g];
+        const ScalePair sp = make_scale(scq[0], has_zero, zpq[0]);
+#pragma unroll
+        for (int d = 0; d + 1 < TS_SCALE_AHEAD; ++d) {
+          scq[d] = scq[d + 1];
+          zpq[d] = zpq[d + 1];
+        }
+        if (kb + TS_SCALE_AHEAD * TS_PHASES < num_kb) {
+          const int g = ((kb + TS_SCALE_AHEAD * TS_PHASES) * TS_BK) / p.block_size;
+          scq[TS_SCALE_AHEAD - 1] = p.scales[srow + g];
+          if (has_zero) zpq[TS_SCALE_AHEAD - 1] = p.zeros[srow + g];
         }
         if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[s], (unsigned)(it / Cfg::STAGES) & 1u));
         uint4 w[4];
         if (ok) {
           const uint8_t* wrow = stages + (size_t)s * Cfg::STAGE_BYTES + Cfg::X_BYTES + row * TS_BK;
 #pragma unroll
-          for (int c = 0; c < 4; ++c) w[c] = *reinterpret_cast<const uint4*>(wrow + c * 16);
+          for (int c = 0; c < 4; ++c) w[c] = *reinterpret_cast<const uint4*>(wrow + ((c ^ wswz) * 16));
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);  // the weights of the stage are in registers
@@ -252,30 +268,40 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
       // `phase`.  Passes of 8 tokens: the thread (= weight row) writes its 8 fp32 results into
       // the warp's [8 tokens][32 rows] tile, then every lane takes one piece (8 consecutive rows
       // of one token): old outputs read and new ones written as 16-byte vectors.
+      constexpr int QT = BT / TS_PHASES;  // tokens per warp
+      constexpr int PASSES = QT / TS_EPI_TOK;
+      const int nq0 = n0 + quarter * 32;  // first output column of this warp
+      const bool vec = (p.n % 8 == 0) && nq0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0;
+      const int tk = lane >> 2, seg = lane & 3;  // this lane's piece of a pass
+      // The old outputs of all this warp's pieces are requested before the accumulator is
+      // awaited: their latency (DRAM, the first time a buffer is touched) then overlaps the
+      // last MMAs of the tile instead of being paid once per pass.
+      uint4 oldv[PASSES];
+      if (ok && vec) {
+#pragma unroll
+        for (int c = 0; c < PASSES; ++c) {
+          const int tok = t0 + phase * QT + c * TS_EPI_TOK + tk;
+          oldv[c] = make_uint4(0, 0, 0, 0);
+          if (tok < p.m) oldv[c] = *reinterpret_cast<const uint4*>(p.out + (size_t)tok * p.n + nq0 + seg * 8);
+        }
+      }
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, (unsigned)local & 1u));
       tc_fence_after_sync();
       if (ok) {
-        constexpr int QT = BT / TS_PHASES;  // tokens per warp
         float* tile = reinterpret_cast<float*>(epi + (size_t)warp * TS_EPI_BYTES);
-        const int nq0 = n0 + quarter * 32;  // first output column of this warp
-        const bool vec = (p.n % 8 == 0) && nq0 + 32 <= p.n && (reinterpret_cast<uintptr_t>(p.out) & 15u) == 0;
-        const int tk = lane >> 2, seg = lane & 3;  // this lane's piece of a pass
-#pragma unroll 1
-        for (int c = 0; c < QT / TS_EPI_TOK; ++c) {
-          const int tok0 = t0 + phase * QT + c * TS_EPI_TOK;
-          if (tok0 >= p.m) break;  // uniform across the warp
-          uint32_t acc[8];
-          asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                       : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]),
-                         "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7])
-                       : "r"(tmem_base + lane_base + (uint32_t)(phase * QT + c * TS_EPI_TOK))
-                       : "memory");
-          if (vec) {
-            // old outputs of this lane's piece, requested before the accumulator is awaited
-            uint4 oldv = make_uint4(0, 0, 0, 0);
+        if (vec) {
+#pragma unroll
+          for (int c = 0; c < PASSES; ++c) {
+            const int tok0 = t0 + phase * QT + c * TS_EPI_TOK;
+            if (tok0 >= p.m) break;  // uniform across the warp
+            uint32_t acc[8];
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]),
+                           "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7])
+                         : "r"(tmem_base + lane_base + (uint32_t)(phase * QT + c * TS_EPI_TOK))
+                         : "memory");
             __half* optr = p.out + (size_t)(tok0 + tk) * p.n + nq0 + seg * 8;
             const bool live = tok0 + tk < p.m;
-            if (live) oldv = *reinterpret_cast<const uint4*>(optr);
             tmem_ld_wait();
 #pragma unroll
             for (int j = 0; j < TS_EPI_TOK; ++j) tile[j * TS_EPI_LD + lane] = __uint_as_float(acc[j]);
@@ -283,7 +309,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
             if (live) {
               const float4 a0 = *reinterpret_cast<const float4*>(tile + tk * TS_EPI_LD + seg * 8);
               const float4 a1 = *reinterpret_cast<const float4*>(tile + tk * TS_EPI_LD + seg * 8 + 4);
-              const __half2* o2 = reinterpret_cast<const __half2*>(&oldv);
+              const __half2* o2 = reinterpret_cast<const __half2*>(&oldv[c]);
               const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
               uint4 res;
               __half2* r2 = reinterpret_cast<__half2*>(&res);
@@ -295,7 +321,18 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
               *reinterpret_cast<uint4*>(optr) = res;
             }
             __syncwarp();
-          } else {
+          }
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < PASSES; ++c) {
+            const int tok0 = t0 + phase * QT + c * TS_EPI_TOK;
+            if (tok0 >= p.m) break;  // uniform across the warp
+            uint32_t acc[8];
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]),
+                           "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7])
+                         : "r"(tmem_base + lane_base + (uint32_t)(phase * QT + c * TS_EPI_TOK))
+                         : "memory");
             const bool row_ok = n_row < p.n;
             unsigned short old[TS_EPI_TOK];
 #pragma unroll
@@ -342,7 +379,7 @@ int launch_u8_ts_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
     const uint64_t strides[1] = {(uint64_t)a.p};
     const uint32_t box[2] = {TS_BK, TS_ROWS};
     int rc = tma_get(ctx, &map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, a.rhs, dims, strides, box,
-                     CU_TENSOR_MAP_SWIZZLE_NONE);
+                     CU_TENSOR_MAP_SWIZZLE_64B);
     if (rc != ADR_OK) return rc;
   }
   {
@@ -373,9 +410,22 @@ bool u8_ts_supports(const adr_ctx* ctx, const U8Args& a) {
 
 int launch_u8_ts(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
   if (!u8_ts_supports(ctx, a)) return ADR_ERR_SHAPE;
-  // 256 tokens per tile unless that would leave more than half of a tile empty
-  if (a.m > 128) return launch_u8_ts_t<256>(ctx, stream, a);
-  return launch_u8_ts_t<128>(ctx, stream, a);
+  // Tiles run in waves of one per SM, and a tile of 128 tokens takes almost as long as one of
+  // 256 (measured: 37.6 against 39.6 us at k = 4096; the k-step rate is set by the hand-overs
+  // of the ring, not by the tensor core), so 128 is chosen only where it does not add a wave:
+  // 512 tokens x [4096, 4096] then fill 128 SMs instead of 64.
+  const int forced = ctx->tune_ts_bt.load();
+  if (forced == 128) return launch_u8_ts_t<128>(ctx, stream, a);
+  if (forced == 256) return launch_u8_ts_t<256>(ctx, stream, a);
+  if (a.m <= 128) return launch_u8_ts_t<128>(ctx, stream, a);
+  const long long sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+  const long long nb = (a.n + TS_ROWS - 1) / TS_ROWS;
+  auto cost = [&](int bt) {
+    const long long tiles = nb * ((a.m + bt - 1) / bt);
+    return ((tiles + sms - 1) / sms) * (bt == 128 ? 19 : 20);
+  };
+  if (cost(128) < cost(256)) return launch_u8_ts_t<128>(ctx, stream, a);
+  return launch_u8_ts_t<256>(ctx, stream, a);
 }
 
 }  // namespace adr

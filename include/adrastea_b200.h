@@ -119,6 +119,8 @@ int adr_force_kernel(adr_ctx* ctx, int kernel);
  *               on).  Default 15; 0 shows what the guard is worth (CTAs then land two to an SM
  *               on half the SMs).  Measured in a LLaMA-7B decode step: 15 against 3 is 9 %
  *               faster at batch 4 and 1 % slower at batch 1.
+ *   "ts_bt":    tokens per tile of the tensor-memory prefill kernel, 128/256 (0 = the
+ *               launcher's choice: 128 only where it does not add a wave of tiles).
  *   "ks_pdl":   0 = the cluster k-split kernel never starts early under "pdl" (default 1).
  *   "ks_off":   1 = the dispatcher never picks the cluster k-split kernel (A/B runs).
  *   "ks_slack": 1 (default) = behind a small kernel of this library the cluster k-split kernel
