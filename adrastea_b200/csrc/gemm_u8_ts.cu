@@ -41,7 +41,6 @@ constexpr int TS_PHASES = 4;         // converter phases (k-step index % 4)
 constexpr int TS_CONV_WARPS = 4 * TS_PHASES;
 constexpr int TS_W_PRODUCER = 16, TS_W_MMA = 17;
 constexpr int TS_THREADS = 18 * 32;
-constexpr int TS_SCALE_AHEAD = 4;    // k-steps of a warp whose scales are requested in advance
 constexpr int TS_EPI_TOK = 8;        // tokens per transposition pass
 constexpr int TS_EPI_LD = 36;        // floats between token rows of the tile (16 bytes more than 32:
                                      // the eight token rows then start in different bank groups)
@@ -99,9 +98,9 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
   uint8_t* stages = smem;  // per stage: activations (1024-aligned), then weights
   uint8_t* epi = smem + (size_t)Cfg::STAGES * Cfg::STAGE_BYTES;  // [warp][16 tokens][32 rows] fp16
   uint64_t* full = reinterpret_cast<uint64_t*>(epi + Cfg::EPI_BYTES);
-  uint64_t* empty = full + Cfg::STAGES;      // 4 converter warps + the MMA commit
+  uint64_t* empty = full + Cfg::STAGES;      // the weights of the stage are in registers
   uint64_t* a_ready = empty + Cfg::STAGES;   // [TS_NA]
-  uint64_t* a_free = a_ready + TS_NA;        // [TS_NA]
+  uint64_t* a_free = a_ready + TS_NA;        // [TS_NA] the MMAs of k-step (index % TS_NA) are done
   uint64_t* acc_full = a_free + TS_NA;
   uint64_t* acc_empty = acc_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
@@ -117,7 +116,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
     tma_prefetch_desc(&map_x);
     for (int s = 0; s < Cfg::STAGES; ++s) {
       mbar_init(&full[s], 1);
-      mbar_init(&empty[s], 5);  // the four converter warps of the step's phase + the MMA commit
+      mbar_init(&empty[s], 4);  // the four converter warps of the step's phase
     }
     for (int i = 0; i < TS_NA; ++i) {
       mbar_init(&a_ready[i], 4);
@@ -146,6 +145,12 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % Cfg::STAGES;
           if (!mbar_wait(&empty[s], ((unsigned)(it / Cfg::STAGES) & 1u) ^ 1u)) { ok = false; break; }
+          // ... and its activations read by the MMAs of the k-step that used the stage (one
+          // commit per k-step serves the converters' buffer and the stage)
+          if (it >= Cfg::STAGES) {
+            const int j = it - Cfg::STAGES;
+            if (!mbar_wait(&a_free[j & (TS_NA - 1)], (unsigned)(j / TS_NA) & 1u)) { ok = false; break; }
+          }
           uint8_t* st = stages + (size_t)s * Cfg::STAGE_BYTES;
           mbar_expect_tx(&full[s], Cfg::STAGE_BYTES);
           tma_load_2d(st, &map_x, kb * TS_BK, t0, &full[s]);
@@ -161,10 +166,13 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
       for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
         // the single accumulator is free once the epilogue of the previous tile has read it
         if (!mbar_wait(acc_empty, ((unsigned)local & 1u) ^ 1u)) { ok = false; break; }
-        // two k-steps per round: the waits and the bookkeeping of this single thread are the
-        // tensor core's idle time, so they are paid once per eight MMAs where possible
-        for (int kb = 0; kb < num_kb && ok; kb += 2) {
-          const int steps = min(2, num_kb - kb);
+        // several k-steps per round: the waits and the bookkeeping of this single thread are
+        // the tensor core's idle time, so they are paid once per round.  A round must leave the
+        // ring room to load and convert the next one while it runs: two k-steps with five
+        // stages, four with eight.
+        constexpr int ROUND = Cfg::STAGES >= 8 ? 4 : 2;
+        for (int kb = 0; kb < num_kb && ok; kb += ROUND) {
+          const int steps = min(ROUND, num_kb - kb);
           // (the converters waited for a stage's copies before they converted, so the
           // activations of the stage have landed too)
           for (int u = 0; u < steps; ++u) {
@@ -183,7 +191,6 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
             ts_mma<true>(tmem_base, a_addr + 16, xdesc + 4, idesc);
             ts_mma<true>(tmem_base, a_addr + 24, xdesc + 6, idesc);
             umma_commit(&a_free[ab]);
-            umma_commit(&empty[s]);
           }
         }
         umma_commit(acc_full);
@@ -204,36 +211,29 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
       const int n0 = tile_n0(t), t0 = tile_t0(t);
       const int n_row = n0 + row;
       const size_t srow = (size_t)min(n_row, p.n - 1) * groups;
-      // Scales (and zero points) of this warp's next TS_SCALE_AHEAD k-steps wait in registers:
-      // the 2-byte loads (one row per lane, a row's groups apart) take longer than a k-step's
-      // conversion, so requesting only one step ahead left every warp waiting for its scale.
+      // Scales (and zero points) are requested TWO of this warp's k-steps ahead, into two
+      // register pairs used in turn (the loop body is written out twice, so that no register
+      // move waits for a load in flight): the 2-byte loads, one row per lane, take longer than
+      // a k-step's conversion, and requested one step ahead they were what every warp waited
+      // for.
       const int kb_mine = (phase - (it & (TS_PHASES - 1)) + TS_PHASES) & (TS_PHASES - 1);
-      __half scq[TS_SCALE_AHEAD], zpq[TS_SCALE_AHEAD];
-#pragma unroll
-      for (int d = 0; d < TS_SCALE_AHEAD; ++d) {
-        scq[d] = zpq[d] = __float2half(0.f);
-        const int kq = kb_mine + d * TS_PHASES;
+      const int it0 = it;
+      auto fetch = [&](int kq, __half& sc, __half& zp) {
         if (kq < num_kb) {
           const int g = (kq * TS_BK) / p.block_size;
-          scq[d] = p.scales[srow + g];
-          if (has_zero) zpq[d] = p.zeros[srow + g];
+          sc = p.scales[srow + g];
+          if (has_zero) zp = p.zeros[srow + g];
         }
-      }
-      for (int kb = 0; kb < num_kb; ++kb, ++it) {
-        if ((it & (TS_PHASES - 1)) != phase) continue;
-        const int s = it % Cfg::STAGES, ab = it & (TS_NA - 1);
-        const ScalePair sp = make_scale(scq[0], has_zero, zpq[0]);
-#pragma unroll
-        for (int d = 0; d + 1 < TS_SCALE_AHEAD; ++d) {
-          scq[d] = scq[d + 1];
-          zpq[d] = zpq[d + 1];
-        }
-        if (kb + TS_SCALE_AHEAD * TS_PHASES < num_kb) {
-          const int g = ((kb + TS_SCALE_AHEAD * TS_PHASES) * TS_BK) / p.block_size;
-          scq[TS_SCALE_AHEAD - 1] = p.scales[srow + g];
-          if (has_zero) zpq[TS_SCALE_AHEAD - 1] = p.zeros[srow + g];
-        }
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[s], (unsigned)(it / Cfg::STAGES) & 1u));
+      };
+      __half sc_a = __float2half(0.f), zp_a = sc_a, sc_b = sc_a, zp_b = sc_a;
+      fetch(kb_mine, sc_a, zp_a);
+      fetch(kb_mine + TS_PHASES, sc_b, zp_b);
+      auto convert_step = [&](int kb, __half& sc, __half& zp) {
+        const int itk = it0 + kb;
+        const int s = itk % Cfg::STAGES, ab = itk & (TS_NA - 1);
+        const ScalePair sp = make_scale(sc, has_zero, zp);
+        fetch(kb + 2 * TS_PHASES, sc, zp);
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[s], (unsigned)(itk / Cfg::STAGES) & 1u));
         uint4 w[4];
         if (ok) {
           const uint8_t* wrow = stages + (size_t)s * Cfg::STAGE_BYTES + Cfg::X_BYTES + row * TS_BK;
@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);  // the weights of the stage are in registers
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&a_free[ab], ((unsigned)(it / TS_NA) & 1u) ^ 1u));
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&a_free[ab], ((unsigned)(itk / TS_NA) & 1u) ^ 1u));
         tc_fence_after_sync();
         if (ok) {
 #pragma unroll
@@ -263,7 +263,12 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) mbar_arrive(&a_ready[ab]);
+      };
+      for (int kb = kb_mine; kb < num_kb; kb += 2 * TS_PHASES) {
+        convert_step(kb, sc_a, zp_a);
+        if (kb + TS_PHASES < num_kb) convert_step(kb + TS_PHASES, sc_b, zp_b);
       }
+      it = it0 + num_kb;
       // ---- epilogue of the tile: this warp's lane quarter (32 weight rows), token quarter
       // `phase`.  Passes of 8 tokens: the thread (= weight row) writes its 8 fp32 results into
       // the warp's [8 tokens][32 rows] tile, then every lane takes one piece (8 consecutive rows
@@ -410,10 +415,10 @@ bool u8_ts_supports(const adr_ctx* ctx, const U8Args& a) {
 
 int launch_u8_ts(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
   if (!u8_ts_supports(ctx, a)) return ADR_ERR_SHAPE;
-  // Tiles run in waves of one per SM, and a tile of 128 tokens takes almost as long as one of
-  // 256 (measured: 37.6 against 39.6 us at k = 4096; the k-step rate is set by the hand-overs
-  // of the ring, not by the tensor core), so 128 is chosen only where it does not add a wave:
-  // 512 tokens x [4096, 4096] then fill 128 SMs instead of 64.
+  // Tiles run in waves of one per SM, and a tile of 128 tokens takes about 0.8 of the time of
+  // one of 256 (measured at k = 4096 and 11008: the k-step rate is set by the tensor core at
+  // 256 tokens and by the hand-overs of the ring at 128), so 128 is chosen only where it saves
+  // waves: 384 tokens x [12288, 4096] run as two waves of the shorter tiles.
   const int forced = ctx->tune_ts_bt.load();
   if (forced == 128) return launch_u8_ts_t<128>(ctx, stream, a);
   if (forced == 256) return launch_u8_ts_t<256>(ctx, stream, a);
@@ -422,7 +427,7 @@ int launch_u8_ts(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
   const long long nb = (a.n + TS_ROWS - 1) / TS_ROWS;
   auto cost = [&](int bt) {
     const long long tiles = nb * ((a.m + bt - 1) / bt);
-    return ((tiles + sms - 1) / sms) * (bt == 128 ? 19 : 20);
+    return ((tiles + sms - 1) / sms) * (bt == 128 ? 16 : 20);
   };
   if (cost(128) < cost(256)) return launch_u8_ts_t<128>(ctx, stream, a);
   return launch_u8_ts_t<256>(ctx, stream, a);
