@@ -167,6 +167,7 @@ int adr_set_tunable(adr_ctx* ctx, const char* name, int value) {
   else if (!strcmp(name, "u8_cps_m")) ctx->tune_u8_cps_m = value;
   else if (!strcmp(name, "u8_cps_x4")) ctx->tune_u8_cps_x4 = value;
   else if (!strcmp(name, "ts_bt")) ctx->tune_ts_bt = value;
+  else if (!strcmp(name, "ts_split")) ctx->tune_ts_split = value;
   else return ADR_ERR_INVALID;
   return ADR_OK;
 }

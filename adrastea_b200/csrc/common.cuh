@@ -76,6 +76,7 @@ struct adr_ctx {
   std::atomic<int> tune_u8_cps_m{2}, tune_u8_cps_x4{16};
   std::atomic<int> tune_ks_clusters{0}, tune_ks_stages{0}, tune_ks_off{0}, tune_ks_slack{1};  // cluster k-split kernel: clusters in the grid, ring stages
   std::atomic<int> tune_pdl_guard{15};
+  std::atomic<int> tune_ts_split{0};  // k-split of the tensor-memory prefill kernel (1 = never, 2/4)
   std::atomic<int> tune_ts_bt{0};  // tokens per tile of the tensor-memory prefill kernel (128/256)
   std::atomic<int> tune_ks_pdl{1};  // the cluster k-split kernel may start early under "pdl"  // which SM-filling launches end a chain of early starts (bit 0: two CTAs per SM, bit 1: one large CTA)
   // the last launch whose CTAs left no room beside them on an SM: its number and its stream

@@ -87,7 +87,7 @@ __device__ __forceinline__ void ts_mma(uint32_t tmem_d, uint32_t tmem_a, uint64_
                  : "memory");
 }
 
-template <int BT>
+template <int BT, bool SPLIT>
 __global__ void __launch_bounds__(TS_THREADS, 1)
     gemm_u8_ts_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                       TsParams p) {
@@ -107,6 +107,14 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int num_kb = p.p / TS_BK;
+  // SPLIT: grid (S, tiles), cluster (S, 1, 1): CTA `rank` of a cluster accumulates k-steps
+  // [rank * num_kb / S, (rank + 1) * num_kb / S) of the cluster's one tile, and the partial
+  // accumulators are summed through distributed shared memory before the single rounding.
+  const int S = SPLIT ? (int)gridDim.x : 1, rank = SPLIT ? (int)blockIdx.x : 0;
+  const int kb_begin = SPLIT ? (int)((long long)rank * num_kb / S) : 0;
+  const int kb_end = SPLIT ? (int)((long long)(rank + 1) * num_kb / S) : num_kb;
+  const int tile_first = SPLIT ? (int)blockIdx.y : (int)blockIdx.x;
+  const int tile_stride = SPLIT ? (1 << 30) : (int)gridDim.x;
   const int nb = (p.n + TS_ROWS - 1) / TS_ROWS, tt = (p.m + BT - 1) / BT;
   const int total_tiles = nb * tt;
   const int groups = p.p / p.block_size;
@@ -140,9 +148,9 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
   if (warp == TS_W_PRODUCER) {
     if (lane == 0) {
       int it = 0;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+      for (int t = tile_first; t < total_tiles && ok; t += tile_stride) {
         const int n0 = tile_n0(t), t0 = tile_t0(t);
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = it % Cfg::STAGES;
           if (!mbar_wait(&empty[s], ((unsigned)(it / Cfg::STAGES) & 1u) ^ 1u)) { ok = false; break; }
           // ... and its activations read by the MMAs of the k-step that used the stage (one
@@ -163,7 +171,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_f16(BT, false);
       int it = 0, local = 0;
-      for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, ++local) {
+      for (int t = tile_first; t < total_tiles && ok; t += tile_stride, ++local) {
         // the single accumulator is free once the epilogue of the previous tile has read it
         if (!mbar_wait(acc_empty, ((unsigned)local & 1u) ^ 1u)) { ok = false; break; }
         // several k-steps per round: the waits and the bookkeeping of this single thread are
@@ -171,8 +179,8 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
         // ring room to load and convert the next one while it runs: two k-steps with five
         // stages, four with eight.
         constexpr int ROUND = Cfg::STAGES >= 8 ? 4 : 2;
-        for (int kb = 0; kb < num_kb && ok; kb += ROUND) {
-          const int steps = min(ROUND, num_kb - kb);
+        for (int kb = kb_begin; kb < kb_end && ok; kb += ROUND) {
+          const int steps = min(ROUND, kb_end - kb);
           // (the converters waited for a stage's copies before they converted, so the
           // activations of the stage have landed too)
           for (int u = 0; u < steps; ++u) {
@@ -185,7 +193,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
             const int s = it % Cfg::STAGES, ab = it & (TS_NA - 1);
             const uint64_t xdesc = umma_desc_k_sw128(smem_u32(stages + (size_t)s * Cfg::STAGE_BYTES));
             const uint32_t a_addr = tmem_base + Cfg::A_COL0 + (uint32_t)(ab * 32);
-            if (kb + u == 0) ts_mma<false>(tmem_base, a_addr, xdesc, idesc);
+            if (kb + u == kb_begin) ts_mma<false>(tmem_base, a_addr, xdesc, idesc);
             else ts_mma<true>(tmem_base, a_addr, xdesc, idesc);
             ts_mma<true>(tmem_base, a_addr + 8, xdesc + 2, idesc);
             ts_mma<true>(tmem_base, a_addr + 16, xdesc + 4, idesc);
@@ -207,7 +215,7 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
     const int wswz = (row >> 1) & 3;
     const bool has_zero = p.zeros != nullptr;
     int it = 0, local = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++local) {
+    for (int t = tile_first; t < total_tiles; t += tile_stride, ++local) {
       const int n0 = tile_n0(t), t0 = tile_t0(t);
       const int n_row = n0 + row;
       const size_t srow = (size_t)min(n_row, p.n - 1) * groups;
@@ -219,17 +227,17 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
       const int kb_mine = (phase - (it & (TS_PHASES - 1)) + TS_PHASES) & (TS_PHASES - 1);
       const int it0 = it;
       auto fetch = [&](int kq, __half& sc, __half& zp) {
-        if (kq < num_kb) {
+        if (kq < kb_end) {
           const int g = (kq * TS_BK) / p.block_size;
           sc = p.scales[srow + g];
           if (has_zero) zp = p.zeros[srow + g];
         }
       };
       __half sc_a = __float2half(0.f), zp_a = sc_a, sc_b = sc_a, zp_b = sc_a;
-      fetch(kb_mine, sc_a, zp_a);
-      fetch(kb_mine + TS_PHASES, sc_b, zp_b);
+      fetch(kb_begin + kb_mine, sc_a, zp_a);
+      fetch(kb_begin + kb_mine + TS_PHASES, sc_b, zp_b);
       auto convert_step = [&](int kb, __half& sc, __half& zp) {
-        const int itk = it0 + kb;
+        const int itk = it0 + (kb - kb_begin);
         const int s = itk % Cfg::STAGES, ab = itk & (TS_NA - 1);
         const ScalePair sp = make_scale(sc, has_zero, zp);
         fetch(kb + 2 * TS_PHASES, sc, zp);
@@ -264,11 +272,37 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
         __syncwarp();
         if (lane == 0) mbar_arrive(&a_ready[ab]);
       };
-      for (int kb = kb_mine; kb < num_kb; kb += 2 * TS_PHASES) {
+      for (int kb = kb_begin + kb_mine; kb < kb_end; kb += 2 * TS_PHASES) {
         convert_step(kb, sc_a, zp_a);
-        if (kb + TS_PHASES < num_kb) convert_step(kb + TS_PHASES, sc_b, zp_b);
+        if (kb + TS_PHASES < kb_end) convert_step(kb + TS_PHASES, sc_b, zp_b);
       }
-      it = it0 + num_kb;
+      it = it0 + (kb_end - kb_begin);
+      if constexpr (SPLIT) {
+        // The partial accumulator goes into this CTA's ring as [token][weight row] fp32 (the
+        // ring is idle once the accumulator is complete: every stage has been read, and a
+        // cluster has one tile); the sum over the cluster follows below, outside the roles.
+        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(acc_full, (unsigned)local & 1u));
+        tc_fence_after_sync();
+        if (ok) {
+          constexpr int QTS = BT / TS_PHASES;
+          float* part = reinterpret_cast<float*>(stages);
+#pragma unroll 1
+          for (int c = 0; c < QTS / TS_EPI_TOK; ++c) {
+            const int tl = phase * QTS + c * TS_EPI_TOK;
+            if (t0 + tl >= p.m) break;  // uniform across the warp
+            uint32_t acc[8];
+            asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(acc[0]), "=r"(acc[1]), "=r"(acc[2]), "=r"(acc[3]), "=r"(acc[4]),
+                           "=r"(acc[5]), "=r"(acc[6]), "=r"(acc[7])
+                         : "r"(tmem_base + lane_base + (uint32_t)tl)
+                         : "memory");
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < TS_EPI_TOK; ++j) part[(size_t)(tl + j) * TS_ROWS + row] = __uint_as_float(acc[j]);
+          }
+        }
+        continue;
+      }
       // ---- epilogue of the tile: this warp's lane quarter (32 weight rows), token quarter
       // `phase`.  Passes of 8 tokens: the thread (= weight row) writes its 8 fp32 results into
       // the warp's [8 tokens][32 rows] tile, then every lane takes one piece (8 consecutive rows
@@ -364,6 +398,62 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
     }
     if (!ok && lane == 0) atomicOr(p.status, 8u);
   }
+  if constexpr (SPLIT) {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    // rank r finishes tokens [r * BT / S, (r + 1) * BT / S) of the tile: the S partial tiles are
+    // read through distributed shared memory (all requested before the first is used), summed
+    // in rank order, and rounded once: fp16(sum + beta * old).
+    const int tpr = BT / S;
+    const int n0 = tile_n0(tile_first), t0 = tile_t0(tile_first);
+    const uint32_t pbase = smem_u32(stages);
+    const bool vec4 = (p.n % 4 == 0) && (reinterpret_cast<uintptr_t>(p.out) & 7u) == 0;
+    for (int e = threadIdx.x; e < tpr * (TS_ROWS / 4); e += TS_THREADS) {
+      const int tl = rank * tpr + e / (TS_ROWS / 4), r4 = (e % (TS_ROWS / 4)) * 4;
+      const int tok = t0 + tl, nr = n0 + r4;
+      if (tok >= p.m || nr >= p.n) continue;
+      float4 pv[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        pv[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (r < S) {
+          uint32_t remote;
+          asm("mapa.shared::cluster.u32 %0, %1, %2;"
+              : "=r"(remote)
+              : "r"(pbase + (uint32_t)(tl * TS_ROWS + r4) * 4u), "r"(r));
+          asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];"
+                       : "=f"(pv[r].x), "=f"(pv[r].y), "=f"(pv[r].z), "=f"(pv[r].w)
+                       : "r"(remote));
+        }
+      }
+      float v[4] = {pv[0].x, pv[0].y, pv[0].z, pv[0].w};
+#pragma unroll
+      for (int r = 1; r < 4; ++r)
+        if (r < S) {
+          v[0] += pv[r].x;
+          v[1] += pv[r].y;
+          v[2] += pv[r].z;
+          v[3] += pv[r].w;
+        }
+      __half* optr = p.out + (size_t)tok * p.n + nr;
+      if (vec4 && nr + 4 <= p.n) {
+        const uint2 oldv = *reinterpret_cast<const uint2*>(optr);
+        const __half2* o2 = reinterpret_cast<const __half2*>(&oldv);
+        uint2 res;
+        __half2* r2 = reinterpret_cast<__half2*>(&res);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const float2 ov = __half22float2(o2[h]);
+          r2[h] = __floats2half2_rn(fmaf(p.beta, ov.x, v[2 * h]), fmaf(p.beta, ov.y, v[2 * h + 1]));
+        }
+        *reinterpret_cast<uint2*>(optr) = res;
+      } else {
+        for (int j = 0; j < 4 && nr + j < p.n; ++j)
+          optr[j] = __float2half_rn(fmaf(p.beta, __half2float(optr[j]), v[j]));
+      }
+    }
+    // every CTA stays resident until its peers have read its partial tile
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
   tc_fence_before_sync();
   __syncthreads();
   if (warp == TS_W_MMA) {
@@ -374,10 +464,8 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
 }
 
 template <int BT>
-int launch_u8_ts_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
+int launch_u8_ts_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, int split) {
   using Cfg = TsCfg<BT>;
-  auto kfn = gemm_u8_ts_kernel<BT>;
-  if (int rc = opt_in_smem(ctx, kfn, Cfg::SMEM); rc != ADR_OK) return rc;
   CUtensorMap map_w, map_x;
   {
     const uint64_t dims[2] = {(uint64_t)a.p, (uint64_t)a.n};
@@ -398,6 +486,30 @@ int launch_u8_ts_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
   TsParams p{a.out, a.scales, a.zeros, a.m, a.p, a.n, a.block_size, a.beta, ctx->d_status};
   const long long tiles = (long long)((a.n + TS_ROWS - 1) / TS_ROWS) * ((a.m + BT - 1) / BT);
   const long long sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
+  if (split > 1) {
+    auto kfn = gemm_u8_ts_kernel<BT, true>;
+    if (int rc = opt_in_smem(ctx, kfn, Cfg::SMEM); rc != ADR_OK) return rc;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)split, (unsigned)tiles, 1);
+    cfg.blockDim = dim3(TS_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = Cfg::SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)split;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kfn, map_w, map_x, p);
+    if (e != cudaSuccess) {
+      ctx->last_cuda_error = (int)e;
+      return ADR_ERR_CUDA;
+    }
+    return after_launch(ctx);
+  }
+  auto kfn = gemm_u8_ts_kernel<BT, false>;
+  if (int rc = opt_in_smem(ctx, kfn, Cfg::SMEM); rc != ADR_OK) return rc;
   const unsigned grid = (unsigned)std::min<long long>(tiles, sms);
   kfn<<<grid, TS_THREADS, Cfg::SMEM, stream>>>(map_w, map_x, p);
   return after_launch(ctx);
@@ -420,17 +532,28 @@ int launch_u8_ts(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
   // 256 tokens and by the hand-overs of the ring at 128), so 128 is chosen only where it saves
   // waves: 384 tokens x [12288, 4096] run as two waves of the shorter tiles.
   const int forced = ctx->tune_ts_bt.load();
-  if (forced == 128) return launch_u8_ts_t<128>(ctx, stream, a);
-  if (forced == 256) return launch_u8_ts_t<256>(ctx, stream, a);
-  if (a.m <= 128) return launch_u8_ts_t<128>(ctx, stream, a);
   const long long sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
   const long long nb = (a.n + TS_ROWS - 1) / TS_ROWS;
-  auto cost = [&](int bt) {
-    const long long tiles = nb * ((a.m + bt - 1) / bt);
-    return ((tiles + sms - 1) / sms) * (bt == 128 ? 16 : 20);
-  };
-  if (cost(128) < cost(256)) return launch_u8_ts_t<128>(ctx, stream, a);
-  return launch_u8_ts_t<256>(ctx, stream, a);
+  const int num_kb = a.p / TS_BK;
+  auto tiles_of = [&](int bt) { return nb * ((a.m + bt - 1) / bt); };
+  auto cost = [&](int bt) { return ((tiles_of(bt) + sms - 1) / sms) * (bt == 128 ? 16 : 20); };
+  int bt = a.m <= 128 ? 128 : (cost(128) < cost(256) ? 128 : 256);
+  if (forced == 128 || forced == 256) bt = forced;
+  // Too few tiles for the GPU: a cluster of two or four CTAs shares a tile's k-steps (at least
+  // eight each).  With 256-token tiles where the tokens allow: a cluster then moves the
+  // activations once per 256 tokens.
+  int split = 1;
+  const int want = ctx->tune_ts_split.load();
+  if (want != 1) {
+    if (a.m > 128 && forced != 128 && tiles_of(256) * 2 <= sms) bt = 256;
+    for (int sp = 4; sp >= 2; sp >>= 1)
+      if (tiles_of(bt) * sp <= sms && num_kb / sp >= 8 && (want == 0 || want == sp)) {
+        split = sp;
+        break;
+      }
+  }
+  if (bt == 128) return launch_u8_ts_t<128>(ctx, stream, a, split);
+  return launch_u8_ts_t<256>(ctx, stream, a, split);
 }
 
 }  // namespace adr

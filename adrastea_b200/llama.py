@@ -343,8 +343,10 @@ class LlamaU8:
             for b in range(B):  # one sequence at a time, with the reference's views (llama.rs:503-554)
                 rows = qkv[b * S0:(b + 1) * S0]
                 q_b, k_b, v_b = (rows[:, i * dl:(i + 1) * dl] for i in range(3))
-                self.k.rotary_inplace(TensorView.of(q_b), Hl, 0, sh.theta)
-                self.k.rotary_inplace(TensorView.of(k_b), Hl, 0, sh.theta)
+                # q and k lie side by side in the projection's rows and a head is rotated by its
+                # own pair index and the row's position only: one launch over 2 * Hl heads gives
+                # the bits of the reference's two (llama.rs:509-532)
+                self.k.rotary_inplace(TensorView.of(rows[:, :2 * dl]), 2 * Hl, 0, sh.theta)
                 if self.fused_attention:
                     continue
                 head = lambda t, order: TensorView(t, TensorLayout.new((S0, Hl, hd), (t.stride(0), hd, 1))).permute(order)

@@ -121,6 +121,8 @@ int adr_force_kernel(adr_ctx* ctx, int kernel);
  *               faster at batch 4 and 1 % slower at batch 1.
  *   "ts_bt":    tokens per tile of the tensor-memory prefill kernel, 128/256 (0 = the
  *               launcher's choice: 128 only where it does not add a wave of tiles).
+ *   "ts_split": k-split of the tensor-memory prefill kernel over a cluster of 2 or 4 CTAs when a
+ *               problem has too few tiles for the GPU (0 = the launcher's choice, 1 = never).
  *   "ks_pdl":   0 = the cluster k-split kernel never starts early under "pdl" (default 1).
  *   "ks_off":   1 = the dispatcher never picks the cluster k-split kernel (A/B runs).
  *   "ks_slack": 1 (default) = behind a small kernel of this library the cluster k-split kernel

@@ -635,6 +635,45 @@ def test_u8_prefill_tensor_core_kernel(kernels, zp):
         kernels.force_kernel(Kernel.Auto)
 
 
+@pytest.mark.parametrize("zp", [False, True])
+def test_u8_prefill_cluster_split(kernels, zp):
+    """With too few tiles for the GPU the tensor-memory prefill kernel runs a tile on a cluster
+    of two or four CTAs, each with a share of the k-steps, and sums the partial accumulators
+    through distributed shared memory before the one rounding.  Forced here to 1, 2 and 4 on
+    ragged m and n (n not a multiple of 4 takes the scalar stores), both tile widths, beta and
+    zero points; each against the ideal oracle, repeatable bit for bit."""
+    rng = np.random.default_rng(77 + zp)
+    try:
+        kernels.force_kernel(Kernel.U8Ts)
+        for m, p, n, bs, beta in ((64, 2048, 256, 128, 0.0), (200, 4096, 301, 64, 0.5),
+                                  (512, 2112, 384, 64, 1.0), (33, 1024, 130, 128, 0.5)):
+            x = rng.standard_normal((m, p)).astype(np.float16)
+            q = rng.integers(0, 256, (n, p), dtype=np.uint8)
+            s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
+            z = rng.uniform(120, 136, (n, p // bs)).astype(np.float16) if zp else None
+            out0 = (rng.standard_normal((m, n)) * 0.5).astype(np.float16)
+            want = oracle.matmul_nt_fp16u8(x, q, s, bs, beta, out0, z)
+            for bt in (0, 128, 256):
+                for split in (1, 2, 4):
+                    if (p // 64) // split < 8:
+                        continue
+                    kernels.set_tunable("ts_bt", bt)
+                    kernels.set_tunable("ts_split", split)
+                    res = []
+                    for _ in range(2):
+                        o = dev(out0.copy())
+                        kernels.matmul_nt_fp16u8(o, dev(x), dev(q), dev(s), bs, beta, dev(z) if zp else None)
+                        kernels.device_status()
+                        res.append(o.cpu().numpy())
+                    assert kernels.last_kernel() == Kernel.U8Ts
+                    assert np.array_equal(res[0].view(np.uint16), res[1].view(np.uint16))
+                    assert oracle.max_rel_err(res[0], want) <= TOL, (m, p, n, bt, split)
+    finally:
+        kernels.set_tunable("ts_bt", 0)
+        kernels.set_tunable("ts_split", 0)
+        kernels.force_kernel(Kernel.Auto)
+
+
 def fp16_spacing(v):
     """Distance between neighbouring fp16 values at magnitude |v| (normal range)."""
     v = np.maximum(np.abs(v.astype(np.float64)), 2.0 ** -14)
