@@ -26,6 +26,9 @@
 // Needs p % 64 == 0 and block_size % 64 == 0 (one scale group per k-step); other shapes take
 // the kernel that stages the dequantised operand in shared memory (gemm_u8_tc.cu).
 #include <algorithm>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "tcgen05.cuh"
 #include "u8_common.cuh"
@@ -65,6 +68,7 @@ struct TsParams {
   int m, p, n, block_size;
   float beta;
   unsigned int* status;
+  int tile0, tile1;  // this launch covers tiles [tile0, tile1)
 };
 
 __device__ __forceinline__ void ts_st_x8(uint32_t taddr, const uint32_t (&r)[8]) {
@@ -113,10 +117,10 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
   const int S = SPLIT ? (int)gridDim.x : 1, rank = SPLIT ? (int)blockIdx.x : 0;
   const int kb_begin = SPLIT ? (int)((long long)rank * num_kb / S) : 0;
   const int kb_end = SPLIT ? (int)((long long)(rank + 1) * num_kb / S) : num_kb;
-  const int tile_first = SPLIT ? (int)blockIdx.y : (int)blockIdx.x;
+  const int tile_first = p.tile0 + (SPLIT ? (int)blockIdx.y : (int)blockIdx.x);
   const int tile_stride = SPLIT ? (1 << 30) : (int)gridDim.x;
   const int nb = (p.n + TS_ROWS - 1) / TS_ROWS, tt = (p.m + BT - 1) / BT;
-  const int total_tiles = nb * tt;
+  const int total_tiles = min(nb * tt, p.tile1);
   const int groups = p.p / p.block_size;
 
   if (threadIdx.x == 0) {
@@ -403,14 +407,14 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
     // rank r finishes tokens [r * BT / S, (r + 1) * BT / S) of the tile: the S partial tiles are
     // read through distributed shared memory (all requested before the first is used), summed
     // in rank order, and rounded once: fp16(sum + beta * old).
-    const int tpr = BT / S;
+    const int tpr = (BT + S - 1) / S;
     const int n0 = tile_n0(tile_first), t0 = tile_t0(tile_first);
     const uint32_t pbase = smem_u32(stages);
     const bool vec4 = (p.n % 4 == 0) && (reinterpret_cast<uintptr_t>(p.out) & 7u) == 0;
     for (int e = threadIdx.x; e < tpr * (TS_ROWS / 4); e += TS_THREADS) {
       const int tl = rank * tpr + e / (TS_ROWS / 4), r4 = (e % (TS_ROWS / 4)) * 4;
       const int tok = t0 + tl, nr = n0 + r4;
-      if (tok >= p.m || nr >= p.n) continue;
+      if (tl >= BT || tok >= p.m || nr >= p.n) continue;
       float4 pv[4];
 #pragma unroll
       for (int r = 0; r < 4; ++r) {
@@ -463,8 +467,45 @@ __global__ void __launch_bounds__(TS_THREADS, 1)
   }
 }
 
+// Clusters of `split` CTAs of the split kernel that the GPU holds at the same time (a cluster
+// needs its CTAs on one GPC, so fewer than SMs / split), asked once per configuration.
 template <int BT>
-int launch_u8_ts_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, int split) {
+int ts_clusters_resident(adr_ctx* ctx, int split) {
+  using Cfg = TsCfg<BT>;
+  static std::mutex mu;
+  static std::map<std::pair<int, int>, int> known;
+  std::lock_guard<std::mutex> lock(mu);
+  const auto key = std::make_pair(ctx->device, split);
+  auto it = known.find(key);
+  if (it == known.end()) {
+    auto kfn = gemm_u8_ts_kernel<BT, true>;
+    int nc = 0;
+    if (opt_in_smem(ctx, kfn, Cfg::SMEM) == ADR_OK) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)split, 64, 1);
+      cfg.blockDim = dim3(TS_THREADS, 1, 1);
+      cfg.dynamicSmemBytes = Cfg::SMEM;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = (unsigned)split;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      if (cudaOccupancyMaxActiveClusters(&nc, kfn, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        nc = 0;
+      }
+    }
+    if (nc < 1) nc = std::max(1, (ctx->sm_count > 0 ? ctx->sm_count : 148) / split - 8);
+    it = known.emplace(key, nc).first;
+  }
+  return it->second;
+}
+
+template <int BT>
+int launch_u8_ts_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, int split, long long tile0 = 0,
+                   long long tile1 = -1) {
   using Cfg = TsCfg<BT>;
   CUtensorMap map_w, map_x;
   {
@@ -483,8 +524,11 @@ int launch_u8_ts_t(adr_ctx* ctx, cudaStream_t stream, const U8Args& a, int split
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != ADR_OK) return rc;
   }
-  TsParams p{a.out, a.scales, a.zeros, a.m, a.p, a.n, a.block_size, a.beta, ctx->d_status};
-  const long long tiles = (long long)((a.n + TS_ROWS - 1) / TS_ROWS) * ((a.m + BT - 1) / BT);
+  const long long all_tiles = (long long)((a.n + TS_ROWS - 1) / TS_ROWS) * ((a.m + BT - 1) / BT);
+  if (tile1 < 0) tile1 = all_tiles;
+  const long long tiles = tile1 - tile0;
+  if (tiles <= 0) return ADR_OK;
+  TsParams p{a.out, a.scales, a.zeros, a.m, a.p, a.n, a.block_size, a.beta, ctx->d_status, (int)tile0, (int)tile1};
   const long long sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
   if (split > 1) {
     auto kfn = gemm_u8_ts_kernel<BT, true>;
@@ -544,15 +588,36 @@ int launch_u8_ts(adr_ctx* ctx, cudaStream_t stream, const U8Args& a) {
   // activations once per 256 tokens.
   int split = 1;
   const int want = ctx->tune_ts_split.load();
+  auto resident = [&](int tile_tokens, int sp) {
+    return (long long)(tile_tokens == 128 ? ts_clusters_resident<128>(ctx, sp) : ts_clusters_resident<256>(ctx, sp));
+  };
   if (want != 1) {
-    if (a.m > 128 && forced != 128 && tiles_of(256) * 2 <= sms) bt = 256;
-    for (int sp = 4; sp >= 2; sp >>= 1)
-      if (tiles_of(bt) * sp <= sms && num_kb / sp >= 8 && (want == 0 || want == sp)) {
+    if (a.m > 128 && forced != 128 && tiles_of(256) <= resident(256, 2)) bt = 256;
+    for (int sp = 4; sp >= 2; --sp)
+      if (tiles_of(bt) <= resident(bt, sp) && num_kb / sp >= 8 && (want == 0 || want == sp)) {
         split = sp;
         break;
       }
   }
   if (bt == 128) return launch_u8_ts_t<128>(ctx, stream, a, split);
+  // More than one wave of 256-token tiles with a small last wave: the full waves run as the
+  // persistent kernel, the rest as a second launch with every tile on a cluster, which ends
+  // in a fraction of a tile's time (192 tiles on 148 SMs: 148, then 44 on clusters of three).
+  if (split == 1 && want != 1) {
+    const long long t = tiles_of(256), full = t / sms * sms, rem = t - full;
+    if (full > 0 && rem > 0) {
+      int sp = 0;
+      for (int c = 4; c >= 2; --c)
+        if (rem <= resident(256, c) && num_kb / c >= 8 && (want == 0 || want == c)) {
+          sp = c;
+          break;
+        }
+      if (sp) {
+        if (int rc = launch_u8_ts_t<256>(ctx, stream, a, 1, 0, full); rc != ADR_OK) return rc;
+        return launch_u8_ts_t<256>(ctx, stream, a, sp, full, t);
+      }
+    }
+  }
   return launch_u8_ts_t<256>(ctx, stream, a, split);
 }
 

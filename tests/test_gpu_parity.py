@@ -654,7 +654,7 @@ def test_u8_prefill_cluster_split(kernels, zp):
             out0 = (rng.standard_normal((m, n)) * 0.5).astype(np.float16)
             want = oracle.matmul_nt_fp16u8(x, q, s, bs, beta, out0, z)
             for bt in (0, 128, 256):
-                for split in (1, 2, 4):
+                for split in (1, 2, 3, 4):
                     if (p // 64) // split < 8:
                         continue
                     kernels.set_tunable("ts_bt", bt)
@@ -668,6 +668,21 @@ def test_u8_prefill_cluster_split(kernels, zp):
                     assert kernels.last_kernel() == Kernel.U8Ts
                     assert np.array_equal(res[0].view(np.uint16), res[1].view(np.uint16))
                     assert oracle.max_rel_err(res[0], want) <= TOL, (m, p, n, bt, split)
+        # more than one wave of tiles with a small last wave (150 tiles on 148 SMs): the full
+        # waves run as the persistent kernel, the last two tiles on clusters
+        kernels.set_tunable("ts_bt", 0)
+        kernels.set_tunable("ts_split", 0)
+        m, p, n, bs, beta = 768, 1024, 6400, 128, 0.5
+        x = rng.standard_normal((m, p)).astype(np.float16)
+        q = rng.integers(0, 256, (n, p), dtype=np.uint8)
+        s = rng.uniform(0.001, 0.01, (n, p // bs)).astype(np.float16)
+        z = rng.uniform(120, 136, (n, p // bs)).astype(np.float16) if zp else None
+        out0 = (rng.standard_normal((m, n)) * 0.5).astype(np.float16)
+        want = oracle.matmul_nt_fp16u8(x, q, s, bs, beta, out0, z)
+        o = dev(out0.copy())
+        kernels.matmul_nt_fp16u8(o, dev(x), dev(q), dev(s), bs, beta, dev(z) if zp else None)
+        kernels.device_status()
+        assert oracle.max_rel_err(o.cpu().numpy(), want) <= TOL
     finally:
         kernels.set_tunable("ts_bt", 0)
         kernels.set_tunable("ts_split", 0)
