@@ -497,7 +497,7 @@ int ts_clusters_resident(adr_ctx* ctx, int split) {
         nc = 0;
       }
     }
-    if (nc < 1) nc = std::max(1, (ctx->sm_count > 0 ? ctx->sm_count : 148) / split - 8);
+    if (nc < 1) nc = 0;  // the runtime names no such cluster: this size is not used
     it = known.emplace(key, nc).first;
   }
   return it->second;
