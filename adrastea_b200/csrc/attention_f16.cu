@@ -339,6 +339,146 @@ __global__ void __launch_bounds__(AT_THREADS, HD == 64 ? 2 : 1)
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// The last few query rows of a problem whose length is just over a multiple of the query
+// tile (257 = 2 x 128 + 1 in a ViT-L/14 encoder: a third tile would hold one row and cost a
+// whole tile's MMAs).  One CTA per (row, problem), plain loads, the arithmetic of the tile
+// kernel: s = fp16(fp16(q . k) x fp16(scale)), p = fp16(exp(s - max)), out = fp16(sum p v / sum p).
+// ---------------------------------------------------------------------------------------
+constexpr int AR_THREADS = 128;
+constexpr int AR_MAX_KEYS = 8192;   // scores of a row in shared memory
+constexpr int AR_MAX_ROWS = 2;      // more rows than this take a tile (measured: a row costs 9-26 us
+                                    // over 1024 problems of 257 keys, a third tile 44 us)
+
+struct ArParams {
+  __half* out;
+  const __half* q;
+  const __half* k;
+  const __half* v;
+  int row0, s_k;
+  long long sq[3], sk[3], sv[3], so[3];  // row, inner batch, outer batch (elements)
+  float scale;
+  int causal;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(AR_THREADS) attention_rows_kernel(ArParams p) {
+  // A key or value row (HD fp16) is read by HD / 8 neighbouring lanes, 16 bytes each, and
+  // AR_THREADS / (HD / 8) rows per pass; eight passes' loads are issued before the first is
+  // used: the rows of one problem lie a whole token apart (hundreds of KB in token-major
+  // storage), so the kernel is as fast as it keeps loads in flight.
+  constexpr int LPR = HD / 8;            // lanes per row
+  constexpr int RPP = AR_THREADS / LPR;  // rows per pass
+  constexpr int U = 8;                   // passes in flight
+  extern __shared__ float ar_scores[];          // [s_k] scores, then probabilities
+  __shared__ float red[AR_THREADS / 32];
+  __shared__ float part[RPP * HD];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int rslot = tid / LPR, piece = tid % LPR;
+  const int row = p.row0 + blockIdx.x, bi = blockIdx.y, bo = blockIdx.z;
+  const __half* q = p.q + bo * p.sq[2] + bi * p.sq[1] + (long long)row * p.sq[0];
+  const __half* kb = p.k + bo * p.sk[2] + bi * p.sk[1] + piece * 8;
+  const __half* vb = p.v + bo * p.sv[2] + bi * p.sv[1] + piece * 8;
+  const int klimit = p.causal ? min(p.s_k, row + 1) : p.s_k;
+  float qf[8];
+  {
+    const uint4 qv = *reinterpret_cast<const uint4*>(q + piece * 8);
+    const __half2* q2 = reinterpret_cast<const __half2*>(&qv);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(q2[i]);
+      qf[2 * i] = f.x;
+      qf[2 * i + 1] = f.y;
+    }
+  }
+  const __half hscale = __float2half_rn(p.scale);
+  constexpr float LOG2E = 1.4426950408889634f;
+  float mloc = -INFINITY;
+  for (int j0 = 0; j0 < klimit; j0 += RPP * U) {
+    uint4 kv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + u * RPP + rslot;
+      kv[u] = j < klimit ? *reinterpret_cast<const uint4*>(kb + (long long)j * p.sk[0]) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + u * RPP + rslot;
+      const __half2* k2 = reinterpret_cast<const __half2*>(&kv[u]);
+      float acc = 0.0f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(k2[i]);
+        acc = fmaf(qf[2 * i], f.x, acc);
+        acc = fmaf(qf[2 * i + 1], f.y, acc);
+      }
+#pragma unroll
+      for (int o = LPR / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (j < klimit) {
+        const float sc = __half2float(__hmul(__float2half_rn(acc), hscale));
+        if (piece == 0) ar_scores[j] = sc;
+        mloc = fmaxf(mloc, sc);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mloc = fmaxf(mloc, __shfl_xor_sync(0xffffffffu, mloc, o));
+  if (lane == 0) red[warp] = mloc;
+  __syncthreads();
+  float m = red[0];
+#pragma unroll
+  for (int w = 1; w < AR_THREADS / 32; ++w) m = fmaxf(m, red[w]);
+  const float mo = (m == -INFINITY ? 0.0f : m) * LOG2E;
+  __syncthreads();
+  float lsum = 0.0f;
+  for (int j = tid; j < klimit; j += AR_THREADS) {
+    const float pr = __half2float(__float2half_rn(fast_exp2(fmaf(ar_scores[j], LOG2E, -mo))));
+    ar_scores[j] = pr;
+    lsum += pr;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+  if (lane == 0) red[warp] = lsum;
+  __syncthreads();
+  float l = 0.0f;
+#pragma unroll
+  for (int w = 0; w < AR_THREADS / 32; ++w) l += red[w];
+  // output: this thread's eight columns over the rows of its slot, then the slots are added
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
+  for (int j0 = 0; j0 < klimit; j0 += RPP * U) {
+    uint4 vv[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + u * RPP + rslot;
+      vv[u] = j < klimit ? *reinterpret_cast<const uint4*>(vb + (long long)j * p.sv[0]) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + u * RPP + rslot;
+      const float pr = j < klimit ? ar_scores[j] : 0.0f;
+      const __half2* v2 = reinterpret_cast<const __half2*>(&vv[u]);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(v2[i]);
+        acc[2 * i] = fmaf(pr, f.x, acc[2 * i]);
+        acc[2 * i + 1] = fmaf(pr, f.y, acc[2 * i + 1]);
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) part[rslot * HD + piece * 8 + i] = acc[i];
+  __syncthreads();
+  if (tid < HD) {
+    float o = 0.0f;
+#pragma unroll
+    for (int sl = 0; sl < RPP; ++sl) o += part[sl * HD + tid];
+    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    p.out[bo * p.so[2] + bi * p.so[1] + (long long)row * p.so[0] + tid] = __float2half_rn(o * inv);
+  }
+}
+
 template <int HD>
 int launch_attention(adr_ctx* ctx, cudaStream_t stream, __half* out, const __half* q, const __half* k,
                      const __half* v, int b_outer, int b_inner, int s_q, int s_k,
@@ -363,6 +503,10 @@ int launch_attention(adr_ctx* ctx, cudaStream_t stream, __half* out, const __hal
                      CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc != ADR_OK) return rc;
   }
+  // rows past the last full query tile, when they are few, go to the row kernel
+  int tail = s_q % AT_BM;
+  if (s_q < AT_BM || tail > AR_MAX_ROWS || s_k > AR_MAX_KEYS) tail = 0;
+  s_q -= tail;
   AtParams p;
   p.out = out;
   p.s_q = s_q;
@@ -375,7 +519,28 @@ int launch_attention(adr_ctx* ctx, cudaStream_t stream, __half* out, const __hal
   p.status = ctx->d_status;
   const dim3 grid((s_q + AT_BM - 1) / AT_BM, b_inner, b_outer);
   kfn<<<grid, AT_THREADS, Cfg::SMEM, stream>>>(maps[0], maps[1], maps[2], p);
-  return after_launch(ctx);
+  if (int rc = after_launch(ctx); rc != ADR_OK) return rc;
+  // the tail rows afterwards: their keys and values are then still in L2
+  if (tail > 0) {
+    ArParams r;
+    r.out = out;
+    r.q = q;
+    r.k = k;
+    r.v = v;
+    r.row0 = s_q;
+    r.s_k = s_k;
+    for (int d = 0; d < 3; ++d) {
+      r.sq[d] = sq[d];
+      r.sk[d] = sk[d];
+      r.sv[d] = sv[d];
+      r.so[d] = so[d];
+    }
+    r.scale = scale;
+    r.causal = causal;
+    attention_rows_kernel<HD><<<dim3(tail, b_inner, b_outer), AR_THREADS, (size_t)s_k * sizeof(float), stream>>>(r);
+    return after_launch(ctx);
+  }
+  return ADR_OK;
 }
 
 }  // namespace

@@ -35,6 +35,11 @@ def rel(got, want):
     (128, 1, 17, 17, True),
     (64, 2, 200, 200, True),
     (128, 2, 1, 96, False),       # a single query row
+    (64, 2, 258, 258, True),      # two rows past two query tiles: the row kernel, causal
+    (128, 2, 130, 200, False),    # two rows past a tile, more keys than queries
+    (64, 2, 260, 260, True),      # four rows past two tiles: a third tile
+    (128, 1, 129, 129, True),     # one row past a tile, head_dim 128
+    (64, 3, 129, 129, False),     # one row past a tile, head_dim 64
 ])
 def test_attention_contiguous_heads(kernels, hd, H, sq, sk, causal):
     torch.manual_seed(hd + sq + sk)
