@@ -249,7 +249,8 @@ def test_embed_uint8_same_bits_as_reference_and_oracle(kernels):
     kernels.device_status()
 
 
-@pytest.mark.parametrize("rows,lx", [(5, 1024), (3, 1000), (2, 4100), (4, 64), (1, 8192)])
+@pytest.mark.parametrize("rows,lx", [(5, 1024), (3, 1000), (2, 4100), (4, 64), (1, 8192),
+                                     (1030, 1024), (2051, 1000), (1025, 64)])  # many rows: four rows per CTA
 def test_layer_norm_same_bits_as_reference(kernels, rows, lx):
     """adr_layer_norm against the reference kernel run live (same bits: it keeps the kernel's
     summation order) and against the CPU oracle (one fp16 step: libm division and square root
