@@ -91,9 +91,14 @@ __device__ __forceinline__ __half epilogue_op(const TcParams& p, float a, __half
   }
 }
 
-template <int STORE, int BN>
-__device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_acc, __half* orow,
-                                              int y, int n0, int chunk0, float pre, __half hscale) {
+// `bar` (optional): the barrier that says the accumulator is complete.  It is awaited here,
+// after the old outputs of the warp's first chunk have been requested (later chunks request
+// theirs under their tensor-memory load; requesting them a chunk ahead into a second register
+// set spilled and measured slower; the bias, 64 bytes per chunk, is requested a chunk ahead).  Returns false if the wait ran out.
+template <int STORE, int BN, bool BIAS_AHEAD = false>
+__device__ __forceinline__ bool epilogue_tile(const TcParams& p, uint32_t tmem_acc, __half* orow,
+                                              int y, int n0, int chunk0, float pre, __half hscale,
+                                              uint64_t* bar = nullptr, unsigned parity = 0) {
   const bool causal = p.mask == ADR_MASK_CAUSAL;
   const bool row_ok = y < p.m;
   // tcgen05.ld and its wait are warp-collective: every branch that contains one must be
@@ -102,30 +107,54 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_a
                         (!store_uses_bias(STORE) || (reinterpret_cast<uintptr_t>(p.bias) & 15u) == 0);
   const bool row_vec = __all_sync(0xffffffffu, lane_vec || !row_ok);
   const __half ninf = __ushort_as_half((unsigned short)0xFC00);
-#pragma unroll 1
-  for (int c = chunk0; c < BN / 32; c += 2) {
+  constexpr int NCH = (BN / 32 + 1) / 2;  // chunks per warp (chunk0, chunk0 + 2, ...)
+  uint4 oldw[4], biasw[2][4];
+  auto prefetch_bias = [&](int c, uint4 (&bsv)[4]) {
+    const int x0 = n0 + c * 32;
+    if (c < BN / 32 && row_vec && x0 + 32 <= p.n && row_ok) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) bsv[q] = reinterpret_cast<const uint4*>(p.bias + x0)[q];
+    }
+  };
+  // (BIAS_AHEAD: the bias of the next chunk is requested a chunk ahead into a second register
+  // set; only in the kernel compiled for one store operation, where the registers are there)
+  if (store_uses_bias(STORE)) prefetch_bias(chunk0, biasw[0]);
+  auto prefetch = [&](int c, uint4 (&o)[4]) {
+    const int x0 = n0 + c * 32;
+    if (c < BN / 32 && row_vec && x0 + 32 <= p.n && row_ok) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) o[q] = reinterpret_cast<const uint4*>(orow + x0)[q];
+    }
+  };
+  if (store_reads_out(STORE)) prefetch(chunk0, oldw);
+  if (bar) {
+    if (!mbar_wait(bar, parity)) return false;
+    tc_fence_after_sync();
+  }
+#pragma unroll
+  for (int i = 0; i < NCH; ++i) {
+    const int c = chunk0 + 2 * i;
+    if (c >= BN / 32) break;
     const int x0 = n0 + c * 32;
     if (x0 >= p.n) break;  // uniform across the warp
     uint32_t acc[32];
     __syncwarp();
     tmem_ld_32x32(tmem_acc + (uint32_t)(c * 32), acc);
+    if (i > 0 && store_reads_out(STORE)) prefetch(c, oldw);
+    if (BIAS_AHEAD) {
+      if (i + 1 < NCH) prefetch_bias(c + 2, biasw[(i + 1) & 1]);
+    } else if (i > 0 && store_uses_bias(STORE)) {
+      prefetch_bias(c, biasw[0]);
+    }
     if (row_vec && x0 + 32 <= p.n) {
-      // 64 contiguous, aligned bytes per row: vector loads in flight under the TMEM load
-      uint4 oldw[4], biasw[4];
-      if (row_ok) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if (store_reads_out(STORE)) oldw[q] = reinterpret_cast<const uint4*>(orow + x0)[q];
-          if (store_uses_bias(STORE)) biasw[q] = reinterpret_cast<const uint4*>(p.bias + x0)[q];
-        }
-      }
       __syncwarp();
       tmem_ld_wait();
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
         if (!row_ok) break;
-        const uint32_t ow[4] = {oldw[q].x, oldw[q].y, oldw[q].z, oldw[q].w};
-        const uint32_t bw[4] = {biasw[q].x, biasw[q].y, biasw[q].z, biasw[q].w};
+        const uint4 oq = oldw[q], bq = biasw[BIAS_AHEAD ? (i & 1) : 0][q];
+        const uint32_t ow[4] = {oq.x, oq.y, oq.z, oq.w};
+        const uint32_t bw[4] = {bq.x, bq.y, bq.z, bq.w};
         uint32_t rw[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
@@ -161,20 +190,22 @@ __device__ __forceinline__ void epilogue_tile(const TcParams& p, uint32_t tmem_a
       }
     }
   }
+  return true;
 }
 
 template <int BN>
-__device__ __forceinline__ void epilogue_tile_rt(const TcParams& p, uint32_t tmem_acc, __half* orow,
+__device__ __forceinline__ bool epilogue_tile_rt(const TcParams& p, uint32_t tmem_acc, __half* orow,
                                                  int y, int n0, int chunk0, float pre,
-                                                 __half hscale) {
+                                                 __half hscale, uint64_t* bar = nullptr,
+                                                 unsigned parity = 0) {
   switch (p.store) {
-    case ADR_STORE_SCALE: epilogue_tile<ADR_STORE_SCALE, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
-    case ADR_STORE_ADD: epilogue_tile<ADR_STORE_ADD, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
-    case ADR_STORE_BETA_BIAS: epilogue_tile<ADR_STORE_BETA_BIAS, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
-    case ADR_STORE_BETA_GELU_BIAS: epilogue_tile<ADR_STORE_BETA_GELU_BIAS, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
-    case ADR_STORE_QUICK_GELU_BIAS: epilogue_tile<ADR_STORE_QUICK_GELU_BIAS, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
-    case STORE_NT_BETA: epilogue_tile<STORE_NT_BETA, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
-    default: epilogue_tile<ADR_STORE_IDENTITY, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale); break;
+    case ADR_STORE_SCALE: return epilogue_tile<ADR_STORE_SCALE, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale, bar, parity);
+    case ADR_STORE_ADD: return epilogue_tile<ADR_STORE_ADD, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale, bar, parity);
+    case ADR_STORE_BETA_BIAS: return epilogue_tile<ADR_STORE_BETA_BIAS, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale, bar, parity);
+    case ADR_STORE_BETA_GELU_BIAS: return epilogue_tile<ADR_STORE_BETA_GELU_BIAS, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale, bar, parity);
+    case ADR_STORE_QUICK_GELU_BIAS: return epilogue_tile<ADR_STORE_QUICK_GELU_BIAS, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale, bar, parity);
+    case STORE_NT_BETA: return epilogue_tile<STORE_NT_BETA, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale, bar, parity);
+    default: return epilogue_tile<ADR_STORE_IDENTITY, BN>(p, tmem_acc, orow, y, n0, chunk0, pre, hscale, bar, parity);
   }
 }
 
@@ -226,7 +257,9 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int mt, int nt, int bn) {
   return {(first_m + local % gsz) * BM, (local / gsz) * bn, b};
 }
 
-template <int BN, bool B_MN>
+// ONLY_STORE >= 0: the kernel compiled for that one store operation (its epilogue then has the
+// registers to request the bias a chunk ahead); -1: the store operation is chosen at run time.
+template <int BN, bool B_MN, int ONLY_STORE = -1>
 __global__ void __launch_bounds__(TCP_THREADS, 1)
     gemm_f16_tc_kernel(const __grid_constant__ CUtensorMap map_a,
                        const __grid_constant__ CUtensorMap map_b, TcParams p) {
@@ -320,12 +353,19 @@ __global__ void __launch_bounds__(TCP_THREADS, 1)
       const TileCoord tc = tile_coord(t, mt, nt, BN);
       const int buf = local & 1;
       const unsigned use = (unsigned)(local >> 1) & 1u;
-      if (!mbar_wait(&acc_full[buf], use)) { ok = false; break; }
-      tc_fence_after_sync();
       const int y = tc.m0 + row;
       __half* orow = p.out + (int64_t)tc.b * p.s_oz + (int64_t)y * p.s_oy;
-      epilogue_tile_rt<BN>(p, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN),
-                           orow, y, tc.n0, chunk0, pre, hscale);
+      // (the accumulator's barrier is awaited inside, behind the first loads of old outputs)
+      const uint32_t tacc = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+      bool done;
+      if constexpr (ONLY_STORE >= 0)
+        done = epilogue_tile<ONLY_STORE, BN, true>(p, tacc, orow, y, tc.n0, chunk0, pre, hscale, &acc_full[buf], use);
+      else
+        done = epilogue_tile_rt<BN>(p, tacc, orow, y, tc.n0, chunk0, pre, hscale, &acc_full[buf], use);
+      if (!done) {
+        ok = false;
+        break;
+      }
       // this warp's reads of the buffer are complete: hand it back to the MMA warp
       tc_fence_before_sync();
       __syncwarp();
@@ -709,12 +749,26 @@ int launch_tc(adr_ctx* ctx, cudaStream_t stream, const MatmulArgs& a, int S) {
   if (rc != ADR_OK) return rc;
   const int nt = (a.n + BN - 1) / BN, mt = (a.m + BM - 1) / BM;
   if (S <= 1) {
-    auto kfn = gemm_f16_tc_kernel<BN, B_MN>;
-    rc = opt_in_smem(ctx, kfn, Cfg::SMEM);
-    if (rc != ADR_OK) return rc;
     const long long tiles = (long long)nt * mt * a.batches;
     const long long sms = ctx->sm_count > 0 ? ctx->sm_count : 148;
     const unsigned grid = (unsigned)std::min<long long>(tiles, sms);
+    // The encoder's products with k = 1024 (bias, or bias + QuickGelu, on 256-wide tiles): their
+    // epilogue, not their MMAs, sets the pace, and a kernel compiled for the one store operation
+    // runs it 5-25 % faster than the one that chooses at run time (registers).
+    if constexpr (BN == 256 && !B_MN) {
+      if (p.store == ADR_STORE_QUICK_GELU_BIAS || p.store == ADR_STORE_BETA_BIAS) {
+        auto kfn = p.store == ADR_STORE_QUICK_GELU_BIAS
+                       ? gemm_f16_tc_kernel<BN, B_MN, (int)ADR_STORE_QUICK_GELU_BIAS>
+                       : gemm_f16_tc_kernel<BN, B_MN, (int)ADR_STORE_BETA_BIAS>;
+        rc = opt_in_smem(ctx, kfn, Cfg::SMEM);
+        if (rc != ADR_OK) return rc;
+        kfn<<<grid, TCP_THREADS, Cfg::SMEM, stream>>>(map_a, map_b, p);
+        return after_launch(ctx);
+      }
+    }
+    auto kfn = gemm_f16_tc_kernel<BN, B_MN>;
+    rc = opt_in_smem(ctx, kfn, Cfg::SMEM);
+    if (rc != ADR_OK) return rc;
     kfn<<<grid, TCP_THREADS, Cfg::SMEM, stream>>>(map_a, map_b, p);
     return after_launch(ctx);
   }
