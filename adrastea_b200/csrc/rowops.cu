@@ -297,6 +297,27 @@ __global__ void __launch_bounds__(256)
   dst[s_ox] = __high2half(turned);
 }
 
+// The same rotation with the turn computed once per (row, pair of a head) and applied to every
+// fourth head by the same thread: cos, sin and powf depend on the position and on the pair's
+// index within its head only, and they are most of the kernel's instructions (q and k of a
+// 512-token LLaMA-7B prefill, 64 heads: 21 -> 6 us).  Contiguous columns, 4-byte aligned rows.
+template <bool PDL>
+__global__ void __launch_bounds__(256)
+    rope_rows_heads_kernel(__half* out, const __half* in, int head_dim, int ly, int s_oy, int s_iy,
+                           int n_heads, int pos_offset, float theta) {
+  pdl_enter<PDL>();
+  const int row = blockIdx.y;
+  const int pair = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= ly || 2 * pair >= head_dim) return;
+  const Turn w = rope_turn(pos_offset + row, 2 * pair, head_dim, theta);
+  const __half* src = in + (int64_t)row * s_iy + 2 * pair;
+  __half* dst = out + (int64_t)row * s_oy + 2 * pair;
+  for (int h = threadIdx.y; h < n_heads; h += blockDim.y) {
+    const __half2 v = *reinterpret_cast<const __half2*>(src + (int64_t)h * head_dim);
+    *reinterpret_cast<__half2*>(dst + (int64_t)h * head_dim) = rope_apply(__low2half(v), __high2half(v), w);
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // elementwise_binary_2d_f16 (elementwise.cu:16-33): Add = left +h right,
 // SiluMul = fp16(float(left) / (1 + expf(-left)) * float(right))
@@ -844,6 +865,15 @@ int adr_rotary(adr_ctx* ctx, adr_stream stream, void* out, const void* in, int l
   if (length_x <= 0 || length_y <= 0 || n_heads <= 0) return ADR_ERR_INVALID;
   if (length_x % n_heads != 0 || (length_x / n_heads) % 2 != 0) return ADR_ERR_SHAPE;
   if (stride_ox < 0 || stride_oy < 0 || stride_ix < 0 || stride_iy < 0) return ADR_ERR_INVALID;
+  const int head_dim = length_x / n_heads;
+  if (stride_ox == 1 && stride_ix == 1 && n_heads >= 4 && length_y <= 65535 && stride_oy % 2 == 0 &&
+      stride_iy % 2 == 0 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(in)) & 3u) == 0) {
+    const dim3 hblock(64, 4);
+    const dim3 hgrid((head_dim / 2 + 63) / 64, length_y);
+    return launch_row(ctx, (cudaStream_t)stream, rope_rows_heads_kernel<false>, rope_rows_heads_kernel<true>,
+                      hgrid, hblock, 0, (__half*)out, (const __half*)in, head_dim, length_y, stride_oy,
+                      stride_iy, n_heads, pos_offset, theta);
+  }
   const dim3 block(64, 4);
   const dim3 grid((length_x / 2 + 63) / 64, (length_y + 3) / 4);
   if (grid.y > 65535) return ADR_ERR_SHAPE;

@@ -188,6 +188,32 @@ def test_decode_rope_append_and_attention(kernels, B, H, hd, S, pos):
     assert torch.equal(out, again), "not deterministic"
 
 
+@pytest.mark.parametrize("rows,heads,hd,pos", [(40, 64, 128, 7), (5, 6, 32, 2000), (130, 8, 64, 0), (3, 4, 256, 511)])
+def test_rotary_many_heads_same_bits(kernels, rows, heads, hd, pos):
+    """From four heads on (contiguous columns) the rotation computes cos, sin and the power once
+    per (row, pair of a head) and applies them to every head.  Same bits as the kernel that
+    computes them per element (reached here through two-head column slices), as the reference
+    kernel run live, and within two units in the last place of the CPU oracle (libm against the
+    device's functions; where the two products nearly cancel the second unit shows)."""
+    from adrastea_b200 import TensorView
+    rng = np.random.default_rng(rows + heads + hd)
+    x = rng.standard_normal((rows, heads * hd)).astype(np.float16)
+    got = dev(x.copy())
+    kernels.rotary_inplace(TensorView.of(got), heads, pos, 10000.0)
+    kernels.device_status()
+    per_pair = dev(x.copy())
+    for h0 in range(0, heads, 2):
+        kernels.rotary_inplace(TensorView.of(per_pair[:, h0 * hd:(h0 + 2) * hd]), 2, pos, 10000.0)
+    assert torch.equal(got.view(torch.int16), per_pair.view(torch.int16))
+    assert ulp_diff(got.cpu().numpy(), oracle.rotary(x, heads, pos, 10000.0)).max() <= 2
+    if refcubin.available():
+        xd, r = dev(x), torch.zeros_like(got)
+        lx = heads * hd
+        refcubin.rotary(r.data_ptr(), xd.data_ptr(), lx, rows, 1, lx, 1, lx, heads, pos, 10000.0)
+        torch.cuda.synchronize()
+        assert torch.equal(r.view(torch.int16), got.view(torch.int16))
+
+
 def test_rowop_argument_errors(kernels):
     from adrastea_b200 import AdrError, TensorLayout, TensorView
     x = torch.zeros((4, 30), dtype=torch.float16, device="cuda")
