@@ -1,0 +1,107 @@
+"""Bit comparisons of the row ops and the (de)quantisation with the reference's own kernels run
+live, on millions of elements per op: a difference in how a sum of products is contracted shows in
+about one element in twenty thousand (the rotary kernel had one), which the small cases of
+test_gpu_rowops.py cannot see.  Skipped when the reference kernels were not built beside the oracle."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import refcubin
+
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not refcubin.available(), reason="reference kernels not built")]
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def same_bits(got, ref):
+    view = torch.int16 if got.dtype == torch.float16 else torch.uint8
+    return int((got.contiguous().view(view) != ref.contiguous().view(view)).sum()) == 0
+
+
+@pytest.mark.parametrize("rows,lx", [(600, 4096), (300, 5120), (2000, 1000)])
+def test_rms_norm_large(kernels, rows, lx):
+    from adrastea_b200 import TensorView
+    rng = np.random.default_rng(rows + lx)
+    x = dev((rng.standard_normal((rows, lx)) * rng.uniform(0.2, 3, (rows, 1))).astype(np.float16))
+    w = dev(rng.uniform(0.5, 1.5, lx).astype(np.float16))
+    o, r = torch.zeros_like(x), torch.zeros_like(x)
+    kernels.rms_norm(TensorView.of(o), TensorView.of(x), TensorView.of(w), 1e-6)
+    refcubin.rms_norm(r.data_ptr(), x.data_ptr(), w.data_ptr(), lx, rows, 1, lx, 1, lx, 1e-6)
+    torch.cuda.synchronize()
+    assert same_bits(o, r)
+
+
+@pytest.mark.parametrize("rows,lx", [(4000, 1024), (600, 1024), (3000, 768), (200, 4096)])
+def test_layer_norm_large(kernels, rows, lx):
+    """Both forms: four rows per CTA (many short rows) and one row per CTA."""
+    from adrastea_b200 import TensorView
+    rng = np.random.default_rng(rows + lx)
+    x = dev((rng.standard_normal((rows, lx)) * rng.uniform(0.2, 3, (rows, 1)) + rng.uniform(-1, 1, (rows, 1))).astype(np.float16))
+    w, b = dev(rng.uniform(0.5, 1.5, lx).astype(np.float16)), dev(rng.uniform(-0.5, 0.5, lx).astype(np.float16))
+    o, r = torch.zeros_like(x), torch.zeros_like(x)
+    kernels.layer_norm(TensorView.of(o), TensorView.of(x), TensorView.of(w), TensorView.of(b), 1e-5)
+    refcubin.layer_norm(r.data_ptr(), x.data_ptr(), w.data_ptr(), b.data_ptr(), lx, rows, 1, lx, 1, lx, 1e-5)
+    torch.cuda.synchronize()
+    assert same_bits(o, r)
+
+
+@pytest.mark.parametrize("heads,h,w", [(32, 128, 512), (16, 257, 264), (8, 64, 2000)])
+def test_softmax_rows_large(kernels, heads, h, w):
+    from adrastea_b200 import TensorView
+    rng = np.random.default_rng(heads + h + w)
+    x = dev((rng.standard_normal((heads, h, w)) * 3).astype(np.float16))
+    o, r = x.clone(), torch.zeros_like(x)
+    kernels.softmax_rows_inplace(TensorView.of(o), 1.0)
+    refcubin.softmax_rows(r.data_ptr(), x.data_ptr(), heads, h, w, 1.0)
+    torch.cuda.synchronize()
+    assert same_bits(o, r)
+
+
+@pytest.mark.parametrize("rows,heads,hd,pos", [(64, 64, 128, 100), (300, 32, 128, 0), (500, 16, 64, 1500)])
+def test_rotary_large(kernels, rows, heads, hd, pos):
+    from adrastea_b200 import TensorView
+    rng = np.random.default_rng(rows + heads + hd)
+    x = dev(rng.standard_normal((rows, heads * hd)).astype(np.float16))
+    o, r = x.clone(), torch.zeros_like(x)
+    kernels.rotary_inplace(TensorView.of(o), heads, pos, 10000.0)
+    lx = heads * hd
+    refcubin.rotary(r.data_ptr(), x.data_ptr(), lx, rows, 1, lx, 1, lx, heads, pos, 10000.0)
+    torch.cuda.synchronize()
+    assert same_bits(o, r)
+
+
+@pytest.mark.parametrize("rows,cols", [(512, 11008), (300, 1000)])
+def test_elementwise_binary_large(kernels, rows, cols):
+    from adrastea_b200 import BinaryOp, TensorView
+    rng = np.random.default_rng(rows + cols)
+    left, right = dev((rng.standard_normal((rows, cols)) * 2.5).astype(np.float16)), dev(rng.standard_normal((rows, cols)).astype(np.float16))
+    for op in (BinaryOp.Add, BinaryOp.SiluMul):
+        o, r = torch.zeros_like(left), torch.zeros_like(left)
+        kernels.elementwise_binary_2d_f16(TensorView.of(o), TensorView.of(left), TensorView.of(right), op)
+        refcubin.elementwise_binary_2d_f16(r.data_ptr(), left.data_ptr(), right.data_ptr(), rows, cols, int(op))
+        torch.cuda.synchronize()
+        assert same_bits(o, r), op
+
+
+@pytest.mark.parametrize("rows,k,bs", [(1024, 4096, 128), (512, 4096, 64), (300, 1024, 32)])
+def test_quantize_and_dequantize_large(kernels, rows, k, bs):
+    rng = np.random.default_rng(rows + k + bs)
+    q = dev(rng.integers(0, 256, (rows, k), dtype=np.uint8))
+    s = dev(rng.uniform(0.0005, 0.02, (rows, k // bs)).astype(np.float16))
+    o = torch.zeros((rows, k), dtype=torch.float16, device="cuda")
+    r = torch.zeros_like(o)
+    kernels.dequantize_absmax_uint8(o, s, q)
+    refcubin.dequantize_absmax_uint8(r.data_ptr(), s.data_ptr(), q.data_ptr(), rows, k, bs)
+    torch.cuda.synchronize()
+    assert same_bits(o, r)
+    x = dev((rng.standard_normal((rows, k)) * rng.uniform(0.01, 2, (rows, 1))).astype(np.float16))
+    q1 = torch.zeros((rows, k), dtype=torch.uint8, device="cuda")
+    s1 = torch.zeros((rows, k // bs), dtype=torch.float16, device="cuda")
+    q2, s2 = torch.zeros_like(q1), torch.zeros_like(s1)
+    kernels.quantize_absmax_uint8(q1, s1, x)
+    refcubin.quantize_absmax_uint8(q2.data_ptr(), s2.data_ptr(), x.data_ptr(), rows, k, bs)
+    torch.cuda.synchronize()
+    assert same_bits(q1, q2) and same_bits(s1, s2)
+    kernels.device_status()
