@@ -507,10 +507,15 @@ def extra_llama7b(kern, batch, prefill=512, decode=128):
     hbm, _ = measured_peak()
     ceiling = batch / (wb / (hbm * 1e9))
     tok_s = batch / (ms_dec * 1e-3)
+    # the KV cache read by a step: keys and values of every layer over the context so far
+    # (its mean over the timed steps); at batch 16 it is two thirds of the weights' bytes
+    kv = 2 * LLAMA_7B.n_layers * batch * (prefill + decode / 2.0) * LLAMA_7B.dim * 2
     del model
     torch.cuda.empty_cache()
     return {"decode_ms_per_step": ms_dec, "decode_tok_s": tok_s, "weight_bytes_per_step": wb,
             "weight_stream_ceiling_tok_s": ceiling, "frac_of_ceiling": tok_s / ceiling,
+            "kv_cache_bytes_per_step": kv,
+            "frac_of_hbm_weights_and_kv": (wb + kv) / (ms_dec * 1e-3) / 1e9 / hbm,
             "prefill_tokens": batch * prefill, "prefill_ms": ms_pre,
             "prefill_tok_s": batch * prefill / (ms_pre * 1e-3)}
 
