@@ -360,8 +360,11 @@ class LlamaU8:
                 hv = lambda t: TensorView(t, TensorLayout.new((B, Hl, S0, hd), (S0 * t.stride(0), hd, t.stride(0), 1)))
                 self.k.attention_f16(hv(att), hv(qkv[:, :dl]), hv(qkv[:, dl:2 * dl]), hv(qkv[:, 2 * dl:]),
                                      scale, MatmulMask.Causal)
-            self.k_cache[li][:, :S0].copy_(qkv[:, dl:2 * dl].view(B, S0, dl))
-            self.v_cache[li][:, :S0].copy_(qkv[:, 2 * dl:].view(B, S0, dl))
+            # the strided row copies go through 16-byte elements: PyTorch's copy of a strided fp16
+            # view moves one element per thread step (78 us for 67 MB; 8x fewer elements this way)
+            wide = torch.complex128 if dl % 8 == 0 else torch.float16
+            self.k_cache[li][:, :S0].view(wide).copy_(qkv[:, dl:2 * dl].view(wide).view(B, S0, -1))
+            self.v_cache[li][:, :S0].view(wide).copy_(qkv[:, 2 * dl:].view(wide).view(B, S0, -1))
             self._prefill_linear(ly.wo, h, att, part, residual=True)
             self._norm(x, h, ly.ffn_norm)
             self._prefill_linear(ly.wgu, gu, x)
