@@ -106,6 +106,61 @@ __global__ void __launch_bounds__(ROW_THREADS)
   }
 }
 
+// rms_norm on R rows per CTA at once, thread for thread the arithmetic above (contiguous rows of
+// at most 4096 elements, many rows: a prefill's 8192 x 4096 activations took 41 us with one row
+// per CTA).  See layer_norm_rows_kernel below for the reasoning.
+template <bool PDL, int R>
+__global__ void __launch_bounds__(ROW_THREADS)
+    rms_norm_rows_kernel(__half* __restrict__ out, const __half* __restrict__ in,
+                         const __half* __restrict__ w, int lx, int ly, int s_oy, int s_iy, float eps) {
+  __shared__ float s_warp[R][8];
+  pdl_enter<PDL>();
+  constexpr int KEEP = 16;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int row0 = blockIdx.x * R;
+  float v[R][KEEP];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const __half* irow = in + (int64_t)min(row0 + r, ly - 1) * s_iy;
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+      const int i = tid + j * ROW_THREADS;
+      v[r][j] = i < lx ? __half2float(irow[i]) : 0.0f;
+    }
+  }
+  float acc[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float sum = 0.0f;
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j)
+      if (tid + j * ROW_THREADS < lx) sum += v[r][j] * v[r][j];
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane == 0) s_warp[r][warp] = sum;
+    acc[r] = sum;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    float t = lane < 8 ? s_warp[r][lane] : 0.0f;
+#pragma unroll
+    for (int off = 4; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+    acc[r] = __shfl_sync(0xffffffffu, t, 0);
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    if (row0 + r >= ly) break;
+    const float rms_inv = rsqrtf((acc[r] / lx) + eps);
+    __half* orow = out + (int64_t)(row0 + r) * s_oy;
+#pragma unroll
+    for (int j = 0; j < KEEP; ++j) {
+      const int i = tid + j * ROW_THREADS;
+      if (i < lx) orow[i] = __hmul(w[i], __float2half(v[r][j] * rms_inv));
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // layer_norm (normalize.cu:60-145): out[r,i] = fp16((in[r,i] - mean) / sqrt(var + eps) * w[i] + b[i])
 // with mean and the (biased) variance in fp32, each summed in the reference's order: thread t
@@ -821,6 +876,12 @@ int adr_rms_norm(adr_ctx* ctx, adr_stream stream, void* out, const void* in, con
   DeviceGuard guard(ctx);
   if (length_x <= 0 || length_y <= 0) return ADR_ERR_INVALID;
   if (stride_ox < 0 || stride_oy < 0 || stride_ix < 0 || stride_iy < 0) return ADR_ERR_INVALID;
+  constexpr int RMS_ROWS = 2;
+  if (stride_ox == 1 && stride_ix == 1 && length_x <= 16 * ROW_THREADS && length_y >= 1024)
+    return launch_row(ctx, (cudaStream_t)stream, rms_norm_rows_kernel<false, RMS_ROWS>,
+                      rms_norm_rows_kernel<true, RMS_ROWS>, dim3((length_y + RMS_ROWS - 1) / RMS_ROWS),
+                      dim3(ROW_THREADS), 0, (__half*)out, (const __half*)in, (const __half*)weights,
+                      length_x, length_y, stride_oy, stride_iy, eps);
   return launch_row(ctx, (cudaStream_t)stream, rms_norm_kernel<false>, rms_norm_kernel<true>,
                     dim3(length_y), dim3(ROW_THREADS), 0, (__half*)out, (const __half*)in,
                     (const __half*)weights, length_x, stride_ox, stride_oy, stride_ix, stride_iy, eps);

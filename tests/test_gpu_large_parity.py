@@ -20,7 +20,7 @@ def same_bits(got, ref):
     return int((got.contiguous().view(view) != ref.contiguous().view(view)).sum()) == 0
 
 
-@pytest.mark.parametrize("rows,lx", [(600, 4096), (300, 5120), (2000, 1000)])
+@pytest.mark.parametrize("rows,lx", [(600, 4096), (300, 5120), (2000, 1000), (2049, 4096), (1500, 3000)])
 def test_rms_norm_large(kernels, rows, lx):
     from adrastea_b200 import TensorView
     rng = np.random.default_rng(rows + lx)
